@@ -1,0 +1,448 @@
+// Attention operators of the decode path.
+//   * attention_scores / softmax_value: the two-kernel split form of kmll
+//     (crates/inference/src/kernels/inference.rs:1165-1222, :1311-1417), any head_dim.
+//   * single_query_attention: decode attention, split along the sequence so that the whole GPU
+//     streams the f32 KV cache ("flash-decoding"); the query heads that share a KV head are
+//     processed together so K and V are read from HBM exactly once.  The last block to finish a
+//     KV head merges the per-split partial results.
+//   * prefill_causal_attention: tiled causal attention with an online softmax.
+// Math contract (all f32): score = dot * (1/sqrt(head_dim)); weights exp(s - max); out = sum(w*v)/sum(w)
+// (crates/inference/src/model.rs:11581-11649).  KV cache layout [max_seq, n_kv_heads, head_dim].
+#include "common.cuh"
+
+namespace kmll {
+
+// ---- split form -------------------------------------------------------------------------------
+__global__ void attention_scores_kernel(const float* __restrict__ q, const float* __restrict__ k_cache, int seq_len,
+                                        int max_seq_len, int n_heads, int n_kv_heads, int head_dim,
+                                        float* __restrict__ scores) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= n_heads * seq_len) return;
+    const int head = item / seq_len;
+    const int pos = item - head * seq_len;
+    const int kv_head = head / (n_heads / n_kv_heads);
+    const float* qh = q + (size_t)head * head_dim;
+    const float* kr = k_cache + ((size_t)pos * n_kv_heads + kv_head) * head_dim;
+    float dot = 0.0f;
+    for (int d = lane; d < head_dim; d += 32) dot += qh[d] * kr[d];
+    dot = warp_sum(dot);
+    if (lane == 0) scores[(size_t)head * max_seq_len + pos] = dot * (1.0f / sqrtf((float)head_dim));
+}
+
+__global__ void __launch_bounds__(256) softmax_value_kernel(const float* __restrict__ scores,
+                                                            const float* __restrict__ v_cache, int seq_len,
+                                                            int max_seq_len, int n_heads, int n_kv_heads, int head_dim,
+                                                            float* __restrict__ out) {
+    __shared__ float scratch[40];
+    pdl_wait();
+    const int head = blockIdx.x;
+    const int kv_head = head / (n_heads / n_kv_heads);
+    const float* sc = scores + (size_t)head * max_seq_len;
+    float m = -INFINITY;
+    for (int p = threadIdx.x; p < seq_len; p += blockDim.x) m = fmaxf(m, sc[p]);
+    m = block_max(m, scratch);
+    float denom = 0.0f;
+    for (int p = threadIdx.x; p < seq_len; p += blockDim.x) denom += expf(sc[p] - m);
+    denom = block_sum(denom, scratch);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int p = 0; p < seq_len; ++p)
+            acc += expf(sc[p] - m) * v_cache[((size_t)p * n_kv_heads + kv_head) * head_dim + d];
+        out[(size_t)head * head_dim + d] = acc / denom;
+    }
+}
+
+// ---- decode attention, split along the sequence ---------------------------------------------------
+constexpr int kAttnWarps = 4;
+constexpr int kMaxGq = 8;  // query heads per KV head handled by the fused kernel
+
+struct DecodeAttnParams {
+    const float* q;        // [n_heads, head_dim]
+    const float* k_cache;  // [max_seq, n_kv, head_dim]
+    const float* v_cache;
+    const int* seq_len_ptr;  // device-side sequence length (CUDA-graph replays), or null
+    int seq_len;             // used when seq_len_ptr is null
+    int n_heads, n_kv_heads, gq;
+    int chunk;    // positions per block
+    int nsplit;   // gridDim.y
+    float* part_acc;  // [n_heads, nsplit, HD]
+    float* part_ml;   // [n_heads, nsplit, 2]
+    unsigned int* counters;  // [n_kv_heads], zero on entry, zero on exit
+    float* out;       // [n_heads, head_dim]
+};
+
+template <int EPL>
+__device__ inline void load_lane_slice(const float* src, float (&dst)[EPL]);
+template <>
+__device__ inline void load_lane_slice<4>(const float* src, float (&dst)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(src);
+    dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
+}
+template <>
+__device__ inline void load_lane_slice<2>(const float* src, float (&dst)[2]) {
+    const float2 t = *reinterpret_cast<const float2*>(src);
+    dst[0] = t.x; dst[1] = t.y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(const DecodeAttnParams p) {
+    constexpr int EPL = HD / 32;  // elements per lane
+    extern __shared__ __align__(16) float smem[];
+    pdl_wait();
+    const int seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
+    const int kv_head = blockIdx.x;
+    const int split = blockIdx.y;
+    const int gq = p.gq;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int s0 = split * p.chunk;
+    const int s1 = min(s0 + p.chunk, seq_len);
+    const int n = s1 - s0;  // may be <= 0 for trailing splits
+
+    float* sc = smem;                          // [gq][chunk]
+    float* red = sc + gq * p.chunk;            // [kAttnWarps][gq][HD]
+    float* ml = red + kAttnWarps * gq * HD;    // [gq][2]
+    __shared__ bool is_last;
+
+    const size_t kv_stride = (size_t)p.n_kv_heads * HD;
+    const float scale = 1.0f / sqrtf((float)HD);
+
+    if (n > 0) {
+        // q of this KV group, this lane's slice
+        float qv[kMaxGq][EPL];
+#pragma unroll
+        for (int h = 0; h < kMaxGq; ++h)
+#pragma unroll
+            for (int e = 0; e < EPL; ++e)
+                qv[h][e] = h < gq ? p.q[(size_t)(kv_head * gq + h) * HD + lane * EPL + e] : 0.0f;
+
+        // pass 1: scores, one warp per position
+        const float* kbase = p.k_cache + (size_t)kv_head * HD + lane * EPL;
+        for (int i = warp; i < n; i += kAttnWarps) {
+            const float* kr = kbase + (size_t)(s0 + i) * kv_stride;
+            float kv[EPL];
+            load_lane_slice<EPL>(kr, kv);
+#pragma unroll
+            for (int h = 0; h < kMaxGq; ++h) {
+                if (h < gq) {
+                    float d = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) d += qv[h][e] * kv[e];
+                    d = warp_sum(d);
+                    if (lane == 0) sc[h * p.chunk + i] = d * scale;
+                }
+            }
+        }
+        __syncthreads();
+        // pass 2a: per-head max and exp-sum over the chunk
+        for (int h = warp; h < gq; h += kAttnWarps) {
+            float m = -INFINITY;
+            for (int i = lane; i < n; i += 32) m = fmaxf(m, sc[h * p.chunk + i]);
+            m = warp_max(m);
+            float l = 0.0f;
+            for (int i = lane; i < n; i += 32) {
+                const float e = expf(sc[h * p.chunk + i] - m);
+                sc[h * p.chunk + i] = e;
+                l += e;
+            }
+            l = warp_sum(l);
+            if (lane == 0) { ml[h * 2] = m; ml[h * 2 + 1] = l; }
+        }
+        __syncthreads();
+        // pass 2b: weighted sum of V, one warp per position
+        float acc[kMaxGq][EPL];
+#pragma unroll
+        for (int h = 0; h < kMaxGq; ++h)
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
+        const float* vbase = p.v_cache + (size_t)kv_head * HD + lane * EPL;
+        for (int i = warp; i < n; i += kAttnWarps) {
+            const float* vr = vbase + (size_t)(s0 + i) * kv_stride;
+            float vv[EPL];
+            load_lane_slice<EPL>(vr, vv);
+#pragma unroll
+            for (int h = 0; h < kMaxGq; ++h) {
+                if (h < gq) {
+                    const float w = sc[h * p.chunk + i];
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(w, vv[e], acc[h][e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < kMaxGq; ++h)
+            if (h < gq)
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
+        __syncthreads();
+    }
+    pdl_launch_dependents();
+
+    // write this split's partial (or the final result when there is a single split)
+    for (int idx = threadIdx.x; idx < gq * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx - h * HD;
+        const int head = kv_head * gq + h;
+        float v = 0.0f;
+        if (n > 0) {
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
+        }
+        if (p.nsplit == 1) {
+            p.out[(size_t)head * HD + d] = n > 0 ? v / ml[h * 2 + 1] : 0.0f;
+        } else {
+            p.part_acc[((size_t)head * p.nsplit + split) * HD + d] = v;
+            if (d == 0) {
+                p.part_ml[((size_t)head * p.nsplit + split) * 2] = n > 0 ? ml[h * 2] : -INFINITY;
+                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = n > 0 ? ml[h * 2 + 1] : 0.0f;
+            }
+        }
+    }
+    if (p.nsplit == 1) return;
+
+    // last block of this KV head merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(&p.counters[kv_head], 1u);
+        is_last = (prev == (unsigned int)p.nsplit - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < gq * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx - h * HD;
+        const int head = kv_head * gq + h;
+        const volatile float* pml = p.part_ml + (size_t)head * p.nsplit * 2;
+        float m = -INFINITY;
+        for (int s = 0; s < p.nsplit; ++s) m = fmaxf(m, pml[s * 2]);
+        float l = 0.0f, a = 0.0f;
+        for (int s = 0; s < p.nsplit; ++s) {
+            const float ms = pml[s * 2];
+            if (ms == -INFINITY) continue;
+            const float f = expf(ms - m);
+            l += pml[s * 2 + 1] * f;
+            a += ((const volatile float*)p.part_acc)[((size_t)head * p.nsplit + s) * HD + d] * f;
+        }
+        p.out[(size_t)head * HD + d] = a / l;
+    }
+    if (threadIdx.x == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
+}
+
+// ---- prefill: tiled causal attention ---------------------------------------------------------------
+constexpr int kPfBQ = 16;  // query rows per block
+constexpr int kPfBK = 32;  // key positions per tile
+
+template <int HD>
+__global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __restrict__ q_batch,
+                                                                const float* __restrict__ k_cache,
+                                                                const float* __restrict__ v_cache, int prompt_len,
+                                                                int n_heads, int n_kv_heads, float* __restrict__ out) {
+    constexpr int EPL = HD / 32;
+    constexpr int KP = HD + 4;  // padded K row: 16-byte lane accesses hit disjoint banks
+    __shared__ __align__(16) float Qs[kPfBQ][HD];
+    __shared__ __align__(16) float Ks[kPfBK][KP];
+    __shared__ __align__(16) float Vs[kPfBK][HD];
+    pdl_wait();
+    const int head = blockIdx.x;
+    const int r0 = blockIdx.y * kPfBQ;
+    const int kv_head = head / (n_heads / n_kv_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t q_len = (size_t)n_heads * HD;
+    const size_t kv_stride = (size_t)n_kv_heads * HD;
+    const float scale = 1.0f / sqrtf((float)HD);
+
+    for (int idx = threadIdx.x; idx < kPfBQ * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx - r * HD;
+        Qs[r][d] = (r0 + r) < prompt_len ? q_batch[(size_t)(r0 + r) * q_len + (size_t)head * HD + d] : 0.0f;
+    }
+    constexpr int QPW = kPfBQ / 4;  // queries per warp
+    float m[QPW], l[QPW], acc[QPW][EPL];
+#pragma unroll
+    for (int j = 0; j < QPW; ++j) {
+        m[j] = -INFINITY;
+        l[j] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[j][e] = 0.0f;
+    }
+    const int last_row = min(r0 + kPfBQ, prompt_len) - 1;
+    for (int t0 = 0; t0 <= last_row; t0 += kPfBK) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kPfBK * HD; idx += blockDim.x) {
+            const int kk = idx / HD, d = idx - kk * HD;
+            const int pos = t0 + kk;
+            const bool ok = pos <= last_row;
+            Ks[kk][d] = ok ? k_cache[(size_t)pos * kv_stride + (size_t)kv_head * HD + d] : 0.0f;
+            Vs[kk][d] = ok ? v_cache[(size_t)pos * kv_stride + (size_t)kv_head * HD + d] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < QPW; ++j) {
+            const int r = warp * QPW + j;
+            const int row = r0 + r;
+            if (row >= prompt_len || t0 > row) continue;  // warp-uniform
+            // lane = key index inside the tile
+            float s = 0.0f;
+#pragma unroll 8
+            for (int d = 0; d < HD; d += 4) {
+                const float4 kq = *reinterpret_cast<const float4*>(&Ks[lane][d]);
+                const float4 qq = *reinterpret_cast<const float4*>(&Qs[r][d]);
+                s += qq.x * kq.x;
+                s += qq.y * kq.y;
+                s += qq.z * kq.z;
+                s += qq.w * kq.w;
+            }
+            s = (t0 + lane) <= row ? s * scale : -INFINITY;
+            const float m_new = fmaxf(m[j], warp_max(s));
+            const float pexp = expf(s - m_new);  // exp(-inf) = 0 for masked keys
+            const float corr = expf(m[j] - m_new);
+            l[j] = l[j] * corr + warp_sum(pexp);
+            m[j] = m_new;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[j][e] *= corr;
+            for (int kk = 0; kk < kPfBK; ++kk) {
+                const float w = __shfl_sync(0xffffffffu, pexp, kk);
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[j][e] = fmaf(w, Vs[kk][lane * EPL + e], acc[j][e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < QPW; ++j) {
+        const int row = r0 + warp * QPW + j;
+        if (row < prompt_len) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e)
+                out[(size_t)row * q_len + (size_t)head * HD + lane * EPL + e] = acc[j][e] / l[j];
+        }
+    }
+}
+
+struct AttnPlan {
+    int chunk;
+    int nsplit;
+};
+
+// Split plan: a pure function of the sequence capacity, so a CUDA graph captured for a given
+// max_seq_len stays valid while the device-side sequence length grows.
+static AttnPlan plan_decode_attention(int seq_cap) {
+    AttnPlan pl;
+    int nsplit = (seq_cap + 63) / 64;
+    if (nsplit > 64) nsplit = 64;
+    if (nsplit < 1) nsplit = 1;
+    int chunk = (seq_cap + nsplit - 1) / nsplit;
+    chunk = (chunk + 3) & ~3;
+    pl.chunk = chunk;
+    pl.nsplit = (seq_cap + chunk - 1) / chunk;
+    if (pl.nsplit < 1) pl.nsplit = 1;
+    return pl;
+}
+
+int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_cache, const float* v_cache,
+                            const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
+                            int head_dim, float* workspace, float* out) {
+    const int gq = n_heads / n_kv_heads;
+    AttnPlan pl = plan_decode_attention(seq_cap);
+    DecodeAttnParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
+    p.seq_len_ptr = seq_len_ptr; p.seq_len = seq_len;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.gq = gq;
+    p.chunk = pl.chunk; p.nsplit = pl.nsplit;
+    p.part_acc = workspace;
+    p.part_ml = workspace + (size_t)n_heads * pl.nsplit * head_dim;
+    p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
+    p.out = out;
+    const size_t smem = ((size_t)gq * pl.chunk + (size_t)kAttnWarps * gq * head_dim + (size_t)gq * 2) * sizeof(float);
+    cudaError_t e;
+    if (head_dim == 128) {
+        static thread_local bool cfg = false;
+        if (!cfg) { cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
+        e = launch(decode_attention_kernel<128>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnWarps * 32), smem, stream, true, p);
+    } else {
+        static thread_local bool cfg = false;
+        if (!cfg) { cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
+        e = launch(decode_attention_kernel<64>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnWarps * 32), smem, stream, true, p);
+    }
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+size_t decode_attention_workspace_floats(int n_heads, int head_dim, int seq_cap) {
+    AttnPlan pl = plan_decode_attention(seq_cap);
+    return (size_t)n_heads * pl.nsplit * (head_dim + 2) + (size_t)n_heads + 16;  // counters <= n_kv_heads <= n_heads
+}
+
+static int check_geometry(const char* name, int seq_len, int max_seq_len, int n_heads, int n_kv_heads, int head_dim) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0)
+        return fail(KMLL_ERR_SHAPE, "%s: attention geometry must be positive", name);
+    if (n_heads % n_kv_heads != 0) return fail(KMLL_ERR_SHAPE, "%s: n_heads must be divisible by n_kv_heads", name);
+    if (seq_len <= 0 || seq_len > max_seq_len)
+        return fail(KMLL_ERR_SHAPE, "%s: seq_len %d outside 1..max_seq_len %d", name, seq_len, max_seq_len);
+    return KMLL_OK;
+}
+
+}  // namespace kmll
+
+using namespace kmll;
+
+extern "C" {
+
+int kmll_attention_scores(kmll_stream_t s, const float* q, const float* k_cache, int seq_len, int max_seq_len, int n_heads,
+                          int n_kv_heads, int head_dim, float* scores) {
+    KMLL_REQUIRE_PTR(q); KMLL_REQUIRE_PTR(k_cache); KMLL_REQUIRE_PTR(scores);
+    int rc = check_geometry("attention_scores", seq_len, max_seq_len, n_heads, n_kv_heads, head_dim);
+    if (rc) return rc;
+    const int items = n_heads * seq_len;
+    cudaError_t e = launch(attention_scores_kernel, dim3((items + 3) / 4), dim3(128), 0, as_stream(s), true, q, k_cache, seq_len,
+                           max_seq_len, n_heads, n_kv_heads, head_dim, scores);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "attention_scores: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int kmll_softmax_value(kmll_stream_t s, const float* scores, const float* v_cache, int seq_len, int max_seq_len, int n_heads,
+                       int n_kv_heads, int head_dim, float* out) {
+    KMLL_REQUIRE_PTR(scores); KMLL_REQUIRE_PTR(v_cache); KMLL_REQUIRE_PTR(out);
+    int rc = check_geometry("softmax_value", seq_len, max_seq_len, n_heads, n_kv_heads, head_dim);
+    if (rc) return rc;
+    cudaError_t e = launch(softmax_value_kernel, dim3(n_heads), dim3(256), 0, as_stream(s), true, scores, v_cache, seq_len,
+                           max_seq_len, n_heads, n_kv_heads, head_dim, out);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "softmax_value: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+size_t kmll_single_query_attention_workspace_floats(int n_heads, int head_dim, int max_seq_len) {
+    if (n_heads <= 0 || head_dim <= 0 || max_seq_len <= 0) return 0;
+    return decode_attention_workspace_floats(n_heads, head_dim, max_seq_len);
+}
+
+int kmll_single_query_attention(kmll_stream_t s, const float* q, const float* k_cache, const float* v_cache, int seq_len,
+                                int max_seq_len, int n_heads, int n_kv_heads, int head_dim, float* workspace, float* out) {
+    KMLL_REQUIRE_PTR(q); KMLL_REQUIRE_PTR(k_cache); KMLL_REQUIRE_PTR(v_cache); KMLL_REQUIRE_PTR(out); KMLL_REQUIRE_PTR(workspace);
+    int rc = check_geometry("single_query_attention", seq_len, max_seq_len, n_heads, n_kv_heads, head_dim);
+    if (rc) return rc;
+    if ((head_dim != 64 && head_dim != 128) || n_heads / n_kv_heads > kMaxGq)
+        return fail(KMLL_ERR_UNSUPPORTED, "single_query_attention: head_dim must be 64 or 128 and n_heads/n_kv_heads <= %d; use attention_scores + softmax_value", kMaxGq);
+    if (max_seq_len > 131072) return fail(KMLL_ERR_CAPACITY, "single_query_attention: max_seq_len %d beyond 131072", max_seq_len);
+    return decode_attention_launch(as_stream(s), q, k_cache, v_cache, nullptr, seq_len, max_seq_len, n_heads, n_kv_heads, head_dim,
+                                   workspace, out);
+}
+
+int kmll_prefill_causal_attention(kmll_stream_t s, const float* q_batch, const float* k_cache, const float* v_cache, int prompt_len,
+                                  int max_seq_len, int n_heads, int n_kv_heads, int head_dim, float* out) {
+    KMLL_REQUIRE_PTR(q_batch); KMLL_REQUIRE_PTR(k_cache); KMLL_REQUIRE_PTR(v_cache); KMLL_REQUIRE_PTR(out);
+    int rc = check_geometry("prefill_causal_attention", prompt_len, max_seq_len, n_heads, n_kv_heads, head_dim);
+    if (rc) return rc;
+    const dim3 grid(n_heads, (prompt_len + kPfBQ - 1) / kPfBQ);
+    cudaError_t e;
+    if (head_dim == 128) {
+        e = launch(prefill_attention_kernel<128>, grid, dim3(128), 0, as_stream(s), true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out);
+    } else if (head_dim == 64) {
+        e = launch(prefill_attention_kernel<64>, grid, dim3(128), 0, as_stream(s), true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out);
+    } else {
+        return fail(KMLL_ERR_UNSUPPORTED, "prefill_causal_attention: head_dim must be 64 or 128, got %d", head_dim);
+    }
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prefill_causal_attention: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,859 @@
+// Quantized linear layers (matvec and small-batch) for sm_100a.
+//
+// One kernel template serves RS-I8 and W4-G128 weights and every fused form (plain, +residual,
+// Q/K/V triple, SiLU gate*up, lm_head arg-max, optional RMSNorm prologue).
+//
+// How one thread block works
+//   * It owns RB = 16*MT output rows and ALL of K.  Its warps split K into contiguous runs of
+//     "units" (W4: one 128-column quantization group = 64 B per row; I8: 64 columns = 64 B per
+//     row).  Per unit each lane issues one 16-byte streaming load per row it holds, so a warp
+//     request covers 8 rows x 64 B, fully using every 32 B sector.
+//   * The integer weights are widened to exact binary16 values in registers (magic-number
+//     lop3/prmt tricks, no int->float conversion instructions) and multiplied on the tensor
+//     cores with mma.sync m16n8k16 (f32 accumulate): weights are the 16-row A operand, the
+//     activations the 8-column B operand.  Each batch row occupies TWO columns: x scaled by a
+//     power of two and split as hi = f16(x*s), lo = f16(x*s - hi), which carries ~22 bits of x,
+//     so the products are exact and the result is an f32-accurate dot product.  The tensor pipe
+//     does the multiply-adds; the CUDA cores only unpack, which keeps the kernel HBM-bound
+//     (a plain f32 FMA loop would need ~4 instructions per 4-bit weight and be issue-bound).
+//   * The k order inside an MMA is free as long as A and B agree, so activations are staged in
+//     shared memory in the order the unpack produces; no shuffles are needed.
+//   * W4 group scales multiply the per-group accumulator (exact dequantised value * x summed in
+//     f32); the RS-I8 row scale multiplies the row total once.  kmll multiplies scale per
+//     element ((w*scale)*x, crates/inference/src/kernels/inference.rs:778-781); the difference is
+//     a re-association of f32 roundings, far inside kmll's own 1e-4*sqrt(K) tolerance.
+//   * Warps combine their K-partials through shared memory in a fixed order, so results are
+//     deterministic run to run.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace kmll {
+
+enum { FMT_I8 = 0, FMT_W4 = 1 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_TOP1 = 3 };
+
+struct LinearMat {
+    const uint8_t* w;       // int8 values [rows, K] or packed nibbles [rows, K/2]
+    const void* scales;     // float[rows] (I8) or half[rows, K/128] (W4)
+    float* out;             // [M, ldo]
+    const float* residual;  // [M, ldo] or null
+    int rows;
+    int ldo;
+};
+
+struct LinearParams {
+    const float* x;  // [M, ldx]
+    int M;
+    int K;
+    int ldx;
+    int kc;                  // K chunk staged in shared memory at a time (multiple of the unit)
+    const uint16_t* norm_w;  // optional fused RMSNorm weight (bf16 bits), null = none
+    float eps;
+    LinearMat mat[3];
+    int nmat;
+    int block_start[4];  // first blockIdx.x of each matrix; [nmat] = grid size
+    uint32_t* partial_tokens;
+    float* partial_logits;
+};
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+
+template <int FMT>
+struct Fmt;
+template <>
+struct Fmt<FMT_W4> {
+    static constexpr int kUnit = 128;       // columns per unit
+    static constexpr int kRowPad = 32;      // halves: row stride = kc + 32 (64 B) -> g=0/1 rows hit disjoint banks
+};
+template <>
+struct Fmt<FMT_I8> {
+    static constexpr int kUnit = 64;
+    static constexpr int kRowPad = 8;       // halves: 16 B
+};
+
+// Position of column k inside the staged activation row.
+template <int FMT>
+__device__ inline int stage_index(int k) {
+    if (FMT == FMT_W4) {
+        // k = unit*128 + t*32 + i*8 + p  ->  unit*128 + i*32 + t*8 + perm(p), perm = [0,4,1,5,2,6,3,7]^-1
+        const int unit = k >> 7, t = (k >> 5) & 3, i = (k >> 3) & 3, p = k & 7;
+        const int pp = ((p & 3) << 1) | (p >> 2);
+        return (unit << 7) | (i << 5) | (t << 3) | pp;
+    }
+    return k;
+}
+
+__device__ inline void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ inline uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & b) | c
+    return r;
+}
+
+// 8 nibbles of one 32-bit word -> 4 half2 registers holding (q0,q4) (q1,q5) (q2,q6) (q3,q7),
+// q = nibble - 8, exact.
+__device__ inline void unpack_w4(uint32_t w, uint32_t (&h)[4]) {
+    const uint32_t kMagic = 0x64006400u;          // half2(1024, 1024)
+    const uint32_t kSubLo = 0x64086408u;          // half2(1032, 1032)
+    const uint32_t kMulHi = 0x2c002c00u;          // half2(1/16, 1/16)
+    const uint32_t kAddHi = 0xd480d480u;          // half2(-72, -72)
+    uint32_t lo0 = lop3_and_or(w, 0x000f000fu, kMagic);
+    uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, kMagic);
+    uint32_t w8 = w >> 8;
+    uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, kMagic);
+    uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, kMagic);
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2*>(&lo0), *reinterpret_cast<const __half2*>(&kSubLo));
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2*>(&hi0), *reinterpret_cast<const __half2*>(&kMulHi),
+                         *reinterpret_cast<const __half2*>(&kAddHi));
+    __half2 r2 = __hsub2(*reinterpret_cast<__half2*>(&lo1), *reinterpret_cast<const __half2*>(&kSubLo));
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2*>(&hi1), *reinterpret_cast<const __half2*>(&kMulHi),
+                         *reinterpret_cast<const __half2*>(&kAddHi));
+    h[0] = *reinterpret_cast<uint32_t*>(&r0);
+    h[1] = *reinterpret_cast<uint32_t*>(&r1);
+    h[2] = *reinterpret_cast<uint32_t*>(&r2);
+    h[3] = *reinterpret_cast<uint32_t*>(&r3);
+}
+
+// 4 signed bytes -> 2 half2 registers (b0,b1) (b2,b3), exact.
+__device__ inline void unpack_i8(uint32_t w, uint32_t (&h)[2]) {
+    const uint32_t kSub = 0x64806480u;  // half2(1152, 1152) = 1024 + 128
+    uint32_t u = w ^ 0x80808080u;       // bias to unsigned
+    uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140);
+    uint32_t hi = __byte_perm(u, 0x64646464u, 0x4342);
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&kSub));
+    __half2 r1 = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&kSub));
+    h[0] = *reinterpret_cast<uint32_t*>(&r0);
+    h[1] = *reinterpret_cast<uint32_t*>(&r1);
+}
+
+template <int FMT, int MT, int NT, int EPI, int DEPTH>
+__global__ void __launch_bounds__(kThreads, (MT * NT <= 2) ? 2 : 1) linear_mma_kernel(const LinearParams p) {
+    using F = Fmt<FMT>;
+    constexpr int UNIT = F::kUnit;
+    constexpr int RB = 16 * MT;  // tile rows held by a block (for EPI_SILU: 16 gate + 16 up)
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int M = p.M;
+    const int K = p.K;
+    const int kc = p.kc;
+    const int row_stride = kc + F::kRowPad;  // halves
+
+    // shared memory carve-up
+    __half* xs = reinterpret_cast<__half*>(smem_raw);                    // [2*M][row_stride]
+    float* red = reinterpret_cast<float*>(xs + (size_t)2 * M * row_stride + 8);  // [kWarps][RB][NT*4]
+    float* misc = red + kWarps * RB * NT * 4;                            // [64]: reductions, inv, scale
+
+    // which matrix / row block
+    int mi = 0;
+#pragma unroll
+    for (int i = 1; i < 3; ++i)
+        if (i < p.nmat && (int)blockIdx.x >= p.block_start[i]) mi = i;
+    const int rb = blockIdx.x - p.block_start[mi];
+    const int row0 = (EPI == EPI_SILU) ? rb * 16 : rb * RB;
+
+    // per-thread row pointers (clamped for loads)
+    const uint8_t* wrow[MT][2];
+    const void* srow_base[MT];
+    int rows_mt[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
+        const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
+        rows_mt[mt] = m.rows;
+        const size_t row_bytes = (FMT == FMT_W4) ? (size_t)K / 2 : (size_t)K;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int r = base + g + h * 8;
+            r = r < m.rows ? r : m.rows - 1;
+            wrow[mt][h] = m.w + (size_t)r * row_bytes + t * 16;
+        }
+        srow_base[mt] = m.scales;
+    }
+
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[mt][nt][j] = 0.0f;
+
+    bool bvalid[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) bvalid[nt] = (nt * 8 + g) < 2 * M;
+
+    uint4 wreg[DEPTH][MT][2];
+
+    // The weights do not depend on the previous kernel; the activations do.
+    // (first batch of weight loads is issued before waiting on the producer of x)
+    const int nchunks = (K + kc - 1) / kc;
+    bool waited = false;
+
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+        const int k0 = chunk * kc;
+        const int klen = min(kc, K - k0);
+        const int nunits = klen / UNIT;
+        const int per = (nunits + kWarps - 1) / kWarps;
+        const int u_begin = min(warp * per, nunits);
+        const int u_end = min(u_begin + per, nunits);
+
+        auto load_batch = [&](int ub) {
+#pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                const int u = ub + d;
+                if (u < u_end) {
+                    const size_t off = (FMT == FMT_W4) ? ((size_t)(k0 + u * UNIT) >> 1) : (size_t)(k0 + u * UNIT);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        wreg[d][mt][0] = ld_stream_u4(wrow[mt][0] + off);
+                        wreg[d][mt][1] = ld_stream_u4(wrow[mt][1] + off);
+                    }
+                }
+            }
+        };
+        load_batch(u_begin);
+
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
+        __syncthreads();  // previous chunk fully consumed before xs is overwritten
+
+        // ---- stage activations: (optional RMSNorm) -> scale by 2^e -> hi/lo binary16 ----------
+        // pass A: sum of squares over the whole row (first chunk only) and max |v| of this chunk
+        if (p.norm_w != nullptr && chunk == 0) {
+            for (int m = 0; m < M; ++m) {
+                float ss = 0.0f;
+                for (int k = tid; k < K; k += kThreads) {
+                    const float v = p.x[(size_t)m * p.ldx + k];
+                    ss += v * v;
+                }
+                ss = block_sum(ss, misc);
+                if (tid == 0) misc[40 + m] = 1.0f / sqrtf(ss / (float)K + p.eps);
+            }
+            __syncthreads();
+        }
+        float amax = 0.0f;
+        for (int idx = tid; idx < M * klen; idx += kThreads) {
+            const int m = idx / klen;
+            const int kk = idx - m * klen;
+            float v = p.x[(size_t)m * p.ldx + k0 + kk];
+            if (p.norm_w != nullptr) v = v * misc[40 + m] * bf16_bits_to_f32(p.norm_w[k0 + kk]);
+            amax = fmaxf(amax, fabsf(v));
+        }
+        amax = block_max(amax, misc);
+        // power-of-two scale that puts the chunk maximum in [2^13, 2^14)
+        float xscale = 1.0f, inv_xscale = 1.0f;
+        if (amax > 0.0f && amax < INFINITY) {
+            const int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;  // floor(log2(amax)) for normals
+            int sh = 13 - e;
+            sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+            xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
+            inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
+        }
+        for (int idx = tid; idx < M * klen; idx += kThreads) {
+            const int m = idx / klen;
+            const int kk = idx - m * klen;
+            float v = p.x[(size_t)m * p.ldx + k0 + kk];
+            if (p.norm_w != nullptr) v = v * misc[40 + m] * bf16_bits_to_f32(p.norm_w[k0 + kk]);
+            v *= xscale;
+            const __half hi = __float2half_rn(v);
+            const __half lo = __float2half_rn(v - __half2float(hi));
+            const int si = stage_index<FMT>(kk);
+            xs[(size_t)(2 * m) * row_stride + si] = hi;
+            xs[(size_t)(2 * m + 1) * row_stride + si] = lo;
+        }
+        __syncthreads();
+
+        // ---- stream this warp's units ----------------------------------------------------------
+        float c[MT][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[mt][nt][j] = 0.0f;
+
+        for (int ub = u_begin; ub < u_end; ub += DEPTH) {
+            if (ub != u_begin) load_batch(ub);
+#pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                const int u = ub + d;
+                if (u >= u_end) break;
+                if (FMT == FMT_W4) {
+                    // B fragments: for word i the lane reads 8 halves (16 B) of its column
+                    uint4 bq[NT][4];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (bvalid[nt]) {
+                                bq[nt][i] = *reinterpret_cast<const uint4*>(
+                                    xs + (size_t)(nt * 8 + g) * row_stride + u * 128 + i * 32 + t * 8);
+                            } else {
+                                bq[nt][i] = make_uint4(0, 0, 0, 0);
+                            }
+                        }
+                    }
+                    // group scales of the rows this lane holds
+                    float gs[MT][2];
+                    const int gidx = (k0 >> 7) + u;
+                    const int gpr = K >> 7;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            int r = base + g + h * 8;
+                            r = r < rows_mt[mt] ? r : rows_mt[mt] - 1;
+                            const __half s = __ldg(reinterpret_cast<const __half*>(srow_base[mt]) + (size_t)r * gpr + gidx);
+                            gs[mt][h] = __half2float(s) * inv_xscale;
+                        }
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint32_t wlo[4] = {wreg[d][mt][0].x, wreg[d][mt][0].y, wreg[d][mt][0].z, wreg[d][mt][0].w};
+                        const uint32_t whi[4] = {wreg[d][mt][1].x, wreg[d][mt][1].y, wreg[d][mt][1].z, wreg[d][mt][1].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t al[4], ah[4];
+                            unpack_w4(wlo[i], al);
+                            unpack_w4(whi[i], ah);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                mma_f16(c[mt][nt], al[0], ah[0], al[1], ah[1], bq[nt][i].x, bq[nt][i].y);
+                                mma_f16(c[mt][nt], al[2], ah[2], al[3], ah[3], bq[nt][i].z, bq[nt][i].w);
+                            }
+                        }
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            acc[mt][nt][0] = fmaf(c[mt][nt][0], gs[mt][0], acc[mt][nt][0]);
+                            acc[mt][nt][1] = fmaf(c[mt][nt][1], gs[mt][0], acc[mt][nt][1]);
+                            acc[mt][nt][2] = fmaf(c[mt][nt][2], gs[mt][1], acc[mt][nt][2]);
+                            acc[mt][nt][3] = fmaf(c[mt][nt][3], gs[mt][1], acc[mt][nt][3]);
+                            c[mt][nt][0] = c[mt][nt][1] = c[mt][nt][2] = c[mt][nt][3] = 0.0f;
+                        }
+                    }
+                } else {
+                    // I8: 16 columns per lane, natural order: two 16 B reads of the lane's column
+                    uint4 bq[NT][2];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            if (bvalid[nt]) {
+                                bq[nt][i] = *reinterpret_cast<const uint4*>(
+                                    xs + (size_t)(nt * 8 + g) * row_stride + u * 64 + t * 16 + i * 8);
+                            } else {
+                                bq[nt][i] = make_uint4(0, 0, 0, 0);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint32_t wlo[4] = {wreg[d][mt][0].x, wreg[d][mt][0].y, wreg[d][mt][0].z, wreg[d][mt][0].w};
+                        const uint32_t whi[4] = {wreg[d][mt][1].x, wreg[d][mt][1].y, wreg[d][mt][1].z, wreg[d][mt][1].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t al[2], ah[2];
+                            unpack_i8(wlo[i], al);
+                            unpack_i8(whi[i], ah);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const uint4 b = bq[nt][i >> 1];
+                                const uint32_t b0 = (i & 1) ? b.z : b.x;
+                                const uint32_t b1 = (i & 1) ? b.w : b.y;
+                                mma_f16(c[mt][nt], al[0], ah[0], al[1], ah[1], b0, b1);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (FMT == FMT_I8) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[mt][nt][j] = fmaf(c[mt][nt][j], inv_xscale, acc[mt][nt][j]);
+        }
+    }
+    pdl_launch_dependents();
+
+    // ---- combine the warps' K-partials (fixed order) -------------------------------------------
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m = nt * 4 + t;
+            red[((size_t)warp * RB + mt * 16 + g) * (NT * 4) + m] = acc[mt][nt][0] + acc[mt][nt][1];
+            red[((size_t)warp * RB + mt * 16 + g + 8) * (NT * 4) + m] = acc[mt][nt][2] + acc[mt][nt][3];
+        }
+    __syncthreads();
+
+    constexpr int RO = (EPI == EPI_SILU) ? 16 : RB;  // output rows per block
+    const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
+    for (int idx = tid; idx < RO * M; idx += kThreads) {
+        const int r = idx % RO;
+        const int m = idx / RO;
+        const int row = row0 + r;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) v += red[((size_t)w * RB + r) * (NT * 4) + m];
+        if (FMT == FMT_I8 && row < om.rows) v *= reinterpret_cast<const float*>(om.scales)[row];
+        if (EPI == EPI_SILU) {
+            float u = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) u += red[((size_t)w * RB + 16 + r) * (NT * 4) + m];
+            if (FMT == FMT_I8 && row < om.rows) u *= reinterpret_cast<const float*>(p.mat[1].scales)[row];
+            v = (v / (1.0f + expf(-v))) * u;  // silu(gate) * up, crates/inference/src/kernels/inference.rs:995
+        }
+        if (EPI == EPI_TOP1) {
+            misc[idx] = row < om.rows ? v : -INFINITY;  // M == 1, idx == r
+        } else if (row < om.rows) {
+            const size_t o = (size_t)m * om.ldo + row;
+            if (EPI == EPI_RESIDUAL) v = om.residual[o] + v;
+            om.out[o] = v;
+        }
+    }
+    if (EPI == EPI_TOP1) {
+        __syncthreads();
+        if (warp == 0) {
+            float best = -INFINITY;
+            uint32_t tok = 0xffffffffu;
+            for (int r = lane; r < RB; r += 32) {
+                const float v = misc[r];
+                const uint32_t tk = (row0 + r) < om.rows ? (uint32_t)(row0 + r) : 0xffffffffu;
+                if (top1_better(v, tk, best, tok)) { best = v; tok = tk; }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+                const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
+                if (top1_better(ov, ot, best, tok)) { best = ov; tok = ot; }
+            }
+            if (lane == 0) {
+                p.partial_tokens[blockIdx.x] = tok;
+                p.partial_logits[blockIdx.x] = best;
+            }
+        }
+    }
+}
+
+// Reference-order fallback for shapes the tensor-core kernel does not take (K not a multiple of
+// the unit): one warp per row, lane-strided columns, (w*scale)*x per element and the
+// shuffle-down tree of kmll's matvec_i8_scaled_kernel
+// (crates/inference/src/kernels/inference.rs:742-800, :180-187).
+template <int EPI>
+__global__ void linear_i8_rowwarp_kernel(const float* __restrict__ x, int M, int ldx, const int8_t* __restrict__ w,
+                                         const float* __restrict__ scales, int rows, int K,
+                                         const float* __restrict__ residual, float* __restrict__ out, int ldo) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float scale = scales[row];
+    const int8_t* wr = w + (size_t)row * K;
+    for (int m = 0; m < M; ++m) {
+        const float* xr = x + (size_t)m * ldx;
+        float acc = 0.0f;
+        for (int col = lane; col < K; col += 32) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn((float)wr[col], scale), xr[col]));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
+        if (lane == 0) {
+            const size_t o = (size_t)m * ldo + row;
+            out[o] = (EPI == EPI_RESIDUAL) ? residual[o] + acc : acc;
+        }
+    }
+}
+
+// Reference-order lm_head + arg-max for shapes the tensor-core kernel does not take: 32 warps per
+// block, one row per warp, block arg-max -> one partial per 32 rows
+// (matvec_top1_i8_scaled_stage_kernel, crates/inference/src/kernels/inference.rs:331-417).
+__global__ void __launch_bounds__(1024) linear_i8_rowwarp_top1_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
+                                                                      const float* __restrict__ scales, int rows, int K,
+                                                                      uint32_t* __restrict__ partial_tokens,
+                                                                      float* __restrict__ partial_logits) {
+    __shared__ float s_logit[32];
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * 32 + warp;
+    float acc = -INFINITY;
+    if (row < rows) {
+        const float scale = scales[row];
+        const int8_t* wr = w + (size_t)row * K;
+        float part = 0.0f;
+        for (int col = lane; col < K; col += 32) part = __fadd_rn(part, __fmul_rn(__fmul_rn((float)wr[col], scale), x[col]));
+        acc = part;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
+    if (lane == 0) s_logit[warp] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        const int r = blockIdx.x * 32 + lane;
+        float best = r < rows ? s_logit[lane] : -INFINITY;
+        uint32_t tok = r < rows ? (uint32_t)r : 0xffffffffu;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
+            if (top1_better(ov, ot, best, tok)) { best = ov; tok = ot; }
+        }
+        if (lane == 0) {
+            partial_tokens[blockIdx.x] = tok;
+            partial_logits[blockIdx.x] = best;
+        }
+    }
+}
+
+// Second stage of the fused arg-max: one block reduces the per-block partials
+// (argmax_pairs_f32_packed_kernel, crates/inference/src/kernels/inference.rs:1812-1878).
+__global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const float* __restrict__ logits, int count,
+                                   uint64_t* __restrict__ packed_out) {
+    pdl_wait();
+    __shared__ float s_logit[32];
+    __shared__ uint32_t s_tok[32];
+    float best = -INFINITY;
+    uint32_t tok = 0xffffffffu;
+    bool have = false;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        const float v = logits[i];
+        const uint32_t tk = tokens[i];
+        if (!have || top1_better(v, tk, best, tok)) { best = v; tok = tk; have = true; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
+        if (top1_better(ov, ot, best, tok)) { best = ov; tok = ot; }
+    }
+    if (lane == 0) { s_logit[warp] = best; s_tok[warp] = tok; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? s_logit[lane] : -INFINITY;
+        tok = lane < nw ? s_tok[lane] : 0xffffffffu;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
+            if (top1_better(ov, ot, best, tok)) { best = ov; tok = ot; }
+        }
+        if (lane == 0) packed_out[0] = pack_top1(best, tok);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+static size_t linear_smem_bytes(int fmt, int M, int kc, int MT, int NT) {
+    const int pad = fmt == FMT_W4 ? Fmt<FMT_W4>::kRowPad : Fmt<FMT_I8>::kRowPad;
+    size_t xs = (size_t)2 * M * (kc + pad) * sizeof(__half) + 16;
+    size_t red = (size_t)kWarps * 16 * MT * NT * 4 * sizeof(float);
+    return xs + red + 64 * sizeof(float);
+}
+
+template <int FMT, int MT, int NT, int EPI, int DEPTH>
+static int launch_variant(cudaStream_t stream, LinearParams& p, int grid) {
+    auto kern = linear_mma_kernel<FMT, MT, NT, EPI, DEPTH>;
+    // choose the K chunk so that the staged activations stay within ~96 KB
+    const int unit = Fmt<FMT>::kUnit;
+    int kc_max = (96 * 1024) / (2 * p.M * (int)sizeof(__half));
+    kc_max = (kc_max / unit) * unit;
+    if (kc_max < unit) kc_max = unit;
+    p.kc = p.K < kc_max ? p.K : kc_max;
+    const size_t smem = linear_smem_bytes(FMT, p.M, p.kc, MT, NT);
+    static thread_local bool configured = false;  // one flag per template instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaError_t e = launch(kern, dim3(grid), dim3(kThreads), smem, stream, true, p);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear launch: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+template <int FMT, int EPI>
+static int launch_linear(cudaStream_t stream, LinearParams& p) {
+    // rows per block: 32 when that still gives every SM a few blocks, else 16
+    int total32 = 0, total16 = 0;
+    for (int i = 0; i < p.nmat; ++i) {
+        total32 += (p.mat[i].rows + 31) / 32;
+        total16 += (p.mat[i].rows + 15) / 16;
+    }
+    const bool silu = (EPI == EPI_SILU);
+    (void)total16;
+    // the arg-max form always uses 32-row blocks so its partial count depends on rows only
+    const bool mt2 = silu || EPI == EPI_TOP1 || total32 >= 2 * 148;
+    int grid = 0;
+    if (silu) {
+        p.block_start[0] = 0;
+        grid = (p.mat[0].rows + 15) / 16;
+        p.block_start[1] = p.block_start[2] = p.block_start[3] = grid;
+        p.nmat = 1;  // block lookup uses matrix 0 only; gate/up are mat[0], mat[1]
+    } else {
+        const int rb = mt2 ? 32 : 16;
+        for (int i = 0; i < p.nmat; ++i) {
+            p.block_start[i] = grid;
+            grid += (p.mat[i].rows + rb - 1) / rb;
+        }
+        for (int i = p.nmat; i < 4; ++i) p.block_start[i] = grid;
+    }
+    const int M = p.M;
+    if (EPI == EPI_TOP1 || EPI == EPI_SILU) {
+        // rows-per-block fixed at 32 tile rows so the partial count is a pure function of rows
+        if (M <= 4) return launch_variant<FMT, 2, 1, EPI, 4>(stream, p, grid);
+        return fail(KMLL_ERR_UNSUPPORTED, "fused epilogue supports batch <= 4 per call");
+    }
+    if (M <= 4) {
+        if (mt2) return launch_variant<FMT, 2, 1, EPI, 4>(stream, p, grid);
+        return launch_variant<FMT, 1, 1, EPI, 4>(stream, p, grid);
+    }
+    if (M <= 8) {
+        if (mt2) return launch_variant<FMT, 2, 2, EPI, 2>(stream, p, grid);
+        return launch_variant<FMT, 1, 2, EPI, 2>(stream, p, grid);
+    }
+    if (mt2) return launch_variant<FMT, 2, 4, EPI, 1>(stream, p, grid);
+    return launch_variant<FMT, 1, 4, EPI, 2>(stream, p, grid);
+}
+
+static bool fast_shape(int fmt, int K) { return fmt == FMT_W4 ? (K % 128 == 0) : (K % 64 == 0); }
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct MatArg {
+    const void* w;
+    const void* scales;
+    int rows;
+    float* out;
+    const float* residual;
+};
+
+// Common entry: validates, then dispatches batch chunks of up to 16 rows.
+template <int FMT, int EPI>
+static int run_linear(const char* name, cudaStream_t stream, const float* x, int M, int K, int ldx,
+                      const uint16_t* norm_w, float eps, const MatArg* mats, int nmat, int ldo_override,
+                      uint32_t* partial_tokens, float* partial_logits) {
+    if (x == nullptr) return fail(KMLL_ERR_NULL, "%s: null input", name);
+    if (M <= 0 || K <= 0) return fail(KMLL_ERR_SHAPE, "%s: batch=%d in_dim=%d must be positive", name, M, K);
+    for (int i = 0; i < nmat; ++i) {
+        if (mats[i].w == nullptr || mats[i].scales == nullptr) return fail(KMLL_ERR_NULL, "%s: null weight", name);
+        if (EPI != EPI_TOP1 && mats[i].out == nullptr && !(EPI == EPI_SILU && i == 1))
+            return fail(KMLL_ERR_NULL, "%s: null output", name);
+        if (mats[i].rows <= 0) return fail(KMLL_ERR_SHAPE, "%s: weight must have rows", name);
+        if (EPI == EPI_RESIDUAL && mats[i].residual == nullptr) return fail(KMLL_ERR_NULL, "%s: null residual", name);
+    }
+    if (FMT == FMT_W4 && K % 128 != 0)
+        return fail(KMLL_ERR_SHAPE, "%s: W4-G128 needs in_dim %% 128 == 0, got %d", name, K);
+    const bool fast = fast_shape(FMT, K) && aligned16(mats[0].w) && (nmat < 2 || aligned16(mats[1].w)) &&
+                      (nmat < 3 || aligned16(mats[2].w));
+    if (!fast) {
+        if constexpr (FMT == FMT_I8 && (EPI == EPI_STORE || EPI == EPI_RESIDUAL || EPI == EPI_TOP1)) {
+            if (norm_w != nullptr)
+                return fail(KMLL_ERR_UNSUPPORTED, "%s: fused RMSNorm needs in_dim %% 64 == 0, got %d", name, K);
+            if constexpr (EPI == EPI_TOP1) {
+                const int grid = (mats[0].rows + 31) / 32;
+                cudaError_t e = launch(linear_i8_rowwarp_top1_kernel, dim3(grid), dim3(1024), 0, stream, true, x,
+                                       reinterpret_cast<const int8_t*>(mats[0].w), reinterpret_cast<const float*>(mats[0].scales),
+                                       mats[0].rows, K, partial_tokens, partial_logits);
+                if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
+                return KMLL_OK;
+            } else {
+                for (int i = 0; i < nmat; ++i) {
+                    const int ldo = ldo_override > 0 ? ldo_override : mats[i].rows;
+                    const int wpb = 4;
+                    cudaError_t e = launch(linear_i8_rowwarp_kernel<EPI>, dim3((mats[i].rows + wpb - 1) / wpb), dim3(wpb * 32), 0,
+                                           stream, true, x, M, ldx, reinterpret_cast<const int8_t*>(mats[i].w),
+                                           reinterpret_cast<const float*>(mats[i].scales), mats[i].rows, K, mats[i].residual,
+                                           mats[i].out, ldo);
+                    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
+                }
+                return KMLL_OK;
+            }
+        } else {
+            return fail(KMLL_ERR_UNSUPPORTED, "%s: in_dim=%d needs a multiple of %d and 16-byte aligned weights", name, K,
+                        FMT == FMT_W4 ? 128 : 64);
+        }
+    }
+    for (int m0 = 0; m0 < M; m0 += 16) {
+        LinearParams p;
+        memset(&p, 0, sizeof(p));
+        p.x = x + (size_t)m0 * ldx;
+        p.M = (M - m0) < 16 ? (M - m0) : 16;
+        p.K = K;
+        p.ldx = ldx;
+        p.norm_w = norm_w;
+        p.eps = eps;
+        p.nmat = nmat;
+        for (int i = 0; i < nmat; ++i) {
+            const int ldo = ldo_override > 0 ? ldo_override : mats[i].rows;
+            p.mat[i].w = reinterpret_cast<const uint8_t*>(mats[i].w);
+            p.mat[i].scales = mats[i].scales;
+            p.mat[i].rows = mats[i].rows;
+            p.mat[i].ldo = ldo;
+            p.mat[i].out = mats[i].out ? mats[i].out + (size_t)m0 * ldo : nullptr;
+            p.mat[i].residual = mats[i].residual ? mats[i].residual + (size_t)m0 * ldo : nullptr;
+        }
+        p.partial_tokens = partial_tokens;
+        p.partial_logits = partial_logits;
+        int rc = launch_linear<FMT, EPI>(stream, p);
+        if (rc != KMLL_OK) return rc;
+    }
+    return KMLL_OK;
+}
+
+template <int FMT>
+static int run_top1(const char* name, cudaStream_t stream, const float* x, const uint16_t* norm_w, float eps,
+                    const void* w, const void* scales, int rows, int cols, uint32_t* partial_tokens,
+                    float* partial_logits, uint64_t* packed_out) {
+    if (partial_tokens == nullptr || partial_logits == nullptr || packed_out == nullptr)
+        return fail(KMLL_ERR_NULL, "%s: null partial/packed buffer", name);
+    MatArg m = {w, scales, rows, nullptr, nullptr};
+    int rc = run_linear<FMT, EPI_TOP1>(name, stream, x, 1, cols, cols, norm_w, eps, &m, 1, 0, partial_tokens, partial_logits);
+    if (rc != KMLL_OK) return rc;
+    const int count = kmll_linear_top1_partial_count(rows);
+    cudaError_t e = launch(top1_reduce_kernel, dim3(1), dim3(256), 0, stream, true, (const uint32_t*)partial_tokens,
+                           (const float*)partial_logits, count, packed_out);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+}  // namespace kmll
+
+using namespace kmll;
+
+extern "C" {
+
+int kmll_linear_top1_partial_count(int rows) { return rows <= 0 ? 0 : (rows + 31) / 32; }
+
+int kmll_linear_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, int rows, int cols, float* y) {
+    MatArg m = {w, scales, rows, y, nullptr};
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+}
+int kmll_linear_w4g128(kmll_stream_t s, const float* x, const uint8_t* packed, const uint16_t* gs, int rows, int cols, float* y) {
+    MatArg m = {packed, gs, rows, y, nullptr};
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+}
+int kmll_linear_residual_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, const float* residual,
+                            int rows, int cols, float* out) {
+    MatArg m = {w, scales, rows, out, residual};
+    return run_linear<FMT_I8, EPI_RESIDUAL>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+}
+int kmll_linear_residual_w4g128(kmll_stream_t s, const float* x, const uint8_t* packed, const uint16_t* gs,
+                                const float* residual, int rows, int cols, float* out) {
+    MatArg m = {packed, gs, rows, out, residual};
+    return run_linear<FMT_W4, EPI_RESIDUAL>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+}
+
+int kmll_linear_triple_i8(kmll_stream_t s, const float* x, const int8_t* wq, const float* sq, const int8_t* wk,
+                          const float* sk, const int8_t* wv, const float* sv, int q_rows, int kv_rows, int cols,
+                          float* q, float* k, float* v) {
+    MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
+}
+int kmll_linear_triple_w4g128(kmll_stream_t s, const float* x, const uint8_t* wq, const uint16_t* sq, const uint8_t* wk,
+                              const uint16_t* sk, const uint8_t* wv, const uint16_t* sv, int q_rows, int kv_rows, int cols,
+                              float* q, float* k, float* v) {
+    MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
+}
+int kmll_rmsnorm_linear_triple_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* wq,
+                                  const float* sq, const int8_t* wk, const float* sk, const int8_t* wv, const float* sv,
+                                  int q_rows, int kv_rows, int cols, float* q, float* k, float* v) {
+    KMLL_REQUIRE_PTR(nw);
+    MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 3, 0, nullptr, nullptr);
+}
+int kmll_rmsnorm_linear_triple_w4g128(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const uint8_t* wq,
+                                      const uint16_t* sq, const uint8_t* wk, const uint16_t* sk, const uint8_t* wv,
+                                      const uint16_t* sv, int q_rows, int kv_rows, int cols, float* q, float* k, float* v) {
+    KMLL_REQUIRE_PTR(nw);
+    MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 3, 0, nullptr, nullptr);
+}
+
+int kmll_silu_gate_up_i8(kmll_stream_t s, const float* x, const int8_t* wg, const float* sg, const int8_t* wu,
+                         const float* su, int rows, int cols, float* out) {
+    MatArg m[2] = {{wg, sg, rows, out, nullptr}, {wu, su, rows, nullptr, nullptr}};
+    return run_linear<FMT_I8, EPI_SILU>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 2, 0, nullptr, nullptr);
+}
+int kmll_silu_gate_up_w4g128(kmll_stream_t s, const float* x, const uint8_t* wg, const uint16_t* sg, const uint8_t* wu,
+                             const uint16_t* su, int rows, int cols, float* out) {
+    MatArg m[2] = {{wg, sg, rows, out, nullptr}, {wu, su, rows, nullptr, nullptr}};
+    return run_linear<FMT_W4, EPI_SILU>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 2, 0, nullptr, nullptr);
+}
+int kmll_rmsnorm_silu_gate_up_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* wg,
+                                 const float* sg, const int8_t* wu, const float* su, int rows, int cols, float* out) {
+    KMLL_REQUIRE_PTR(nw);
+    MatArg m[2] = {{wg, sg, rows, out, nullptr}, {wu, su, rows, nullptr, nullptr}};
+    return run_linear<FMT_I8, EPI_SILU>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 2, 0, nullptr, nullptr);
+}
+int kmll_rmsnorm_silu_gate_up_w4g128(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const uint8_t* wg,
+                                     const uint16_t* sg, const uint8_t* wu, const uint16_t* su, int rows, int cols,
+                                     float* out) {
+    KMLL_REQUIRE_PTR(nw);
+    MatArg m[2] = {{wg, sg, rows, out, nullptr}, {wu, su, rows, nullptr, nullptr}};
+    return run_linear<FMT_W4, EPI_SILU>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 2, 0, nullptr, nullptr);
+}
+
+int kmll_linear_top1_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, int rows, int cols,
+                        uint32_t* pt, float* pl, uint64_t* packed_out) {
+    return run_top1<FMT_I8>(__func__, as_stream(s), x, nullptr, 0.f, w, scales, rows, cols, pt, pl, packed_out);
+}
+int kmll_linear_top1_w4g128(kmll_stream_t s, const float* x, const uint8_t* packed, const uint16_t* gs, int rows, int cols,
+                            uint32_t* pt, float* pl, uint64_t* packed_out) {
+    return run_top1<FMT_W4>(__func__, as_stream(s), x, nullptr, 0.f, packed, gs, rows, cols, pt, pl, packed_out);
+}
+int kmll_rmsnorm_linear_top1_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* w,
+                                const float* scales, int rows, int cols, uint32_t* pt, float* pl, uint64_t* packed_out) {
+    KMLL_REQUIRE_PTR(nw);
+    return run_top1<FMT_I8>(__func__, as_stream(s), x, nw, eps, w, scales, rows, cols, pt, pl, packed_out);
+}
+int kmll_rmsnorm_linear_top1_w4g128(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const uint8_t* packed,
+                                    const uint16_t* gs, int rows, int cols, uint32_t* pt, float* pl, uint64_t* packed_out) {
+    KMLL_REQUIRE_PTR(nw);
+    return run_top1<FMT_W4>(__func__, as_stream(s), x, nw, eps, packed, gs, rows, cols, pt, pl, packed_out);
+}
+
+int kmll_linear_batched_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, int batch, int in_dim,
+                           int out_dim, float* y) {
+    MatArg m = {w, scales, out_dim, y, nullptr};
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+}
+int kmll_linear_batched_w4g128(kmll_stream_t s, const float* x, const uint8_t* packed, const uint16_t* gs, int batch,
+                               int in_dim, int out_dim, float* y) {
+    MatArg m = {packed, gs, out_dim, y, nullptr};
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+}
+int kmll_linear_qkv_batched_i8(kmll_stream_t s, const float* x, const int8_t* wq, const float* sq, const int8_t* wk,
+                               const float* sk, const int8_t* wv, const float* sv, int batch, int in_dim, int q_dim,
+                               int kv_dim, float* q, float* k, float* v) {
+    MatArg m[3] = {{wq, sq, q_dim, q, nullptr}, {wk, sk, kv_dim, k, nullptr}, {wv, sv, kv_dim, v, nullptr}};
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
+}
+int kmll_linear_qkv_batched_w4g128(kmll_stream_t s, const float* x, const uint8_t* wq, const uint16_t* sq, const uint8_t* wk,
+                                   const uint16_t* sk, const uint8_t* wv, const uint16_t* sv, int batch, int in_dim,
+                                   int q_dim, int kv_dim, float* q, float* k, float* v) {
+    MatArg m[3] = {{wq, sq, q_dim, q, nullptr}, {wk, sk, kv_dim, k, nullptr}, {wv, sv, kv_dim, v, nullptr}};
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
+}
+
+}  // extern "C"
