@@ -379,7 +379,7 @@ def test_softmax_rows_vs_oracle(cuda, rows, cols):
     rng = np.random.default_rng(rows + cols)
     x = rng.normal(0, 3, (rows, cols)).astype(F)
     got, ref = host(ops.softmax_rows(dev(x))), oracle.softmax_rows(x)
-    assert np.max(np.abs(got - ref)) <= 1e-6
+    assert np.max(np.abs(got - ref) / np.maximum(ref, 1e-3)) <= 1e-5  # summation order differs
     assert np.max(np.abs(got.sum(axis=1) - 1.0)) <= 1e-5
 
 
