@@ -51,6 +51,9 @@ enum {
 const char* kmll_last_error(void);
 /* Library version and the SM architecture the kernels were compiled for (100 = sm_100a). */
 int kmll_version(void);
+/* Device-side status word of the current device: 0 = ok, 1 = a bounded wait inside a kernel timed
+ * out (the kernel returned early; its output is invalid).  Synchronises the device. */
+int kmll_device_status(int* status_out);
 int kmll_compiled_arch(void);
 
 /* ------------------------------------------------------------------------------------------

@@ -42,7 +42,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("KMLL_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
         if ptxas_verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -24,6 +24,7 @@
 //     a re-association of f32 roundings, far inside kmll's own 1e-4*sqrt(K) tolerance.
 //   * Warps combine their K-partials through shared memory in a fixed order, so results are
 //     deterministic run to run.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -561,7 +562,114 @@ __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const fl
     }
 }
 
+}  // namespace kmll
+
+#include "linear_stream.cuh"
+
+namespace kmll {
+
 // ---- host side --------------------------------------------------------------------------------
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int num_sms() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+        return v;
+    }();
+    return n;
+}
+
+static bool stream_kernel_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("KMLL_LINEAR");
+        return !(v != nullptr && std::strcmp(v, "legacy") == 0);
+    }();
+    return on;
+}
+
+// Plans and launches the persistent streaming kernel.  *launched stays false when the shape does
+// not fit its shared-memory plan (the caller then uses the tiled kernel).
+template <int FMT, int MT, int NT, int EPI>
+static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bool* launched, int* top1_count) {
+    constexpr int ROWS = 16 * MT;
+    constexpr int RU = (EPI == EPI_SILU) ? 16 : ROWS;
+    StreamParams sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.x = lp.x; sp.M = lp.M; sp.K = lp.K; sp.ldx = lp.ldx;
+    sp.norm_w = lp.norm_w; sp.eps = lp.eps;
+    for (int i = 0; i < 3; ++i) sp.mat[i] = lp.mat[i];
+    sp.partial_tokens = lp.partial_tokens;
+    sp.partial_logits = lp.partial_logits;
+    const int K = lp.K, M = lp.M;
+    const int rowbytes = FMT == FMT_W4 ? K / 2 : K;
+    const int chb_max = MT == 1 ? 2048 : 1024;
+    sp.chb = rowbytes < chb_max ? rowbytes : chb_max;
+    sp.row_pitch = sp.chb + ((sp.chb % 128 == 0) ? 64 : 0);  // pitch = 64 mod 128: 16-byte reads of two rows never collide
+    // digit rows: 16-byte reads of two rows (lanes g, g+1) must fall into different banks
+    sp.xs_pitch = K + (FMT == FMT_W4 ? 16 : 64);
+    const int ngr = K / 128;
+    bool sc_in_stage = FMT == FMT_W4 && (ngr % 8 == 0) && ((sp.chb / 64) % 8 == 0);
+    for (int i = 0; i < lp.nmat && sc_in_stage; ++i) sc_in_stage = aligned16(lp.mat[i].scales);
+    sp.sc_in_stage = sc_in_stage ? 1 : 0;
+    auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
+    const size_t xs_bytes = up128((size_t)4 * M * sp.xs_pitch);
+    const size_t xsum_bytes = FMT == FMT_W4 ? up128((size_t)2 * M * ngr * sizeof(int)) : 0;
+    sp.sc_pitch = (sp.chb / 64) * 2 + 16;
+    const size_t stage_bytes = up128((size_t)ROWS * sp.row_pitch + (sc_in_stage ? (size_t)ROWS * sp.sc_pitch : 0));
+    sp.stage_bytes = (int)stage_bytes;
+    const size_t red_bytes = (size_t)2 * kSWarps * ROWS * 4 * sizeof(float);
+    const size_t bars_bytes = 128;
+    const size_t misc_bytes = 1024;
+    const size_t fixed = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes;
+    const size_t budget = 226 * 1024;
+    if (fixed + 2 * stage_bytes > budget) return KMLL_OK;  // *launched stays false
+    // the activation staging keeps x in registers (M*K <= 24576) and reads it with 16-byte loads
+    if ((size_t)M * K > (size_t)kStageBlocks * 8 * kSThreads || (lp.ldx & 3) != 0 ||
+        (reinterpret_cast<uintptr_t>(lp.x) & 15) != 0 || (lp.norm_w != nullptr && (reinterpret_cast<uintptr_t>(lp.norm_w) & 15) != 0))
+        return KMLL_OK;
+    int ns = (int)((budget - fixed) / stage_bytes);
+    sp.ns = ns > 4 ? 4 : ns;
+    sp.off_xsum = (int)xs_bytes;
+    sp.off_ring = sp.off_xsum + (int)xsum_bytes;
+    sp.off_red = sp.off_ring + (int)(sp.ns * stage_bytes);
+    sp.off_bars = sp.off_red + (int)red_bytes;
+    sp.off_misc = sp.off_bars + (int)bars_bytes;
+    const size_t smem = (size_t)sp.off_misc + misc_bytes;
+
+    int units = 0;
+    if (EPI == EPI_SILU) {
+        sp.nmat = 1;
+        sp.unit_start[0] = 0;
+        units = (lp.mat[0].rows + 15) / 16;
+        sp.unit_start[1] = sp.unit_start[2] = sp.unit_start[3] = units;
+    } else {
+        sp.nmat = lp.nmat;
+        for (int i = 0; i < lp.nmat; ++i) {
+            sp.unit_start[i] = units;
+            units += (lp.mat[i].rows + RU - 1) / RU;
+        }
+        for (int i = lp.nmat; i < 4; ++i) sp.unit_start[i] = units;
+    }
+    sp.total_units = units;
+    int grid = units < num_sms() ? units : num_sms();
+    if (top1_count) *top1_count = grid;
+
+    auto kern = linear_stream_kernel<FMT, MT, NT, EPI>;
+    static thread_local bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaError_t e = launch(kern, dim3(grid), dim3(kSBlock), smem, stream, true, sp);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear stream launch: %s", cudaGetErrorString(e));
+    *launched = true;
+    return KMLL_OK;
+}
+
 
 static size_t linear_smem_bytes(int fmt, int M, int kc, int MT, int NT) {
     const int pad = fmt == FMT_W4 ? Fmt<FMT_W4>::kRowPad : Fmt<FMT_I8>::kRowPad;
@@ -592,7 +700,19 @@ static int launch_variant(cudaStream_t stream, LinearParams& p, int grid) {
 }
 
 template <int FMT, int EPI>
-static int launch_linear(cudaStream_t stream, LinearParams& p) {
+static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) {
+    if (p.M <= 4 && stream_kernel_enabled()) {
+        bool launched = false;
+        constexpr int MT = (EPI == EPI_SILU || EPI == EPI_TOP1) ? 2 : 1;
+        const int rc = p.M <= 2 ? launch_stream_variant<FMT, MT, 1, EPI>(stream, p, &launched, top1_count)
+                                : launch_stream_variant<FMT, MT, 2, EPI>(stream, p, &launched, top1_count);
+        if (rc != KMLL_OK || launched) return rc;
+    }
+    if (top1_count) {
+        int n = 0;
+        for (int i = 0; i < p.nmat; ++i) n += (p.mat[i].rows + 31) / 32;
+        *top1_count = n;
+    }
     // rows per block: 32 when that still gives every SM a few blocks, else 16
     int total32 = 0, total16 = 0;
     for (int i = 0; i < p.nmat; ++i) {
@@ -637,7 +757,6 @@ static int launch_linear(cudaStream_t stream, LinearParams& p) {
 
 static bool fast_shape(int fmt, int K) { return fmt == FMT_W4 ? (K % 128 == 0) : (K % 64 == 0); }
 
-static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct MatArg {
     const void* w;
@@ -651,7 +770,7 @@ struct MatArg {
 template <int FMT, int EPI>
 static int run_linear(const char* name, cudaStream_t stream, const float* x, int M, int K, int ldx,
                       const uint16_t* norm_w, float eps, const MatArg* mats, int nmat, int ldo_override,
-                      uint32_t* partial_tokens, float* partial_logits) {
+                      uint32_t* partial_tokens, float* partial_logits, int* top1_count = nullptr) {
     if (x == nullptr) return fail(KMLL_ERR_NULL, "%s: null input", name);
     if (M <= 0 || K <= 0) return fail(KMLL_ERR_SHAPE, "%s: batch=%d in_dim=%d must be positive", name, M, K);
     for (int i = 0; i < nmat; ++i) {
@@ -675,6 +794,7 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
                                        reinterpret_cast<const int8_t*>(mats[0].w), reinterpret_cast<const float*>(mats[0].scales),
                                        mats[0].rows, K, partial_tokens, partial_logits);
                 if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
+                if (top1_count) *top1_count = grid;
                 return KMLL_OK;
             } else {
                 for (int i = 0; i < nmat; ++i) {
@@ -714,7 +834,7 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
         }
         p.partial_tokens = partial_tokens;
         p.partial_logits = partial_logits;
-        int rc = launch_linear<FMT, EPI>(stream, p);
+        int rc = launch_linear<FMT, EPI>(stream, p, top1_count);
         if (rc != KMLL_OK) return rc;
     }
     return KMLL_OK;
@@ -727,9 +847,9 @@ static int run_top1(const char* name, cudaStream_t stream, const float* x, const
     if (partial_tokens == nullptr || partial_logits == nullptr || packed_out == nullptr)
         return fail(KMLL_ERR_NULL, "%s: null partial/packed buffer", name);
     MatArg m = {w, scales, rows, nullptr, nullptr};
-    int rc = run_linear<FMT, EPI_TOP1>(name, stream, x, 1, cols, cols, norm_w, eps, &m, 1, 0, partial_tokens, partial_logits);
+    int count = 0;
+    int rc = run_linear<FMT, EPI_TOP1>(name, stream, x, 1, cols, cols, norm_w, eps, &m, 1, 0, partial_tokens, partial_logits, &count);
     if (rc != KMLL_OK) return rc;
-    const int count = kmll_linear_top1_partial_count(rows);
     cudaError_t e = launch(top1_reduce_kernel, dim3(1), dim3(256), 0, stream, true, (const uint32_t*)partial_tokens,
                            (const float*)partial_logits, count, packed_out);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
@@ -743,6 +863,19 @@ using namespace kmll;
 extern "C" {
 
 int kmll_linear_top1_partial_count(int rows) { return rows <= 0 ? 0 : (rows + 31) / 32; }
+
+#ifdef KMLL_TRACE
+int kmll_debug_trace(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (kSWarps + 1) * 16) == cudaSuccess ? 0 : -4;
+}
+#endif
+
+int kmll_device_status(int* status_out) {
+    KMLL_REQUIRE_PTR(status_out);
+    cudaError_t e = cudaMemcpyFromSymbol(status_out, g_device_status, sizeof(int));
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
 
 int kmll_linear_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, int rows, int cols, float* y) {
     MatArg m = {w, scales, rows, y, nullptr};

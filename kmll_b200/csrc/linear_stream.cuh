@@ -1,0 +1,558 @@
+// Persistent streaming form of the quantized linear kernel (batch <= 4), included by linear.cu.
+//
+// One thread block per SM stays resident and walks over "units" of 16 (or 32) weight rows.
+// The activations are staged in shared memory ONCE per block.  The weights never touch the
+// register file on their way in: a dedicated producer warp fills a ring of shared-memory stages
+// with bulk asynchronous copies (cp.async.bulk, completion counted in bytes on an mbarrier), one
+// copy of up to 2 KB per weight row per stage (bulk copies cost ~10 issue cycles each whatever
+// their size, so they must be large), plus one small copy per row for the W4 group scales of the
+// same columns.  Eight consumer warps split the columns of a stage, multiply on the tensor cores
+// and release the stage through a second mbarrier; up to four stages (~130 KB) are in flight per
+// SM.  Partial sums of the warps meet in shared memory once per unit, in a fixed order.
+//
+// Arithmetic: the integer tensor-core MMA (mma.sync m16n8k32, s8 x s8 -> s32).  The activations
+// are scaled by a power of two, rounded to integers below 2^27 and split into four balanced
+// base-128 digits, each an int8: x*2^sh = d3*128^3 + d2*128^2 + d1*128 + d0.  The four digits of
+// a batch row are four of the eight MMA columns, so one MMA multiplies 16 weight rows by all
+// digits at once, exactly (int32 accumulation cannot round).  RS-I8 weights are the A operand
+// as they lie in memory - no unpack instruction at all; W4 nibbles become bytes with three
+// logic operations per eight weights, and their +8 offset is removed with a per-group sum of
+// the digits.  The only roundings are x -> 27-bit integer (at most 2^-28 of max|x|, f32 itself
+// carries 24 bits) and the final few f32 operations per output row.
+// Every wait on an mbarrier is bounded and the kernel has no other blocking wait: on time-out a
+// warp raises the device status word, stops and lets the others time out as well.
+#pragma once
+
+namespace kmll {
+
+constexpr int kSWarps = 16;
+constexpr int kSThreads = kSWarps * 32;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
+
+__device__ int g_device_status = 0;  // 0 = ok; first failure wins (1 = mbarrier wait timed out)
+#ifdef KMLL_TRACE
+__device__ long long g_trace[(kSWarps + 1) * 16];
+#define KTRACE(i) do { if (blockIdx.x == 0 && lane == 0) g_trace[warp * 16 + (i)] = clock64(); } while (0)
+#else
+#define KTRACE(i) do {} while (0)
+#endif
+
+struct StreamParams {
+    const float* x;
+    int M, K, ldx;
+    const uint16_t* norm_w;
+    float eps;
+    LinearMat mat[3];
+    int nmat;
+    int unit_start[4];
+    int total_units;
+    int chb;        // weight bytes per row per stage (multiple of 64)
+    int ns;         // stages
+    int xs_pitch;   // bytes per staged digit row of the activations
+    int row_pitch;  // bytes per weight row inside a stage (chb + 64: conflict-free 16-byte reads)
+    int sc_in_stage;  // W4: group scales travel with the stage (needs K/128 % 8 == 0)
+    int sc_pitch;     // bytes per row of the scales area of a stage (2*chb/64 + 16: conflict-free)
+    int stage_bytes;  // weights + scales of one stage
+    int off_xsum, off_ring, off_red, off_bars, off_misc;  // shared-memory offsets in bytes
+    uint32_t* partial_tokens;
+    float* partial_logits;
+};
+
+__device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ inline void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ inline void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ inline void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ inline bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ inline unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait; false = timed out (the caller raises the status word and unwinds).  There is no
+// blocking hardware barrier anywhere in the kernel, so a time-out in one warp can never leave
+// another warp waiting forever.
+__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+__device__ inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+constexpr int kProducerWarp = kSWarps;           // the last warp issues the copies
+constexpr int kSBlock = (kSWarps + 1) * 32;      // consumers + one producer warp
+
+// Barrier among the 256 consumer threads only (the producer warp never joins it).
+__device__ inline void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kSThreads) : "memory"); }
+
+__device__ inline void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Stages x (M <= 4 rows of K) into shared memory as four int8 digit rows per batch row
+// (row 4*m + j holds digit 3-j, most significant first) and, for W4, the per-group offset terms.
+// W4 order inside each 8-column block: even columns first ([0,2,4,6,1,3,5,7]), because
+// `w & 0x0f0f0f0f` yields the even nibbles of a weight word as four bytes and
+// `(w >> 4) & 0x0f0f0f0f` the odd ones; I8: natural order.
+// xcomb[group][2*m + p] = 8 * (128 * sum(d_{3-2p}) + sum(d_{2-2p})) over the group's 128 columns: what
+// the +8 offset of the stored nibbles adds to the combined digit pair p of batch row m.
+// Returns 2^-sh.  One pass: each thread keeps its (at most kStageBlocks) 8-column blocks of x in
+// registers between the block-wide reduction and the conversion.
+constexpr int kStageBlocks = 6;  // M*K <= 6*8*512 = 24576
+__device__ inline int bfe_s7(int x) {
+    int d;
+    asm("bfe.s32 %0, %1, 0, 7;" : "=r"(d) : "r"(x));
+    return d;
+}
+__device__ inline uint32_t bfi_byte(uint32_t word, int value, int byte) {
+    uint32_t r;
+    asm("bfi.b32 %0, %1, %2, %3, 8;" : "=r"(r) : "r"(value), "r"(word), "r"(byte * 8));
+    return r;
+}
+template <int FMT>
+__device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int* xcomb, float* misc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int M = p.M, K = p.K;
+    const int nblk = (M * K) >> 3;  // 8-element blocks; a multiple of 16
+    const bool norm = p.norm_w != nullptr;
+    float v[kStageBlocks][8];
+    float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float mx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < kStageBlocks; ++j) {
+        const int wbase = j * kSThreads + warp * 32;
+        if (wbase < nblk) {  // warp-uniform
+            const int blk = wbase + lane;
+            const bool active = blk < nblk;
+            const int e = (active ? blk : wbase) << 3;
+            const int m = (M == 1) ? 0 : e / K;
+            const int k = e - m * K;
+            const float4* src = reinterpret_cast<const float4*>(p.x + (size_t)m * p.ldx + k);
+            const float4 a = src[0], b = src[1];
+            v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+            v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+            float s_ = 0.0f, m_ = 0.0f;
+            if (norm) {
+                const uint4 w4 = *reinterpret_cast<const uint4*>(p.norm_w + k);
+                const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    s_ += v[j][2 * q] * v[j][2 * q] + v[j][2 * q + 1] * v[j][2 * q + 1];
+                    m_ = fmaxf(m_, fmaxf(fabsf(v[j][2 * q] * __uint_as_float(ww[q] << 16)),
+                                         fabsf(v[j][2 * q + 1] * __uint_as_float(ww[q] & 0xffff0000u))));
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) m_ = fmaxf(m_, fabsf(v[j][q]));
+            }
+            if (active) {
+#pragma unroll
+                for (int mm = 0; mm < 4; ++mm)
+                    if (m == mm) { ss[mm] += s_; mx[mm] = fmaxf(mx[mm], m_); }
+            }
+        }
+    }
+    KTRACE(11);
+#pragma unroll
+    for (int mm = 0; mm < 4; ++mm) {
+        ss[mm] = warp_sum(ss[mm]);
+        mx[mm] = warp_max(mx[mm]);
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int mm = 0; mm < 4; ++mm) { misc[warp * 8 + mm] = ss[mm]; misc[warp * 8 + 4 + mm] = mx[mm]; }
+    }
+    consumer_bar_sync();
+    KTRACE(12);
+    float inv[4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int mm = 0; mm < 4; ++mm) {
+        float s_ = 0.0f, m_ = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kSWarps; ++w) { s_ += misc[w * 8 + mm]; m_ = fmaxf(m_, misc[w * 8 + 4 + mm]); }
+        inv[mm] = norm ? 1.0f / sqrtf(s_ / (float)K + p.eps) : 1.0f;
+        amax = fmaxf(amax, m_ * inv[mm]);
+    }
+    // power-of-two scale: |x * 2^sh| < 2^27 for every element
+    float xscale = 1.0f, inv_xscale = 1.0f;
+    if (amax > 0.0f && amax < INFINITY) {
+        const int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;  // floor(log2(amax)) (denormals: -127)
+        int sh = 26 - e;
+        sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+        xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
+        inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
+    }
+#pragma unroll
+    for (int j = 0; j < kStageBlocks; ++j) {
+        const int wbase = j * kSThreads + warp * 32;
+        if (wbase < nblk) {
+            const int blk = wbase + lane;
+            const bool active = blk < nblk;
+            const int e = (active ? blk : wbase) << 3;
+            const int m = (M == 1) ? 0 : e / K;
+            const int k = e - m * K;
+            if (norm) {
+                const uint4 w4 = *reinterpret_cast<const uint4*>(p.norm_w + k);
+                const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+                const float im = inv[0] * (m == 0) + inv[1] * (m == 1) + inv[2] * (m == 2) + inv[3] * (m == 3);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
+                    v[j][2 * q] = v[j][2 * q] * im * __uint_as_float(ww[q] << 16);
+                    v[j][2 * q + 1] = v[j][2 * q + 1] * im * __uint_as_float(ww[q] & 0xffff0000u);
+                }
+            }
+            uint32_t dig[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // [digit row][word]
+            int dsum[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float f = v[j][q] * xscale;
+                f = fminf(fmaxf(f, -134217728.0f), 134217728.0f);  // inf/huge inputs saturate instead of wrapping
+                const int x0 = __float2int_rn(f);
+                // balanced base-128 digits: d = sign-extended low 7 bits, carry = (x + 64) >> 7
+                const int d0 = bfe_s7(x0), x1 = (x0 + 64) >> 7;
+                const int d1 = bfe_s7(x1), x2 = (x1 + 64) >> 7;
+                const int d2 = bfe_s7(x2), d3 = (x2 + 64) >> 7;  // |d3| <= 65
+                const int pos = (FMT == FMT_W4) ? (((q & 1) << 2) | (q >> 1)) : q;  // byte position inside the block
+                dig[3][pos >> 2] = bfi_byte(dig[3][pos >> 2], d0, pos & 3);
+                dig[2][pos >> 2] = bfi_byte(dig[2][pos >> 2], d1, pos & 3);
+                dig[1][pos >> 2] = bfi_byte(dig[1][pos >> 2], d2, pos & 3);
+                dig[0][pos >> 2] = bfi_byte(dig[0][pos >> 2], d3, pos & 3);
+                if (FMT == FMT_W4) { dsum[3] += d0; dsum[2] += d1; dsum[1] += d2; dsum[0] += d3; }
+            }
+            if (active) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + r) * p.xs_pitch + k) = make_uint2(dig[r][0], dig[r][1]);
+            }
+            if (FMT == FMT_W4) {
+                // the 16 threads that hold one 128-column group are 16 consecutive lanes
+                int c01 = 128 * dsum[0] + dsum[1], c23 = 128 * dsum[2] + dsum[3];
+#pragma unroll
+                for (int off = 1; off < 16; off <<= 1) {
+                    c01 += __shfl_xor_sync(0xffffffffu, c01, off);
+                    c23 += __shfl_xor_sync(0xffffffffu, c23, off);
+                }
+                if (active && (lane & 15) == 0) {
+                    xcomb[(k >> 7) * (2 * M) + 2 * m] = 8 * c01;
+                    xcomb[(k >> 7) * (2 * M) + 2 * m + 1] = 8 * c23;
+                }
+            }
+        }
+    }
+    KTRACE(13);
+    consumer_bar_sync();
+    return inv_xscale;
+}
+
+template <int FMT, int MT, int NT, int EPI>
+__global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamParams p) {
+    constexpr int ROWS = 16 * MT;                       // weight rows per stage
+    constexpr int RU = (EPI == EPI_SILU) ? 16 : ROWS;   // output rows per unit
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int M = p.M, K = p.K;
+    const int rowbytes = (FMT == FMT_W4) ? (K >> 1) : K;
+    const int chb = p.chb;
+    const int nchunks = (rowbytes + chb - 1) / chb;   // stages per unit
+    const int ns = p.ns;
+    const int xs_pitch = p.xs_pitch, row_pitch = p.row_pitch;
+    const int ngr = K >> 7;  // W4 groups per row
+    const int sc_off = ROWS * row_pitch;  // scales area inside a stage: [ROWS][sc_pitch bytes] binary16
+    const int sc_pitch = p.sc_pitch;
+
+    int8_t* xs = reinterpret_cast<int8_t*>(smem);                       // [4*M][xs_pitch] digit rows
+    int* xcomb = reinterpret_cast<int*>(smem + p.off_xsum);             // [ngr][2*M] W4 offset terms of the digit pairs
+    unsigned char* ring = smem + p.off_ring;
+    float* red = reinterpret_cast<float*>(smem + p.off_red);            // [2][kSWarps][ROWS][4]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [4] stage filled (bytes landed)
+    uint64_t* empty = full + 4;                                         // [4] stage released by the 8 consumers
+    uint64_t* ubar = full + 8;                                          // [2] all consumers wrote their partials
+    uint64_t* done = full + 10;                                         // [2] warp 0 consumed the partials
+    float* misc = reinterpret_cast<float*>(smem + p.off_misc);
+
+    KTRACE(0);
+    if (tid == 0) {
+        for (int s = 0; s < ns; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kSWarps); }
+        mbar_init(&ubar[0], kSWarps); mbar_init(&ubar[1], kSWarps);
+        mbar_init(&done[0], 1); mbar_init(&done[1], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    KTRACE(1);
+
+    auto unit_rows = [&](int unit, int& mi, int& row0) {
+        mi = 0;
+#pragma unroll
+        for (int i = 1; i < 3; ++i)
+            if (i < p.nmat && unit >= p.unit_start[i]) mi = i;
+        row0 = (unit - p.unit_start[mi]) * RU;
+    };
+
+    if (warp == kProducerWarp) {
+        // ---- producer: per stage one bulk copy per weight row (+ one for its group scales) ------
+        int stage = 0, fills = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < p.total_units && ok; unit += gridDim.x) {
+            int mi, row0;
+            unit_rows(unit, mi, row0);
+            for (int ch = 0; ch < nchunks; ++ch, ++fills) {
+                // wait until the consumers have released this stage (the first ns fills find it empty)
+                if (fills >= ns && !mbar_wait(&empty[stage], phase ^ 1u)) { ok = false; break; }
+                const int bytes = min(chb, rowbytes - ch * chb);
+                const int sc_bytes = (FMT == FMT_W4 && p.sc_in_stage) ? (bytes >> 6) * 2 : 0;
+                if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)(bytes + sc_bytes) * ROWS);
+                __syncwarp();
+                if (lane < ROWS) {
+                    const LinearMat& m = (EPI == EPI_SILU) ? p.mat[lane >> 4] : p.mat[mi];
+                    int r = (EPI == EPI_SILU) ? row0 + (lane & 15) : row0 + lane;
+                    r = r < m.rows ? r : m.rows - 1;  // rows past the end re-read the last row; never stored
+                    unsigned char* st = ring + (size_t)stage * p.stage_bytes;
+                    bulk_g2s(st + (size_t)lane * row_pitch, m.w + (size_t)r * rowbytes + (size_t)ch * chb, (uint32_t)bytes, &full[stage]);
+                    if (sc_bytes)
+                        bulk_g2s(st + sc_off + (size_t)lane * sc_pitch,
+                                 reinterpret_cast<const unsigned char*>(m.scales) + ((size_t)r * ngr + (size_t)ch * (chb >> 6)) * 2,
+                                 (uint32_t)sc_bytes, &full[stage]);
+                }
+                if (++stage == ns) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) atomicCAS(&g_device_status, 0, 1);
+        return;
+    }
+
+    // ---- consumers: stage the activations once (weights are already on their way) --------------
+    KTRACE(2);
+    pdl_wait();
+    KTRACE(3);
+    const float inv_xscale = stage_activations<FMT>(p, xs, xcomb, misc);
+    KTRACE(4);
+
+    // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns
+    bool bvalid[NT];
+    const int8_t* xcol[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        bvalid[nt] = (nt * 8 + g) < 4 * M;
+        xcol[nt] = xs + (size_t)(bvalid[nt] ? nt * 8 + g : 0) * xs_pitch;
+    }
+    // this lane's C columns 2t, 2t+1 of each n-tile: digits (3,2) of a batch row for even t, (1,0) for
+    // odd t; the pair is combined as 128*c[2t] + c[2t+1] and weighted by 128^2 resp. 1
+    const float w_pair = ((t & 1) ? 1.0f : 16384.0f) * inv_xscale;
+    bool cvalid[NT];
+    const int* xcp[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        cvalid[nt] = (nt * 8 + 2 * t) < 4 * M;
+        xcp[nt] = xcomb + (cvalid[nt] ? nt * 4 + t : 0);
+    }
+
+    float best_logit = -INFINITY;  // EPI_TOP1 running best (warp 0)
+    uint32_t best_token = 0xffffffffu;
+
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int it = 0;
+    for (int unit = blockIdx.x; unit < p.total_units && ok; unit += gridDim.x, ++it) {
+        int mi, row0;
+        unit_rows(unit, mi, row0);
+        const int par = it & 1;
+        float acc[MT][NT][2];  // W4: group-scaled sums of this lane's digit pair, rows g and g+8
+        int c[MT][NT][4];      // exact integer dot products
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                acc[mt][nt][0] = acc[mt][nt][1] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[mt][nt][j] = 0;
+            }
+
+        for (int ch = 0; ch < nchunks; ++ch) {
+            if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
+            if (it == 0 && ch == 0) KTRACE(6);
+            const unsigned char* st = ring + (size_t)stage * p.stage_bytes;
+            const int nsegs = min(chb, rowbytes - ch * chb) >> 6;  // 64-byte segments in this stage
+            const int j0 = (warp * nsegs) / kSWarps, j1 = ((warp + 1) * nsegs) / kSWarps;
+#pragma unroll 2
+            for (int j = j0; j < j1; ++j) {
+                const int sg = ch * (chb >> 6) + j;  // segment index within the row
+                if (FMT == FMT_W4) {
+                    // 128 columns: this lane's 32 columns of its digit row -> 32 bytes
+                    uint4 bq[NT][2];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        bq[nt][0] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32) : make_uint4(0, 0, 0, 0);
+                        bq[nt][1] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32 + 16) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint4 lo4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g) * row_pitch + j * 64 + t * 16);
+                        const uint4 hi4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g + 8) * row_pitch + j * 64 + t * 16);
+                        float gs0, gs1;
+                        if (p.sc_in_stage) {
+                            gs0 = __half2float(*reinterpret_cast<const __half*>(st + sc_off + (mt * 16 + g) * sc_pitch + j * 2));
+                            gs1 = __half2float(*reinterpret_cast<const __half*>(st + sc_off + (mt * 16 + g + 8) * sc_pitch + j * 2));
+                        } else {
+                            const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
+                            const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
+                            const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);
+                            gs0 = __half2float(__ldg(reinterpret_cast<const __half*>(m.scales) + (size_t)r0 * ngr + sg));
+                            gs1 = __half2float(__ldg(reinterpret_cast<const __half*>(m.scales) + (size_t)r1 * ngr + sg));
+                        }
+                        const uint32_t wlo[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
+                        const uint32_t whi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            // word i: even nibbles -> a0/a1, odd nibbles -> a2/a3 (values 1..15, offset removed below)
+                            const uint32_t a0 = wlo[i] & 0x0f0f0f0fu, a2 = (wlo[i] >> 4) & 0x0f0f0f0fu;
+                            const uint32_t a1 = whi[i] & 0x0f0f0f0fu, a3 = (whi[i] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const uint4 b = bq[nt][i >> 1];
+                                mma_s8(c[mt][nt], a0, a1, a2, a3, (i & 1) ? b.z : b.x, (i & 1) ? b.w : b.y);
+                            }
+                        }
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            // sum (n - 8) * d = sum n*d - 8 * sum d for the digit pair (all exact, |.| < 2^24),
+                            // then the group scale in f32
+                            const int off = cvalid[nt] ? xcp[nt][sg * (2 * M)] : 0;
+                            acc[mt][nt][0] = fmaf((float)(c[mt][nt][0] * 128 + c[mt][nt][1] - off), gs0, acc[mt][nt][0]);
+                            acc[mt][nt][1] = fmaf((float)(c[mt][nt][2] * 128 + c[mt][nt][3] - off), gs1, acc[mt][nt][1]);
+                            c[mt][nt][0] = c[mt][nt][1] = c[mt][nt][2] = c[mt][nt][3] = 0;
+                        }
+                    }
+                } else {
+                    // 64 columns: this lane's 16 columns -> 16 bytes of its digit row, natural order
+                    uint4 bq[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                        bq[nt] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 64 + t * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint4 lo4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g) * row_pitch + j * 64 + t * 16);
+                        const uint4 hi4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g + 8) * row_pitch + j * 64 + t * 16);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            mma_s8(c[mt][nt], lo4.x, hi4.x, lo4.y, hi4.y, bq[nt].x, bq[nt].y);
+                            mma_s8(c[mt][nt], lo4.z, hi4.z, lo4.w, hi4.w, bq[nt].z, bq[nt].w);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);  // this warp is done with the stage
+            if (++stage == ns) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (it == 0) KTRACE(7);
+        if (it == 1) KTRACE(10);
+        // partials of this warp -> shared memory; the buffer of this parity was last used two units
+        // ago: wait until it has been consumed
+        const uint32_t upar = (uint32_t)(it >> 1) & 1u;
+        if (it >= 2 && !mbar_wait(&done[par], upar ^ 1u)) { ok = false; break; }
+        float* rp = red + ((size_t)par * kSWarps + warp) * ROWS * 4;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float v0, v1;  // rows g and g+8: this lane's two digits, weighted
+                if (FMT == FMT_W4) {
+                    v0 = acc[mt][nt][0] * w_pair;
+                    v1 = acc[mt][nt][1] * w_pair;
+                } else {
+                    v0 = ((float)c[mt][nt][0] * 128.0f + (float)c[mt][nt][1]) * w_pair;
+                    v1 = ((float)c[mt][nt][2] * 128.0f + (float)c[mt][nt][3]) * w_pair;
+                }
+                v0 += __shfl_xor_sync(0xffffffffu, v0, 1);  // digits (3,2) + digits (1,0)
+                v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                const int b = nt * 2 + (t >> 1);  // batch row
+                if ((t & 1) == 0 && b < 4) {
+                    rp[(mt * 16 + g) * 4 + b] = v0;
+                    rp[(mt * 16 + g + 8) * 4 + b] = v1;
+                }
+            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ubar[par]);
+        if (warp == 0) {
+            if (!mbar_wait(&ubar[par], upar)) { ok = false; break; }
+            if (it == 0) KTRACE(8);
+            const float* rb = red + (size_t)par * kSWarps * ROWS * 4;
+            const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
+            float cand = -INFINITY;
+            uint32_t cand_tok = 0xffffffffu;
+            for (int idx = lane; idx < RU * M; idx += 32) {
+                const int r = idx % RU, m = idx / RU;
+                const int row = row0 + r;
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kSWarps; ++w) v += rb[((size_t)w * ROWS + r) * 4 + m];
+                if (FMT == FMT_I8 && row < om.rows) v *= reinterpret_cast<const float*>(om.scales)[row];
+                if (EPI == EPI_SILU) {
+                    float u = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < kSWarps; ++w) u += rb[((size_t)w * ROWS + 16 + r) * 4 + m];
+                    if (FMT == FMT_I8 && row < om.rows) u *= reinterpret_cast<const float*>(p.mat[1].scales)[row];
+                    v = (v / (1.0f + expf(-v))) * u;
+                }
+                if (EPI == EPI_TOP1) {
+                    if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
+                } else if (row < om.rows) {
+                    const size_t o = (size_t)m * om.ldo + row;
+                    if (EPI == EPI_RESIDUAL) v = om.residual[o] + v;
+                    om.out[o] = v;
+                }
+            }
+            if (EPI == EPI_TOP1) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, cand, off);
+                    const uint32_t ot = __shfl_xor_sync(0xffffffffu, cand_tok, off);
+                    if (top1_better(ov, ot, cand, cand_tok)) { cand = ov; cand_tok = ot; }
+                }
+                if (top1_better(cand, cand_tok, best_logit, best_token)) { best_logit = cand; best_token = cand_tok; }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&done[par]);
+        }
+    }
+    KTRACE(9);
+    pdl_launch_dependents();
+    if (EPI == EPI_TOP1 && warp == 0 && lane == 0) {
+        p.partial_tokens[blockIdx.x] = best_token;
+        p.partial_logits[blockIdx.x] = best_logit;
+    }
+    if (!ok) atomicCAS(&g_device_status, 0, 1);
+}
+
+}  // namespace kmll
