@@ -8,7 +8,7 @@
 //   * prefill_causal_attention: tiled causal attention with an online softmax.
 // Math contract (all f32): score = dot * (1/sqrt(head_dim)); weights exp(s - max); out = sum(w*v)/sum(w)
 // (crates/inference/src/model.rs:11581-11649).  KV cache layout [max_seq, n_kv_heads, head_dim].
-#include "common.cuh"
+#include "internal.cuh"
 
 namespace kmll {
 

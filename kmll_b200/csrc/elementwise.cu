@@ -1,7 +1,7 @@
 // Row-reduction and elementwise operators of the decode path: RMSNorm, add, SiLU*up, RoPE,
 // KV-cache writes, row softmax, embedding lookup, arg-max / top-k.  Each makes one pass over
 // HBM with 128-bit accesses where alignment allows; all arithmetic is f32 in kmll's order.
-#include "common.cuh"
+#include "internal.cuh"
 
 namespace kmll {
 
@@ -376,6 +376,88 @@ __global__ void __launch_bounds__(1024) top_k_kernel(const float* __restrict__ l
         __syncthreads();
     }
     (void)s_idx;
+}
+
+// ---- decode-loop glue: operands that live in device memory --------------------------------------
+__global__ void prepare_incremental_dyn_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                               const float* __restrict__ v, const float* __restrict__ freqs, int half,
+                                               const DecodeState* __restrict__ state, int q_len, int kv_len, int head_dim,
+                                               float* __restrict__ q_rot, float* __restrict__ k_cache,
+                                               float* __restrict__ v_cache) {
+    pdl_wait();
+    const int position = state->position;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < q_len) {
+        const int head = i / head_dim;
+        q_rot[i] = rope_value(q, (size_t)head * head_dim, i - head * head_dim, freqs, half, (float)position);
+    }
+    if (i < kv_len) {
+        const int head = i / head_dim;
+        const size_t off = (size_t)position * kv_len + i;
+        k_cache[off] = rope_value(k, (size_t)head * head_dim, i - head * head_dim, freqs, half, (float)position);
+        v_cache[off] = v[i];
+    }
+}
+
+__global__ void decode_begin_kernel(const uint16_t* __restrict__ table, int vocab, int dim, DecodeState* state,
+                                    uint64_t* __restrict__ history, int history_cap, float* __restrict__ hidden) {
+    pdl_wait();
+    const uint64_t packed = state->next_top;
+    uint32_t token = (uint32_t)(packed & 0xffffffffull);
+    if (token >= (uint32_t)vocab) token = (uint32_t)vocab - 1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < dim) hidden[i] = bf16_bits_to_f32(table[(size_t)token * dim + i]);
+    if (i == 0) {
+        const int step = state->step;
+        if (step < history_cap) history[step] = packed;
+        state->seq_len = state->position + 1;
+    }
+}
+
+__global__ void decode_end_kernel(const uint64_t* __restrict__ packed, DecodeState* state) {
+    pdl_wait();
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        state->next_top = packed[0];
+        state->position += 1;
+        state->step += 1;
+    }
+}
+
+int prepare_incremental_dyn(cudaStream_t stream, const float* q, const float* k, const float* v, const float* freqs,
+                            int n_freqs, const DecodeState* state, int max_seq_len, int n_heads, int n_kv_heads,
+                            int head_dim, float* q_rot, float* k_cache, float* v_cache) {
+    (void)max_seq_len;
+    const int q_len = n_heads * head_dim, kv_len = n_kv_heads * head_dim;
+    const int width = q_len > kv_len ? q_len : kv_len;
+    cudaError_t e = launch(prepare_incremental_dyn_kernel, dim3((width + 255) / 256), dim3(256), 0, stream, true, q, k, v,
+                           freqs, n_freqs, state, q_len, kv_len, head_dim, q_rot, k_cache, v_cache);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prepare_incremental_dyn: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int prepare_prefill_offset(cudaStream_t stream, const float* q, const float* k, const float* v, const float* freqs,
+                           int n_freqs, int rows, int q_len, int kv_len, int head_dim, int position0, float* q_rot,
+                           float* k_cache, float* v_cache) {
+    const int width = q_len > kv_len ? q_len : kv_len;
+    const size_t total = (size_t)rows * width;
+    cudaError_t e = launch(prepare_prefill_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, true, q, k, v,
+                           freqs, n_freqs, rows, q_len, kv_len, head_dim, position0, q_rot, k_cache, v_cache);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prepare_prefill: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int decode_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim, DecodeState* state, uint64_t* history,
+                 int history_cap, float* hidden) {
+    cudaError_t e = launch(decode_begin_kernel, dim3((dim + 255) / 256), dim3(256), 0, stream, true, table, vocab, dim, state,
+                           history, history_cap, hidden);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "decode_begin: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int decode_end(cudaStream_t stream, const uint64_t* packed, DecodeState* state) {
+    cudaError_t e = launch(decode_end_kernel, dim3(1), dim3(32), 0, stream, true, packed, state);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "decode_end: %s", cudaGetErrorString(e));
+    return KMLL_OK;
 }
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

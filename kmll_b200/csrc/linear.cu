@@ -27,7 +27,7 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "common.cuh"
+#include "internal.cuh"
 
 namespace kmll {
 
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(1024) linear_i8_rowwarp_top1_kernel(const floa
 // Second stage of the fused arg-max: one block reduces the per-block partials
 // (argmax_pairs_f32_packed_kernel, crates/inference/src/kernels/inference.rs:1812-1878).
 __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const float* __restrict__ logits, int count,
-                                   uint64_t* __restrict__ packed_out) {
+                                   uint32_t token_offset, uint64_t* __restrict__ packed_out) {
     pdl_wait();
     __shared__ float s_logit[32];
     __shared__ uint32_t s_tok[32];
@@ -558,7 +558,7 @@ __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const fl
             const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
             if (top1_better(ov, ot, best, tok)) { best = ov; tok = ot; }
         }
-        if (lane == 0) packed_out[0] = pack_top1(best, tok);
+        if (lane == 0) packed_out[0] = pack_top1(best, tok == 0xffffffffu ? tok : tok + token_offset);
     }
 }
 
@@ -843,7 +843,7 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
 template <int FMT>
 static int run_top1(const char* name, cudaStream_t stream, const float* x, const uint16_t* norm_w, float eps,
                     const void* w, const void* scales, int rows, int cols, uint32_t* partial_tokens,
-                    float* partial_logits, uint64_t* packed_out) {
+                    float* partial_logits, uint64_t* packed_out, uint32_t token_offset = 0) {
     if (partial_tokens == nullptr || partial_logits == nullptr || packed_out == nullptr)
         return fail(KMLL_ERR_NULL, "%s: null partial/packed buffer", name);
     MatArg m = {w, scales, rows, nullptr, nullptr};
@@ -851,8 +851,39 @@ static int run_top1(const char* name, cudaStream_t stream, const float* x, const
     int rc = run_linear<FMT, EPI_TOP1>(name, stream, x, 1, cols, cols, norm_w, eps, &m, 1, 0, partial_tokens, partial_logits, &count);
     if (rc != KMLL_OK) return rc;
     cudaError_t e = launch(top1_reduce_kernel, dim3(1), dim3(256), 0, stream, true, (const uint32_t*)partial_tokens,
-                           (const float*)partial_logits, count, packed_out);
+                           (const float*)partial_logits, count, token_offset, packed_out);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+// Merge of per-rank packed arg-max results (tensor parallel lm_head): higher logit, then lower token.
+__global__ void merge_packed_kernel(const uint64_t* __restrict__ packed_all, int n, uint64_t* __restrict__ packed_out) {
+    pdl_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float best = -INFINITY;
+    uint32_t tok = 0xffffffffu;
+    for (int i = 0; i < n; ++i) {
+        const uint64_t p = packed_all[i];
+        const float v = __uint_as_float((uint32_t)(p >> 32));
+        const uint32_t tk = (uint32_t)(p & 0xffffffffull);
+        if (i == 0 || top1_better(v, tk, best, tok)) { best = v; tok = tk; }
+    }
+    packed_out[0] = pack_top1(best, tok);
+}
+
+int linear_top1_offset(cudaStream_t stream, int fmt, const float* x, const uint16_t* norm_w, float eps, const void* w,
+                       const void* scales, int rows, int cols, uint32_t token_offset, uint32_t* partial_tokens,
+                       float* partial_logits, uint64_t* packed_out) {
+    if (fmt == FMT_W4)
+        return run_top1<FMT_W4>("linear_top1", stream, x, norm_w, eps, w, scales, rows, cols, partial_tokens, partial_logits,
+                                packed_out, token_offset);
+    return run_top1<FMT_I8>("linear_top1", stream, x, norm_w, eps, w, scales, rows, cols, partial_tokens, partial_logits,
+                            packed_out, token_offset);
+}
+
+int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out) {
+    cudaError_t e = launch(merge_packed_kernel, dim3(1), dim3(32), 0, stream, true, packed_all, n, packed_out);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "merge_packed_top1: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }
 

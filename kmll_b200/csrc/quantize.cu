@@ -2,7 +2,7 @@
 // (RowwiseScaledI8Matrix::from_bf16_rows_symmetric, crates/inference/src/rowwise_scaled.rs:21-51)
 // with IEEE f32 division and round-half-away-from-zero, so the produced bytes are identical to
 // the host result; max() is order-independent, hence the parallel reduction is exact.
-#include "common.cuh"
+#include "internal.cuh"
 
 namespace kmll {
 
@@ -70,6 +70,11 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ src, size_t n, uint
     if (i < n) dst[i] = f32_to_bf16_bits(src[i]);
 }
 
+__global__ void widen_bf16_kernel(const uint16_t* __restrict__ src, size_t n, float* __restrict__ dst) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = bf16_bits_to_f32(src[i]);
+}
+
 __device__ inline uint64_t splitmix64(uint64_t x) {
     x += 0x9e3779b97f4a7c15ull;
     x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
@@ -85,6 +90,12 @@ __global__ void fill_normal_kernel(float* __restrict__ dst, size_t n, uint64_t s
     const float u1 = ((float)((r >> 40) & 0xffffffull) + 1.0f) * (1.0f / 16777216.0f);  // (0,1]
     const float u2 = (float)((r >> 16) & 0xffffffull) * (1.0f / 16777216.0f);           // [0,1)
     dst[i] = stddev * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+
+int widen_bf16(cudaStream_t stream, const uint16_t* src, size_t n, float* dst) {
+    if (n == 0) return KMLL_OK;
+    widen_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(src, n, dst);
+    return check_launch("widen_bf16");
 }
 
 }  // namespace kmll

@@ -33,7 +33,7 @@ _SCALARS = {
 
 def _ctype(decl: str):
     decl = decl.strip()
-    if "*" in decl:
+    if "*" in decl or "[" in decl:
         return C.c_void_p
     decl = decl.replace("const ", "").strip()
     base = decl.rsplit(" ", 1)[0] if " " in decl else decl
