@@ -55,8 +55,10 @@ __global__ void __launch_bounds__(256) softmax_value_kernel(const float* __restr
 }
 
 // ---- decode attention, split along the sequence ---------------------------------------------------
-constexpr int kAttnWarps = 4;
-constexpr int kMaxGq = 8;  // query heads per KV head handled by the fused kernel
+constexpr int kAttnWarps = 8;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kAttnTile = 64;  // positions staged in shared memory at a time
+constexpr int kMaxGq = 8;      // query heads per KV head handled by the fused kernel
 
 struct DecodeAttnParams {
     const float* q;        // [n_heads, head_dim]
@@ -86,90 +88,128 @@ __device__ inline void load_lane_slice<2>(const float* src, float (&dst)[2]) {
     dst[0] = t.x; dst[1] = t.y;
 }
 
+__device__ inline void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
+}
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One block = one KV head x one slice of the sequence.  The K and V rows of up to 64 positions are
+// brought into shared memory with 16-byte asynchronous copies that are all issued up front
+// (64 KB in flight per block, two blocks per SM), so the f32 KV cache streams at HBM rate; the
+// query heads sharing the KV head are processed together, so K and V are read once.
 template <int HD>
-__global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(const DecodeAttnParams p) {
-    constexpr int EPL = HD / 32;  // elements per lane
+__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p) {
+    constexpr int EPL = HD / 32;        // elements per lane
+    constexpr int V16 = HD / 4;         // 16-byte pieces per row
     extern __shared__ __align__(16) float smem[];
+    float* Ks = smem;                         // [kAttnTile][HD]
+    float* Vs = Ks + kAttnTile * HD;          // [kAttnTile][HD]
+    float* sc = Vs + kAttnTile * HD;          // [kMaxGq][kAttnTile] scores, then weights
+    float* hstat = sc + kMaxGq * kAttnTile;   // [kMaxGq][4]: running max, running sum, correction
+    float* red = Ks;                          // [kAttnWarps][gq][HD] (reuses the K/V tiles at the end)
+    __shared__ bool is_last;
+
     pdl_wait();
     const int seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
-    const int kv_head = blockIdx.x;
-    const int split = blockIdx.y;
-    const int gq = p.gq;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kv_head = blockIdx.x, split = blockIdx.y, gq = p.gq;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s0 = split * p.chunk;
     const int s1 = min(s0 + p.chunk, seq_len);
     const int n = s1 - s0;  // may be <= 0 for trailing splits
-
-    float* sc = smem;                          // [gq][chunk]
-    float* red = sc + gq * p.chunk;            // [kAttnWarps][gq][HD]
-    float* ml = red + kAttnWarps * gq * HD;    // [gq][2]
-    __shared__ bool is_last;
-
     const size_t kv_stride = (size_t)p.n_kv_heads * HD;
     const float scale = 1.0f / sqrtf((float)HD);
 
+    float acc[kMaxGq][EPL];
+#pragma unroll
+    for (int h = 0; h < kMaxGq; ++h)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
+
     if (n > 0) {
-        // q of this KV group, this lane's slice
         float qv[kMaxGq][EPL];
 #pragma unroll
         for (int h = 0; h < kMaxGq; ++h)
 #pragma unroll
             for (int e = 0; e < EPL; ++e)
                 qv[h][e] = h < gq ? p.q[(size_t)(kv_head * gq + h) * HD + lane * EPL + e] : 0.0f;
+        if (tid < kMaxGq) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
 
-        // pass 1: scores, one warp per position
-        const float* kbase = p.k_cache + (size_t)kv_head * HD + lane * EPL;
-        for (int i = warp; i < n; i += kAttnWarps) {
-            const float* kr = kbase + (size_t)(s0 + i) * kv_stride;
-            float kv[EPL];
-            load_lane_slice<EPL>(kr, kv);
+        for (int t0 = 0; t0 < n; t0 += kAttnTile) {
+            const int nt = min(kAttnTile, n - t0);
+            __syncthreads();  // the previous tile has been consumed
+            const float* kg = p.k_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+            const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+            for (int i = tid; i < nt * V16; i += kAttnThreads) {
+                const int r = i / V16, cidx = i - r * V16;
+                cp_async16(Ks + r * HD + cidx * 4, kg + (size_t)r * kv_stride + cidx * 4);
+            }
+            cp_async_commit();
+            for (int i = tid; i < nt * V16; i += kAttnThreads) {
+                const int r = i / V16, cidx = i - r * V16;
+                cp_async16(Vs + r * HD + cidx * 4, vg + (size_t)r * kv_stride + cidx * 4);
+            }
+            cp_async_commit();
+            cp_async_wait<1>();  // K has landed
+            __syncthreads();
+            // scores: one warp per position
+            for (int i = warp; i < nt; i += kAttnWarps) {
+                float kvv[EPL];
+                load_lane_slice<EPL>(Ks + i * HD + lane * EPL, kvv);
 #pragma unroll
-            for (int h = 0; h < kMaxGq; ++h) {
+                for (int h = 0; h < kMaxGq; ++h) {
+                    if (h < gq) {
+                        float d = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) d += qv[h][e] * kvv[e];
+                        d = warp_sum(d);
+                        if (lane == 0) sc[h * kAttnTile + i] = d * scale;
+                    }
+                }
+            }
+            __syncthreads();
+            // running softmax statistics: one warp per query head
+            for (int h = warp; h < gq; h += kAttnWarps) {
+                float m_old = hstat[h * 4], l_old = hstat[h * 4 + 1];
+                float m = m_old;
+                for (int i = lane; i < nt; i += 32) m = fmaxf(m, sc[h * kAttnTile + i]);
+                m = warp_max(m);
+                float l = 0.0f;
+                for (int i = lane; i < nt; i += 32) {
+                    const float e = expf(sc[h * kAttnTile + i] - m);
+                    sc[h * kAttnTile + i] = e;
+                    l += e;
+                }
+                l = warp_sum(l);
+                const float corr = expf(m_old - m);  // exp(-inf) = 0 on the first tile
+                if (lane == 0) { hstat[h * 4] = m; hstat[h * 4 + 1] = l_old * corr + l; hstat[h * 4 + 2] = corr; }
+            }
+            cp_async_wait<0>();  // V has landed
+            __syncthreads();
+            // weighted sum of V: one warp per position
+#pragma unroll
+            for (int h = 0; h < kMaxGq; ++h)
                 if (h < gq) {
-                    float d = 0.0f;
+                    const float corr = hstat[h * 4 + 2];
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) d += qv[h][e] * kv[e];
-                    d = warp_sum(d);
-                    if (lane == 0) sc[h * p.chunk + i] = d * scale;
+                    for (int e = 0; e < EPL; ++e) acc[h][e] *= corr;
+                }
+            for (int i = warp; i < nt; i += kAttnWarps) {
+                float vv[EPL];
+                load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
+#pragma unroll
+                for (int h = 0; h < kMaxGq; ++h) {
+                    if (h < gq) {
+                        const float w = sc[h * kAttnTile + i];
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(w, vv[e], acc[h][e]);
+                    }
                 }
             }
         }
-        __syncthreads();
-        // pass 2a: per-head max and exp-sum over the chunk
-        for (int h = warp; h < gq; h += kAttnWarps) {
-            float m = -INFINITY;
-            for (int i = lane; i < n; i += 32) m = fmaxf(m, sc[h * p.chunk + i]);
-            m = warp_max(m);
-            float l = 0.0f;
-            for (int i = lane; i < n; i += 32) {
-                const float e = expf(sc[h * p.chunk + i] - m);
-                sc[h * p.chunk + i] = e;
-                l += e;
-            }
-            l = warp_sum(l);
-            if (lane == 0) { ml[h * 2] = m; ml[h * 2 + 1] = l; }
-        }
-        __syncthreads();
-        // pass 2b: weighted sum of V, one warp per position
-        float acc[kMaxGq][EPL];
-#pragma unroll
-        for (int h = 0; h < kMaxGq; ++h)
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
-        const float* vbase = p.v_cache + (size_t)kv_head * HD + lane * EPL;
-        for (int i = warp; i < n; i += kAttnWarps) {
-            const float* vr = vbase + (size_t)(s0 + i) * kv_stride;
-            float vv[EPL];
-            load_lane_slice<EPL>(vr, vv);
-#pragma unroll
-            for (int h = 0; h < kMaxGq; ++h) {
-                if (h < gq) {
-                    const float w = sc[h * p.chunk + i];
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(w, vv[e], acc[h][e]);
-                }
-            }
-        }
+        __syncthreads();  // K/V tiles are free: reuse them for the cross-warp reduction
 #pragma unroll
         for (int h = 0; h < kMaxGq; ++h)
             if (h < gq)
@@ -180,7 +220,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(const
     pdl_launch_dependents();
 
     // write this split's partial (or the final result when there is a single split)
-    for (int idx = threadIdx.x; idx < gq * HD; idx += blockDim.x) {
+    for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
         float v = 0.0f;
@@ -189,12 +229,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(const
             for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
         }
         if (p.nsplit == 1) {
-            p.out[(size_t)head * HD + d] = n > 0 ? v / ml[h * 2 + 1] : 0.0f;
+            p.out[(size_t)head * HD + d] = n > 0 ? v / hstat[h * 4 + 1] : 0.0f;
         } else {
             p.part_acc[((size_t)head * p.nsplit + split) * HD + d] = v;
             if (d == 0) {
-                p.part_ml[((size_t)head * p.nsplit + split) * 2] = n > 0 ? ml[h * 2] : -INFINITY;
-                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = n > 0 ? ml[h * 2 + 1] : 0.0f;
+                p.part_ml[((size_t)head * p.nsplit + split) * 2] = n > 0 ? hstat[h * 4] : -INFINITY;
+                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = n > 0 ? hstat[h * 4 + 1] : 0.0f;
             }
         }
     }
@@ -203,14 +243,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(const
     // last block of this KV head merges the splits
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         const unsigned int prev = atomicAdd(&p.counters[kv_head], 1u);
         is_last = (prev == (unsigned int)p.nsplit - 1);
     }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int idx = threadIdx.x; idx < gq * HD; idx += blockDim.x) {
+    for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
         const volatile float* pml = p.part_ml + (size_t)head * p.nsplit * 2;
@@ -226,7 +266,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(const
         }
         p.out[(size_t)head * HD + d] = a / l;
     }
-    if (threadIdx.x == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
+    if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
 }
 
 // ---- prefill: tiled causal attention ---------------------------------------------------------------
@@ -352,16 +392,18 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.part_ml = workspace + (size_t)n_heads * pl.nsplit * head_dim;
     p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
     p.out = out;
-    const size_t smem = ((size_t)gq * pl.chunk + (size_t)kAttnWarps * gq * head_dim + (size_t)gq * 2) * sizeof(float);
+    size_t smem = ((size_t)2 * kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile + (size_t)kMaxGq * 4) * sizeof(float);
+    const size_t red_bytes = (size_t)kAttnWarps * gq * head_dim * sizeof(float);
+    if (red_bytes > (size_t)2 * kAttnTile * head_dim * sizeof(float)) smem += red_bytes;  // never for gq <= 8
     cudaError_t e;
     if (head_dim == 128) {
         static thread_local bool cfg = false;
         if (!cfg) { cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
-        e = launch(decode_attention_kernel<128>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnWarps * 32), smem, stream, true, p);
+        e = launch(decode_attention_kernel<128>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnThreads), smem, stream, true, p);
     } else {
         static thread_local bool cfg = false;
         if (!cfg) { cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
-        e = launch(decode_attention_kernel<64>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnWarps * 32), smem, stream, true, p);
+        e = launch(decode_attention_kernel<64>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnThreads), smem, stream, true, p);
     }
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention: %s", cudaGetErrorString(e));
     return KMLL_OK;

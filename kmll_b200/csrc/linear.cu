@@ -604,40 +604,25 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     sp.partial_tokens = lp.partial_tokens;
     sp.partial_logits = lp.partial_logits;
     const int K = lp.K, M = lp.M;
-    const int rowbytes = FMT == FMT_W4 ? K / 2 : K;
-    const int chb_max = MT == 1 ? 2048 : 1024;
-    sp.chb = rowbytes < chb_max ? rowbytes : chb_max;
-    sp.row_pitch = sp.chb + ((sp.chb % 128 == 0) ? 64 : 0);  // pitch = 64 mod 128: 16-byte reads of two rows never collide
     // digit rows: 16-byte reads of two rows (lanes g, g+1) must fall into different banks
     sp.xs_pitch = K + (FMT == FMT_W4 ? 16 : 64);
     const int ngr = K / 128;
-    bool sc_in_stage = FMT == FMT_W4 && (ngr % 8 == 0) && ((sp.chb / 64) % 8 == 0);
-    for (int i = 0; i < lp.nmat && sc_in_stage; ++i) sc_in_stage = aligned16(lp.mat[i].scales);
-    sp.sc_in_stage = sc_in_stage ? 1 : 0;
     auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
     const size_t xs_bytes = up128((size_t)4 * M * sp.xs_pitch);
     const size_t xsum_bytes = FMT == FMT_W4 ? up128((size_t)2 * M * ngr * sizeof(int)) : 0;
-    sp.sc_pitch = (sp.chb / 64) * 2 + 16;
-    const size_t stage_bytes = up128((size_t)ROWS * sp.row_pitch + (sc_in_stage ? (size_t)ROWS * sp.sc_pitch : 0));
-    sp.stage_bytes = (int)stage_bytes;
     const size_t red_bytes = (size_t)2 * kSWarps * ROWS * 4 * sizeof(float);
     const size_t bars_bytes = 128;
     const size_t misc_bytes = 1024;
-    const size_t fixed = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes;
-    const size_t budget = 226 * 1024;
-    if (fixed + 2 * stage_bytes > budget) return KMLL_OK;  // *launched stays false
+    const size_t smem = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes;
+    if (smem > 226 * 1024) return KMLL_OK;  // *launched stays false
     // the activation staging keeps x in registers (M*K <= 24576) and reads it with 16-byte loads
     if ((size_t)M * K > (size_t)kStageBlocks * 8 * kSThreads || (lp.ldx & 3) != 0 ||
         (reinterpret_cast<uintptr_t>(lp.x) & 15) != 0 || (lp.norm_w != nullptr && (reinterpret_cast<uintptr_t>(lp.norm_w) & 15) != 0))
         return KMLL_OK;
-    int ns = (int)((budget - fixed) / stage_bytes);
-    sp.ns = ns > 4 ? 4 : ns;
     sp.off_xsum = (int)xs_bytes;
-    sp.off_ring = sp.off_xsum + (int)xsum_bytes;
-    sp.off_red = sp.off_ring + (int)(sp.ns * stage_bytes);
+    sp.off_red = sp.off_xsum + (int)xsum_bytes;
     sp.off_bars = sp.off_red + (int)red_bytes;
     sp.off_misc = sp.off_bars + (int)bars_bytes;
-    const size_t smem = (size_t)sp.off_misc + misc_bytes;
 
     int units = 0;
     if (EPI == EPI_SILU) {
@@ -894,12 +879,6 @@ using namespace kmll;
 extern "C" {
 
 int kmll_linear_top1_partial_count(int rows) { return rows <= 0 ? 0 : (rows + 31) / 32; }
-
-#ifdef KMLL_TRACE
-int kmll_debug_trace(long long* out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (kSWarps + 1) * 16) == cudaSuccess ? 0 : -4;
-}
-#endif
 
 int kmll_device_status(int* status_out) {
     KMLL_REQUIRE_PTR(status_out);

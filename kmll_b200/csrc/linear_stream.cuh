@@ -1,14 +1,15 @@
 // Persistent streaming form of the quantized linear kernel (batch <= 4), included by linear.cu.
 //
-// One thread block per SM stays resident and walks over "units" of 16 (or 32) weight rows.
-// The activations are staged in shared memory ONCE per block.  The weights never touch the
-// register file on their way in: a dedicated producer warp fills a ring of shared-memory stages
-// with bulk asynchronous copies (cp.async.bulk, completion counted in bytes on an mbarrier), one
-// copy of up to 2 KB per weight row per stage (bulk copies cost ~10 issue cycles each whatever
-// their size, so they must be large), plus one small copy per row for the W4 group scales of the
-// same columns.  Eight consumer warps split the columns of a stage, multiply on the tensor cores
-// and release the stage through a second mbarrier; up to four stages (~130 KB) are in flight per
-// SM.  Partial sums of the warps meet in shared memory once per unit, in a fixed order.
+// One thread block (16 warps) per SM stays resident and walks over "units" of 16 (or 32) weight rows.
+// The activations are staged in shared memory ONCE per block as int8 digits (see below).  The
+// weights stream straight into registers: every lane keeps a ring of four 32-byte tiles in flight
+// with 128-bit no-allocate loads (64 KB outstanding per SM, the pattern that reads HBM at full rate
+// on this part), a warp request covering 8 rows x 64 B.  The 16 warps split the columns of a unit;
+// their partial sums meet in shared memory once per unit, in a fixed order, through two small
+// mbarriers (no block-wide barrier in the loop, so warps drift freely and loads never drain).
+// Bulk-copy (TMA) staging of the weights was measured and rejected for this kernel: issuing a
+// bulk copy blocks the issuing lane for hundreds of cycles, and routing the weights through shared
+// memory nearly saturates the shared-memory pipe that the activation digits also need.
 //
 // Arithmetic: the integer tensor-core MMA (mma.sync m16n8k32, s8 x s8 -> s32).  The activations
 // are scaled by a power of two, rounded to integers below 2^27 and split into four balanced
@@ -30,12 +31,6 @@ constexpr int kSThreads = kSWarps * 32;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
 
 __device__ int g_device_status = 0;  // 0 = ok; first failure wins (1 = mbarrier wait timed out)
-#ifdef KMLL_TRACE
-__device__ long long g_trace[(kSWarps + 1) * 16];
-#define KTRACE(i) do { if (blockIdx.x == 0 && lane == 0) g_trace[warp * 16 + (i)] = clock64(); } while (0)
-#else
-#define KTRACE(i) do {} while (0)
-#endif
 
 struct StreamParams {
     const float* x;
@@ -46,14 +41,8 @@ struct StreamParams {
     int nmat;
     int unit_start[4];
     int total_units;
-    int chb;        // weight bytes per row per stage (multiple of 64)
-    int ns;         // stages
     int xs_pitch;   // bytes per staged digit row of the activations
-    int row_pitch;  // bytes per weight row inside a stage (chb + 64: conflict-free 16-byte reads)
-    int sc_in_stage;  // W4: group scales travel with the stage (needs K/128 % 8 == 0)
-    int sc_pitch;     // bytes per row of the scales area of a stage (2*chb/64 + 16: conflict-free)
-    int stage_bytes;  // weights + scales of one stage
-    int off_xsum, off_ring, off_red, off_bars, off_misc;  // shared-memory offsets in bytes
+    int off_xsum, off_red, off_bars, off_misc;  // shared-memory offsets in bytes
     uint32_t* partial_tokens;
     float* partial_logits;
 };
@@ -101,11 +90,9 @@ __device__ inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint
                  : "memory");
 }
 
-constexpr int kProducerWarp = kSWarps;           // the last warp issues the copies
-constexpr int kSBlock = (kSWarps + 1) * 32;      // consumers + one producer warp
+constexpr int kSBlock = kSThreads;
 
-// Barrier among the 256 consumer threads only (the producer warp never joins it).
-__device__ inline void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kSThreads) : "memory"); }
+__device__ inline void consumer_bar_sync() { __syncthreads(); }
 
 __device__ inline void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -177,7 +164,6 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int
             }
         }
     }
-    KTRACE(11);
 #pragma unroll
     for (int mm = 0; mm < 4; ++mm) {
         ss[mm] = warp_sum(ss[mm]);
@@ -188,7 +174,6 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int
         for (int mm = 0; mm < 4; ++mm) { misc[warp * 8 + mm] = ss[mm]; misc[warp * 8 + 4 + mm] = mx[mm]; }
     }
     consumer_bar_sync();
-    KTRACE(12);
     float inv[4];
     float amax = 0.0f;
 #pragma unroll
@@ -265,48 +250,41 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int
             }
         }
     }
-    KTRACE(13);
     consumer_bar_sync();
     return inv_xscale;
 }
 
+
 template <int FMT, int MT, int NT, int EPI>
 __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamParams p) {
-    constexpr int ROWS = 16 * MT;                       // weight rows per stage
+    constexpr int ROWS = 16 * MT;                       // weight rows per unit tile
     constexpr int RU = (EPI == EPI_SILU) ? 16 : ROWS;   // output rows per unit
+    constexpr int kDepth = 4 / MT;  // weight tiles in flight per lane: 128 B x 512 threads = 64 KB per SM
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int M = p.M, K = p.K;
     const int rowbytes = (FMT == FMT_W4) ? (K >> 1) : K;
-    const int chb = p.chb;
-    const int nchunks = (rowbytes + chb - 1) / chb;   // stages per unit
-    const int ns = p.ns;
-    const int xs_pitch = p.xs_pitch, row_pitch = p.row_pitch;
+    const int nseg = rowbytes >> 6;  // 64-byte segments per row (W4: quantization groups)
+    const int j0 = (warp * nseg) / kSWarps, j1 = ((warp + 1) * nseg) / kSWarps;  // this warp's K slice
+    const int spu = j1 - j0;         // tiles per unit for this warp
+    const int xs_pitch = p.xs_pitch;
     const int ngr = K >> 7;  // W4 groups per row
-    const int sc_off = ROWS * row_pitch;  // scales area inside a stage: [ROWS][sc_pitch bytes] binary16
-    const int sc_pitch = p.sc_pitch;
 
     int8_t* xs = reinterpret_cast<int8_t*>(smem);                       // [4*M][xs_pitch] digit rows
     int* xcomb = reinterpret_cast<int*>(smem + p.off_xsum);             // [ngr][2*M] W4 offset terms of the digit pairs
-    unsigned char* ring = smem + p.off_ring;
     float* red = reinterpret_cast<float*>(smem + p.off_red);            // [2][kSWarps][ROWS][4]
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [4] stage filled (bytes landed)
-    uint64_t* empty = full + 4;                                         // [4] stage released by the 8 consumers
-    uint64_t* ubar = full + 8;                                          // [2] all consumers wrote their partials
-    uint64_t* done = full + 10;                                         // [2] warp 0 consumed the partials
+    uint64_t* ubar = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [2] all warps wrote their partials
+    uint64_t* done = ubar + 2;                                          // [2] warp 0 consumed the partials
     float* misc = reinterpret_cast<float*>(smem + p.off_misc);
 
-    KTRACE(0);
     if (tid == 0) {
-        for (int s = 0; s < ns; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kSWarps); }
         mbar_init(&ubar[0], kSWarps); mbar_init(&ubar[1], kSWarps);
         mbar_init(&done[0], 1); mbar_init(&done[1], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-    KTRACE(1);
 
     auto unit_rows = [&](int unit, int& mi, int& row0) {
         mi = 0;
@@ -316,45 +294,36 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         row0 = (unit - p.unit_start[mi]) * RU;
     };
 
-    if (warp == kProducerWarp) {
-        // ---- producer: per stage one bulk copy per weight row (+ one for its group scales) ------
-        int stage = 0, fills = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int unit = blockIdx.x; unit < p.total_units && ok; unit += gridDim.x) {
+    // ---- weight stream: a ring of kDepth tiles per lane, filled with 128-bit streaming loads ---------
+    // A tile is 16*MT rows x 64 bytes; this lane holds 16 bytes of rows g and g+8 of each 16-row block.
+    uint4 wreg[kDepth][MT][2];
+    uint32_t sreg[kDepth][MT];  // W4: binary16 group scales of rows g (low half) and g+8 (high half)
+    int l_unit = blockIdx.x, l_seg = j0;  // load cursor
+    auto load_tile = [&](uint4 (&w)[MT][2], uint32_t (&sc)[MT]) {
+        if (l_unit < p.total_units && spu > 0) {
             int mi, row0;
-            unit_rows(unit, mi, row0);
-            for (int ch = 0; ch < nchunks; ++ch, ++fills) {
-                // wait until the consumers have released this stage (the first ns fills find it empty)
-                if (fills >= ns && !mbar_wait(&empty[stage], phase ^ 1u)) { ok = false; break; }
-                const int bytes = min(chb, rowbytes - ch * chb);
-                const int sc_bytes = (FMT == FMT_W4 && p.sc_in_stage) ? (bytes >> 6) * 2 : 0;
-                if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)(bytes + sc_bytes) * ROWS);
-                __syncwarp();
-                if (lane < ROWS) {
-                    const LinearMat& m = (EPI == EPI_SILU) ? p.mat[lane >> 4] : p.mat[mi];
-                    int r = (EPI == EPI_SILU) ? row0 + (lane & 15) : row0 + lane;
-                    r = r < m.rows ? r : m.rows - 1;  // rows past the end re-read the last row; never stored
-                    unsigned char* st = ring + (size_t)stage * p.stage_bytes;
-                    bulk_g2s(st + (size_t)lane * row_pitch, m.w + (size_t)r * rowbytes + (size_t)ch * chb, (uint32_t)bytes, &full[stage]);
-                    if (sc_bytes)
-                        bulk_g2s(st + sc_off + (size_t)lane * sc_pitch,
-                                 reinterpret_cast<const unsigned char*>(m.scales) + ((size_t)r * ngr + (size_t)ch * (chb >> 6)) * 2,
-                                 (uint32_t)sc_bytes, &full[stage]);
+            unit_rows(l_unit, mi, row0);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
+                const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
+                const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);  // rows past the end re-read the last row
+                w[mt][0] = ld_stream_u4(m.w + (size_t)r0 * rowbytes + (size_t)l_seg * 64 + t * 16);
+                w[mt][1] = ld_stream_u4(m.w + (size_t)r1 * rowbytes + (size_t)l_seg * 64 + t * 16);
+                if (FMT == FMT_W4) {
+                    const unsigned short* sp = reinterpret_cast<const unsigned short*>(m.scales);
+                    sc[mt] = (uint32_t)__ldg(sp + (size_t)r0 * ngr + l_seg) | ((uint32_t)__ldg(sp + (size_t)r1 * ngr + l_seg) << 16);
                 }
-                if (++stage == ns) { stage = 0; phase ^= 1u; }
             }
+            if (++l_seg == j1) { l_seg = j0; l_unit += gridDim.x; }
         }
-        if (!ok) atomicCAS(&g_device_status, 0, 1);
-        return;
-    }
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) load_tile(wreg[d], sreg[d]);  // weights do not depend on the previous kernel
 
-    // ---- consumers: stage the activations once (weights are already on their way) --------------
-    KTRACE(2);
+    // ---- stage the activations once -----------------------------------------------------------------
     pdl_wait();
-    KTRACE(3);
     const float inv_xscale = stage_activations<FMT>(p, xs, xcomb, misc);
-    KTRACE(4);
 
     // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns
     bool bvalid[NT];
@@ -377,17 +346,11 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     float best_logit = -INFINITY;  // EPI_TOP1 running best (warp 0)
     uint32_t best_token = 0xffffffffu;
-
-    int stage = 0;
-    uint32_t phase = 0;
     bool ok = true;
-    int it = 0;
-    for (int unit = blockIdx.x; unit < p.total_units && ok; unit += gridDim.x, ++it) {
-        int mi, row0;
-        unit_rows(unit, mi, row0);
-        const int par = it & 1;
-        float acc[MT][NT][2];  // W4: group-scaled sums of this lane's digit pair, rows g and g+8
-        int c[MT][NT][4];      // exact integer dot products
+
+    float acc[MT][NT][2];  // W4: group-scaled sums of this lane's digit pair, rows g and g+8
+    int c[MT][NT][4];      // exact integer dot products
+    auto reset_acc = [&]() {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -396,97 +359,72 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 #pragma unroll
                 for (int j = 0; j < 4; ++j) c[mt][nt][j] = 0;
             }
+    };
+    reset_acc();
 
-        for (int ch = 0; ch < nchunks; ++ch) {
-            if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
-            if (it == 0 && ch == 0) KTRACE(6);
-            const unsigned char* st = ring + (size_t)stage * p.stage_bytes;
-            const int nsegs = min(chb, rowbytes - ch * chb) >> 6;  // 64-byte segments in this stage
-            const int j0 = (warp * nsegs) / kSWarps, j1 = ((warp + 1) * nsegs) / kSWarps;
-#pragma unroll 2
-            for (int j = j0; j < j1; ++j) {
-                const int sg = ch * (chb >> 6) + j;  // segment index within the row
-                if (FMT == FMT_W4) {
-                    // 128 columns: this lane's 32 columns of its digit row -> 32 bytes
-                    uint4 bq[NT][2];
+    // multiply one tile (segment sg of the current unit) held in registers
+    auto compute_tile = [&](const uint4 (&w)[MT][2], const uint32_t (&sc)[MT], int sg) {
+        if (FMT == FMT_W4) {
+            uint4 bq[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                bq[nt][0] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32) : make_uint4(0, 0, 0, 0);
+                bq[nt][1] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32 + 16) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t wlo[4] = {w[mt][0].x, w[mt][0].y, w[mt][0].z, w[mt][0].w};
+                const uint32_t whi[4] = {w[mt][1].x, w[mt][1].y, w[mt][1].z, w[mt][1].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // word i: even nibbles -> a0/a1, odd nibbles -> a2/a3 (values 1..15, offset removed below)
+                    const uint32_t a0 = wlo[i] & 0x0f0f0f0fu, a2 = (wlo[i] >> 4) & 0x0f0f0f0fu;
+                    const uint32_t a1 = whi[i] & 0x0f0f0f0fu, a3 = (whi[i] >> 4) & 0x0f0f0f0fu;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
-                        bq[nt][0] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32) : make_uint4(0, 0, 0, 0);
-                        bq[nt][1] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32 + 16) : make_uint4(0, 0, 0, 0);
-                    }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint4 lo4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g) * row_pitch + j * 64 + t * 16);
-                        const uint4 hi4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g + 8) * row_pitch + j * 64 + t * 16);
-                        float gs0, gs1;
-                        if (p.sc_in_stage) {
-                            gs0 = __half2float(*reinterpret_cast<const __half*>(st + sc_off + (mt * 16 + g) * sc_pitch + j * 2));
-                            gs1 = __half2float(*reinterpret_cast<const __half*>(st + sc_off + (mt * 16 + g + 8) * sc_pitch + j * 2));
-                        } else {
-                            const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
-                            const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
-                            const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);
-                            gs0 = __half2float(__ldg(reinterpret_cast<const __half*>(m.scales) + (size_t)r0 * ngr + sg));
-                            gs1 = __half2float(__ldg(reinterpret_cast<const __half*>(m.scales) + (size_t)r1 * ngr + sg));
-                        }
-                        const uint32_t wlo[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
-                        const uint32_t whi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            // word i: even nibbles -> a0/a1, odd nibbles -> a2/a3 (values 1..15, offset removed below)
-                            const uint32_t a0 = wlo[i] & 0x0f0f0f0fu, a2 = (wlo[i] >> 4) & 0x0f0f0f0fu;
-                            const uint32_t a1 = whi[i] & 0x0f0f0f0fu, a3 = (whi[i] >> 4) & 0x0f0f0f0fu;
-#pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) {
-                                const uint4 b = bq[nt][i >> 1];
-                                mma_s8(c[mt][nt], a0, a1, a2, a3, (i & 1) ? b.z : b.x, (i & 1) ? b.w : b.y);
-                            }
-                        }
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            // sum (n - 8) * d = sum n*d - 8 * sum d for the digit pair (all exact, |.| < 2^24),
-                            // then the group scale in f32
-                            const int off = cvalid[nt] ? xcp[nt][sg * (2 * M)] : 0;
-                            acc[mt][nt][0] = fmaf((float)(c[mt][nt][0] * 128 + c[mt][nt][1] - off), gs0, acc[mt][nt][0]);
-                            acc[mt][nt][1] = fmaf((float)(c[mt][nt][2] * 128 + c[mt][nt][3] - off), gs1, acc[mt][nt][1]);
-                            c[mt][nt][0] = c[mt][nt][1] = c[mt][nt][2] = c[mt][nt][3] = 0;
-                        }
-                    }
-                } else {
-                    // 64 columns: this lane's 16 columns -> 16 bytes of its digit row, natural order
-                    uint4 bq[NT];
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-                        bq[nt] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 64 + t * 16) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint4 lo4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g) * row_pitch + j * 64 + t * 16);
-                        const uint4 hi4 = *reinterpret_cast<const uint4*>(st + (size_t)(mt * 16 + g + 8) * row_pitch + j * 64 + t * 16);
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            mma_s8(c[mt][nt], lo4.x, hi4.x, lo4.y, hi4.y, bq[nt].x, bq[nt].y);
-                            mma_s8(c[mt][nt], lo4.z, hi4.z, lo4.w, hi4.w, bq[nt].z, bq[nt].w);
-                        }
+                        const uint4 b = bq[nt][i >> 1];
+                        mma_s8(c[mt][nt], a0, a1, a2, a3, (i & 1) ? b.z : b.x, (i & 1) ? b.w : b.y);
                     }
                 }
+                const float gs0 = __half2float(__ushort_as_half((unsigned short)(sc[mt] & 0xffffu)));
+                const float gs1 = __half2float(__ushort_as_half((unsigned short)(sc[mt] >> 16)));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    // sum (n - 8) * d = sum n*d - 8 * sum d for the digit pair (all exact, |.| < 2^24), then the group scale
+                    const int off = cvalid[nt] ? xcp[nt][sg * (2 * M)] : 0;
+                    acc[mt][nt][0] = fmaf((float)(c[mt][nt][0] * 128 + c[mt][nt][1] - off), gs0, acc[mt][nt][0]);
+                    acc[mt][nt][1] = fmaf((float)(c[mt][nt][2] * 128 + c[mt][nt][3] - off), gs1, acc[mt][nt][1]);
+                    c[mt][nt][0] = c[mt][nt][1] = c[mt][nt][2] = c[mt][nt][3] = 0;
+                }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[stage]);  // this warp is done with the stage
-            if (++stage == ns) { stage = 0; phase ^= 1u; }
+        } else {
+            uint4 bq[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                bq[nt] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 64 + t * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_s8(c[mt][nt], w[mt][0].x, w[mt][1].x, w[mt][0].y, w[mt][1].y, bq[nt].x, bq[nt].y);
+                    mma_s8(c[mt][nt], w[mt][0].z, w[mt][1].z, w[mt][0].w, w[mt][1].w, bq[nt].z, bq[nt].w);
+                }
+            }
         }
-        if (!ok) break;
-        if (it == 0) KTRACE(7);
-        if (it == 1) KTRACE(10);
-        // partials of this warp -> shared memory; the buffer of this parity was last used two units
-        // ago: wait until it has been consumed
+    };
+
+    // end of a unit: partial sums of the 16 warps meet in shared memory; warp 0 finishes the rows
+    auto finish_unit = [&](int it, int unit) {
+        const int par = it & 1;
         const uint32_t upar = (uint32_t)(it >> 1) & 1u;
-        if (it >= 2 && !mbar_wait(&done[par], upar ^ 1u)) { ok = false; break; }
+        // the buffer of this parity was last used two units ago: wait until it has been consumed
+        if (it >= 2 && !mbar_wait(&done[par], upar ^ 1u)) { ok = false; return; }
         float* rp = red + ((size_t)par * kSWarps + warp) * ROWS * 4;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                float v0, v1;  // rows g and g+8: this lane's two digits, weighted
+                float v0, v1;  // rows g and g+8: this lane's digit pair, weighted
                 if (FMT == FMT_W4) {
                     v0 = acc[mt][nt][0] * w_pair;
                     v1 = acc[mt][nt][1] * w_pair;
@@ -502,51 +440,74 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                     rp[(mt * 16 + g + 8) * 4 + b] = v1;
                 }
             }
+        reset_acc();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ubar[par]);
-        if (warp == 0) {
-            if (!mbar_wait(&ubar[par], upar)) { ok = false; break; }
-            if (it == 0) KTRACE(8);
-            const float* rb = red + (size_t)par * kSWarps * ROWS * 4;
-            const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
-            float cand = -INFINITY;
-            uint32_t cand_tok = 0xffffffffu;
-            for (int idx = lane; idx < RU * M; idx += 32) {
-                const int r = idx % RU, m = idx / RU;
-                const int row = row0 + r;
-                float v = 0.0f;
+        if (warp != 0) return;
+        if (!mbar_wait(&ubar[par], upar)) { ok = false; return; }
+        int mi, row0;
+        unit_rows(unit, mi, row0);
+        const float* rb = red + (size_t)par * kSWarps * ROWS * 4;
+        const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
+        float cand = -INFINITY;
+        uint32_t cand_tok = 0xffffffffu;
+        for (int idx = lane; idx < RU * M; idx += 32) {
+            const int r = idx % RU, m = idx / RU;
+            const int row = row0 + r;
+            float v = 0.0f;
 #pragma unroll
-                for (int w = 0; w < kSWarps; ++w) v += rb[((size_t)w * ROWS + r) * 4 + m];
-                if (FMT == FMT_I8 && row < om.rows) v *= reinterpret_cast<const float*>(om.scales)[row];
-                if (EPI == EPI_SILU) {
-                    float u = 0.0f;
+            for (int w = 0; w < kSWarps; ++w) v += rb[((size_t)w * ROWS + r) * 4 + m];
+            if (FMT == FMT_I8 && row < om.rows) v *= reinterpret_cast<const float*>(om.scales)[row];
+            if (EPI == EPI_SILU) {
+                float u = 0.0f;
 #pragma unroll
-                    for (int w = 0; w < kSWarps; ++w) u += rb[((size_t)w * ROWS + 16 + r) * 4 + m];
-                    if (FMT == FMT_I8 && row < om.rows) u *= reinterpret_cast<const float*>(p.mat[1].scales)[row];
-                    v = (v / (1.0f + expf(-v))) * u;
-                }
-                if (EPI == EPI_TOP1) {
-                    if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
-                } else if (row < om.rows) {
-                    const size_t o = (size_t)m * om.ldo + row;
-                    if (EPI == EPI_RESIDUAL) v = om.residual[o] + v;
-                    om.out[o] = v;
-                }
+                for (int w = 0; w < kSWarps; ++w) u += rb[((size_t)w * ROWS + 16 + r) * 4 + m];
+                if (FMT == FMT_I8 && row < om.rows) u *= reinterpret_cast<const float*>(p.mat[1].scales)[row];
+                v = (v / (1.0f + expf(-v))) * u;
             }
             if (EPI == EPI_TOP1) {
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-                    const float ov = __shfl_xor_sync(0xffffffffu, cand, off);
-                    const uint32_t ot = __shfl_xor_sync(0xffffffffu, cand_tok, off);
-                    if (top1_better(ov, ot, cand, cand_tok)) { cand = ov; cand_tok = ot; }
-                }
-                if (top1_better(cand, cand_tok, best_logit, best_token)) { best_logit = cand; best_token = cand_tok; }
+                if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
+            } else if (row < om.rows) {
+                const size_t o = (size_t)m * om.ldo + row;
+                if (EPI == EPI_RESIDUAL) v = om.residual[o] + v;
+                om.out[o] = v;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&done[par]);
         }
+        if (EPI == EPI_TOP1) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, cand, off);
+                const uint32_t ot = __shfl_xor_sync(0xffffffffu, cand_tok, off);
+                if (top1_better(ov, ot, cand, cand_tok)) { cand = ov; cand_tok = ot; }
+            }
+            if (top1_better(cand, cand_tok, best_logit, best_token)) { best_logit = cand; best_token = cand_tok; }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&done[par]);
+    };
+
+    // ---- main loop: consume a tile, refill its register slot with the tile kDepth ahead ------------
+    int c_unit = blockIdx.x, c_seg = j0, it = 0;
+    if (spu > 0) {
+        while (c_unit < p.total_units && ok) {
+#pragma unroll
+            for (int d = 0; d < kDepth; ++d) {
+                if (c_unit < p.total_units && ok) {
+                    compute_tile(wreg[d], sreg[d], c_seg);
+                    load_tile(wreg[d], sreg[d]);
+                    if (++c_seg == j1) {
+                        c_seg = j0;
+                        finish_unit(it, c_unit);
+                        ++it;
+                        c_unit += gridDim.x;
+                    }
+                }
+            }
+        }
+    } else {
+        // fewer segments than warps: this warp has no columns but still takes part in the unit hand-shake
+        for (; c_unit < p.total_units && ok; c_unit += gridDim.x, ++it) finish_unit(it, c_unit);
     }
-    KTRACE(9);
     pdl_launch_dependents();
     if (EPI == EPI_TOP1 && warp == 0 && lane == 0) {
         p.partial_tokens[blockIdx.x] = best_token;

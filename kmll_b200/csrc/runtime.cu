@@ -102,6 +102,7 @@ struct Decoder {
     bool have_next = false;
     bool warmed = false;
     cudaGraphExec_t graph = nullptr;
+    cudaStream_t capture_stream = nullptr;  // the caller's stream may be the legacy default stream, which cannot capture
     ncclComm_t comm = nullptr;
     std::vector<void*> allocs;
     size_t weight_bytes = 0, kv_bytes = 0;
@@ -344,9 +345,10 @@ static int ensure_graph(Decoder* d, cudaStream_t s) {
         d->warmed = true;
     }
     cudaGraph_t g = nullptr;
-    KMLL_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_step_fused(d, s, &d->launches_per_step);
-    cudaError_t e = cudaStreamEndCapture(s, &g);
+    if (d->capture_stream == nullptr) KMLL_CUDA(cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking));
+    KMLL_CUDA(cudaStreamBeginCapture(d->capture_stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_step_fused(d, d->capture_stream, &d->launches_per_step);
+    cudaError_t e = cudaStreamEndCapture(d->capture_stream, &g);
     if (rc != KMLL_OK) {
         if (g) cudaGraphDestroy(g);
         return rc;
@@ -516,6 +518,7 @@ int kmll_decoder_destroy(kmll_decoder_t dec) {
     if (dec == nullptr) return KMLL_OK;
     Decoder* d = static_cast<Decoder*>(dec);
     if (d->graph) cudaGraphExecDestroy(d->graph);
+    if (d->capture_stream) cudaStreamDestroy(d->capture_stream);
     if (d->comm) {
         NcclApi* api = nccl_api();
         if (api && api->CommDestroy) api->CommDestroy(d->comm);
