@@ -250,21 +250,41 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // merge: bring every split's (max, sum) into shared memory with independent loads, derive the
+    // weights exp(m_s - m) once per head, then combine the partial accumulators (loads are
+    // independent of each other, so they pipeline instead of paying one L2 round trip per split)
+    float* ml_s = Ks;                       // [gq][nsplit][2]
+    float* f_s = Ks + 2 * kMaxGq * 64;      // [gq][nsplit] weights, then [gq] denominators after them
+    float* l_s = f_s + kMaxGq * 64;
+    const int ns = p.nsplit;
+    for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
+        const int h = idx / (ns * 2), r = idx - h * ns * 2;
+        ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * ns * 2 + r);
+    }
+    __syncthreads();
+    for (int h = warp; h < gq; h += kAttnWarps) {
+        float m = -INFINITY;
+        for (int s = lane; s < ns; s += 32) m = fmaxf(m, ml_s[(h * ns + s) * 2]);
+        m = warp_max(m);
+        float l = 0.0f;
+        for (int s = lane; s < ns; s += 32) {
+            const float ms = ml_s[(h * ns + s) * 2];
+            const float f = ms == -INFINITY ? 0.0f : expf(ms - m);
+            f_s[h * ns + s] = f;
+            l += ml_s[(h * ns + s) * 2 + 1] * f;
+        }
+        l = warp_sum(l);
+        if (lane == 0) l_s[h] = l;
+    }
+    __syncthreads();
     for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
-        const volatile float* pml = p.part_ml + (size_t)head * p.nsplit * 2;
-        float m = -INFINITY;
-        for (int s = 0; s < p.nsplit; ++s) m = fmaxf(m, pml[s * 2]);
-        float l = 0.0f, a = 0.0f;
-        for (int s = 0; s < p.nsplit; ++s) {
-            const float ms = pml[s * 2];
-            if (ms == -INFINITY) continue;
-            const float f = expf(ms - m);
-            l += pml[s * 2 + 1] * f;
-            a += ((const volatile float*)p.part_acc)[((size_t)head * p.nsplit + s) * HD + d] * f;
-        }
-        p.out[(size_t)head * HD + d] = a / l;
+        const float* pa = p.part_acc + (size_t)head * ns * HD + d;
+        float a = 0.0f;
+#pragma unroll 4
+        for (int s = 0; s < ns; ++s) a = fmaf(__ldcg(pa + (size_t)s * HD), f_s[h * ns + s], a);
+        p.out[(size_t)head * HD + d] = a / l_s[h];
     }
     if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
 }

@@ -610,7 +610,7 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
     const size_t xs_bytes = up128((size_t)4 * M * sp.xs_pitch);
     const size_t xsum_bytes = FMT == FMT_W4 ? up128((size_t)2 * M * ngr * sizeof(int)) : 0;
-    const size_t red_bytes = (size_t)2 * kSWarps * ROWS * 4 * sizeof(float);
+    const size_t red_bytes = up128((size_t)kRedBufs * kSWarps * ROWS * M * sizeof(float));
     const size_t bars_bytes = 128;
     const size_t misc_bytes = 1024;
     const size_t smem = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes;

@@ -91,6 +91,7 @@ __device__ inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint
 }
 
 constexpr int kSBlock = kSThreads;
+constexpr int kRedBufs = 8;  // units whose partial sums may be pending at once
 
 __device__ inline void consumer_bar_sync() { __syncthreads(); }
 
@@ -274,14 +275,13 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     int8_t* xs = reinterpret_cast<int8_t*>(smem);                       // [4*M][xs_pitch] digit rows
     int* xcomb = reinterpret_cast<int*>(smem + p.off_xsum);             // [ngr][2*M] W4 offset terms of the digit pairs
-    float* red = reinterpret_cast<float*>(smem + p.off_red);            // [2][kSWarps][ROWS][4]
-    uint64_t* ubar = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [2] all warps wrote their partials
-    uint64_t* done = ubar + 2;                                          // [2] warp 0 consumed the partials
+    float* red = reinterpret_cast<float*>(smem + p.off_red);            // [kRedBufs][kSWarps][ROWS][M]
+    uint64_t* ubar = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [kRedBufs] all warps wrote their partials
+    uint64_t* done = ubar + kRedBufs;                                   // [kRedBufs] the finishing warp consumed them
     float* misc = reinterpret_cast<float*>(smem + p.off_misc);
 
     if (tid == 0) {
-        mbar_init(&ubar[0], kSWarps); mbar_init(&ubar[1], kSWarps);
-        mbar_init(&done[0], 1); mbar_init(&done[1], 1);
+        for (int b = 0; b < kRedBufs; ++b) { mbar_init(&ubar[b], kSWarps); mbar_init(&done[b], 1); }
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
@@ -299,23 +299,45 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
     uint4 wreg[kDepth][MT][2];
     uint32_t sreg[kDepth][MT];  // W4: binary16 group scales of rows g (low half) and g+8 (high half)
     int l_unit = blockIdx.x, l_seg = j0;  // load cursor
+    const unsigned char* lw[MT][2];   // this lane's 16 bytes of the cursor's segment, rows g and g+8
+    const unsigned short* ls[MT][2];  // W4: the group scales of the same rows
+    auto enter_unit = [&]() {         // row pointers of the cursor's unit (rows past the end re-read the last row)
+        if (l_unit >= p.total_units || spu <= 0) return;
+        int mi, row0;
+        unit_rows(l_unit, mi, row0);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
+            const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
+            const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);
+            lw[mt][0] = m.w + (size_t)r0 * rowbytes + (size_t)j0 * 64 + t * 16;
+            lw[mt][1] = m.w + (size_t)r1 * rowbytes + (size_t)j0 * 64 + t * 16;
+            if (FMT == FMT_W4) {
+                ls[mt][0] = reinterpret_cast<const unsigned short*>(m.scales) + (size_t)r0 * ngr + j0;
+                ls[mt][1] = reinterpret_cast<const unsigned short*>(m.scales) + (size_t)r1 * ngr + j0;
+            }
+        }
+    };
+    enter_unit();
     auto load_tile = [&](uint4 (&w)[MT][2], uint32_t (&sc)[MT]) {
         if (l_unit < p.total_units && spu > 0) {
-            int mi, row0;
-            unit_rows(l_unit, mi, row0);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
-                const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
-                const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);  // rows past the end re-read the last row
-                w[mt][0] = ld_stream_u4(m.w + (size_t)r0 * rowbytes + (size_t)l_seg * 64 + t * 16);
-                w[mt][1] = ld_stream_u4(m.w + (size_t)r1 * rowbytes + (size_t)l_seg * 64 + t * 16);
+                w[mt][0] = ld_stream_u4(lw[mt][0]);
+                w[mt][1] = ld_stream_u4(lw[mt][1]);
+                lw[mt][0] += 64;
+                lw[mt][1] += 64;
                 if (FMT == FMT_W4) {
-                    const unsigned short* sp = reinterpret_cast<const unsigned short*>(m.scales);
-                    sc[mt] = (uint32_t)__ldg(sp + (size_t)r0 * ngr + l_seg) | ((uint32_t)__ldg(sp + (size_t)r1 * ngr + l_seg) << 16);
+                    sc[mt] = (uint32_t)__ldg(ls[mt][0]) | ((uint32_t)__ldg(ls[mt][1]) << 16);
+                    ls[mt][0] += 1;
+                    ls[mt][1] += 1;
                 }
             }
-            if (++l_seg == j1) { l_seg = j0; l_unit += gridDim.x; }
+            if (++l_seg == j1) {
+                l_seg = j0;
+                l_unit += gridDim.x;
+                enter_unit();
+            }
         }
     };
 #pragma unroll
@@ -413,13 +435,39 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         }
     };
 
-    // end of a unit: partial sums of the 16 warps meet in shared memory; warp 0 finishes the rows
+    // End of a unit: the partial sums of the 16 warps meet in shared memory and ONE warp finishes the
+    // rows (sum in fixed warp order, scale, epilogue).  The finishing duty rotates over the warps
+    // (unit it -> warp it % 16) and kRedBufs units may be pending, so no warp is a serial bottleneck;
+    // the finisher fetches what its epilogue needs from global memory (residual, RS-I8 row scales)
+    // when the unit starts, long before it is used.
+    float pre_res[(RU + 31) / 32 * 4];  // prefetched residual values of the unit this warp will finish
+    float pre_s0[(RU + 31) / 32], pre_s1[(RU + 31) / 32];
+    auto prefetch_epilogue = [&](int it, int unit) {
+        if ((it % kSWarps) != warp) return;
+        int mi, row0;
+        unit_rows(unit, mi, row0);
+        const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
+#pragma unroll
+        for (int q = 0; q < (RU + 31) / 32; ++q) {
+            const int r = lane + q * 32;
+            const int row = row0 + r;
+            const bool okrow = r < RU && row < om.rows;
+            if (FMT == FMT_I8) {
+                pre_s0[q] = okrow ? reinterpret_cast<const float*>(om.scales)[row] : 0.0f;
+                if (EPI == EPI_SILU) pre_s1[q] = okrow ? reinterpret_cast<const float*>(p.mat[1].scales)[row] : 0.0f;
+            }
+            if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+                for (int m = 0; m < 4; ++m) pre_res[q * 4 + m] = (okrow && m < M) ? om.residual[(size_t)m * om.ldo + row] : 0.0f;
+            }
+        }
+    };
     auto finish_unit = [&](int it, int unit) {
-        const int par = it & 1;
-        const uint32_t upar = (uint32_t)(it >> 1) & 1u;
-        // the buffer of this parity was last used two units ago: wait until it has been consumed
-        if (it >= 2 && !mbar_wait(&done[par], upar ^ 1u)) { ok = false; return; }
-        float* rp = red + ((size_t)par * kSWarps + warp) * ROWS * 4;
+        const int buf = it % kRedBufs;
+        const uint32_t bpar = (uint32_t)(it / kRedBufs) & 1u;
+        // this buffer was last used kRedBufs units ago: wait until that unit has been finished
+        if (it >= kRedBufs && !mbar_wait(&done[buf], bpar ^ 1u)) { ok = false; return; }
+        float* rp = red + ((size_t)buf * kSWarps + warp) * ROWS * M;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -435,42 +483,46 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                 v0 += __shfl_xor_sync(0xffffffffu, v0, 1);  // digits (3,2) + digits (1,0)
                 v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
                 const int b = nt * 2 + (t >> 1);  // batch row
-                if ((t & 1) == 0 && b < 4) {
-                    rp[(mt * 16 + g) * 4 + b] = v0;
-                    rp[(mt * 16 + g + 8) * 4 + b] = v1;
+                if ((t & 1) == 0 && b < M) {
+                    rp[(mt * 16 + g) * M + b] = v0;
+                    rp[(mt * 16 + g + 8) * M + b] = v1;
                 }
             }
         reset_acc();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ubar[par]);
-        if (warp != 0) return;
-        if (!mbar_wait(&ubar[par], upar)) { ok = false; return; }
+        if (lane == 0) mbar_arrive(&ubar[buf]);
+        if ((it % kSWarps) != warp) return;
+        if (!mbar_wait(&ubar[buf], bpar)) { ok = false; return; }
         int mi, row0;
         unit_rows(unit, mi, row0);
-        const float* rb = red + (size_t)par * kSWarps * ROWS * 4;
+        const float* rb = red + (size_t)buf * kSWarps * ROWS * M;
         const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
         float cand = -INFINITY;
         uint32_t cand_tok = 0xffffffffu;
-        for (int idx = lane; idx < RU * M; idx += 32) {
-            const int r = idx % RU, m = idx / RU;
+#pragma unroll
+        for (int q = 0; q < (RU + 31) / 32; ++q) {
+            const int r = lane + q * 32;
             const int row = row0 + r;
-            float v = 0.0f;
+            if (r < RU) {
+                for (int m = 0; m < M; ++m) {
+                    float v = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kSWarps; ++w) v += rb[((size_t)w * ROWS + r) * 4 + m];
-            if (FMT == FMT_I8 && row < om.rows) v *= reinterpret_cast<const float*>(om.scales)[row];
-            if (EPI == EPI_SILU) {
-                float u = 0.0f;
+                    for (int w = 0; w < kSWarps; ++w) v += rb[((size_t)w * ROWS + r) * M + m];
+                    if (FMT == FMT_I8) v *= pre_s0[q];
+                    if (EPI == EPI_SILU) {
+                        float u = 0.0f;
 #pragma unroll
-                for (int w = 0; w < kSWarps; ++w) u += rb[((size_t)w * ROWS + 16 + r) * 4 + m];
-                if (FMT == FMT_I8 && row < om.rows) u *= reinterpret_cast<const float*>(p.mat[1].scales)[row];
-                v = (v / (1.0f + expf(-v))) * u;
-            }
-            if (EPI == EPI_TOP1) {
-                if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
-            } else if (row < om.rows) {
-                const size_t o = (size_t)m * om.ldo + row;
-                if (EPI == EPI_RESIDUAL) v = om.residual[o] + v;
-                om.out[o] = v;
+                        for (int w = 0; w < kSWarps; ++w) u += rb[((size_t)w * ROWS + 16 + r) * M + m];
+                        if (FMT == FMT_I8) u *= pre_s1[q];
+                        v = (v / (1.0f + expf(-v))) * u;
+                    }
+                    if (EPI == EPI_TOP1) {
+                        if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
+                    } else if (row < om.rows) {
+                        if (EPI == EPI_RESIDUAL) v = pre_res[q * 4 + (m & 3)] + v;
+                        om.out[(size_t)m * om.ldo + row] = v;
+                    }
+                }
             }
         }
         if (EPI == EPI_TOP1) {
@@ -483,11 +535,12 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
             if (top1_better(cand, cand_tok, best_logit, best_token)) { best_logit = cand; best_token = cand_tok; }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&done[par]);
+        if (lane == 0) mbar_arrive(&done[buf]);
     };
 
     // ---- main loop: consume a tile, refill its register slot with the tile kDepth ahead ------------
     int c_unit = blockIdx.x, c_seg = j0, it = 0;
+    if (c_unit < p.total_units) prefetch_epilogue(0, c_unit);
     if (spu > 0) {
         while (c_unit < p.total_units && ok) {
 #pragma unroll
@@ -500,18 +553,35 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                         finish_unit(it, c_unit);
                         ++it;
                         c_unit += gridDim.x;
+                        if (c_unit < p.total_units) prefetch_epilogue(it, c_unit);
                     }
                 }
             }
         }
     } else {
         // fewer segments than warps: this warp has no columns but still takes part in the unit hand-shake
-        for (; c_unit < p.total_units && ok; c_unit += gridDim.x, ++it) finish_unit(it, c_unit);
+        for (; c_unit < p.total_units && ok; c_unit += gridDim.x, ++it) {
+            finish_unit(it, c_unit);
+            if (c_unit + (int)gridDim.x < p.total_units) prefetch_epilogue(it + 1, c_unit + gridDim.x);
+        }
     }
     pdl_launch_dependents();
-    if (EPI == EPI_TOP1 && warp == 0 && lane == 0) {
-        p.partial_tokens[blockIdx.x] = best_token;
-        p.partial_logits[blockIdx.x] = best_logit;
+    if (EPI == EPI_TOP1) {
+        // every warp finished some units: merge the 16 running bests (fixed order) into one partial per block
+        __syncthreads();
+        if (lane == 0) { misc[warp * 2] = best_logit; misc[warp * 2 + 1] = __uint_as_float(best_token); }
+        __syncthreads();
+        if (tid == 0) {
+            float bl = -INFINITY;
+            uint32_t bt = 0xffffffffu;
+            for (int w = 0; w < kSWarps; ++w) {
+                const float l = misc[w * 2];
+                const uint32_t tk = __float_as_uint(misc[w * 2 + 1]);
+                if (top1_better(l, tk, bl, bt)) { bl = l; bt = tk; }
+            }
+            p.partial_tokens[blockIdx.x] = bt;
+            p.partial_logits[blockIdx.x] = bl;
+        }
     }
     if (!ok) atomicCAS(&g_device_status, 0, 1);
 }
