@@ -73,7 +73,30 @@ struct DecodeAttnParams {
     float* part_ml;   // [n_heads, nsplit, 2]
     unsigned int* counters;  // [n_kv_heads], zero on entry, zero on exit
     float* out;       // [n_heads, head_dim]
+    // fused form (prepare_incremental_attention folded in): q is NOT yet rotated; the new K / V rows of
+    // position seq_len-1 are rotated / copied into the caches by the block whose slice holds that position
+    const float* k_new;   // [n_kv, head_dim] or null
+    const float* v_new;
+    const float* freqs;   // [head_dim / 2]
+    float* k_cache_w;
+    float* v_cache_w;
 };
+
+// Half-split RoPE of a head slice held 4 (or 2) consecutive dims per lane: the partner dim d +- HD/2 lives
+// in lane ^ 16 (crates/inference/src/kernels/inference.rs:1078-1098 with rotary_dim == head_dim).
+template <int EPL>
+__device__ inline void rope_lane_slice(float (&x)[EPL], const float* freqs, float position, int lane) {
+    constexpr int HALF_LANES = 16;
+    const bool upper = lane >= HALF_LANES;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[e], HALF_LANES);
+        const int pair = (lane & (HALF_LANES - 1)) * EPL + e;
+        const float angle = position * freqs[pair];
+        const float sn = sinf(angle), cs = cosf(angle);
+        x[e] = upper ? x[e] * cs + other * sn : x[e] * cs - other * sn;
+    }
+}
 
 template <int EPL>
 __device__ inline void load_lane_slice(const float* src, float (&dst)[EPL]);
@@ -118,7 +141,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s0 = split * p.chunk;
     const int s1 = min(s0 + p.chunk, seq_len);
-    const int n = s1 - s0;  // may be <= 0 for trailing splits
+    const int n = s1 - s0;
+    const int nactive = (seq_len + p.chunk - 1) / p.chunk;  // splits that hold positions; the others leave at once
+    if (n <= 0) return;
     const size_t kv_stride = (size_t)p.n_kv_heads * HD;
     const float scale = 1.0f / sqrtf((float)HD);
 
@@ -135,6 +160,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll
             for (int e = 0; e < EPL; ++e)
                 qv[h][e] = h < gq ? p.q[(size_t)(kv_head * gq + h) * HD + lane * EPL + e] : 0.0f;
+        const bool fused = p.k_new != nullptr;
+        const float position = (float)(seq_len - 1);
+        if (fused) {
+#pragma unroll
+            for (int h = 0; h < kMaxGq; ++h)
+                if (h < gq) rope_lane_slice<EPL>(qv[h], p.freqs, position, lane);
+        }
         if (tid < kMaxGq) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
 
         for (int t0 = 0; t0 < n; t0 += kAttnTile) {
@@ -154,6 +186,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             cp_async_commit();
             cp_async_wait<1>();  // K has landed
             __syncthreads();
+            const int newrow = seq_len - 1 - s0 - t0;  // row of this tile that is the position being written
+            if (fused && newrow >= 0 && newrow < nt && warp == 0) {
+                float kn[EPL];
+                load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kn);
+                rope_lane_slice<EPL>(kn, p.freqs, position, lane);
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    Ks[newrow * HD + lane * EPL + e] = kn[e];
+                    p.k_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kn[e];
+                }
+            }
+            if (fused && newrow >= 0 && newrow < nt) __syncthreads();
             // scores: one warp per position
             for (int i = warp; i < nt; i += kAttnWarps) {
                 float kvv[EPL];
@@ -188,6 +232,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
             cp_async_wait<0>();  // V has landed
             __syncthreads();
+            if (fused && newrow >= 0 && newrow < nt) {
+                if (warp == 0) {
+                    float vn[EPL];
+                    load_lane_slice<EPL>(p.v_new + (size_t)kv_head * HD + lane * EPL, vn);
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) {
+                        Vs[newrow * HD + lane * EPL + e] = vn[e];
+                        p.v_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = vn[e];
+                    }
+                }
+                __syncthreads();
+            }
             // weighted sum of V: one warp per position
 #pragma unroll
             for (int h = 0; h < kMaxGq; ++h)
@@ -238,14 +294,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
         }
     }
-    if (p.nsplit == 1) return;
+    if (nactive == 1 && p.nsplit == 1) return;
 
     // last block of this KV head merges the splits
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const unsigned int prev = atomicAdd(&p.counters[kv_head], 1u);
-        is_last = (prev == (unsigned int)p.nsplit - 1);
+        is_last = (prev == (unsigned int)nactive - 1);
     }
     __syncthreads();
     if (!is_last) return;
@@ -256,10 +312,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     float* ml_s = Ks;                       // [gq][nsplit][2]
     float* f_s = Ks + 2 * kMaxGq * 64;      // [gq][nsplit] weights, then [gq] denominators after them
     float* l_s = f_s + kMaxGq * 64;
-    const int ns = p.nsplit;
+    const int ns = nactive;  // only these splits wrote partials
     for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
         const int h = idx / (ns * 2), r = idx - h * ns * 2;
-        ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * ns * 2 + r);
+        ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * p.nsplit * 2 + r);
     }
     __syncthreads();
     for (int h = warp; h < gq; h += kAttnWarps) {
@@ -280,11 +336,19 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
-        const float* pa = p.part_acc + (size_t)head * ns * HD + d;
-        float a = 0.0f;
-#pragma unroll 4
-        for (int s = 0; s < ns; ++s) a = fmaf(__ldcg(pa + (size_t)s * HD), f_s[h * ns + s], a);
-        p.out[(size_t)head * HD + d] = a / l_s[h];
+        const float* pa = p.part_acc + (size_t)head * p.nsplit * HD + d;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // independent chains: the loads of a round overlap
+        int s = 0;
+        for (; s + 4 <= ns; s += 4) {
+            const float v0 = __ldcg(pa + (size_t)s * HD), v1 = __ldcg(pa + (size_t)(s + 1) * HD);
+            const float v2 = __ldcg(pa + (size_t)(s + 2) * HD), v3 = __ldcg(pa + (size_t)(s + 3) * HD);
+            a0 = fmaf(v0, f_s[h * ns + s], a0);
+            a1 = fmaf(v1, f_s[h * ns + s + 1], a1);
+            a2 = fmaf(v2, f_s[h * ns + s + 2], a2);
+            a3 = fmaf(v3, f_s[h * ns + s + 3], a3);
+        }
+        for (; s < ns; ++s) a0 = fmaf(__ldcg(pa + (size_t)s * HD), f_s[h * ns + s], a0);
+        p.out[(size_t)head * HD + d] = ((a0 + a1) + (a2 + a3)) / l_s[h];
     }
     if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
 }
@@ -400,7 +464,8 @@ static AttnPlan plan_decode_attention(int seq_cap) {
 
 int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_cache, const float* v_cache,
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
-                            int head_dim, float* workspace, float* out) {
+                            int head_dim, float* workspace, float* out, const float* k_new, const float* v_new,
+                            const float* freqs, float* k_cache_w, float* v_cache_w) {
     const int gq = n_heads / n_kv_heads;
     AttnPlan pl = plan_decode_attention(seq_cap);
     DecodeAttnParams p;
@@ -412,6 +477,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.part_ml = workspace + (size_t)n_heads * pl.nsplit * head_dim;
     p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
     p.out = out;
+    p.k_new = k_new; p.v_new = v_new; p.freqs = freqs; p.k_cache_w = k_cache_w; p.v_cache_w = v_cache_w;
     size_t smem = ((size_t)2 * kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile + (size_t)kMaxGq * 4) * sizeof(float);
     const size_t red_bytes = (size_t)kAttnWarps * gq * head_dim * sizeof(float);
     if (red_bytes > (size_t)2 * kAttnTile * head_dim * sizeof(float)) smem += red_bytes;  // never for gq <= 8
@@ -486,7 +552,7 @@ int kmll_single_query_attention(kmll_stream_t s, const float* q, const float* k_
         return fail(KMLL_ERR_UNSUPPORTED, "single_query_attention: head_dim must be 64 or 128 and n_heads/n_kv_heads <= %d; use attention_scores + softmax_value", kMaxGq);
     if (max_seq_len > 131072) return fail(KMLL_ERR_CAPACITY, "single_query_attention: max_seq_len %d beyond 131072", max_seq_len);
     return decode_attention_launch(as_stream(s), q, k_cache, v_cache, nullptr, seq_len, max_seq_len, n_heads, n_kv_heads, head_dim,
-                                   workspace, out);
+                                   workspace, out, nullptr, nullptr, nullptr, nullptr, nullptr);
 }
 
 int kmll_prefill_causal_attention(kmll_stream_t s, const float* q_batch, const float* k_cache, const float* v_cache, int prompt_len,

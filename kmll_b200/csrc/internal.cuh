@@ -19,7 +19,9 @@ struct DecodeState {
 // attention.cu
 int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_cache, const float* v_cache,
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
-                            int head_dim, float* workspace, float* out);
+                            int head_dim, float* workspace, float* out, const float* k_new = nullptr,
+                            const float* v_new = nullptr, const float* freqs = nullptr, float* k_cache_w = nullptr,
+                            float* v_cache_w = nullptr);
 size_t decode_attention_workspace_floats(int n_heads, int head_dim, int seq_cap);
 
 // elementwise.cu

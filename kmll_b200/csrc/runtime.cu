@@ -245,10 +245,17 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
                                                    (const int8_t*)L.wk.w, (const float*)L.wk.scales, (const int8_t*)L.wv.w,
                                                    (const float*)L.wv.scales, q_len, kv_len, c.dim, d->q, d->k, d->v));
         }
-        KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l, d->n_kv_l,
-                                         c.head_dim, d->q_rot, L.key_cache, L.value_cache));
-        KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                         d->n_kv_l, c.head_dim, d->attn_ws, d->attn));
+        if (c.rotary_dim == c.head_dim) {
+            // RoPE of q and of the new K row and the KV-cache write happen inside the attention kernel
+            KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache));
+            --n;
+        } else {
+            KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache));
+            KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn));
+        }
         KMLL_TRY(row_parallel_residual(d, s, d->attn, L.wo, hidden, d->hidden_mid));
         if (w4) {
             KMLL_TRY(kmll_rmsnorm_silu_gate_up_w4g128(s, d->hidden_mid, L.ffn_norm, c.norm_eps, (const uint8_t*)L.w1.w,
