@@ -257,6 +257,19 @@ int kmll_single_query_attention(kmll_stream_t stream, const float* query, const 
                                 const float* value_cache, int seq_len, int max_seq_len,
                                 int n_heads, int n_kv_heads, int head_dim, float* workspace,
                                 float* out);
+/* Same operator for hosts that cannot hand over a workspace because they cannot allocate device memory at
+ * all: a thread that was given a stream and the operator bindings but no allocator, or a latency-bound loop
+ * where a cudaMalloc would stall the whole device.  It has no counterpart in the reference.  The scratch is a
+ * fixed 2.08 MiB array inside the library image (every GPU that loads the library holds it until the
+ * process exits), so the geometry is limited: kmll_single_query_attention_workspace_floats(n_heads, head_dim,
+ * max_seq_len) must not exceed 544768, otherwise KMLL_ERR_CAPACITY is returned and nothing runs.  The entry
+ * point calls no allocating routine.  The first call on a device looks up the device address of the array;
+ * make that first call outside any stream capture.  All calls on a device share the one array: two calls
+ * that overlap on the GPU (different streams) race on it and must be serialised by the caller. */
+int kmll_single_query_attention_noalloc(kmll_stream_t stream, const float* query,
+                                        const float* key_cache, const float* value_cache,
+                                        int seq_len, int max_seq_len, int n_heads, int n_kv_heads,
+                                        int head_dim, float* out);
 /* prefill_causal_attention, crates/inference/src/ops/inference.rs:1713-1771: row r attends to
  * cache positions 0..=r. */
 int kmll_prefill_causal_attention(kmll_stream_t stream, const float* query_batch,

@@ -8,6 +8,8 @@
 //   * prefill_causal_attention: tiled causal attention with an online softmax.
 // Math contract (all f32): score = dot * (1/sqrt(head_dim)); weights exp(s - max); out = sum(w*v)/sum(w)
 // (crates/inference/src/model.rs:11581-11649).  KV cache layout [max_seq, n_kv_heads, head_dim].
+#include <mutex>
+
 #include "internal.cuh"
 
 namespace kmll {
@@ -553,6 +555,63 @@ int kmll_single_query_attention(kmll_stream_t s, const float* q, const float* k_
     if (max_seq_len > 131072) return fail(KMLL_ERR_CAPACITY, "single_query_attention: max_seq_len %d beyond 131072", max_seq_len);
     return decode_attention_launch(as_stream(s), q, k_cache, v_cache, nullptr, seq_len, max_seq_len, n_heads, n_kv_heads, head_dim,
                                    workspace, out, nullptr, nullptr, nullptr, nullptr, nullptr);
+}
+
+// ---- decode attention for callers that cannot allocate device memory -----------------------------
+// The split-sequence kernel needs scratch for the per-split partial results.  Hosts that bind only the
+// operator layer (a worker thread that owns a stream and nothing else, or a serving loop in which a
+// cudaMalloc would stall every stream of the device) have no way to provide it, so this entry point keeps
+// its scratch in a fixed array that lives inside the loaded library image on every GPU that loads it.
+constexpr size_t kNoAllocScratchFloats = 544768;  // 2.08 MiB: e.g. 64 heads x 64 splits x (128 + 2) floats + counters
+static __device__ __align__(256) float g_attention_scratch[kNoAllocScratchFloats];
+
+// Device address of the scratch array, looked up once per device while that device is current.  In host code
+// the array's name is only a handle for the runtime; a kernel needs the address cudaGetSymbolAddress returns.
+static int attention_scratch_address(float** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex lock;
+    static float* cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(KMLL_ERR_CAPACITY, "single_query_attention_noalloc: device index %d beyond %d", dev, kMaxDevices);
+    std::lock_guard<std::mutex> guard(lock);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_attention_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(KMLL_ERR_CUDA, "single_query_attention_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        cached[dev] = static_cast<float*>(ptr);
+    }
+    *out = cached[dev];
+    return KMLL_OK;
+}
+
+int kmll_single_query_attention_noalloc(kmll_stream_t s, const float* q, const float* k_cache, const float* v_cache, int seq_len,
+                                        int max_seq_len, int n_heads, int n_kv_heads, int head_dim, float* out) {
+    KMLL_REQUIRE_PTR(q); KMLL_REQUIRE_PTR(k_cache); KMLL_REQUIRE_PTR(v_cache); KMLL_REQUIRE_PTR(out);
+    int rc = check_geometry("single_query_attention_noalloc", seq_len, max_seq_len, n_heads, n_kv_heads, head_dim);
+    if (rc) return rc;
+    if ((head_dim != 64 && head_dim != 128) || n_heads / n_kv_heads > kMaxGq)
+        return fail(KMLL_ERR_UNSUPPORTED, "single_query_attention_noalloc: head_dim must be 64 or 128 and n_heads/n_kv_heads <= %d", kMaxGq);
+    if (max_seq_len > 131072) return fail(KMLL_ERR_CAPACITY, "single_query_attention_noalloc: max_seq_len %d beyond 131072", max_seq_len);
+    const size_t need = decode_attention_workspace_floats(n_heads, head_dim, max_seq_len);
+    if (need > kNoAllocScratchFloats)
+        return fail(KMLL_ERR_CAPACITY,
+                    "single_query_attention_noalloc: this geometry needs %zu floats of scratch, the built-in array holds %zu; "
+                    "use kmll_single_query_attention with a caller-owned workspace",
+                    need, (size_t)kNoAllocScratchFloats);
+    float* scratch = nullptr;
+    rc = attention_scratch_address(&scratch);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left.  Only the per-KV-head arrival counters have to start at
+    // zero; they sit behind the partial results (same layout as the caller-owned workspace).
+    AttnPlan pl = plan_decode_attention(max_seq_len);
+    float* counters = scratch + (size_t)n_heads * pl.nsplit * (head_dim + 2);
+    cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(unsigned int) * (size_t)n_kv_heads, as_stream(s));
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return decode_attention_launch(as_stream(s), q, k_cache, v_cache, nullptr, seq_len, max_seq_len, n_heads, n_kv_heads, head_dim,
+                                   scratch, out, nullptr, nullptr, nullptr, nullptr, nullptr);
 }
 
 int kmll_prefill_causal_attention(kmll_stream_t s, const float* q_batch, const float* k_cache, const float* v_cache, int prompt_len,

@@ -436,6 +436,14 @@ def single_query_attention(query, key_cache, value_cache, seq_len, max_seq_len, 
     return out
 
 
+def single_query_attention_noalloc(query, key_cache, value_cache, seq_len, max_seq_len, n_heads, n_kv_heads, head_dim, out=None):
+    """single_query_attention with the library's built-in scratch array (no workspace argument, nothing allocated by the C call)."""
+    out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=query.device) if out is None else out
+    check(load().kmll_single_query_attention_noalloc(_stream(), _p(query), _p(key_cache), _p(value_cache), seq_len, max_seq_len, n_heads,
+                                                     n_kv_heads, head_dim, _p(out)))
+    return out
+
+
 def prefill_causal_attention(query_batch, key_cache, value_cache, prompt_len, max_seq_len, n_heads, n_kv_heads, head_dim, out=None):
     """ops::prefill_causal_attention (ops/inference.rs:1713-1771)."""
     out = torch.empty((prompt_len, n_heads * head_dim), dtype=torch.float32, device=query_batch.device) if out is None else out
