@@ -1,0 +1,74 @@
+"""Tensor-parallel decode on 2 GPUs must generate the same greedy tokens as the single-GPU decoder
+(weights are quantized before sharding, so the shards are slices of the same tensors)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _cfg(rt, fmt, rank, size):
+    return rt.DecoderConfig(n_layers=2, dim=256, n_heads=4, n_kv_heads=2, head_dim=64, hidden_dim=512, vocab_size=640, rope_theta=1e6,
+                            norm_eps=1e-6, max_seq_len=48, format=fmt, tp_rank=rank, tp_size=size)
+
+
+def _worker(rank, world, port, fmt, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    from kmll_b200 import runtime as rt
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)  # plumbing only: carries the NCCL id
+    try:
+        dec = rt.Decoder(_cfg(rt, fmt, rank, world))
+        uid = [rt.Decoder.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, 0)
+        dec.tp_init(uid[0])
+        dec.init_random(5, 0.05, False)
+        prompt = np.arange(3, 14)
+        dec.prefill(prompt)
+        tokens, logits = dec.generate_greedy(8)
+        dec.prefill(prompt, token_loop=True)
+        tokens2, _ = dec.generate_greedy(8)
+        if rank == 0:
+            out.put((tokens.tolist(), logits.tolist(), tokens2.tolist()))
+        dist.barrier()
+        dec.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+def test_tp2_matches_single_gpu(cuda, fmt):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from kmll_b200 import runtime as rt
+    single = rt.Decoder(_cfg(rt, fmt, 0, 1))
+    single.init_random(5, 0.05, False)
+    single.prefill(np.arange(3, 14))
+    ref_tokens, ref_logits = single.generate_greedy(8)
+    single.close()
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, fmt, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    tokens, logits, tokens2 = out.get(timeout=10)
+    assert tokens == ref_tokens.tolist()
+    assert tokens2 == ref_tokens.tolist()
+    assert np.max(np.abs(np.array(logits) - ref_logits)) <= 1e-3 * max(1.0, float(np.max(np.abs(ref_logits))))
