@@ -231,10 +231,14 @@ def run_ours(args):
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profile:
+        torch.cuda.profiler.start()
     e0.record()
     dec.enqueue_steps(K)
     e1.record()
     barrier()
+    if args.profile:
+        torch.cuda.profiler.stop()
     clocks = sampler.stop()
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
 
@@ -332,6 +336,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

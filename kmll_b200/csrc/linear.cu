@@ -613,7 +613,9 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     const size_t red_bytes = up128((size_t)kRedBufs * kSWarps * ROWS * M * sizeof(float));
     const size_t bars_bytes = 128;
     const size_t misc_bytes = 1024;
-    const size_t smem = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes;
+    const size_t ring_bytes = (size_t)8 * 2 * kSThreads * 16;  // 8 tile halves in flight per lane (128 KB)
+    const size_t sring_bytes = FMT == FMT_W4 ? (size_t)8 * 2 * kSWarps * 32 : 0;  // scale words of the tiles in flight
+    const size_t smem = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes + ring_bytes + sring_bytes;
     if (smem > 226 * 1024) return KMLL_OK;  // *launched stays false
     // the activation staging keeps x in registers (M*K <= 24576) and reads it with 16-byte loads
     if ((size_t)M * K > (size_t)kStageBlocks * 8 * kSThreads || (lp.ldx & 3) != 0 ||
@@ -623,6 +625,8 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     sp.off_red = sp.off_xsum + (int)xsum_bytes;
     sp.off_bars = sp.off_red + (int)red_bytes;
     sp.off_misc = sp.off_bars + (int)bars_bytes;
+    sp.off_ring = sp.off_misc + (int)misc_bytes;
+    sp.off_sring = sp.off_ring + (int)ring_bytes;
 
     int units = 0;
     if (EPI == EPI_SILU) {
@@ -767,6 +771,9 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
     }
     if (FMT == FMT_W4 && K % 128 != 0)
         return fail(KMLL_ERR_SHAPE, "%s: W4-G128 needs in_dim %% 128 == 0, got %d", name, K);
+    for (int i = 0; i < nmat; ++i)
+        if ((reinterpret_cast<uintptr_t>(mats[i].scales) & 3u) != 0)
+            return fail(KMLL_ERR_UNSUPPORTED, "%s: scales must be 4-byte aligned", name);
     const bool fast = fast_shape(FMT, K) && aligned16(mats[0].w) && (nmat < 2 || aligned16(mats[1].w)) &&
                       (nmat < 3 || aligned16(mats[2].w));
     if (!fast) {

@@ -42,7 +42,7 @@ struct StreamParams {
     int unit_start[4];
     int total_units;
     int xs_pitch;   // bytes per staged digit row of the activations
-    int off_xsum, off_red, off_bars, off_misc;  // shared-memory offsets in bytes
+    int off_xsum, off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
     uint32_t* partial_tokens;
     float* partial_logits;
 };
@@ -83,6 +83,13 @@ __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
             if (mbar_try_wait(bar, parity)) return true;
         if (global_timer_ns() - t0 > kWaitLimitNs) return false;
     }
+}
+// 16-byte asynchronous global->shared copy that bypasses L1 (weights are read once).
+__device__ inline void cp_async_stream16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ inline void cp_async_word(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
 }
 __device__ inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
@@ -194,30 +201,41 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int
         xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
         inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
-#pragma unroll
+    // The conversion is a ROLLED loop: block j is always taken from v[0] and the remaining blocks move down one
+    // place, so the long conversion sequence exists once in the instruction stream (a kernel whose code is
+    // executed once per launch is bound by instruction fetch, not by issue).
+#pragma unroll 1
     for (int j = 0; j < kStageBlocks; ++j) {
         const int wbase = j * kSThreads + warp * 32;
-        if (wbase < nblk) {
+        if (wbase >= nblk) break;  // warp-uniform
+        {
             const int blk = wbase + lane;
             const bool active = blk < nblk;
             const int e = (active ? blk : wbase) << 3;
             const int m = (M == 1) ? 0 : e / K;
             const int k = e - m * K;
+            float u[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) u[q] = v[0][q];
+#pragma unroll
+            for (int jj = 0; jj + 1 < kStageBlocks; ++jj)
+#pragma unroll
+                for (int q = 0; q < 8; ++q) v[jj][q] = v[jj + 1][q];
             if (norm) {
                 const uint4 w4 = *reinterpret_cast<const uint4*>(p.norm_w + k);
                 const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
                 const float im = inv[0] * (m == 0) + inv[1] * (m == 1) + inv[2] * (m == 2) + inv[3] * (m == 3);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
-                    v[j][2 * q] = v[j][2 * q] * im * __uint_as_float(ww[q] << 16);
-                    v[j][2 * q + 1] = v[j][2 * q + 1] * im * __uint_as_float(ww[q] & 0xffff0000u);
+                    u[2 * q] = u[2 * q] * im * __uint_as_float(ww[q] << 16);
+                    u[2 * q + 1] = u[2 * q + 1] * im * __uint_as_float(ww[q] & 0xffff0000u);
                 }
             }
             uint32_t dig[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // [digit row][word]
             int dsum[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                float f = v[j][q] * xscale;
+                float f = u[q] * xscale;
                 f = fminf(fmaxf(f, -134217728.0f), 134217728.0f);  // inf/huge inputs saturate instead of wrapping
                 const int x0 = __float2int_rn(f);
                 // balanced base-128 digits: d = sign-extended low 7 bits, carry = (x + 64) >> 7
@@ -260,7 +278,7 @@ template <int FMT, int MT, int NT, int EPI>
 __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamParams p) {
     constexpr int ROWS = 16 * MT;                       // weight rows per unit tile
     constexpr int RU = (EPI == EPI_SILU) ? 16 : ROWS;   // output rows per unit
-    constexpr int kDepth = 4 / MT;  // weight tiles in flight per lane: 128 B x 512 threads = 64 KB per SM
+    constexpr int kDepth = 8 / MT;  // weight tiles in flight per lane: 256 B x 512 threads = 128 KB per SM
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -294,10 +312,17 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         row0 = (unit - p.unit_start[mi]) * RU;
     };
 
-    // ---- weight stream: a ring of kDepth tiles per lane, filled with 128-bit streaming loads ---------
-    // A tile is 16*MT rows x 64 bytes; this lane holds 16 bytes of rows g and g+8 of each 16-row block.
-    uint4 wreg[kDepth][MT][2];
-    uint32_t sreg[kDepth][MT];  // W4: binary16 group scales of rows g (low half) and g+8 (high half)
+    // ---- weight stream: a ring of kDepth tiles per lane, filled with 16-byte asynchronous copies ----
+    // A tile is 16*MT rows x 64 bytes; this lane owns 16 bytes of rows g and g+8 of each 16-row block.  The
+    // ring lives in shared memory but is PRIVATE to each lane: a lane reads back exactly the bytes its own
+    // cp.async wrote (slot plane + tid*16, conflict-free both ways), so cp.async.wait_group is the only
+    // synchronisation and no registers are spent on data in flight.
+    unsigned char* ring = smem + p.off_ring + (size_t)tid * 16;  // plane stride = kSThreads * 16 bytes
+    constexpr int kPlane = kSThreads * 16;
+    // W4 group scales ride in a second, tiny ring: per (slot, 16-row block, row half) one 4-byte word per row
+    // (the aligned word that contains the binary16 scale), copied by the t == 0 lane of each row
+    unsigned char* sring = smem + p.off_sring + warp * 32 + g * 4;
+    constexpr int kSPlane = kSWarps * 32;
     int l_unit = blockIdx.x, l_seg = j0;  // load cursor
     const unsigned char* lw[MT][2];   // this lane's 16 bytes of the cursor's segment, rows g and g+8
     const unsigned short* ls[MT][2];  // W4: the group scales of the same rows
@@ -319,16 +344,19 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         }
     };
     enter_unit();
-    auto load_tile = [&](uint4 (&w)[MT][2], uint32_t (&sc)[MT]) {
+    auto load_tile = [&](int slot) {
         if (l_unit < p.total_units && spu > 0) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                w[mt][0] = ld_stream_u4(lw[mt][0]);
-                w[mt][1] = ld_stream_u4(lw[mt][1]);
+                cp_async_stream16(ring + (size_t)((slot * MT + mt) * 2) * kPlane, lw[mt][0]);
+                cp_async_stream16(ring + (size_t)((slot * MT + mt) * 2 + 1) * kPlane, lw[mt][1]);
                 lw[mt][0] += 64;
                 lw[mt][1] += 64;
                 if (FMT == FMT_W4) {
-                    sc[mt] = (uint32_t)__ldg(ls[mt][0]) | ((uint32_t)__ldg(ls[mt][1]) << 16);
+                    if (t == 0) {
+                        cp_async_word(sring + (size_t)((slot * MT + mt) * 2) * kSPlane, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ls[mt][0]) & ~(uintptr_t)3));
+                        cp_async_word(sring + (size_t)((slot * MT + mt) * 2 + 1) * kSPlane, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ls[mt][1]) & ~(uintptr_t)3));
+                    }
                     ls[mt][0] += 1;
                     ls[mt][1] += 1;
                 }
@@ -339,9 +367,10 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                 enter_unit();
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, also when nothing was left to copy
     };
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d) load_tile(wreg[d], sreg[d]);  // weights do not depend on the previous kernel
+#pragma unroll 1
+    for (int d = 0; d < kDepth; ++d) load_tile(d);  // weights do not depend on the previous kernel
 
     // ---- stage the activations once -----------------------------------------------------------------
     pdl_wait();
@@ -384,8 +413,15 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
     };
     reset_acc();
 
-    // multiply one tile (segment sg of the current unit) held in registers
-    auto compute_tile = [&](const uint4 (&w)[MT][2], const uint32_t (&sc)[MT], int sg) {
+    int c_par = 0;  // W4: parity of row*ngr for the rows this lane holds in the current unit (bit 2*mt + half)
+    // multiply one tile (segment sg of the current unit) from the lane's ring slot
+    auto compute_tile = [&](int slot, int sg) {
+        uint4 w[MT][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            w[mt][0] = *reinterpret_cast<const uint4*>(ring + (size_t)((slot * MT + mt) * 2) * kPlane);
+            w[mt][1] = *reinterpret_cast<const uint4*>(ring + (size_t)((slot * MT + mt) * 2 + 1) * kPlane);
+        }
         if (FMT == FMT_W4) {
             uint4 bq[NT][2];
 #pragma unroll
@@ -408,8 +444,12 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                         mma_s8(c[mt][nt], a0, a1, a2, a3, (i & 1) ? b.z : b.x, (i & 1) ? b.w : b.y);
                     }
                 }
-                const float gs0 = __half2float(__ushort_as_half((unsigned short)(sc[mt] & 0xffffu)));
-                const float gs1 = __half2float(__ushort_as_half((unsigned short)(sc[mt] >> 16)));
+                // the aligned word holds scales of groups (2i, 2i+1) of the row: pick by the parity of row*ngr + sg
+                const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(sring + (size_t)((slot * MT + mt) * 2) * kSPlane);
+                const uint32_t sw1 = *reinterpret_cast<const uint32_t*>(sring + (size_t)((slot * MT + mt) * 2 + 1) * kSPlane);
+                const int par0 = ((c_par >> (mt * 2)) ^ sg) & 1, par1 = ((c_par >> (mt * 2 + 1)) ^ sg) & 1;
+                const float gs0 = __half2float(__ushort_as_half((unsigned short)(par0 ? sw0 >> 16 : sw0 & 0xffffu)));
+                const float gs1 = __half2float(__ushort_as_half((unsigned short)(par1 ? sw1 >> 16 : sw1 & 0xffffu)));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     // sum (n - 8) * d = sum n*d - 8 * sum d for the digit pair (all exact, |.| < 2^24), then the group scale
@@ -540,31 +580,43 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     // ---- main loop: consume a tile, refill its register slot with the tile kDepth ahead ------------
     int c_unit = blockIdx.x, c_seg = j0, it = 0;
-    if (c_unit < p.total_units) prefetch_epilogue(0, c_unit);
-    if (spu > 0) {
-        while (c_unit < p.total_units && ok) {
+    auto enter_unit_consumer = [&]() {
+        if (c_unit >= p.total_units) return;
+        prefetch_epilogue(it, c_unit);
+        if (FMT == FMT_W4 && (ngr & 1)) {  // odd group count (e.g. K = 896): the word parity depends on the row
+            int mi, row0;
+            unit_rows(c_unit, mi, row0);
+            c_par = 0;
 #pragma unroll
-            for (int d = 0; d < kDepth; ++d) {
-                if (c_unit < p.total_units && ok) {
-                    compute_tile(wreg[d], sreg[d], c_seg);
-                    load_tile(wreg[d], sreg[d]);
-                    if (++c_seg == j1) {
-                        c_seg = j0;
-                        finish_unit(it, c_unit);
-                        ++it;
-                        c_unit += gridDim.x;
-                        if (c_unit < p.total_units) prefetch_epilogue(it, c_unit);
-                    }
-                }
+            for (int mt = 0; mt < MT; ++mt) {
+                const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
+                const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
+                const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);
+                c_par |= ((r0 & 1) << (mt * 2)) | ((r1 & 1) << (mt * 2 + 1));
             }
         }
-    } else {
-        // fewer segments than warps: this warp has no columns but still takes part in the unit hand-shake
-        for (; c_unit < p.total_units && ok; c_unit += gridDim.x, ++it) {
-            finish_unit(it, c_unit);
-            if (c_unit + (int)gridDim.x < p.total_units) prefetch_epilogue(it + 1, c_unit + gridDim.x);
+    };
+    enter_unit_consumer();
+    // one loop for both kinds of warp: a warp with no columns (fewer segments than warps) still takes part in
+    // the unit hand-shake
+    int slot = 0;
+    while (c_unit < p.total_units && ok) {
+        if (spu > 0) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");  // this lane's oldest tile has landed
+            if (FMT == FMT_W4) __syncwarp();  // scale words were copied by the t == 0 lanes
+            compute_tile(slot, c_seg);
+            if (FMT == FMT_W4) __syncwarp();  // every lane has read the slot's scale words before they are replaced
+            load_tile(slot);
+            if (++slot == kDepth) slot = 0;
+            if (++c_seg != j1) continue;
+            c_seg = j0;
         }
+        finish_unit(it, c_unit);
+        ++it;
+        c_unit += gridDim.x;
+        enter_unit_consumer();
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     pdl_launch_dependents();
     if (EPI == EPI_TOP1) {
         // every warp finished some units: merge the 16 running bests (fixed order) into one partial per block
