@@ -86,17 +86,16 @@ struct DecodeAttnParams {
 
 // Half-split RoPE of a head slice held 4 (or 2) consecutive dims per lane: the partner dim d +- HD/2 lives
 // in lane ^ 16 (crates/inference/src/kernels/inference.rs:1078-1098 with rotary_dim == head_dim).
+// `cs_sn` holds (cos, sin) of position * freqs[pair] for the HD/2 pairs, computed once per block.
 template <int EPL>
-__device__ inline void rope_lane_slice(float (&x)[EPL], const float* freqs, float position, int lane) {
+__device__ inline void rope_lane_slice(float (&x)[EPL], const float2* cs_sn, int lane) {
     constexpr int HALF_LANES = 16;
     const bool upper = lane >= HALF_LANES;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
         const float other = __shfl_xor_sync(0xffffffffu, x[e], HALF_LANES);
-        const int pair = (lane & (HALF_LANES - 1)) * EPL + e;
-        const float angle = position * freqs[pair];
-        const float sn = sinf(angle), cs = cosf(angle);
-        x[e] = upper ? x[e] * cs + other * sn : x[e] * cs - other * sn;
+        const float2 t = cs_sn[(lane & (HALF_LANES - 1)) * EPL + e];
+        x[e] = upper ? x[e] * t.x + other * t.y : x[e] * t.x - other * t.y;
     }
 }
 
@@ -136,6 +135,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     float* hstat = sc + kMaxGq * kAttnTile;   // [kMaxGq][4]: running max, running sum, correction
     float* red = Ks;                          // [kAttnWarps][gq][HD] (reuses the K/V tiles at the end)
     __shared__ bool is_last;
+    __shared__ float2 cs_sn[HD / 2];  // fused form: (cos, sin) of the rotation angles of this position
 
     pdl_wait();
     const int seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
@@ -165,22 +165,31 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         const bool fused = p.k_new != nullptr;
         const float position = (float)(seq_len - 1);
         if (fused) {
+            // one sine / cosine evaluation per pair and block (the accurate sinf / cosf are long code)
+            if (tid < HD / 2) {
+                const float angle = position * p.freqs[tid];
+                cs_sn[tid] = make_float2(cosf(angle), sinf(angle));
+            }
+            __syncthreads();
 #pragma unroll
             for (int h = 0; h < kMaxGq; ++h)
-                if (h < gq) rope_lane_slice<EPL>(qv[h], p.freqs, position, lane);
+                if (h < gq) rope_lane_slice<EPL>(qv[h], cs_sn, lane);
         }
         if (tid < kMaxGq) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
 
+        #pragma unroll 1
         for (int t0 = 0; t0 < n; t0 += kAttnTile) {
             const int nt = min(kAttnTile, n - t0);
             __syncthreads();  // the previous tile has been consumed
             const float* kg = p.k_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
             const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+            #pragma unroll 1
             for (int i = tid; i < nt * V16; i += kAttnThreads) {
                 const int r = i / V16, cidx = i - r * V16;
                 cp_async16(Ks + r * HD + cidx * 4, kg + (size_t)r * kv_stride + cidx * 4);
             }
             cp_async_commit();
+            #pragma unroll 1
             for (int i = tid; i < nt * V16; i += kAttnThreads) {
                 const int r = i / V16, cidx = i - r * V16;
                 cp_async16(Vs + r * HD + cidx * 4, vg + (size_t)r * kv_stride + cidx * 4);
@@ -192,7 +201,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             if (fused && newrow >= 0 && newrow < nt && warp == 0) {
                 float kn[EPL];
                 load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kn);
-                rope_lane_slice<EPL>(kn, p.freqs, position, lane);
+                rope_lane_slice<EPL>(kn, cs_sn, lane);
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) {
                     Ks[newrow * HD + lane * EPL + e] = kn[e];
@@ -201,6 +210,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
             if (fused && newrow >= 0 && newrow < nt) __syncthreads();
             // scores: one warp per position
+            #pragma unroll 1
             for (int i = warp; i < nt; i += kAttnWarps) {
                 float kvv[EPL];
                 load_lane_slice<EPL>(Ks + i * HD + lane * EPL, kvv);
@@ -217,12 +227,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
             __syncthreads();
             // running softmax statistics: one warp per query head
+            #pragma unroll 1
             for (int h = warp; h < gq; h += kAttnWarps) {
                 float m_old = hstat[h * 4], l_old = hstat[h * 4 + 1];
                 float m = m_old;
+                #pragma unroll 1
                 for (int i = lane; i < nt; i += 32) m = fmaxf(m, sc[h * kAttnTile + i]);
                 m = warp_max(m);
                 float l = 0.0f;
+                #pragma unroll 1
                 for (int i = lane; i < nt; i += 32) {
                     const float e = expf(sc[h * kAttnTile + i] - m);
                     sc[h * kAttnTile + i] = e;
@@ -254,6 +267,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll
                     for (int e = 0; e < EPL; ++e) acc[h][e] *= corr;
                 }
+            #pragma unroll 1
             for (int i = warp; i < nt; i += kAttnWarps) {
                 float vv[EPL];
                 load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
@@ -278,6 +292,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     pdl_launch_dependents();
 
     // write this split's partial (or the final result when there is a single split)
+    #pragma unroll 1
     for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
@@ -315,16 +330,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     float* f_s = Ks + 2 * kMaxGq * 64;      // [gq][nsplit] weights, then [gq] denominators after them
     float* l_s = f_s + kMaxGq * 64;
     const int ns = nactive;  // only these splits wrote partials
+    #pragma unroll 1
     for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
         const int h = idx / (ns * 2), r = idx - h * ns * 2;
         ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * p.nsplit * 2 + r);
     }
     __syncthreads();
+    #pragma unroll 1
     for (int h = warp; h < gq; h += kAttnWarps) {
         float m = -INFINITY;
+        #pragma unroll 1
         for (int s = lane; s < ns; s += 32) m = fmaxf(m, ml_s[(h * ns + s) * 2]);
         m = warp_max(m);
         float l = 0.0f;
+        #pragma unroll 1
         for (int s = lane; s < ns; s += 32) {
             const float ms = ml_s[(h * ns + s) * 2];
             const float f = ms == -INFINITY ? 0.0f : expf(ms - m);
@@ -335,12 +354,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         if (lane == 0) l_s[h] = l;
     }
     __syncthreads();
+    #pragma unroll 1
     for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
         const float* pa = p.part_acc + (size_t)head * p.nsplit * HD + d;
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // independent chains: the loads of a round overlap
         int s = 0;
+        #pragma unroll 1
         for (; s + 4 <= ns; s += 4) {
             const float v0 = __ldcg(pa + (size_t)s * HD), v1 = __ldcg(pa + (size_t)(s + 1) * HD);
             const float v2 = __ldcg(pa + (size_t)(s + 2) * HD), v3 = __ldcg(pa + (size_t)(s + 3) * HD);
@@ -349,6 +370,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             a2 = fmaf(v2, f_s[h * ns + s + 2], a2);
             a3 = fmaf(v3, f_s[h * ns + s + 3], a3);
         }
+        #pragma unroll 1
         for (; s < ns; ++s) a0 = fmaf(__ldcg(pa + (size_t)s * HD), f_s[h * ns + s], a0);
         p.out[(size_t)head * HD + d] = ((a0 + a1) + (a2 + a3)) / l_s[h];
     }

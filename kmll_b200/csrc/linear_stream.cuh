@@ -117,155 +117,188 @@ __device__ inline void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2
 // xcomb[group][2*m + p] = 8 * (128 * sum(d_{3-2p}) + sum(d_{2-2p})) over the group's 128 columns: what
 // the +8 offset of the stored nibbles adds to the combined digit pair p of batch row m.
 // Returns 2^-sh.  One pass: each thread keeps its (at most kStageBlocks) 8-column blocks of x in
-// registers between the block-wide reduction and the conversion.
+// registers between the block-wide reduction and the conversion.  SINGLE fixes M = 1 at compile time.
+//
+// Digits: X = round(x * 2^sh) with |X| <= 2^26.  Y = X + 64*(1 + 128 + 128^2 + 128^3) lies in [0, 2^28), its
+// four 7-bit fields u_j are spread to the four bytes of a word, and d_j = u_j - 64 in [-64, 63] gives
+// X = sum d_j * 128^j.  All of it is plain logic / integer arithmetic on whole words.
 constexpr int kStageBlocks = 6;  // M*K <= 6*8*512 = 24576
-__device__ inline int bfe_s7(int x) {
-    int d;
-    asm("bfe.s32 %0, %1, 0, 7;" : "=r"(d) : "r"(x));
-    return d;
+constexpr uint32_t kDigitBias = 64u * (1u + 128u + 16384u + 2097152u);
+__device__ inline uint32_t digit_word(float f) {
+    f = fminf(fmaxf(f, -67108864.0f), 67108864.0f);  // inf/huge inputs saturate instead of wrapping
+    const uint32_t y = (uint32_t)__float2int_rn(f) + kDigitBias;
+    uint32_t lo = y & 0x3fffu, hi = y >> 14;
+    lo += lo & 0x3f80u;  // u0 | u1 << 8
+    hi += hi & 0x3f80u;  // u2 | u3 << 8
+    const uint32_t u = __byte_perm(lo, hi, 0x5410);
+    // per byte u - 64: flip bit 6, then copy the new bit 6 into bit 7 (sign extension of a 7-bit value)
+    const uint32_t t = ~u & 0x40404040u;
+    return (u ^ 0x40404040u) + t * 2u;
 }
-__device__ inline uint32_t bfi_byte(uint32_t word, int value, int byte) {
-    uint32_t r;
-    asm("bfi.b32 %0, %1, %2, %3, 8;" : "=r"(r) : "r"(value), "r"(word), "r"(byte * 8));
-    return r;
+// rows[r] = byte r of (a, b, c, d)
+__device__ inline void transpose_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&rows)[4]) {
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+    const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+    rows[0] = __byte_perm(t0, t1, 0x5410);
+    rows[1] = __byte_perm(t0, t1, 0x7632);
+    rows[2] = __byte_perm(t2, t3, 0x5410);
+    rows[3] = __byte_perm(t2, t3, 0x7632);
 }
-template <int FMT>
+template <int FMT, bool SINGLE>
 __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int* xcomb, float* misc) {
+    constexpr int NM = SINGLE ? 1 : 4;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int M = p.M, K = p.K;
-    const int nblk = (M * K) >> 3;  // 8-element blocks; a multiple of 16
+    const int M = SINGLE ? 1 : p.M, K = p.K;
+    const int nblk = (M * K) >> 3;  // 8-element blocks; a multiple of 8 (W4: of 16)
     const bool norm = p.norm_w != nullptr;
     float v[kStageBlocks][8];
-    float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float mx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    uint4 nw[kStageBlocks];  // bf16 RMSNorm weights of the block
+#pragma unroll
+    for (int j = 0; j < kStageBlocks; ++j) {  // every load is issued before anything is consumed
+        const int blk = j * kSThreads + tid;
+        const int e = (blk < nblk ? blk : 0) << 3;
+        const int m = SINGLE ? 0 : e / K;
+        const int k = e - m * K;
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b = a;
+        nw[j] = make_uint4(0, 0, 0, 0);
+        if (j * kSThreads + warp * 32 < nblk) {  // warp-uniform; lanes past the end re-read block 0 and are masked later
+            const float4* src = reinterpret_cast<const float4*>(p.x + (size_t)m * p.ldx + k);
+            a = src[0];
+            b = src[1];
+            if (norm) nw[j] = *reinterpret_cast<const uint4*>(p.norm_w + k);
+        }
+        v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+        v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+    }
+    float ss[NM], mx[NM];
+#pragma unroll
+    for (int mm = 0; mm < NM; ++mm) ss[mm] = mx[mm] = 0.0f;
 #pragma unroll
     for (int j = 0; j < kStageBlocks; ++j) {
-        const int wbase = j * kSThreads + warp * 32;
-        if (wbase < nblk) {  // warp-uniform
-            const int blk = wbase + lane;
-            const bool active = blk < nblk;
-            const int e = (active ? blk : wbase) << 3;
-            const int m = (M == 1) ? 0 : e / K;
-            const int k = e - m * K;
-            const float4* src = reinterpret_cast<const float4*>(p.x + (size_t)m * p.ldx + k);
-            const float4 a = src[0], b = src[1];
-            v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
-            v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
-            float s_ = 0.0f, m_ = 0.0f;
-            if (norm) {
-                const uint4 w4 = *reinterpret_cast<const uint4*>(p.norm_w + k);
-                const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+        const int blk = j * kSThreads + tid;
+        const bool active = blk < nblk;
+        const int m = SINGLE ? 0 : ((active ? blk : 0) << 3) / K;
+        float s_ = 0.0f, m_ = 0.0f;
+        if (norm) {
+            const uint32_t ww[4] = {nw[j].x, nw[j].y, nw[j].z, nw[j].w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    s_ += v[j][2 * q] * v[j][2 * q] + v[j][2 * q + 1] * v[j][2 * q + 1];
-                    m_ = fmaxf(m_, fmaxf(fabsf(v[j][2 * q] * __uint_as_float(ww[q] << 16)),
-                                         fabsf(v[j][2 * q + 1] * __uint_as_float(ww[q] & 0xffff0000u))));
-                }
-            } else {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) m_ = fmaxf(m_, fabsf(v[j][q]));
+            for (int q = 0; q < 4; ++q) {
+                s_ += v[j][2 * q] * v[j][2 * q] + v[j][2 * q + 1] * v[j][2 * q + 1];
+                m_ = fmaxf(m_, fmaxf(fabsf(v[j][2 * q] * __uint_as_float(ww[q] << 16)),
+                                     fabsf(v[j][2 * q + 1] * __uint_as_float(ww[q] & 0xffff0000u))));
             }
-            if (active) {
+        } else {
 #pragma unroll
-                for (int mm = 0; mm < 4; ++mm)
-                    if (m == mm) { ss[mm] += s_; mx[mm] = fmaxf(mx[mm], m_); }
-            }
+            for (int q = 0; q < 8; ++q) m_ = fmaxf(m_, fabsf(v[j][q]));
         }
+        if (!active) s_ = m_ = 0.0f;
+#pragma unroll
+        for (int mm = 0; mm < NM; ++mm)
+            if (SINGLE || m == mm) { ss[mm] += s_; mx[mm] = fmaxf(mx[mm], m_); }
     }
 #pragma unroll
-    for (int mm = 0; mm < 4; ++mm) {
+    for (int mm = 0; mm < NM; ++mm) {
         ss[mm] = warp_sum(ss[mm]);
         mx[mm] = warp_max(mx[mm]);
     }
     if (lane == 0) {
 #pragma unroll
-        for (int mm = 0; mm < 4; ++mm) { misc[warp * 8 + mm] = ss[mm]; misc[warp * 8 + 4 + mm] = mx[mm]; }
+        for (int mm = 0; mm < NM; ++mm) { misc[warp * 8 + mm] = ss[mm]; misc[warp * 8 + 4 + mm] = mx[mm]; }
     }
     consumer_bar_sync();
-    float inv[4];
+    // second level: lanes 0..15 fold the 16 warps' sums, lanes 16..31 their maxima (a butterfly over 16 lanes)
+    float inv[NM];
     float amax = 0.0f;
+    {
+        const bool upper = lane >= 16;
+        float r[NM];
 #pragma unroll
-    for (int mm = 0; mm < 4; ++mm) {
-        float s_ = 0.0f, m_ = 0.0f;
+        for (int mm = 0; mm < NM; ++mm) r[mm] = misc[(lane & 15) * 8 + (upper ? 4 : 0) + mm];
 #pragma unroll
-        for (int w = 0; w < kSWarps; ++w) { s_ += misc[w * 8 + mm]; m_ = fmaxf(m_, misc[w * 8 + 4 + mm]); }
-        inv[mm] = norm ? 1.0f / sqrtf(s_ / (float)K + p.eps) : 1.0f;
-        amax = fmaxf(amax, m_ * inv[mm]);
+        for (int off = 1; off < 16; off <<= 1)
+#pragma unroll
+            for (int mm = 0; mm < NM; ++mm) {
+                const float o = __shfl_xor_sync(0xffffffffu, r[mm], off);
+                r[mm] = upper ? fmaxf(r[mm], o) : r[mm] + o;
+            }
+#pragma unroll
+        for (int mm = 0; mm < NM; ++mm) {
+            const float s_ = __shfl_sync(0xffffffffu, r[mm], 0), m_ = __shfl_sync(0xffffffffu, r[mm], 16);
+            inv[mm] = norm ? 1.0f / sqrtf(s_ / (float)K + p.eps) : 1.0f;
+            amax = fmaxf(amax, m_ * inv[mm]);
+        }
     }
-    // power-of-two scale: |x * 2^sh| < 2^27 for every element
+    // power-of-two scale: |x * 2^sh| < 2^26 for every element
     float xscale = 1.0f, inv_xscale = 1.0f;
     if (amax > 0.0f && amax < INFINITY) {
         const int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;  // floor(log2(amax)) (denormals: -127)
-        int sh = 26 - e;
+        int sh = 25 - e;
         sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
         xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
         inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
     // The conversion is a ROLLED loop: block j is always taken from v[0] and the remaining blocks move down one
-    // place, so the long conversion sequence exists once in the instruction stream (a kernel whose code is
-    // executed once per launch is bound by instruction fetch, not by issue).
+    // place, so the conversion sequence exists once in the instruction stream (code that runs once per launch
+    // costs instruction fetches, not issue slots).
 #pragma unroll 1
     for (int j = 0; j < kStageBlocks; ++j) {
         const int wbase = j * kSThreads + warp * 32;
         if (wbase >= nblk) break;  // warp-uniform
-        {
-            const int blk = wbase + lane;
-            const bool active = blk < nblk;
-            const int e = (active ? blk : wbase) << 3;
-            const int m = (M == 1) ? 0 : e / K;
-            const int k = e - m * K;
-            float u[8];
+        const int blk = wbase + lane;
+        const bool active = blk < nblk;
+        const int e = (active ? blk : wbase) << 3;
+        const int m = SINGLE ? 0 : e / K;
+        const int k = e - m * K;
+        float u[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) u[q] = v[0][q];
+        for (int q = 0; q < 8; ++q) u[q] = v[0][q];
+        const uint32_t ww[4] = {nw[0].x, nw[0].y, nw[0].z, nw[0].w};
 #pragma unroll
-            for (int jj = 0; jj + 1 < kStageBlocks; ++jj)
+        for (int jj = 0; jj + 1 < kStageBlocks; ++jj) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) v[jj][q] = v[jj + 1][q];
-            if (norm) {
-                const uint4 w4 = *reinterpret_cast<const uint4*>(p.norm_w + k);
-                const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
-                const float im = inv[0] * (m == 0) + inv[1] * (m == 1) + inv[2] * (m == 2) + inv[3] * (m == 3);
+            for (int q = 0; q < 8; ++q) v[jj][q] = v[jj + 1][q];
+            nw[jj] = nw[jj + 1];
+        }
+        if (norm) {
+            float im = inv[0];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
-                    u[2 * q] = u[2 * q] * im * __uint_as_float(ww[q] << 16);
-                    u[2 * q + 1] = u[2 * q + 1] * im * __uint_as_float(ww[q] & 0xffff0000u);
-                }
+            for (int mm = 1; mm < NM; ++mm) im = (m == mm) ? inv[mm] : im;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
+                u[2 * q] = u[2 * q] * im * __uint_as_float(ww[q] << 16);
+                u[2 * q + 1] = u[2 * q + 1] * im * __uint_as_float(ww[q] & 0xffff0000u);
             }
-            uint32_t dig[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // [digit row][word]
-            int dsum[4] = {0, 0, 0, 0};
+        }
+        uint32_t d[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                float f = u[q] * xscale;
-                f = fminf(fmaxf(f, -134217728.0f), 134217728.0f);  // inf/huge inputs saturate instead of wrapping
-                const int x0 = __float2int_rn(f);
-                // balanced base-128 digits: d = sign-extended low 7 bits, carry = (x + 64) >> 7
-                const int d0 = bfe_s7(x0), x1 = (x0 + 64) >> 7;
-                const int d1 = bfe_s7(x1), x2 = (x1 + 64) >> 7;
-                const int d2 = bfe_s7(x2), d3 = (x2 + 64) >> 7;  // |d3| <= 65
-                const int pos = (FMT == FMT_W4) ? (((q & 1) << 2) | (q >> 1)) : q;  // byte position inside the block
-                dig[3][pos >> 2] = bfi_byte(dig[3][pos >> 2], d0, pos & 3);
-                dig[2][pos >> 2] = bfi_byte(dig[2][pos >> 2], d1, pos & 3);
-                dig[1][pos >> 2] = bfi_byte(dig[1][pos >> 2], d2, pos & 3);
-                dig[0][pos >> 2] = bfi_byte(dig[0][pos >> 2], d3, pos & 3);
-                if (FMT == FMT_W4) { dsum[3] += d0; dsum[2] += d1; dsum[1] += d2; dsum[0] += d3; }
+        for (int q = 0; q < 8; ++q) d[q] = digit_word(u[q] * xscale);
+        uint32_t r0[4], r1[4];  // digit j of the block's first / second word (j = 0 least significant)
+        if (FMT == FMT_W4) {
+            transpose_bytes(d[0], d[2], d[4], d[6], r0);
+            transpose_bytes(d[1], d[3], d[5], d[7], r1);
+        } else {
+            transpose_bytes(d[0], d[1], d[2], d[3], r0);
+            transpose_bytes(d[4], d[5], d[6], d[7], r1);
+        }
+        if (active) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + 3 - r) * p.xs_pitch + k) = make_uint2(r0[r], r1[r]);
+        }
+        if (FMT == FMT_W4) {
+            int dsum[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) dsum[r] = __dp4a((int)r1[r], 0x01010101, __dp4a((int)r0[r], 0x01010101, 0));
+            // the 16 threads that hold one 128-column group are 16 consecutive lanes
+            int c01 = 128 * dsum[3] + dsum[2], c23 = 128 * dsum[1] + dsum[0];
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) {
+                c01 += __shfl_xor_sync(0xffffffffu, c01, off);
+                c23 += __shfl_xor_sync(0xffffffffu, c23, off);
             }
-            if (active) {
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + r) * p.xs_pitch + k) = make_uint2(dig[r][0], dig[r][1]);
-            }
-            if (FMT == FMT_W4) {
-                // the 16 threads that hold one 128-column group are 16 consecutive lanes
-                int c01 = 128 * dsum[0] + dsum[1], c23 = 128 * dsum[2] + dsum[3];
-#pragma unroll
-                for (int off = 1; off < 16; off <<= 1) {
-                    c01 += __shfl_xor_sync(0xffffffffu, c01, off);
-                    c23 += __shfl_xor_sync(0xffffffffu, c23, off);
-                }
-                if (active && (lane & 15) == 0) {
-                    xcomb[(k >> 7) * (2 * M) + 2 * m] = 8 * c01;
-                    xcomb[(k >> 7) * (2 * M) + 2 * m + 1] = 8 * c23;
-                }
+            if (active && (lane & 15) == 0) {
+                xcomb[(k >> 7) * (2 * M) + 2 * m] = 8 * c01;
+                xcomb[(k >> 7) * (2 * M) + 2 * m + 1] = 8 * c23;
             }
         }
     }
@@ -283,7 +316,8 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int M = p.M, K = p.K;
+    constexpr bool kSingle = (NT == 1);  // one batch row, known at compile time (the decode path)
+    const int M = kSingle ? 1 : p.M, K = p.K;
     const int rowbytes = (FMT == FMT_W4) ? (K >> 1) : K;
     const int nseg = rowbytes >> 6;  // 64-byte segments per row (W4: quantization groups)
     const int j0 = (warp * nseg) / kSWarps, j1 = ((warp + 1) * nseg) / kSWarps;  // this warp's K slice
@@ -374,7 +408,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     // ---- stage the activations once -----------------------------------------------------------------
     pdl_wait();
-    const float inv_xscale = stage_activations<FMT>(p, xs, xcomb, misc);
+    const float inv_xscale = stage_activations<FMT, kSingle>(p, xs, xcomb, misc);
 
     // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns
     bool bvalid[NT];
