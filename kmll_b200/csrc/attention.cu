@@ -124,30 +124,77 @@ __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" 
 // brought into shared memory with 16-byte asynchronous copies that are all issued up front
 // (64 KB in flight per block, two blocks per SM), so the f32 KV cache streams at HBM rate; the
 // query heads sharing the KV head are processed together, so K and V are read once.
+// In the fused form the copies are issued BEFORE the wait on the previous kernel: rows below
+// seq_len - 1 were written by earlier steps, and the sequence length by a kernel at least two launches back.
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p) {
     constexpr int EPL = HD / 32;        // elements per lane
     constexpr int V16 = HD / 4;         // 16-byte pieces per row
+    constexpr int KP = HD + 16;         // padded K row: the score pass reads 16-byte pieces at stride KP conflict-free
     extern __shared__ __align__(16) float smem[];
-    float* Ks = smem;                         // [kAttnTile][HD]
-    float* Vs = Ks + kAttnTile * HD;          // [kAttnTile][HD]
+    float* Ks = smem;                         // [kAttnTile][KP]
+    float* Vs = Ks + kAttnTile * KP;          // [kAttnTile][HD]
     float* sc = Vs + kAttnTile * HD;          // [kMaxGq][kAttnTile] scores, then weights
     float* hstat = sc + kMaxGq * kAttnTile;   // [kMaxGq][4]: running max, running sum, correction
-    float* red = Ks;                          // [kAttnWarps][gq][HD] (reuses the K/V tiles at the end)
+    float* qs = hstat + kMaxGq * 4;           // [kMaxGq][HD] rotated query heads
+    float* red = Vs;                          // [kAttnWarps][gq][HD] (reuses the V tile at the end)
     __shared__ bool is_last;
     __shared__ float2 cs_sn[HD / 2];  // fused form: (cos, sin) of the rotation angles of this position
 
-    pdl_wait();
-    const int seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
     const int kv_head = blockIdx.x, split = blockIdx.y, gq = p.gq;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t kv_stride = (size_t)p.n_kv_heads * HD;
+    const bool fused = p.k_new != nullptr;
     const int s0 = split * p.chunk;
-    const int s1 = min(s0 + p.chunk, seq_len);
-    const int n = s1 - s0;
+    int seq_len = 0, n = 0;
+    auto issue_tile = [&](int t0, int nt) {
+        const float* kg = p.k_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+        const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+#pragma unroll 2
+        for (int i = tid; i < nt * V16; i += kAttnThreads) {
+            const int r = i / V16, cidx = i - r * V16;
+            cp_async16(Ks + r * KP + cidx * 4, kg + (size_t)r * kv_stride + cidx * 4);
+        }
+        cp_async_commit();
+#pragma unroll 2
+        for (int i = tid; i < nt * V16; i += kAttnThreads) {
+            const int r = i / V16, cidx = i - r * V16;
+            cp_async16(Vs + r * HD + cidx * 4, vg + (size_t)r * kv_stride + cidx * 4);
+        }
+        cp_async_commit();
+    };
+    if (fused) {
+        seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
+        n = min(s0 + p.chunk, seq_len) - s0;
+        if (n > 0) issue_tile(0, min(kAttnTile, n));
+    }
+    pdl_wait();
+    if (!fused) {
+        seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
+        n = min(s0 + p.chunk, seq_len) - s0;
+    }
     const int nactive = (seq_len + p.chunk - 1) / p.chunk;  // splits that hold positions; the others leave at once
     if (n <= 0) return;
-    const size_t kv_stride = (size_t)p.n_kv_heads * HD;
     const float scale = 1.0f / sqrtf((float)HD);
+    const float position = (float)(seq_len - 1);
+
+    // query heads (rotated in the fused form) go to shared memory: warp h prepares head h
+    if (fused && tid < HD / 2) {
+        // one sine / cosine evaluation per pair and block (the accurate sinf / cosf are long code)
+        const float angle = position * p.freqs[tid];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        cs_sn[tid] = make_float2(cs, sn);
+    }
+    if (tid < kMaxGq) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
+    float qh[EPL];
+    if (warp < gq) load_lane_slice<EPL>(p.q + (size_t)(kv_head * gq + warp) * HD + lane * EPL, qh);
+    if (fused) __syncthreads();
+    if (warp < gq) {
+        if (fused) rope_lane_slice<EPL>(qh, cs_sn, lane);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) qs[warp * HD + lane * EPL + e] = qh[e];
+    }
 
     float acc[kMaxGq][EPL];
 #pragma unroll
@@ -155,163 +202,126 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll
         for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
 
-    if (n > 0) {
-        float qv[kMaxGq][EPL];
+#pragma unroll 1
+    for (int t0 = 0; t0 < n; t0 += kAttnTile) {
+        const int nt = min(kAttnTile, n - t0);
+        __syncthreads();  // the previous tile has been consumed (first tile: qs / hstat are written)
+        if (!(fused && t0 == 0)) issue_tile(t0, nt);
+        cp_async_wait<1>();  // K has landed
+        __syncthreads();
+        const int newrow = seq_len - 1 - s0 - t0;  // row of this tile that is the position being written
+        const bool has_new = fused && newrow >= 0 && newrow < nt;
+        if (has_new && warp == 0) {
+            float kn[EPL];
+            load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kn);
+            rope_lane_slice<EPL>(kn, cs_sn, lane);
 #pragma unroll
-        for (int h = 0; h < kMaxGq; ++h)
-#pragma unroll
-            for (int e = 0; e < EPL; ++e)
-                qv[h][e] = h < gq ? p.q[(size_t)(kv_head * gq + h) * HD + lane * EPL + e] : 0.0f;
-        const bool fused = p.k_new != nullptr;
-        const float position = (float)(seq_len - 1);
-        if (fused) {
-            // one sine / cosine evaluation per pair and block (the accurate sinf / cosf are long code)
-            if (tid < HD / 2) {
-                const float angle = position * p.freqs[tid];
-                cs_sn[tid] = make_float2(cosf(angle), sinf(angle));
+            for (int e = 0; e < EPL; ++e) {
+                Ks[newrow * KP + lane * EPL + e] = kn[e];
+                p.k_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kn[e];
             }
-            __syncthreads();
-#pragma unroll
-            for (int h = 0; h < kMaxGq; ++h)
-                if (h < gq) rope_lane_slice<EPL>(qv[h], cs_sn, lane);
         }
-        if (tid < kMaxGq) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
-
-        #pragma unroll 1
-        for (int t0 = 0; t0 < n; t0 += kAttnTile) {
-            const int nt = min(kAttnTile, n - t0);
-            __syncthreads();  // the previous tile has been consumed
-            const float* kg = p.k_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
-            const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
-            #pragma unroll 1
-            for (int i = tid; i < nt * V16; i += kAttnThreads) {
-                const int r = i / V16, cidx = i - r * V16;
-                cp_async16(Ks + r * HD + cidx * 4, kg + (size_t)r * kv_stride + cidx * 4);
+        if (has_new) __syncthreads();
+        // scores: four lanes per position, each over an interleaved quarter of the head dimension
+        {
+            const int pl = tid >> 2, c = tid & 3;
+            const float* kr = Ks + (pl < nt ? pl : 0) * KP + c * 4;
+            float4 kk[HD / 16];
+#pragma unroll
+            for (int i = 0; i < HD / 16; ++i) kk[i] = *reinterpret_cast<const float4*>(kr + i * 16);
+#pragma unroll 1
+            for (int h = 0; h < gq; ++h) {
+                const float* qr = qs + h * HD + c * 4;
+                float v = 0.0f;
+#pragma unroll
+                for (int i = 0; i < HD / 16; ++i) {
+                    const float4 qq = *reinterpret_cast<const float4*>(qr + i * 16);
+                    v = fmaf(kk[i].x, qq.x, fmaf(kk[i].y, qq.y, fmaf(kk[i].z, qq.z, fmaf(kk[i].w, qq.w, v))));
+                }
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if (c == 0 && pl < nt) sc[h * kAttnTile + pl] = v * scale;
             }
-            cp_async_commit();
-            #pragma unroll 1
-            for (int i = tid; i < nt * V16; i += kAttnThreads) {
-                const int r = i / V16, cidx = i - r * V16;
-                cp_async16(Vs + r * HD + cidx * 4, vg + (size_t)r * kv_stride + cidx * 4);
-            }
-            cp_async_commit();
-            cp_async_wait<1>();  // K has landed
-            __syncthreads();
-            const int newrow = seq_len - 1 - s0 - t0;  // row of this tile that is the position being written
-            if (fused && newrow >= 0 && newrow < nt && warp == 0) {
-                float kn[EPL];
-                load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kn);
-                rope_lane_slice<EPL>(kn, cs_sn, lane);
+        }
+        __syncthreads();
+        // running softmax statistics: one warp per query head
+        if (warp < gq) {
+            const int h = warp;
+            const float m_old = hstat[h * 4], l_old = hstat[h * 4 + 1];
+            const float s_a = lane < nt ? sc[h * kAttnTile + lane] : -INFINITY;
+            const float s_b = lane + 32 < nt ? sc[h * kAttnTile + lane + 32] : -INFINITY;
+            const float m = warp_max(fmaxf(m_old, fmaxf(s_a, s_b)));
+            const float e_a = lane < nt ? expf(s_a - m) : 0.0f, e_b = lane + 32 < nt ? expf(s_b - m) : 0.0f;
+            if (lane < nt) sc[h * kAttnTile + lane] = e_a;
+            if (lane + 32 < nt) sc[h * kAttnTile + lane + 32] = e_b;
+            const float l = warp_sum(e_a + e_b);
+            const float corr = expf(m_old - m);  // exp(-inf) = 0 on the first tile
+            if (lane == 0) { hstat[h * 4] = m; hstat[h * 4 + 1] = l_old * corr + l; hstat[h * 4 + 2] = corr; }
+        }
+        cp_async_wait<0>();  // V has landed
+        __syncthreads();
+        if (has_new) {
+            if (warp == 0) {
+                float vn[EPL];
+                load_lane_slice<EPL>(p.v_new + (size_t)kv_head * HD + lane * EPL, vn);
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) {
-                    Ks[newrow * HD + lane * EPL + e] = kn[e];
-                    p.k_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kn[e];
-                }
-            }
-            if (fused && newrow >= 0 && newrow < nt) __syncthreads();
-            // scores: one warp per position
-            #pragma unroll 1
-            for (int i = warp; i < nt; i += kAttnWarps) {
-                float kvv[EPL];
-                load_lane_slice<EPL>(Ks + i * HD + lane * EPL, kvv);
-#pragma unroll
-                for (int h = 0; h < kMaxGq; ++h) {
-                    if (h < gq) {
-                        float d = 0.0f;
-#pragma unroll
-                        for (int e = 0; e < EPL; ++e) d += qv[h][e] * kvv[e];
-                        d = warp_sum(d);
-                        if (lane == 0) sc[h * kAttnTile + i] = d * scale;
-                    }
+                    Vs[newrow * HD + lane * EPL + e] = vn[e];
+                    p.v_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = vn[e];
                 }
             }
             __syncthreads();
-            // running softmax statistics: one warp per query head
-            #pragma unroll 1
-            for (int h = warp; h < gq; h += kAttnWarps) {
-                float m_old = hstat[h * 4], l_old = hstat[h * 4 + 1];
-                float m = m_old;
-                #pragma unroll 1
-                for (int i = lane; i < nt; i += 32) m = fmaxf(m, sc[h * kAttnTile + i]);
-                m = warp_max(m);
-                float l = 0.0f;
-                #pragma unroll 1
-                for (int i = lane; i < nt; i += 32) {
-                    const float e = expf(sc[h * kAttnTile + i] - m);
-                    sc[h * kAttnTile + i] = e;
-                    l += e;
-                }
-                l = warp_sum(l);
-                const float corr = expf(m_old - m);  // exp(-inf) = 0 on the first tile
-                if (lane == 0) { hstat[h * 4] = m; hstat[h * 4 + 1] = l_old * corr + l; hstat[h * 4 + 2] = corr; }
-            }
-            cp_async_wait<0>();  // V has landed
-            __syncthreads();
-            if (fused && newrow >= 0 && newrow < nt) {
-                if (warp == 0) {
-                    float vn[EPL];
-                    load_lane_slice<EPL>(p.v_new + (size_t)kv_head * HD + lane * EPL, vn);
+        }
+        // weighted sum of V: one warp per position
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) {
-                        Vs[newrow * HD + lane * EPL + e] = vn[e];
-                        p.v_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = vn[e];
-                    }
-                }
-                __syncthreads();
-            }
-            // weighted sum of V: one warp per position
+        for (int h = 0; h < kMaxGq; ++h)
+            if (h < gq) {
+                const float corr = hstat[h * 4 + 2];
 #pragma unroll
-            for (int h = 0; h < kMaxGq; ++h)
+                for (int e = 0; e < EPL; ++e) acc[h][e] *= corr;
+            }
+#pragma unroll 2
+        for (int i = warp; i < nt; i += kAttnWarps) {
+            float vv[EPL];
+            load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
+#pragma unroll
+            for (int h = 0; h < kMaxGq; ++h) {
                 if (h < gq) {
-                    const float corr = hstat[h * 4 + 2];
+                    const float w = sc[h * kAttnTile + i];
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) acc[h][e] *= corr;
-                }
-            #pragma unroll 1
-            for (int i = warp; i < nt; i += kAttnWarps) {
-                float vv[EPL];
-                load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
-#pragma unroll
-                for (int h = 0; h < kMaxGq; ++h) {
-                    if (h < gq) {
-                        const float w = sc[h * kAttnTile + i];
-#pragma unroll
-                        for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(w, vv[e], acc[h][e]);
-                    }
+                    for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(w, vv[e], acc[h][e]);
                 }
             }
         }
-        __syncthreads();  // K/V tiles are free: reuse them for the cross-warp reduction
-#pragma unroll
-        for (int h = 0; h < kMaxGq; ++h)
-            if (h < gq)
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
-        __syncthreads();
     }
+    __syncthreads();  // the V tile is free: reuse it for the cross-warp reduction
+#pragma unroll
+    for (int h = 0; h < kMaxGq; ++h)
+        if (h < gq)
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
+    __syncthreads();
     pdl_launch_dependents();
 
     // write this split's partial (or the final result when there is a single split)
-    #pragma unroll 1
+#pragma unroll 1
     for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
         const int head = kv_head * gq + h;
         float v = 0.0f;
-        if (n > 0) {
 #pragma unroll
-            for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
-        }
+        for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
         if (p.nsplit == 1) {
-            p.out[(size_t)head * HD + d] = n > 0 ? v / hstat[h * 4 + 1] : 0.0f;
+            p.out[(size_t)head * HD + d] = v / hstat[h * 4 + 1];
         } else {
             p.part_acc[((size_t)head * p.nsplit + split) * HD + d] = v;
             if (d == 0) {
-                p.part_ml[((size_t)head * p.nsplit + split) * 2] = n > 0 ? hstat[h * 4] : -INFINITY;
-                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = n > 0 ? hstat[h * 4 + 1] : 0.0f;
+                p.part_ml[((size_t)head * p.nsplit + split) * 2] = hstat[h * 4];
+                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = hstat[h * 4 + 1];
             }
         }
     }
-    if (nactive == 1 && p.nsplit == 1) return;
+    if (p.nsplit == 1) return;
 
     // last block of this KV head merges the splits
     __threadfence();
@@ -323,56 +333,68 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // merge: bring every split's (max, sum) into shared memory with independent loads, derive the
-    // weights exp(m_s - m) once per head, then combine the partial accumulators (loads are
-    // independent of each other, so they pipeline instead of paying one L2 round trip per split)
+    // merge: bring every split's (max, sum) into shared memory, derive the weights exp(m_s - m) once per head,
+    // then combine the partial accumulators - warp w takes splits w, w+8, ... for all heads, so every load of a
+    // round is independent of the others and a handful of L2 round trips cover the whole merge
     float* ml_s = Ks;                       // [gq][nsplit][2]
     float* f_s = Ks + 2 * kMaxGq * 64;      // [gq][nsplit] weights, then [gq] denominators after them
     float* l_s = f_s + kMaxGq * 64;
     const int ns = nactive;  // only these splits wrote partials
-    #pragma unroll 1
+#pragma unroll 1
     for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
         const int h = idx / (ns * 2), r = idx - h * ns * 2;
         ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * p.nsplit * 2 + r);
     }
     __syncthreads();
-    #pragma unroll 1
-    for (int h = warp; h < gq; h += kAttnWarps) {
-        float m = -INFINITY;
-        #pragma unroll 1
-        for (int s = lane; s < ns; s += 32) m = fmaxf(m, ml_s[(h * ns + s) * 2]);
-        m = warp_max(m);
+    if (warp < gq) {
+        const int h = warp;
+        const float m_a = lane < ns ? ml_s[(h * ns + lane) * 2] : -INFINITY;
+        const float m_b = lane + 32 < ns ? ml_s[(h * ns + lane + 32) * 2] : -INFINITY;
+        const float m = warp_max(fmaxf(m_a, m_b));
+        const float f_a = m_a == -INFINITY ? 0.0f : expf(m_a - m), f_b = m_b == -INFINITY ? 0.0f : expf(m_b - m);
         float l = 0.0f;
-        #pragma unroll 1
-        for (int s = lane; s < ns; s += 32) {
-            const float ms = ml_s[(h * ns + s) * 2];
-            const float f = ms == -INFINITY ? 0.0f : expf(ms - m);
-            f_s[h * ns + s] = f;
-            l += ml_s[(h * ns + s) * 2 + 1] * f;
-        }
+        if (lane < ns) { f_s[h * ns + lane] = f_a; l += ml_s[(h * ns + lane) * 2 + 1] * f_a; }
+        if (lane + 32 < ns) { f_s[h * ns + lane + 32] = f_b; l += ml_s[(h * ns + lane + 32) * 2 + 1] * f_b; }
         l = warp_sum(l);
         if (lane == 0) l_s[h] = l;
     }
     __syncthreads();
-    #pragma unroll 1
+#pragma unroll
+    for (int h = 0; h < kMaxGq; ++h)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
+#pragma unroll 2
+    for (int s = warp; s < ns; s += kAttnWarps) {
+#pragma unroll
+        for (int h = 0; h < kMaxGq; ++h)
+            if (h < gq) {
+                float pv[EPL];
+                const float* src = p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + s) * HD + lane * EPL;
+                if (EPL == 4) {
+                    const float4 t4 = __ldcg(reinterpret_cast<const float4*>(src));
+                    pv[0] = t4.x; pv[1] = t4.y; pv[EPL - 2] = t4.z; pv[EPL - 1] = t4.w;
+                } else {
+                    const float2 t2 = __ldcg(reinterpret_cast<const float2*>(src));
+                    pv[0] = t2.x; pv[1] = t2.y;
+                }
+                const float f = f_s[h * ns + s];
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(pv[e], f, acc[h][e]);
+            }
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxGq; ++h)
+        if (h < gq)
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
+    __syncthreads();
+#pragma unroll 1
     for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
         const int h = idx / HD, d = idx - h * HD;
-        const int head = kv_head * gq + h;
-        const float* pa = p.part_acc + (size_t)head * p.nsplit * HD + d;
-        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // independent chains: the loads of a round overlap
-        int s = 0;
-        #pragma unroll 1
-        for (; s + 4 <= ns; s += 4) {
-            const float v0 = __ldcg(pa + (size_t)s * HD), v1 = __ldcg(pa + (size_t)(s + 1) * HD);
-            const float v2 = __ldcg(pa + (size_t)(s + 2) * HD), v3 = __ldcg(pa + (size_t)(s + 3) * HD);
-            a0 = fmaf(v0, f_s[h * ns + s], a0);
-            a1 = fmaf(v1, f_s[h * ns + s + 1], a1);
-            a2 = fmaf(v2, f_s[h * ns + s + 2], a2);
-            a3 = fmaf(v3, f_s[h * ns + s + 3], a3);
-        }
-        #pragma unroll 1
-        for (; s < ns; ++s) a0 = fmaf(__ldcg(pa + (size_t)s * HD), f_s[h * ns + s], a0);
-        p.out[(size_t)head * HD + d] = ((a0 + a1) + (a2 + a3)) / l_s[h];
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
+        p.out[(size_t)(kv_head * gq + h) * HD + d] = v / l_s[h];
     }
     if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
 }
@@ -502,9 +524,10 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
     p.out = out;
     p.k_new = k_new; p.v_new = v_new; p.freqs = freqs; p.k_cache_w = k_cache_w; p.v_cache_w = v_cache_w;
-    size_t smem = ((size_t)2 * kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile + (size_t)kMaxGq * 4) * sizeof(float);
-    const size_t red_bytes = (size_t)kAttnWarps * gq * head_dim * sizeof(float);
-    if (red_bytes > (size_t)2 * kAttnTile * head_dim * sizeof(float)) smem += red_bytes;  // never for gq <= 8
+    // K tile (padded rows), V tile, scores, statistics, query heads; the cross-warp reduction reuses the V tile
+    // (kAttnWarps * gq <= kAttnTile rows because gq <= kMaxGq)
+    const size_t smem = ((size_t)kAttnTile * (head_dim + 16) + (size_t)kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile +
+                         (size_t)kMaxGq * 4 + (size_t)kMaxGq * head_dim) * sizeof(float);
     cudaError_t e;
     if (head_dim == 128) {
         static thread_local bool cfg = false;
