@@ -114,8 +114,19 @@ __device__ inline uint4 ld_stream_u4(const void* ptr) {
 // Programmatic dependent launch: a kernel launched with the programmatic-stream-serialisation
 // attribute may start before its predecessor has finished; everything that reads the
 // predecessor's output must come after pdl_wait().  Both are no-ops for a normal launch.
-__device__ inline void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+//
+// pdl_wait() also releases this kernel's own dependents at once: they are scheduled as soon as
+// multiprocessors become free (while this grid is still in its tail), run the part of their code
+// that needs no input - above all the first weight loads - and then block in their own wait until
+// this grid has completed.  Because every kernel releases its dependents only AFTER its own wait has
+// returned, a kernel can only start once everything up to its predecessor's predecessor has
+// completed; code placed before pdl_wait() may therefore read constants and data written two or more
+// launches earlier, nothing else.
 __device__ inline void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ inline void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_launch_dependents();
+}
 
 inline cudaStream_t as_stream(kmll_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 

@@ -606,23 +606,20 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     const int K = lp.K, M = lp.M;
     // digit rows: 16-byte reads of two rows (lanes g, g+1) must fall into different banks
     sp.xs_pitch = K + (FMT == FMT_W4 ? 16 : 64);
-    const int ngr = K / 128;
     auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
-    const size_t xs_bytes = up128((size_t)4 * M * sp.xs_pitch);
-    const size_t xsum_bytes = FMT == FMT_W4 ? up128((size_t)2 * M * ngr * sizeof(int)) : 0;
-    const size_t red_bytes = up128((size_t)kRedBufs * kSWarps * ROWS * M * sizeof(float));
+    const size_t xs_bytes = up128((size_t)4 * M * sp.xs_pitch + 16);  // digit rows + 16 zero bytes (absent MMA columns)
+    const size_t red_bytes = up128((size_t)kRedBufs * (kSWarps + 2) * ROWS * M * sizeof(float));  // partials + epilogue operands
     const size_t bars_bytes = 128;
     const size_t misc_bytes = 1024;
     const size_t ring_bytes = (size_t)8 * 2 * kSThreads * 16;  // 8 tile halves in flight per lane (128 KB)
     const size_t sring_bytes = FMT == FMT_W4 ? (size_t)8 * 2 * kSWarps * 32 : 0;  // scale words of the tiles in flight
-    const size_t smem = xs_bytes + xsum_bytes + red_bytes + bars_bytes + misc_bytes + ring_bytes + sring_bytes;
+    const size_t smem = xs_bytes + red_bytes + bars_bytes + misc_bytes + ring_bytes + sring_bytes;
     if (smem > 226 * 1024) return KMLL_OK;  // *launched stays false
     // the activation staging keeps x in registers (M*K <= 24576) and reads it with 16-byte loads
     if ((size_t)M * K > (size_t)kStageBlocks * 8 * kSThreads || (lp.ldx & 3) != 0 ||
         (reinterpret_cast<uintptr_t>(lp.x) & 15) != 0 || (lp.norm_w != nullptr && (reinterpret_cast<uintptr_t>(lp.norm_w) & 15) != 0))
         return KMLL_OK;
-    sp.off_xsum = (int)xs_bytes;
-    sp.off_red = sp.off_xsum + (int)xsum_bytes;
+    sp.off_red = (int)xs_bytes;
     sp.off_bars = sp.off_red + (int)red_bytes;
     sp.off_misc = sp.off_bars + (int)bars_bytes;
     sp.off_ring = sp.off_misc + (int)misc_bytes;

@@ -42,7 +42,7 @@ struct StreamParams {
     int unit_start[4];
     int total_units;
     int xs_pitch;   // bytes per staged digit row of the activations
-    int off_xsum, off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
+    int off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
     uint32_t* partial_tokens;
     float* partial_logits;
 };
@@ -79,8 +79,10 @@ __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const unsigned long long t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < 32; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(64);  // leave the issue slots to the warps that share the scheduler
+        }
         if (global_timer_ns() - t0 > kWaitLimitNs) return false;
     }
 }
@@ -109,13 +111,19 @@ __device__ inline void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// first MMA of a group: the accumulator input is the zero register, so nothing has to be cleared
+__device__ inline void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // Stages x (M <= 4 rows of K) into shared memory as four int8 digit rows per batch row
-// (row 4*m + j holds digit 3-j, most significant first) and, for W4, the per-group offset terms.
-// W4 order inside each 8-column block: even columns first ([0,2,4,6,1,3,5,7]), because
-// `w & 0x0f0f0f0f` yields the even nibbles of a weight word as four bytes and
-// `(w >> 4) & 0x0f0f0f0f` the odd ones; I8: natural order.
-// xcomb[group][2*m + p] = 8 * (128 * sum(d_{3-2p}) + sum(d_{2-2p})) over the group's 128 columns: what
-// the +8 offset of the stored nibbles adds to the combined digit pair p of batch row m.
+// (row 4*m + j holds digit 3-j, most significant first).
+// W4 order inside each 8-column block: even columns first ([0,2,4,6,1,3,5,7]), because the low nibbles
+// of a weight word (the even columns) become one MMA operand register and the high nibbles another;
+// I8: natural order.
 // Returns 2^-sh.  One pass: each thread keeps its (at most kStageBlocks) 8-column blocks of x in
 // registers between the block-wide reduction and the conversion.  SINGLE fixes M = 1 at compile time.
 //
@@ -145,7 +153,7 @@ __device__ inline void transpose_bytes(uint32_t a, uint32_t b, uint32_t c, uint3
     rows[3] = __byte_perm(t2, t3, 0x7632);
 }
 template <int FMT, bool SINGLE>
-__device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int* xcomb, float* misc) {
+__device__ inline float stage_activations(const StreamParams& p, int8_t* xs, float* misc) {
     constexpr int NM = SINGLE ? 1 : 4;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int M = SINGLE ? 1 : p.M, K = p.K;
@@ -155,46 +163,45 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int
     uint4 nw[kStageBlocks];  // bf16 RMSNorm weights of the block
 #pragma unroll
     for (int j = 0; j < kStageBlocks; ++j) {  // every load is issued before anything is consumed
-        const int blk = j * kSThreads + tid;
-        const int e = (blk < nblk ? blk : 0) << 3;
-        const int m = SINGLE ? 0 : e / K;
-        const int k = e - m * K;
-        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b = a;
-        nw[j] = make_uint4(0, 0, 0, 0);
         if (j * kSThreads + warp * 32 < nblk) {  // warp-uniform; lanes past the end re-read block 0 and are masked later
+            const int blk = j * kSThreads + tid;
+            const int e = (blk < nblk ? blk : 0) << 3;
+            const int m = SINGLE ? 0 : e / K;
+            const int k = e - m * K;
             const float4* src = reinterpret_cast<const float4*>(p.x + (size_t)m * p.ldx + k);
-            a = src[0];
-            b = src[1];
+            const float4 a = src[0], b = src[1];
             if (norm) nw[j] = *reinterpret_cast<const uint4*>(p.norm_w + k);
+            v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+            v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
         }
-        v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
-        v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
     }
     float ss[NM], mx[NM];
 #pragma unroll
     for (int mm = 0; mm < NM; ++mm) ss[mm] = mx[mm] = 0.0f;
 #pragma unroll
     for (int j = 0; j < kStageBlocks; ++j) {
-        const int blk = j * kSThreads + tid;
-        const bool active = blk < nblk;
-        const int m = SINGLE ? 0 : ((active ? blk : 0) << 3) / K;
-        float s_ = 0.0f, m_ = 0.0f;
-        if (norm) {
-            const uint32_t ww[4] = {nw[j].x, nw[j].y, nw[j].z, nw[j].w};
+        if (j * kSThreads + warp * 32 < nblk) {  // warp-uniform: blocks that do not exist cost nothing
+            const int blk = j * kSThreads + tid;
+            const bool active = blk < nblk;
+            const int m = SINGLE ? 0 : ((active ? blk : 0) << 3) / K;
+            float s_ = 0.0f, m_ = 0.0f;
+            if (norm) {
+                const uint32_t ww[4] = {nw[j].x, nw[j].y, nw[j].z, nw[j].w};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                s_ += v[j][2 * q] * v[j][2 * q] + v[j][2 * q + 1] * v[j][2 * q + 1];
-                m_ = fmaxf(m_, fmaxf(fabsf(v[j][2 * q] * __uint_as_float(ww[q] << 16)),
-                                     fabsf(v[j][2 * q + 1] * __uint_as_float(ww[q] & 0xffff0000u))));
+                for (int q = 0; q < 4; ++q) {
+                    s_ += v[j][2 * q] * v[j][2 * q] + v[j][2 * q + 1] * v[j][2 * q + 1];
+                    m_ = fmaxf(m_, fmaxf(fabsf(v[j][2 * q] * __uint_as_float(ww[q] << 16)),
+                                         fabsf(v[j][2 * q + 1] * __uint_as_float(ww[q] & 0xffff0000u))));
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) m_ = fmaxf(m_, fabsf(v[j][q]));
             }
-        } else {
+            if (!active) s_ = m_ = 0.0f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) m_ = fmaxf(m_, fabsf(v[j][q]));
+            for (int mm = 0; mm < NM; ++mm)
+                if (SINGLE || m == mm) { ss[mm] += s_; mx[mm] = fmaxf(mx[mm], m_); }
         }
-        if (!active) s_ = m_ = 0.0f;
-#pragma unroll
-        for (int mm = 0; mm < NM; ++mm)
-            if (SINGLE || m == mm) { ss[mm] += s_; mx[mm] = fmaxf(mx[mm], m_); }
     }
 #pragma unroll
     for (int mm = 0; mm < NM; ++mm) {
@@ -285,23 +292,8 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, int
             for (int r = 0; r < 4; ++r)
                 *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + 3 - r) * p.xs_pitch + k) = make_uint2(r0[r], r1[r]);
         }
-        if (FMT == FMT_W4) {
-            int dsum[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) dsum[r] = __dp4a((int)r1[r], 0x01010101, __dp4a((int)r0[r], 0x01010101, 0));
-            // the 16 threads that hold one 128-column group are 16 consecutive lanes
-            int c01 = 128 * dsum[3] + dsum[2], c23 = 128 * dsum[1] + dsum[0];
-#pragma unroll
-            for (int off = 1; off < 16; off <<= 1) {
-                c01 += __shfl_xor_sync(0xffffffffu, c01, off);
-                c23 += __shfl_xor_sync(0xffffffffu, c23, off);
-            }
-            if (active && (lane & 15) == 0) {
-                xcomb[(k >> 7) * (2 * M) + 2 * m] = 8 * c01;
-                xcomb[(k >> 7) * (2 * M) + 2 * m + 1] = 8 * c23;
-            }
-        }
     }
+    if (tid < 4) reinterpret_cast<uint32_t*>(xs + (size_t)4 * M * p.xs_pitch)[tid] = 0u;  // what absent MMA columns read
     consumer_bar_sync();
     return inv_xscale;
 }
@@ -326,14 +318,13 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
     const int ngr = K >> 7;  // W4 groups per row
 
     int8_t* xs = reinterpret_cast<int8_t*>(smem);                       // [4*M][xs_pitch] digit rows
-    int* xcomb = reinterpret_cast<int*>(smem + p.off_xsum);             // [ngr][2*M] W4 offset terms of the digit pairs
-    float* red = reinterpret_cast<float*>(smem + p.off_red);            // [kRedBufs][kSWarps][ROWS][M]
-    uint64_t* ubar = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [kRedBufs] all warps wrote their partials
-    uint64_t* done = ubar + kRedBufs;                                   // [kRedBufs] the finishing warp consumed them
+    float* red = reinterpret_cast<float*>(smem + p.off_red);            // [kRedBufs][kSWarps + 2][ROWS][M]
+    uint64_t* done = reinterpret_cast<uint64_t*>(smem + p.off_bars);    // [kRedBufs] the finishing warp consumed the partials
+    unsigned int* cnt = reinterpret_cast<unsigned int*>(done + kRedBufs);  // [kRedBufs] warps that delivered their partials
     float* misc = reinterpret_cast<float*>(smem + p.off_misc);
 
     if (tid == 0) {
-        for (int b = 0; b < kRedBufs; ++b) { mbar_init(&ubar[b], kSWarps); mbar_init(&done[b], 1); }
+        for (int b = 0; b < kRedBufs; ++b) { mbar_init(&done[b], 1); cnt[b] = 0u; }
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
@@ -408,26 +399,21 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     // ---- stage the activations once -----------------------------------------------------------------
     pdl_wait();
-    const float inv_xscale = stage_activations<FMT, kSingle>(p, xs, xcomb, misc);
+    const float inv_xscale = stage_activations<FMT, kSingle>(p, xs, misc);
 
-    // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns
-    bool bvalid[NT];
+    // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns.  A lane whose
+    // column does not exist reads the 16 zero bytes behind the digit rows with stride 0 (no select in the loop).
     const int8_t* xcol[NT];
+    int bstride[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        bvalid[nt] = (nt * 8 + g) < 4 * M;
-        xcol[nt] = xs + (size_t)(bvalid[nt] ? nt * 8 + g : 0) * xs_pitch;
+        const bool bvalid = (nt * 8 + g) < 4 * M;
+        xcol[nt] = bvalid ? xs + (size_t)(nt * 8 + g) * xs_pitch : xs + (size_t)4 * M * xs_pitch;
+        bstride[nt] = bvalid ? 1 : 0;
     }
     // this lane's C columns 2t, 2t+1 of each n-tile: digits (3,2) of a batch row for even t, (1,0) for
     // odd t; the pair is combined as 128*c[2t] + c[2t+1] and weighted by 128^2 resp. 1
     const float w_pair = ((t & 1) ? 1.0f : 16384.0f) * inv_xscale;
-    bool cvalid[NT];
-    const int* xcp[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        cvalid[nt] = (nt * 8 + 2 * t) < 4 * M;
-        xcp[nt] = xcomb + (cvalid[nt] ? nt * 4 + t : 0);
-    }
 
     float best_logit = -INFINITY;  // EPI_TOP1 running best (warp 0)
     uint32_t best_token = 0xffffffffu;
@@ -460,44 +446,46 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
             uint4 bq[NT][2];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                bq[nt][0] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32) : make_uint4(0, 0, 0, 0);
-                bq[nt][1] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 128 + t * 32 + 16) : make_uint4(0, 0, 0, 0);
+                const int8_t* bp = xcol[nt] + (sg * 128 + t * 32) * bstride[nt];
+                bq[nt][0] = *reinterpret_cast<const uint4*>(bp);
+                bq[nt][1] = *reinterpret_cast<const uint4*>(bp + 16 * bstride[nt]);
             }
+            const int spar = (sg & 1) * 2;  // byte offset of this group's binary16 scale inside the copied word
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t wlo[4] = {w[mt][0].x, w[mt][0].y, w[mt][0].z, w[mt][0].w};
                 const uint32_t whi[4] = {w[mt][1].x, w[mt][1].y, w[mt][1].z, w[mt][1].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    // word i: even nibbles -> a0/a1, odd nibbles -> a2/a3 (values 1..15, offset removed below)
-                    const uint32_t a0 = wlo[i] & 0x0f0f0f0fu, a2 = (wlo[i] >> 4) & 0x0f0f0f0fu;
-                    const uint32_t a1 = whi[i] & 0x0f0f0f0fu, a3 = (whi[i] >> 4) & 0x0f0f0f0fu;
+                    // a stored nibble n = q + 8 moved to the top of a byte and its top bit flipped is the int8
+                    // value 16*q: word i gives the even columns (a0/a1) from the low nibbles and the odd columns
+                    // (a2/a3) from the high nibbles; the factor 16 is shifted out of the group sum below
+                    const uint32_t a0 = ((wlo[i] << 4) & 0xf0f0f0f0u) ^ 0x80808080u, a2 = (wlo[i] & 0xf0f0f0f0u) ^ 0x80808080u;
+                    const uint32_t a1 = ((whi[i] << 4) & 0xf0f0f0f0u) ^ 0x80808080u, a3 = (whi[i] & 0xf0f0f0f0u) ^ 0x80808080u;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         const uint4 b = bq[nt][i >> 1];
-                        mma_s8(c[mt][nt], a0, a1, a2, a3, (i & 1) ? b.z : b.x, (i & 1) ? b.w : b.y);
+                        if (i == 0) mma_s8_first(c[mt][nt], a0, a1, a2, a3, b.x, b.y);
+                        else mma_s8(c[mt][nt], a0, a1, a2, a3, (i & 1) ? b.z : b.x, (i & 1) ? b.w : b.y);
                     }
                 }
-                // the aligned word holds scales of groups (2i, 2i+1) of the row: pick by the parity of row*ngr + sg
-                const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(sring + (size_t)((slot * MT + mt) * 2) * kSPlane);
-                const uint32_t sw1 = *reinterpret_cast<const uint32_t*>(sring + (size_t)((slot * MT + mt) * 2 + 1) * kSPlane);
-                const int par0 = ((c_par >> (mt * 2)) ^ sg) & 1, par1 = ((c_par >> (mt * 2 + 1)) ^ sg) & 1;
-                const float gs0 = __half2float(__ushort_as_half((unsigned short)(par0 ? sw0 >> 16 : sw0 & 0xffffu)));
-                const float gs1 = __half2float(__ushort_as_half((unsigned short)(par1 ? sw1 >> 16 : sw1 & 0xffffu)));
+                // the copied word holds the scales of groups (2i, 2i+1) of the row: pick by the parity of row*ngr + sg
+                const int o0 = (ngr & 1) ? ((((c_par >> (mt * 2)) ^ sg) & 1) * 2) : spar;
+                const int o1 = (ngr & 1) ? ((((c_par >> (mt * 2 + 1)) ^ sg) & 1) * 2) : spar;
+                const float gs0 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sring + (size_t)((slot * MT + mt) * 2) * kSPlane + o0)));
+                const float gs1 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sring + (size_t)((slot * MT + mt) * 2 + 1) * kSPlane + o1)));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    // sum (n - 8) * d = sum n*d - 8 * sum d for the digit pair (all exact, |.| < 2^24), then the group scale
-                    const int off = cvalid[nt] ? xcp[nt][sg * (2 * M)] : 0;
-                    acc[mt][nt][0] = fmaf((float)(c[mt][nt][0] * 128 + c[mt][nt][1] - off), gs0, acc[mt][nt][0]);
-                    acc[mt][nt][1] = fmaf((float)(c[mt][nt][2] * 128 + c[mt][nt][3] - off), gs1, acc[mt][nt][1]);
-                    c[mt][nt][0] = c[mt][nt][1] = c[mt][nt][2] = c[mt][nt][3] = 0;
+                    // combined digit pair (a multiple of 16, |.| < 2^27; after the exact shift < 2^23), then the group scale
+                    acc[mt][nt][0] = fmaf((float)((c[mt][nt][0] * 128 + c[mt][nt][1]) >> 4), gs0, acc[mt][nt][0]);
+                    acc[mt][nt][1] = fmaf((float)((c[mt][nt][2] * 128 + c[mt][nt][3]) >> 4), gs1, acc[mt][nt][1]);
                 }
             }
         } else {
             uint4 bq[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
-                bq[nt] = bvalid[nt] ? *reinterpret_cast<const uint4*>(xcol[nt] + sg * 64 + t * 16) : make_uint4(0, 0, 0, 0);
+                bq[nt] = *reinterpret_cast<const uint4*>(xcol[nt] + (sg * 64 + t * 16) * bstride[nt]);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -541,7 +529,9 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         const uint32_t bpar = (uint32_t)(it / kRedBufs) & 1u;
         // this buffer was last used kRedBufs units ago: wait until that unit has been finished
         if (it >= kRedBufs && !mbar_wait(&done[buf], bpar ^ 1u)) { ok = false; return; }
-        float* rp = red + ((size_t)buf * kSWarps + warp) * ROWS * M;
+        float* ub = red + (size_t)buf * (kSWarps + 2) * ROWS * M;  // 16 partial blocks, then the epilogue operands
+        float* rp = ub + (size_t)warp * ROWS * M;
+        float* ex = ub + (size_t)kSWarps * ROWS * M;  // [RU][M] residual, then (RS-I8) [RU] row scales (x2 for gate/up)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -562,14 +552,38 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                     rp[(mt * 16 + g + 8) * M + b] = v1;
                 }
             }
+        if ((it % kSWarps) == warp) {  // this warp fetched the epilogue operands when the unit started
+#pragma unroll
+            for (int q = 0; q < (RU + 31) / 32; ++q) {
+                const int r = lane + q * 32;
+                if (r < RU) {
+                    if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m)
+                            if (m < M) ex[r * M + m] = pre_res[q * 4 + m];
+                    }
+                    if (FMT == FMT_I8) {
+                        ex[ROWS * M + r] = pre_s0[q];
+                        if (EPI == EPI_SILU) ex[ROWS * M + RU + r] = pre_s1[q];
+                    }
+                }
+            }
+        }
         reset_acc();
+        // The warp that delivers LAST finishes the unit: nobody waits (a spinning warp would take issue slots from
+        // the three warps that share its scheduler); the sum runs over the warps in index order whoever does it.
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ubar[buf]);
-        if ((it % kSWarps) != warp) return;
-        if (!mbar_wait(&ubar[buf], bpar)) { ok = false; return; }
+        unsigned int prev = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            prev = atomicAdd(&cnt[buf], 1u);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev != kSWarps - 1) return;
+        __threadfence_block();
+        if (lane == 0) cnt[buf] = 0u;  // the buffer is handed out again only after `done` below
         int mi, row0;
         unit_rows(unit, mi, row0);
-        const float* rb = red + (size_t)buf * kSWarps * ROWS * M;
         const LinearMat& om = p.mat[(EPI == EPI_SILU) ? 0 : mi];
         float cand = -INFINITY;
         uint32_t cand_tok = 0xffffffffu;
@@ -581,19 +595,19 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                 for (int m = 0; m < M; ++m) {
                     float v = 0.0f;
 #pragma unroll
-                    for (int w = 0; w < kSWarps; ++w) v += rb[((size_t)w * ROWS + r) * M + m];
-                    if (FMT == FMT_I8) v *= pre_s0[q];
+                    for (int w = 0; w < kSWarps; ++w) v += ub[((size_t)w * ROWS + r) * M + m];
+                    if (FMT == FMT_I8) v *= ex[ROWS * M + r];
                     if (EPI == EPI_SILU) {
                         float u = 0.0f;
 #pragma unroll
-                        for (int w = 0; w < kSWarps; ++w) u += rb[((size_t)w * ROWS + 16 + r) * M + m];
-                        if (FMT == FMT_I8) u *= pre_s1[q];
+                        for (int w = 0; w < kSWarps; ++w) u += ub[((size_t)w * ROWS + 16 + r) * M + m];
+                        if (FMT == FMT_I8) u *= ex[ROWS * M + RU + r];
                         v = (v / (1.0f + expf(-v))) * u;
                     }
                     if (EPI == EPI_TOP1) {
                         if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
                     } else if (row < om.rows) {
-                        if (EPI == EPI_RESIDUAL) v = pre_res[q * 4 + (m & 3)] + v;
+                        if (EPI == EPI_RESIDUAL) v = ex[r * M + m] + v;
                         om.out[(size_t)m * om.ldo + row] = v;
                     }
                 }
