@@ -106,7 +106,7 @@ __device__ inline void consumer_bar_sync() { __syncthreads(); }
 
 __device__ inline void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -114,43 +114,34 @@ __device__ inline void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2
 // first MMA of a group: the accumulator input is the zero register, so nothing has to be cleared
 __device__ inline void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// Stages x (M <= 4 rows of K) into shared memory as four int8 digit rows per batch row
-// (row 4*m + j holds digit 3-j, most significant first).
+// Stages x (M <= 4 rows of K) into shared memory as four byte rows per batch row: row 4*m + j holds the
+// MMA B column j of batch row m (u0, u1, top, ones - see below).
 // W4 order inside each 8-column block: even columns first ([0,2,4,6,1,3,5,7]), because the low nibbles
 // of a weight word (the even columns) become one MMA operand register and the high nibbles another;
 // I8: natural order.
 // Returns 2^-sh.  One pass: each thread keeps its (at most kStageBlocks) 8-column blocks of x in
 // registers between the block-wide reduction and the conversion.  SINGLE fixes M = 1 at compile time.
 //
-// Digits: X = round(x * 2^sh) with |X| <= 2^26.  Y = X + 64*(1 + 128 + 128^2 + 128^3) lies in [0, 2^28), its
-// four 7-bit fields u_j are spread to the four bytes of a word, and d_j = u_j - 64 in [-64, 63] gives
-// X = sum d_j * 128^j.  All of it is plain logic / integer arithmetic on whole words.
+// Digits: X = round(x * 2^sh) with |X| < 2^22, obtained with ONE fused multiply-add: x * 2^sh + 1.5 * 2^23
+// is a float in [2^23, 2^24) whose 23 mantissa bits hold 2^22 + X.  Its bytes are the digits as they lie:
+// byte 0 = u0, byte 1 = u1 (unsigned base-256 digits), byte 2 = 64 + (X >> 16) ("top"), so
+//   X = u0 + 256 * u1 + 65536 * (top - 64).
+// The MMA takes the bytes as UNSIGNED operands; a fourth column of ones yields sum(w) per weight row, which
+// removes the offset of the top digit: sum(w * X) = c0 + 256 * c1 + 65536 * (c2 - 64 * c_ones), all integers.
 constexpr int kStageBlocks = 6;  // M*K <= 6*8*512 = 24576
-constexpr uint32_t kDigitBias = 64u * (1u + 128u + 16384u + 2097152u);
-__device__ inline uint32_t digit_word(float f) {
-    f = fminf(fmaxf(f, -67108864.0f), 67108864.0f);  // inf/huge inputs saturate instead of wrapping
-    const uint32_t y = (uint32_t)__float2int_rn(f) + kDigitBias;
-    uint32_t lo = y & 0x3fffu, hi = y >> 14;
-    lo += lo & 0x3f80u;  // u0 | u1 << 8
-    hi += hi & 0x3f80u;  // u2 | u3 << 8
-    const uint32_t u = __byte_perm(lo, hi, 0x5410);
-    // per byte u - 64: flip bit 6, then copy the new bit 6 into bit 7 (sign extension of a 7-bit value)
-    const uint32_t t = ~u & 0x40404040u;
-    return (u ^ 0x40404040u) + t * 2u;
-}
-// rows[r] = byte r of (a, b, c, d)
-__device__ inline void transpose_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&rows)[4]) {
+constexpr float kDigitMagic = 12582912.0f;  // 1.5 * 2^23
+// rows[r] = byte r of (a, b, c, d), r = 0..2
+__device__ inline void transpose_bytes3(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&rows)[3]) {
     const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
     const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
     rows[0] = __byte_perm(t0, t1, 0x5410);
     rows[1] = __byte_perm(t0, t1, 0x7632);
     rows[2] = __byte_perm(t2, t3, 0x5410);
-    rows[3] = __byte_perm(t2, t3, 0x7632);
 }
 template <int FMT, bool SINGLE>
 __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, float* misc) {
@@ -235,11 +226,13 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, flo
             amax = fmaxf(amax, m_ * inv[mm]);
         }
     }
-    // power-of-two scale: |x * 2^sh| < 2^26 for every element
-    float xscale = 1.0f, inv_xscale = 1.0f;
+    // power-of-two scale: |x * 2^sh| < 2^22 for every element (the margin covers the few ulps by which the
+    // product recomputed below may exceed the maximum found above).  A non-finite maximum gives all-zero digits.
+    float xscale = 0.0f, inv_xscale = 1.0f;
+    amax *= 1.00001f;
     if (amax > 0.0f && amax < INFINITY) {
         const int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;  // floor(log2(amax)) (denormals: -127)
-        int sh = 25 - e;
+        int sh = 21 - e;
         sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
         xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
         inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
@@ -278,19 +271,20 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, flo
         }
         uint32_t d[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) d[q] = digit_word(u[q] * xscale);
-        uint32_t r0[4], r1[4];  // digit j of the block's first / second word (j = 0 least significant)
+        for (int q = 0; q < 8; ++q) d[q] = __float_as_uint(fmaf(u[q], xscale, kDigitMagic));
+        uint32_t r0[3], r1[3];  // byte j of the block's first / second word of four elements
         if (FMT == FMT_W4) {
-            transpose_bytes(d[0], d[2], d[4], d[6], r0);
-            transpose_bytes(d[1], d[3], d[5], d[7], r1);
+            transpose_bytes3(d[0], d[2], d[4], d[6], r0);
+            transpose_bytes3(d[1], d[3], d[5], d[7], r1);
         } else {
-            transpose_bytes(d[0], d[1], d[2], d[3], r0);
-            transpose_bytes(d[4], d[5], d[6], d[7], r1);
+            transpose_bytes3(d[0], d[1], d[2], d[3], r0);
+            transpose_bytes3(d[4], d[5], d[6], d[7], r1);
         }
         if (active) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + 3 - r) * p.xs_pitch + k) = make_uint2(r0[r], r1[r]);
+            for (int r = 0; r < 3; ++r)
+                *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + r) * p.xs_pitch + k) = make_uint2(r0[r], r1[r]);
+            *reinterpret_cast<uint2*>(xs + (size_t)(4 * m + 3) * p.xs_pitch + k) = make_uint2(0x01010101u, 0x01010101u);
         }
     }
     if (tid < 4) reinterpret_cast<uint32_t*>(xs + (size_t)4 * M * p.xs_pitch)[tid] = 0u;  // what absent MMA columns read
@@ -411,9 +405,10 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         xcol[nt] = bvalid ? xs + (size_t)(nt * 8 + g) * xs_pitch : xs + (size_t)4 * M * xs_pitch;
         bstride[nt] = bvalid ? 1 : 0;
     }
-    // this lane's C columns 2t, 2t+1 of each n-tile: digits (3,2) of a batch row for even t, (1,0) for
-    // odd t; the pair is combined as 128*c[2t] + c[2t+1] and weighted by 128^2 resp. 1
-    const float w_pair = ((t & 1) ? 1.0f : 16384.0f) * inv_xscale;
+    // this lane's C columns 2t, 2t+1 of each n-tile: (u0, u1) of a batch row for even t, (top, ones) for odd t.
+    // Either pair is combined as c[2t] + pair_mul * c[2t+1] (256 resp. -64) and weighted by 1 resp. 65536.
+    const int pair_mul = (t & 1) ? -64 : 256;
+    const float w_pair = ((t & 1) ? 65536.0f : 1.0f) * inv_xscale * (FMT == FMT_W4 ? 0.0625f : 1.0f);
 
     float best_logit = -INFINITY;  // EPI_TOP1 running best (warp 0)
     uint32_t best_token = 0xffffffffu;
@@ -459,7 +454,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                 for (int i = 0; i < 4; ++i) {
                     // a stored nibble n = q + 8 moved to the top of a byte and its top bit flipped is the int8
                     // value 16*q: word i gives the even columns (a0/a1) from the low nibbles and the odd columns
-                    // (a2/a3) from the high nibbles; the factor 16 is shifted out of the group sum below
+                    // (a2/a3) from the high nibbles; the factor 16 leaves with the final scale
                     const uint32_t a0 = ((wlo[i] << 4) & 0xf0f0f0f0u) ^ 0x80808080u, a2 = (wlo[i] & 0xf0f0f0f0u) ^ 0x80808080u;
                     const uint32_t a1 = ((whi[i] << 4) & 0xf0f0f0f0u) ^ 0x80808080u, a3 = (whi[i] & 0xf0f0f0f0u) ^ 0x80808080u;
 #pragma unroll
@@ -476,9 +471,9 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                 const float gs1 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sring + (size_t)((slot * MT + mt) * 2 + 1) * kSPlane + o1)));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    // combined digit pair (a multiple of 16, |.| < 2^27; after the exact shift < 2^23), then the group scale
-                    acc[mt][nt][0] = fmaf((float)((c[mt][nt][0] * 128 + c[mt][nt][1]) >> 4), gs0, acc[mt][nt][0]);
-                    acc[mt][nt][1] = fmaf((float)((c[mt][nt][2] * 128 + c[mt][nt][3]) >> 4), gs1, acc[mt][nt][1]);
+                    // combined column pair (an integer below 2^30), then the group scale
+                    acc[mt][nt][0] = fmaf((float)(c[mt][nt][0] + pair_mul * c[mt][nt][1]), gs0, acc[mt][nt][0]);
+                    acc[mt][nt][1] = fmaf((float)(c[mt][nt][2] + pair_mul * c[mt][nt][3]), gs1, acc[mt][nt][1]);
                 }
             }
         } else {
@@ -541,10 +536,10 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                     v0 = acc[mt][nt][0] * w_pair;
                     v1 = acc[mt][nt][1] * w_pair;
                 } else {
-                    v0 = ((float)c[mt][nt][0] * 128.0f + (float)c[mt][nt][1]) * w_pair;
-                    v1 = ((float)c[mt][nt][2] * 128.0f + (float)c[mt][nt][3]) * w_pair;
+                    v0 = ((float)c[mt][nt][0] + (float)pair_mul * (float)c[mt][nt][1]) * w_pair;
+                    v1 = ((float)c[mt][nt][2] + (float)pair_mul * (float)c[mt][nt][3]) * w_pair;
                 }
-                v0 += __shfl_xor_sync(0xffffffffu, v0, 1);  // digits (3,2) + digits (1,0)
+                v0 += __shfl_xor_sync(0xffffffffu, v0, 1);  // low pair + top pair
                 v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
                 const int b = nt * 2 + (t >> 1);  // batch row
                 if ((t & 1) == 0 && b < M) {
