@@ -56,6 +56,15 @@ int kmll_version(void);
 int kmll_device_status(int* status_out);
 int kmll_compiled_arch(void);
 
+/* Kernel timeline (diagnostics; no counterpart in kmll).  While a device buffer is attached, every
+ * launch of the batch<=4 linear kernel and of the decode attention kernel takes the next slot of
+ * blocks*6 64-bit words in it, and thread 0 of each block writes the device clock (%globaltimer, ns)
+ * at six points: 0 entry, 1 dependency wait passed, 2 inputs staged, 3 main loop done, 4 block done,
+ * 5 unused.  Launches recorded into a CUDA graph keep their slots across replays.  Attach a null
+ * buffer to stop.  kernel_id: 100 + 10*format + epilogue for the linear kernel, 200 for attention. */
+int kmll_trace_attach(void* device_buffer, size_t bytes);
+int kmll_trace_launches(int* kernel_ids, int* blocks, size_t* offset_words, int max_launches, int* count_out);
+
 /* ------------------------------------------------------------------------------------------
  * Quantization (device-side restatement of the host quantizer; bit-exact with it)
  * ---------------------------------------------------------------------------------------- */

@@ -82,6 +82,7 @@ struct DecodeAttnParams {
     const float* freqs;   // [head_dim / 2]
     float* k_cache_w;
     float* v_cache_w;
+    unsigned long long* trace;  // timeline slot of this launch, or null
 };
 
 // Half-split RoPE of a head slice held 4 (or 2) consecutive dims per lane: the partner dim d +- HD/2 lives
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     __shared__ bool is_last;
     __shared__ float2 cs_sn[HD / 2];  // fused form: (cos, sin) of the rotation angles of this position
 
+    trace_stamp(p.trace, 0);
     const int kv_head = blockIdx.x, split = blockIdx.y, gq = p.gq;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t kv_stride = (size_t)p.n_kv_heads * HD;
@@ -169,6 +171,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         if (n > 0) issue_tile(0, min(kAttnTile, n));
     }
     pdl_wait();
+    trace_stamp(p.trace, 1);
     if (!fused) {
         seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
         n = min(s0 + p.chunk, seq_len) - s0;
@@ -294,6 +297,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
         }
     }
+    trace_stamp(p.trace, 2);
     __syncthreads();  // the V tile is free: reuse it for the cross-warp reduction
 #pragma unroll
     for (int h = 0; h < kMaxGq; ++h)
@@ -321,6 +325,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
         }
     }
+    trace_stamp(p.trace, 3);
     if (p.nsplit == 1) return;
 
     // last block of this KV head merges the splits
@@ -397,6 +402,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         p.out[(size_t)(kv_head * gq + h) * HD + d] = v / l_s[h];
     }
     if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
+    trace_stamp(p.trace, 4);
 }
 
 // ---- prefill: tiled causal attention ---------------------------------------------------------------
@@ -524,6 +530,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
     p.out = out;
     p.k_new = k_new; p.v_new = v_new; p.freqs = freqs; p.k_cache_w = k_cache_w; p.v_cache_w = v_cache_w;
+    p.trace = trace_next_slot(200, n_kv_heads * pl.nsplit);
     // K tile (padded rows), V tile, scores, statistics, query heads; the cross-warp reduction reuses the V tile
     // (kAttnWarps * gq <= kAttnTile rows because gq <= kMaxGq)
     const size_t smem = ((size_t)kAttnTile * (head_dim + 16) + (size_t)kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile +

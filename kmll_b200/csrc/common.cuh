@@ -128,6 +128,30 @@ __device__ inline void pdl_wait() {
     pdl_launch_dependents();
 }
 
+// ---- kernel timeline (diagnostics) -------------------------------------------------------------------
+// While a trace buffer is attached (kmll_trace_attach), every launch of the linear stream kernel and of the
+// decode attention kernel is given a slot in it and thread 0 of each block stamps %globaltimer at fixed
+// points.  Slots are assigned on the host at launch time, so the launches baked into a CUDA graph keep theirs
+// and every replay overwrites the same words.  With no buffer attached the kernels get a null pointer.
+constexpr int kTraceStamps = 6;
+unsigned long long* trace_next_slot(int kernel_id, int blocks);  // host side; null when tracing is off
+__device__ inline void trace_stamp(unsigned long long* base, int stamp) {
+    if (base != nullptr && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        base[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * kTraceStamps + stamp] = t;
+    }
+}
+
+// latest time over all callers (one lane per warp calls it); the buffer must be zero before the launch
+__device__ inline void trace_stamp_latest(unsigned long long* base, int stamp) {
+    if (base != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMax(base + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * kTraceStamps + stamp, t);
+    }
+}
+
 inline cudaStream_t as_stream(kmll_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // Launch helper: optional programmatic dependent launch attribute.

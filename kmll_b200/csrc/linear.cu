@@ -642,6 +642,7 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     sp.total_units = units;
     int grid = units < num_sms() ? units : num_sms();
     if (top1_count) *top1_count = grid;
+    sp.trace = trace_next_slot(100 + FMT * 10 + EPI, grid);
 
     auto kern = linear_stream_kernel<FMT, MT, NT, EPI>;
     static thread_local bool configured = false;

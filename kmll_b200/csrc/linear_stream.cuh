@@ -45,6 +45,7 @@ struct StreamParams {
     int off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
     uint32_t* partial_tokens;
     float* partial_logits;
+    unsigned long long* trace;  // timeline slot of this launch, or null
 };
 
 __device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -300,6 +301,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
     constexpr int kDepth = 8 / MT;  // weight tiles in flight per lane: 256 B x 512 threads = 128 KB per SM
     extern __shared__ __align__(128) unsigned char smem[];
 
+    trace_stamp(p.trace, 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     constexpr bool kSingle = (NT == 1);  // one batch row, known at compile time (the decode path)
@@ -393,7 +395,9 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
 
     // ---- stage the activations once -----------------------------------------------------------------
     pdl_wait();
+    trace_stamp(p.trace, 1);
     const float inv_xscale = stage_activations<FMT, kSingle>(p, xs, misc);
+    trace_stamp(p.trace, 2);
 
     // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns.  A lane whose
     // column does not exist reads the 16 zero bytes behind the digit rows with stride 0 (no select in the loop).
@@ -660,7 +664,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         enter_unit_consumer();
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    pdl_launch_dependents();
+    trace_stamp(p.trace, 3);
     if (EPI == EPI_TOP1) {
         // every warp finished some units: merge the 16 running bests (fixed order) into one partial per block
         __syncthreads();
@@ -678,6 +682,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
             p.partial_logits[blockIdx.x] = bl;
         }
     }
+    if (lane == 0) trace_stamp_latest(p.trace, 4);
     if (!ok) atomicCAS(&g_device_status, 0, 1);
 }
 
