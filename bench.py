@@ -308,7 +308,7 @@ def run_ours(args):
     peak, peak_src = peaks()
     line = {"metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "int4 weights, s8 tensor-core MMA on exact int8 digits of f32 activations, s32/f32 accumulate",
+            "dtype": "int4 weights, s8 x u8 tensor-core MMA on the byte digits of f32 activations (23-bit fixed point), s32/f32 accumulate",
             "data": "synthetic", "config": workload_config(world), "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
                     "ms_per_step": e2e_ms / K, "api": "kmll_decoder_step_host (token from pinned host memory, packed result read back, stream sync)"},

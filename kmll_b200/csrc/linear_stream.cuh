@@ -1,27 +1,27 @@
 // Persistent streaming form of the quantized linear kernel (batch <= 4), included by linear.cu.
 //
 // One thread block (16 warps) per SM stays resident and walks over "units" of 16 (or 32) weight rows.
-// The activations are staged in shared memory ONCE per block as int8 digits (see below).  The
-// weights stream straight into registers: every lane keeps a ring of four 32-byte tiles in flight
-// with 128-bit no-allocate loads (64 KB outstanding per SM, the pattern that reads HBM at full rate
-// on this part), a warp request covering 8 rows x 64 B.  The 16 warps split the columns of a unit;
-// their partial sums meet in shared memory once per unit, in a fixed order, through two small
-// mbarriers (no block-wide barrier in the loop, so warps drift freely and loads never drain).
-// Bulk-copy (TMA) staging of the weights was measured and rejected for this kernel: issuing a
-// bulk copy blocks the issuing lane for hundreds of cycles, and routing the weights through shared
-// memory nearly saturates the shared-memory pipe that the activation digits also need.
+// The activations are staged in shared memory ONCE per block as byte digits (see stage_activations).
+// The weights stream from HBM into a shared-memory ring with 16-byte asynchronous copies; the ring is
+// private to each lane (a lane reads back exactly the bytes its own copies wrote), so
+// cp.async.wait_group is the only synchronisation, accesses are bank-conflict free and no registers
+// hold data in flight.  Eight tiles per lane are in flight: 128 KB per SM.  A warp request covers
+// 8 rows x 64 B.  The 16 warps split the columns of a unit; their partial sums meet in shared memory
+// once per unit and the warp that delivers last adds them in fixed warp order and runs the epilogue,
+// so warps drift freely, loads never drain and nobody spin-waits.
+// Bulk-copy (TMA) staging of the weights was measured and rejected for this kernel: issuing a bulk
+// copy blocks the issuing lane for hundreds of cycles.
 //
-// Arithmetic: the integer tensor-core MMA (mma.sync m16n8k32, s8 x s8 -> s32).  The activations
-// are scaled by a power of two, rounded to integers below 2^27 and split into four balanced
-// base-128 digits, each an int8: x*2^sh = d3*128^3 + d2*128^2 + d1*128 + d0.  The four digits of
-// a batch row are four of the eight MMA columns, so one MMA multiplies 16 weight rows by all
-// digits at once, exactly (int32 accumulation cannot round).  RS-I8 weights are the A operand
-// as they lie in memory - no unpack instruction at all; W4 nibbles become bytes with three
-// logic operations per eight weights, and their +8 offset is removed with a per-group sum of
-// the digits.  The only roundings are x -> 27-bit integer (at most 2^-28 of max|x|, f32 itself
-// carries 24 bits) and the final few f32 operations per output row.
-// Every wait on an mbarrier is bounded and the kernel has no other blocking wait: on time-out a
-// warp raises the device status word, stops and lets the others time out as well.
+// Arithmetic: the integer tensor-core MMA (mma.sync m16n8k32, s8 weights x u8 activation bytes -> s32).
+// x * 2^sh is rounded to an integer X below 2^22 in magnitude whose bytes (u0, u1, 64 + (X >> 16)) are
+// three of the eight MMA columns; a fourth column of ones yields the row sum of the weights, which
+// removes the offset of the top byte.  One MMA multiplies 16 weight rows by all bytes at once,
+// exactly (int32 accumulation cannot round).  RS-I8 weights are the A operand as they lie in memory -
+// no unpack instruction at all; a W4 nibble n = q + 8 becomes the int8 value 16*q with three logic
+// operations per eight weights.  The only roundings are x -> 23-bit fixed point relative to max|x|
+// and the final few f32 operations per output row.
+// The single wait on an mbarrier (reuse of a partial-sum buffer) is bounded: on time-out a warp raises
+// the device status word, stops and lets the others run out as well.
 #pragma once
 
 namespace kmll {
