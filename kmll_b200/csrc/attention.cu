@@ -127,7 +127,9 @@ __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" 
 // query heads sharing the KV head are processed together, so K and V are read once.
 // In the fused form the copies are issued BEFORE the wait on the previous kernel: rows below
 // seq_len - 1 were written by earlier steps, and the sequence length by a kernel at least two launches back.
-template <int HD>
+// GQM bounds the query heads per KV head at compile time (4 or 8): the per-head register arrays and unrolled
+// loops are sized by it.
+template <int HD, int GQM>
 __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p) {
     constexpr int EPL = HD / 32;        // elements per lane
     constexpr int V16 = HD / 4;         // 16-byte pieces per row
@@ -135,9 +137,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     extern __shared__ __align__(16) float smem[];
     float* Ks = smem;                         // [kAttnTile][KP]
     float* Vs = Ks + kAttnTile * KP;          // [kAttnTile][HD]
-    float* sc = Vs + kAttnTile * HD;          // [kMaxGq][kAttnTile] scores, then weights
-    float* hstat = sc + kMaxGq * kAttnTile;   // [kMaxGq][4]: running max, running sum, correction
-    float* qs = hstat + kMaxGq * 4;           // [kMaxGq][HD] rotated query heads
+    float* sc = Vs + kAttnTile * HD;          // [GQM][kAttnTile] scores, then weights
+    float* hstat = sc + GQM * kAttnTile;   // [GQM][4]: running max, running sum, correction
+    float* qs = hstat + GQM * 4;           // [GQM][HD] rotated query heads
     float* red = Vs;                          // [kAttnWarps][gq][HD] (reuses the V tile at the end)
     __shared__ bool is_last;
     __shared__ float2 cs_sn[HD / 2];  // fused form: (cos, sin) of the rotation angles of this position
@@ -168,8 +170,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     if (fused) {
         seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
         n = min(s0 + p.chunk, seq_len) - s0;
-        if (n > 0) issue_tile(0, min(kAttnTile, n));
+        if (n > 0) {
+            issue_tile(0, min(kAttnTile, n));
+            // rotation angles depend on the position only: one sine / cosine evaluation per pair and block, done
+            // while the copies are in flight and before the query exists (the accurate sincosf is long code)
+            if (tid < HD / 2) {
+                float sn, cs;
+                sincosf((float)(seq_len - 1) * p.freqs[tid], &sn, &cs);
+                cs_sn[tid] = make_float2(cs, sn);
+            }
+        }
     }
+    if (tid < GQM) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
     pdl_wait();
     trace_stamp(p.trace, 1);
     if (!fused) {
@@ -179,29 +191,26 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     const int nactive = (seq_len + p.chunk - 1) / p.chunk;  // splits that hold positions; the others leave at once
     if (n <= 0) return;
     const float scale = 1.0f / sqrtf((float)HD);
-    const float position = (float)(seq_len - 1);
 
-    // query heads (rotated in the fused form) go to shared memory: warp h prepares head h
-    if (fused && tid < HD / 2) {
-        // one sine / cosine evaluation per pair and block (the accurate sinf / cosf are long code)
-        const float angle = position * p.freqs[tid];
-        float sn, cs;
-        sincosf(angle, &sn, &cs);
-        cs_sn[tid] = make_float2(cs, sn);
-    }
-    if (tid < kMaxGq) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
-    float qh[EPL];
+    // Everything this block needs from the previous kernel is requested at once: the query heads (warp h loads
+    // head h) and, in the block whose slice holds the position being written, the new K and V rows (warps 6 and 7).
+    const int newpos = seq_len - 1 - s0;  // position being written, relative to this block's slice
+    const bool owns_new = fused && newpos >= 0 && newpos < n;
+    float qh[EPL], kvn[EPL];
     if (warp < gq) load_lane_slice<EPL>(p.q + (size_t)(kv_head * gq + warp) * HD + lane * EPL, qh);
-    if (fused) __syncthreads();
+    if (owns_new && warp == kAttnWarps - 2) load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kvn);
+    if (owns_new && warp == kAttnWarps - 1) load_lane_slice<EPL>(p.v_new + (size_t)kv_head * HD + lane * EPL, kvn);
+    if (fused) __syncthreads();  // cs_sn is visible
     if (warp < gq) {
         if (fused) rope_lane_slice<EPL>(qh, cs_sn, lane);
 #pragma unroll
         for (int e = 0; e < EPL; ++e) qs[warp * HD + lane * EPL + e] = qh[e];
     }
+    if (owns_new && warp == kAttnWarps - 2) rope_lane_slice<EPL>(kvn, cs_sn, lane);
 
-    float acc[kMaxGq][EPL];
+    float acc[GQM][EPL];
 #pragma unroll
-    for (int h = 0; h < kMaxGq; ++h)
+    for (int h = 0; h < GQM; ++h)
 #pragma unroll
         for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
 
@@ -212,16 +221,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         if (!(fused && t0 == 0)) issue_tile(t0, nt);
         cp_async_wait<1>();  // K has landed
         __syncthreads();
-        const int newrow = seq_len - 1 - s0 - t0;  // row of this tile that is the position being written
-        const bool has_new = fused && newrow >= 0 && newrow < nt;
-        if (has_new && warp == 0) {
-            float kn[EPL];
-            load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kn);
-            rope_lane_slice<EPL>(kn, cs_sn, lane);
+        const int newrow = newpos - t0;  // row of this tile that is the position being written
+        const bool has_new = owns_new && newrow >= 0 && newrow < nt;
+        if (has_new && warp == kAttnWarps - 2) {
 #pragma unroll
             for (int e = 0; e < EPL; ++e) {
-                Ks[newrow * KP + lane * EPL + e] = kn[e];
-                p.k_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kn[e];
+                Ks[newrow * KP + lane * EPL + e] = kvn[e];
+                p.k_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kvn[e];
             }
         }
         if (has_new) __syncthreads();
@@ -264,20 +270,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         cp_async_wait<0>();  // V has landed
         __syncthreads();
         if (has_new) {
-            if (warp == 0) {
-                float vn[EPL];
-                load_lane_slice<EPL>(p.v_new + (size_t)kv_head * HD + lane * EPL, vn);
+            if (warp == kAttnWarps - 1) {
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) {
-                    Vs[newrow * HD + lane * EPL + e] = vn[e];
-                    p.v_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = vn[e];
+                    Vs[newrow * HD + lane * EPL + e] = kvn[e];
+                    p.v_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kvn[e];
                 }
             }
             __syncthreads();
         }
         // weighted sum of V: one warp per position
 #pragma unroll
-        for (int h = 0; h < kMaxGq; ++h)
+        for (int h = 0; h < GQM; ++h)
             if (h < gq) {
                 const float corr = hstat[h * 4 + 2];
 #pragma unroll
@@ -288,7 +292,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             float vv[EPL];
             load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
 #pragma unroll
-            for (int h = 0; h < kMaxGq; ++h) {
+            for (int h = 0; h < GQM; ++h) {
                 if (h < gq) {
                     const float w = sc[h * kAttnTile + i];
 #pragma unroll
@@ -300,7 +304,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     trace_stamp(p.trace, 2);
     __syncthreads();  // the V tile is free: reuse it for the cross-warp reduction
 #pragma unroll
-    for (int h = 0; h < kMaxGq; ++h)
+    for (int h = 0; h < GQM; ++h)
         if (h < gq)
 #pragma unroll
             for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
@@ -342,8 +346,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     // then combine the partial accumulators - warp w takes splits w, w+8, ... for all heads, so every load of a
     // round is independent of the others and a handful of L2 round trips cover the whole merge
     float* ml_s = Ks;                       // [gq][nsplit][2]
-    float* f_s = Ks + 2 * kMaxGq * 64;      // [gq][nsplit] weights, then [gq] denominators after them
-    float* l_s = f_s + kMaxGq * 64;
+    float* f_s = Ks + 2 * GQM * 64;      // [gq][nsplit] weights, then [gq] denominators after them
+    float* l_s = f_s + GQM * 64;
     const int ns = nactive;  // only these splits wrote partials
 #pragma unroll 1
     for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
@@ -365,13 +369,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     }
     __syncthreads();
 #pragma unroll
-    for (int h = 0; h < kMaxGq; ++h)
+    for (int h = 0; h < GQM; ++h)
 #pragma unroll
         for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
-#pragma unroll 2
+#pragma unroll(GQM == 4 ? 4 : 2)
     for (int s = warp; s < ns; s += kAttnWarps) {
 #pragma unroll
-        for (int h = 0; h < kMaxGq; ++h)
+        for (int h = 0; h < GQM; ++h)
             if (h < gq) {
                 float pv[EPL];
                 const float* src = p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + s) * HD + lane * EPL;
@@ -388,7 +392,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
     }
 #pragma unroll
-    for (int h = 0; h < kMaxGq; ++h)
+    for (int h = 0; h < GQM; ++h)
         if (h < gq)
 #pragma unroll
             for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
@@ -536,15 +540,13 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     const size_t smem = ((size_t)kAttnTile * (head_dim + 16) + (size_t)kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile +
                          (size_t)kMaxGq * 4 + (size_t)kMaxGq * head_dim) * sizeof(float);
     cudaError_t e;
-    if (head_dim == 128) {
-        static thread_local bool cfg = false;
-        if (!cfg) { cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
-        e = launch(decode_attention_kernel<128>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnThreads), smem, stream, true, p);
-    } else {
-        static thread_local bool cfg = false;
-        if (!cfg) { cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
-        e = launch(decode_attention_kernel<64>, dim3(n_kv_heads, pl.nsplit), dim3(kAttnThreads), smem, stream, true, p);
-    }
+    auto go = [&](auto kern) {
+        // (the attribute is per kernel and per device; setting it again is cheap and keeps this re-entrant)
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        return launch(kern, dim3(n_kv_heads, pl.nsplit), dim3(kAttnThreads), smem, stream, true, p);
+    };
+    if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4>) : go(decode_attention_kernel<128, 8>);
+    else e = gq <= 4 ? go(decode_attention_kernel<64, 4>) : go(decode_attention_kernel<64, 8>);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }

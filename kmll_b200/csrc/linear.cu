@@ -690,7 +690,7 @@ template <int FMT, int EPI>
 static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) {
     if (p.M <= 4 && stream_kernel_enabled()) {
         bool launched = false;
-        constexpr int MT = (EPI == EPI_SILU || EPI == EPI_TOP1) ? 2 : 1;
+        constexpr int MT = (EPI == EPI_SILU || EPI == EPI_TOP1 || EPI == EPI_RESIDUAL) ? 2 : 1;
         const int rc = p.M == 1 ? launch_stream_variant<FMT, MT, 1, EPI>(stream, p, &launched, top1_count)
                                 : launch_stream_variant<FMT, MT, 2, EPI>(stream, p, &launched, top1_count);
         if (rc != KMLL_OK || launched) return rc;
