@@ -52,7 +52,8 @@ const char* kmll_last_error(void);
 /* Library version and the SM architecture the kernels were compiled for (100 = sm_100a). */
 int kmll_version(void);
 /* Device-side status word of the current device: 0 = ok, 1 = a bounded wait inside a kernel timed
- * out (the kernel returned early; its output is invalid).  Synchronises the device. */
+ * out (the kernel returned early; its output is invalid), 2 = a tensor-parallel peer did not deliver
+ * its part of an exchange within the wait limit.  Synchronises the device. */
 int kmll_device_status(int* status_out);
 int kmll_compiled_arch(void);
 

@@ -400,7 +400,8 @@ __global__ void prepare_incremental_dyn_kernel(const float* __restrict__ q, cons
 }
 
 __global__ void decode_begin_kernel(const uint16_t* __restrict__ table, int vocab, int dim, DecodeState* state,
-                                    uint64_t* __restrict__ history, int history_cap, float* __restrict__ hidden) {
+                                    uint64_t* __restrict__ history, int history_cap, float* __restrict__ hidden,
+                                    unsigned int* exchange_epoch) {
     pdl_wait();
     const uint64_t packed = state->next_top;
     uint32_t token = (uint32_t)(packed & 0xffffffffull);
@@ -411,6 +412,7 @@ __global__ void decode_begin_kernel(const uint16_t* __restrict__ table, int voca
         const int step = state->step;
         if (step < history_cap) history[step] = packed;
         state->seq_len = state->position + 1;
+        if (exchange_epoch != nullptr) *exchange_epoch += 1u;  // numbers the peer-memory exchanges of this step
     }
 }
 
@@ -447,9 +449,9 @@ int prepare_prefill_offset(cudaStream_t stream, const float* q, const float* k, 
 }
 
 int decode_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim, DecodeState* state, uint64_t* history,
-                 int history_cap, float* hidden) {
+                 int history_cap, float* hidden, unsigned int* exchange_epoch) {
     cudaError_t e = launch(decode_begin_kernel, dim3((dim + 255) / 256), dim3(256), 0, stream, true, table, vocab, dim, state,
-                           history, history_cap, hidden);
+                           history, history_cap, hidden, exchange_epoch);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "decode_begin: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }

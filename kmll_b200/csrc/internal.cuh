@@ -16,6 +16,42 @@ struct DecodeState {
     uint64_t next_top;   // packed (f32 bits << 32) | token of the pending token
 };
 
+// ---- tensor-parallel exchange over peer memory ------------------------------------------------------
+// Replaces the all-reduce after the row-parallel projections (wo, w2) inside the decode step.  The producing
+// kernel PUSHES its partial output vector into slot [parity][own rank] of every rank's inbox with plain 8-byte
+// stores over NVLink; each store carries one value AND the number of the exchange, so data and "ready" arrive
+// in one indivisible word and no fence, flag or completion counter is needed.  The consuming kernel (the next
+// RMSNorm + projection, which reads the vector anyway) polls the words of all ranks until they carry the
+// expected number - a bounded wait - and adds the partial vectors in rank order, so the sum is deterministic
+// and no separate reduction kernel or library collective runs.  The number of exchange i of decode step n is
+// n * 128 + i + 1 (monotonic), its parity selects one of two inbox halves.  Two halves suffice: a rank can
+// push exchange k+2 only after it consumed k+1, which every rank pushed after consuming k.
+constexpr int kMaxTp = 8;
+struct TpExchange {  // lives in device memory; entry d of each table is rank d's buffer as mapped into this process
+    int tp, rank, dim, pad;
+    uint2* inbox[kMaxTp];      // [2][tp][dim] words (value bits, exchange number)
+    uint2* top_inbox[kMaxTp];  // [2][tp][2] words (logit bits, number), (token, number): each rank's arg-max
+    unsigned int* epoch;       // local: decode steps started (decode_begin increments it)
+};
+__device__ inline uint4 ld_volatile_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ inline unsigned long long device_clock_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;  // a peer that is 2 s late is given up on
+// Arguments for the NEXT linear launch of this thread (consumed and cleared by it): push the output as exchange
+// `push_index` instead of storing it, and / or take the input vector from exchange `gather_index` (writing the
+// summed vector to x_out as well).  -1 = off.
+void set_exchange_args(const TpExchange* xc, int push_index, int gather_index, float* x_out);
+// Publishes this rank's packed arg-max to every rank (top1_reduce does it when xc is given), then
+// decode_end_gather waits for all ranks, merges (higher logit, then lower token) and advances the state.
+int decode_end_gather(cudaStream_t stream, const TpExchange* xc, DecodeState* state, uint64_t* packed_final);
+
 // attention.cu
 int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_cache, const float* v_cache,
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
@@ -34,7 +70,7 @@ int prepare_prefill_offset(cudaStream_t stream, const float* q, const float* k, 
 // hidden = embedding[state->next_top.token]; also records next_top into history[state->step] and
 // sets seq_len = position + 1.
 int decode_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim, DecodeState* state, uint64_t* history,
-                 int history_cap, float* hidden);
+                 int history_cap, float* hidden, unsigned int* exchange_epoch = nullptr);
 // state->next_top = *packed; position += 1; step += 1.
 int decode_end(cudaStream_t stream, const uint64_t* packed, DecodeState* state);
 
@@ -44,7 +80,7 @@ int widen_bf16(cudaStream_t stream, const uint16_t* src, size_t n, float* dst);
 // linear.cu: lm_head arg-max whose token ids are offset (vocabulary shards of tensor parallelism)
 int linear_top1_offset(cudaStream_t stream, int fmt, const float* x, const uint16_t* norm_w, float eps, const void* w,
                        const void* scales, int rows, int cols, uint32_t token_offset, uint32_t* partial_tokens,
-                       float* partial_logits, uint64_t* packed_out);
+                       float* partial_logits, uint64_t* packed_out, const TpExchange* xc = nullptr);
 // Deterministic merge of per-rank packed results: higher logit wins, ties -> lower token.
 int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out);
 

@@ -30,6 +30,12 @@
 #include "internal.cuh"
 
 namespace kmll {
+// 0 = ok; first failure wins: 1 = a wait inside the linear kernel timed out, 2 = a tensor-parallel peer did not
+// deliver its part of an exchange in time
+__device__ int g_device_status = 0;
+}  // namespace kmll
+
+namespace kmll {
 
 enum { FMT_I8 = 0, FMT_W4 = 1 };
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_TOP1 = 3 };
@@ -56,6 +62,9 @@ struct LinearParams {
     int block_start[4];  // first blockIdx.x of each matrix; [nmat] = grid size
     uint32_t* partial_tokens;
     float* partial_logits;
+    const TpExchange* xc;  // tensor-parallel exchange of the next launch (set_exchange_args), or null
+    int push_index, gather_index;
+    float* x_out;
 };
 
 constexpr int kWarps = 8;
@@ -526,8 +535,9 @@ __global__ void __launch_bounds__(1024) linear_i8_rowwarp_top1_kernel(const floa
 
 // Second stage of the fused arg-max: one block reduces the per-block partials
 // (argmax_pairs_f32_packed_kernel, crates/inference/src/kernels/inference.rs:1812-1878).
+constexpr unsigned int kTopExchangeIndex = 127;  // exchange number of the arg-max hand-over within a step
 __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const float* __restrict__ logits, int count,
-                                   uint32_t token_offset, uint64_t* __restrict__ packed_out) {
+                                   uint32_t token_offset, uint64_t* __restrict__ packed_out, const TpExchange* xcp) {
     pdl_wait();
     __shared__ float s_logit[32];
     __shared__ uint32_t s_tok[32];
@@ -558,8 +568,48 @@ __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const fl
             const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
             if (top1_better(ov, ot, best, tok)) { best = ov; tok = ot; }
         }
-        if (lane == 0) packed_out[0] = pack_top1(best, tok == 0xffffffffu ? tok : tok + token_offset);
+        if (lane == 0) {
+            const uint64_t packed = pack_top1(best, tok == 0xffffffffu ? tok : tok + token_offset);
+            packed_out[0] = packed;
+            if (xcp != nullptr) {  // tensor parallel: hand this rank's result to every rank (two 8-byte words)
+                const TpExchange& xc = *xcp;
+                const unsigned int epoch = *xc.epoch * 128u + kTopExchangeIndex + 1u;
+                const size_t slot = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * 2;
+                for (int dst = 0; dst < xc.tp; ++dst) {
+                    xc.top_inbox[dst][slot] = make_uint2((uint32_t)(packed >> 32), epoch);
+                    xc.top_inbox[dst][slot + 1] = make_uint2((uint32_t)(packed & 0xffffffffull), epoch);
+                }
+            }
+        }
     }
+}
+
+// Tensor-parallel end of a decode step: wait (bounded) for the packed arg-max of every rank, merge in rank order
+// (higher logit, then lower token) and advance the decode state.
+__global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* state, uint64_t* __restrict__ packed_final) {
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    const TpExchange& xc = *xcp;
+    const unsigned int epoch = *xc.epoch * 128u + kTopExchangeIndex + 1u;
+    const uint4* box = reinterpret_cast<const uint4*>(xc.top_inbox[xc.rank]) + (size_t)(epoch & 1u) * xc.tp;
+    const unsigned long long t0 = device_clock_ns();
+    float best = -INFINITY;
+    uint32_t tok = 0xffffffffu;
+    for (int r = 0; r < xc.tp; ++r) {
+        uint4 q;
+        for (;;) {
+            q = ld_volatile_u4(box + r);
+            if (q.y == epoch && q.w == epoch) break;
+            if (device_clock_ns() - t0 > kPeerWaitLimitNs) { atomicCAS(&g_device_status, 0, 2); break; }
+        }
+        const float v = __uint_as_float(q.x);
+        if (r == 0 || top1_better(v, q.z, best, tok)) { best = v; tok = q.z; }
+    }
+    const uint64_t merged = pack_top1(best, tok);
+    packed_final[0] = merged;
+    state->next_top = merged;
+    state->position += 1;
+    state->step += 1;
 }
 
 }  // namespace kmll
@@ -603,6 +653,7 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     for (int i = 0; i < 3; ++i) sp.mat[i] = lp.mat[i];
     sp.partial_tokens = lp.partial_tokens;
     sp.partial_logits = lp.partial_logits;
+    sp.xc = lp.xc; sp.push_index = lp.push_index; sp.gather_index = lp.gather_index; sp.x_out = lp.x_out;
     const int K = lp.K, M = lp.M;
     // digit rows: 16-byte reads of two rows (lanes g, g+1) must fall into different banks
     sp.xs_pitch = K + (FMT == FMT_W4 ? 16 : 64);
@@ -695,6 +746,7 @@ static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) 
                                 : launch_stream_variant<FMT, MT, 2, EPI>(stream, p, &launched, top1_count);
         if (rc != KMLL_OK || launched) return rc;
     }
+    if (p.xc != nullptr) return fail(KMLL_ERR_UNSUPPORTED, "linear: this shape cannot use the peer-memory exchange");
     if (top1_count) {
         int n = 0;
         for (int i = 0; i < p.nmat; ++i) n += (p.mat[i].rows + 31) / 32;
@@ -745,6 +797,20 @@ static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) 
 static bool fast_shape(int fmt, int K) { return fmt == FMT_W4 ? (K % 128 == 0) : (K % 64 == 0); }
 
 
+// Exchange arguments for the next linear launch of this thread (internal.cuh).
+struct ExchangeArgs {
+    const TpExchange* xc = nullptr;
+    int push_index = -1, gather_index = -1;
+    float* x_out = nullptr;
+};
+static thread_local ExchangeArgs g_exchange_args;
+void set_exchange_args(const TpExchange* xc, int push_index, int gather_index, float* x_out) {
+    g_exchange_args.xc = xc;
+    g_exchange_args.push_index = push_index;
+    g_exchange_args.gather_index = gather_index;
+    g_exchange_args.x_out = x_out;
+}
+
 struct MatArg {
     const void* w;
     const void* scales;
@@ -758,6 +824,9 @@ template <int FMT, int EPI>
 static int run_linear(const char* name, cudaStream_t stream, const float* x, int M, int K, int ldx,
                       const uint16_t* norm_w, float eps, const MatArg* mats, int nmat, int ldo_override,
                       uint32_t* partial_tokens, float* partial_logits, int* top1_count = nullptr) {
+    const ExchangeArgs xa = g_exchange_args;
+    g_exchange_args = ExchangeArgs();
+    if (xa.xc != nullptr && M != 1) return fail(KMLL_ERR_UNSUPPORTED, "%s: the peer-memory exchange needs batch 1", name);
     if (x == nullptr) return fail(KMLL_ERR_NULL, "%s: null input", name);
     if (M <= 0 || K <= 0) return fail(KMLL_ERR_SHAPE, "%s: batch=%d in_dim=%d must be positive", name, M, K);
     for (int i = 0; i < nmat; ++i) {
@@ -774,6 +843,7 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
             return fail(KMLL_ERR_UNSUPPORTED, "%s: scales must be 4-byte aligned", name);
     const bool fast = fast_shape(FMT, K) && aligned16(mats[0].w) && (nmat < 2 || aligned16(mats[1].w)) &&
                       (nmat < 3 || aligned16(mats[2].w));
+    if (!fast && xa.xc != nullptr) return fail(KMLL_ERR_UNSUPPORTED, "%s: this shape cannot use the peer-memory exchange", name);
     if (!fast) {
         if constexpr (FMT == FMT_I8 && (EPI == EPI_STORE || EPI == EPI_RESIDUAL || EPI == EPI_TOP1)) {
             if (norm_w != nullptr)
@@ -824,6 +894,10 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
         }
         p.partial_tokens = partial_tokens;
         p.partial_logits = partial_logits;
+        p.xc = xa.xc;
+        p.push_index = xa.xc ? xa.push_index : -1;
+        p.gather_index = xa.xc ? xa.gather_index : -1;
+        p.x_out = xa.x_out;
         int rc = launch_linear<FMT, EPI>(stream, p, top1_count);
         if (rc != KMLL_OK) return rc;
     }
@@ -833,7 +907,7 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
 template <int FMT>
 static int run_top1(const char* name, cudaStream_t stream, const float* x, const uint16_t* norm_w, float eps,
                     const void* w, const void* scales, int rows, int cols, uint32_t* partial_tokens,
-                    float* partial_logits, uint64_t* packed_out, uint32_t token_offset = 0) {
+                    float* partial_logits, uint64_t* packed_out, uint32_t token_offset = 0, const TpExchange* xc = nullptr) {
     if (partial_tokens == nullptr || partial_logits == nullptr || packed_out == nullptr)
         return fail(KMLL_ERR_NULL, "%s: null partial/packed buffer", name);
     MatArg m = {w, scales, rows, nullptr, nullptr};
@@ -841,7 +915,7 @@ static int run_top1(const char* name, cudaStream_t stream, const float* x, const
     int rc = run_linear<FMT, EPI_TOP1>(name, stream, x, 1, cols, cols, norm_w, eps, &m, 1, 0, partial_tokens, partial_logits, &count);
     if (rc != KMLL_OK) return rc;
     cudaError_t e = launch(top1_reduce_kernel, dim3(1), dim3(256), 0, stream, true, (const uint32_t*)partial_tokens,
-                           (const float*)partial_logits, count, token_offset, packed_out);
+                           (const float*)partial_logits, count, token_offset, packed_out, xc);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
     return KMLL_OK;
 }
@@ -863,12 +937,18 @@ __global__ void merge_packed_kernel(const uint64_t* __restrict__ packed_all, int
 
 int linear_top1_offset(cudaStream_t stream, int fmt, const float* x, const uint16_t* norm_w, float eps, const void* w,
                        const void* scales, int rows, int cols, uint32_t token_offset, uint32_t* partial_tokens,
-                       float* partial_logits, uint64_t* packed_out) {
+                       float* partial_logits, uint64_t* packed_out, const TpExchange* xc) {
     if (fmt == FMT_W4)
         return run_top1<FMT_W4>("linear_top1", stream, x, norm_w, eps, w, scales, rows, cols, partial_tokens, partial_logits,
-                                packed_out, token_offset);
+                                packed_out, token_offset, xc);
     return run_top1<FMT_I8>("linear_top1", stream, x, norm_w, eps, w, scales, rows, cols, partial_tokens, partial_logits,
-                            packed_out, token_offset);
+                            packed_out, token_offset, xc);
+}
+
+int decode_end_gather(cudaStream_t stream, const TpExchange* xc, DecodeState* state, uint64_t* packed_final) {
+    cudaError_t e = launch(decode_end_gather_kernel, dim3(1), dim3(32), 0, stream, true, xc, state, packed_final);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "decode_end_gather: %s", cudaGetErrorString(e));
+    return KMLL_OK;
 }
 
 int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out) {

@@ -30,7 +30,6 @@ constexpr int kSWarps = 16;
 constexpr int kSThreads = kSWarps * 32;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
 
-__device__ int g_device_status = 0;  // 0 = ok; first failure wins (1 = mbarrier wait timed out)
 
 struct StreamParams {
     const float* x;
@@ -46,6 +45,11 @@ struct StreamParams {
     uint32_t* partial_tokens;
     float* partial_logits;
     unsigned long long* trace;  // timeline slot of this launch, or null
+    // tensor-parallel exchange over peer memory (internal.cuh); indices < 0 = off
+    const TpExchange* xc;
+    int push_index;    // >= 0: the output vector goes to every rank's inbox instead of mat[0].out
+    int gather_index;  // >= 0: x is the rank-ordered sum of the inbox vectors of this exchange
+    float* x_out;      // gather: block 0 also writes the summed vector here (the residual stream)
 };
 
 __device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -144,6 +148,55 @@ __device__ inline void transpose_bytes3(uint32_t a, uint32_t b, uint32_t c, uint
     rows[1] = __byte_perm(t0, t1, 0x7632);
     rows[2] = __byte_perm(t2, t3, 0x5410);
 }
+// Tensor-parallel exchange, consuming side: waits (bounded) until every rank's partial vector of exchange
+// `gather_index` has arrived in this rank's inbox, adds the vectors in rank order and leaves the sum as K floats at
+// `xf` (block 0 also writes it to x_out).  Kept out of line: single-GPU launches never execute it and the decode
+// kernels are sensitive to the size of their instruction stream.
+// (scalar arguments only: a reference to the kernel parameters would force them onto the stack)
+__device__ __noinline__ void gather_exchange(const TpExchange* xcp, int gather_index, int K, float* x_out, float2* xf) {
+    const int tid = threadIdx.x;
+    const TpExchange& xc = *xcp;
+    const unsigned int epoch = *xc.epoch * 128u + (unsigned int)gather_index + 1u;
+    const int tp = xc.tp, npair = K >> 1;  // a 16-byte load = two (value, number) words
+    const uint4* gb = reinterpret_cast<const uint4*>(xc.inbox[xc.rank]) + (size_t)(epoch & 1u) * tp * npair;
+    const unsigned long long t0 = device_clock_ns();
+    bool good = true;
+#pragma unroll 1
+    for (int i0 = tid; i0 < npair; i0 += 4 * kSThreads) {
+        float2 sum[4];
+#pragma unroll 1
+        for (int r = 0; r < tp; ++r) {
+            uint4 q[4];
+            // poll until all four words of this rank carry the number of this exchange (bounded)
+            for (;;) {
+                bool all = true;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * kSThreads;
+                    q[u] = ld_volatile_u4(gb + (size_t)r * npair + (i < npair ? i : i0));
+                    all = all && q[u].y == epoch && q[u].w == epoch;
+                }
+                if (all) break;
+                if (device_clock_ns() - t0 > kPeerWaitLimitNs) { good = false; break; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float2 pv = make_float2(__uint_as_float(q[u].x), __uint_as_float(q[u].z));
+                sum[u] = (r == 0) ? pv : make_float2(sum[u].x + pv.x, sum[u].y + pv.y);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * kSThreads;
+            if (i < npair) {
+                xf[i] = sum[u];
+                if (blockIdx.x == 0 && x_out != nullptr) reinterpret_cast<float2*>(x_out)[i] = sum[u];
+            }
+        }
+    }
+    if (!good) atomicCAS(&g_device_status, 0, 2);
+}
+
 template <int FMT, bool SINGLE>
 __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, float* misc) {
     constexpr int NM = SINGLE ? 1 : 4;
@@ -153,6 +206,14 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, flo
     const bool norm = p.norm_w != nullptr;
     float v[kStageBlocks][8];
     uint4 nw[kStageBlocks];  // bf16 RMSNorm weights of the block
+    // x comes from p.x, or (tensor-parallel exchange) is the rank-ordered sum of the tp partial vectors in this
+    // rank's inbox.  The sum is formed first, as floats in the (not yet used) digit area, and read from there.
+    const float* src_base = p.x;
+    if (SINGLE && p.gather_index >= 0) {
+        gather_exchange(p.xc, p.gather_index, K, p.x_out, reinterpret_cast<float2*>(xs));
+        consumer_bar_sync();
+        src_base = reinterpret_cast<const float*>(xs);
+    }
 #pragma unroll
     for (int j = 0; j < kStageBlocks; ++j) {  // every load is issued before anything is consumed
         if (j * kSThreads + warp * 32 < nblk) {  // warp-uniform; lanes past the end re-read block 0 and are masked later
@@ -160,7 +221,7 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, flo
             const int e = (blk < nblk ? blk : 0) << 3;
             const int m = SINGLE ? 0 : e / K;
             const int k = e - m * K;
-            const float4* src = reinterpret_cast<const float4*>(p.x + (size_t)m * p.ldx + k);
+            const float4* src = reinterpret_cast<const float4*>(src_base + (size_t)m * p.ldx + k);
             const float4 a = src[0], b = src[1];
             if (norm) nw[j] = *reinterpret_cast<const uint4*>(p.norm_w + k);
             v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
@@ -607,7 +668,16 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                         if (row < om.rows) { cand = v; cand_tok = (uint32_t)row; }  // M == 1: one row per lane
                     } else if (row < om.rows) {
                         if (EPI == EPI_RESIDUAL) v = ex[r * M + m] + v;
-                        om.out[(size_t)m * om.ldo + row] = v;
+                        if (kSingle && p.push_index >= 0) {
+                            // tensor-parallel exchange: (value, exchange number) goes to every rank's inbox in one
+                            // 8-byte peer store
+                            const TpExchange& xc = *p.xc;
+                            const unsigned int epoch = *xc.epoch * 128u + (unsigned int)p.push_index + 1u;
+                            const size_t slot = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * xc.dim + row;
+                            for (int dst = 0; dst < xc.tp; ++dst) xc.inbox[dst][slot] = make_uint2(__float_as_uint(v), epoch);
+                        } else {
+                            om.out[(size_t)m * om.ldo + row] = v;
+                        }
                     }
                 }
             }

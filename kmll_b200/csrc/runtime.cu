@@ -104,6 +104,11 @@ struct Decoder {
     cudaGraphExec_t graph = nullptr;
     cudaStream_t capture_stream = nullptr;  // the caller's stream may be the legacy default stream, which cannot capture
     ncclComm_t comm = nullptr;
+    // peer-memory exchange (tensor parallel decode step); null = NCCL collectives
+    TpExchange* xc = nullptr;          // device copy of the tables
+    void* xc_local = nullptr;          // this rank's exchange buffer (shared with the peers through CUDA IPC)
+    unsigned int* xc_epoch = nullptr;  // inside xc_local
+    void* xc_peer_base[kMaxTp] = {};   // peers' buffers as mapped here (null for the own rank)
     std::vector<void*> allocs;
     size_t weight_bytes = 0, kv_bytes = 0;
     int launches_per_step = 0;
@@ -191,20 +196,32 @@ static int op_linear_batched(Decoder* d, cudaStream_t s, const float* x, const Q
 
 // Row-parallel projection followed by the residual add; under tensor parallelism rank 0 adds the
 // residual in its epilogue and the partial sums meet in an all-reduce.
-static int row_parallel_residual(Decoder* d, cudaStream_t s, const float* x, const QWeight& w, const float* residual, float* out) {
+// With push_index >= 0 the partial vector goes to every rank's inbox instead (peer-memory exchange) and the kernel
+// that consumes it does the sum.
+static int row_parallel_residual(Decoder* d, cudaStream_t s, const float* x, const QWeight& w, const float* residual, float* out,
+                                 int push_index = -1) {
+    if (push_index >= 0) set_exchange_args(d->xc, push_index, -1, nullptr);
     if (d->cfg.tp_size == 1 || d->cfg.tp_rank == 0) {
         KMLL_TRY(op_linear_residual(d, s, x, w, residual, out));
     } else {
         KMLL_TRY(op_linear(d, s, x, w, out));
     }
+    if (push_index >= 0) return KMLL_OK;
     return tp_allreduce(d, s, out, (size_t)w.rows);
 }
 
 // lm_head arg-max of `hidden` into d->packed_final (and the decode state is NOT touched).
-static int output_top1(Decoder* d, cudaStream_t s, const float* hidden) {
+// With gather_index >= 0 (peer-memory exchange) the hidden state is first summed from the ranks' partial vectors
+// (and written to `hidden_out`), and this rank's result is pushed to every rank for decode_end_gather.
+static int output_top1(Decoder* d, cudaStream_t s, const float* hidden, int gather_index = -1, float* hidden_out = nullptr) {
     const kmll_decoder_config& c = d->cfg;
     const uint32_t offset = (uint32_t)(c.tp_rank * d->vocab_l);
     uint64_t* dst = c.tp_size == 1 ? d->packed_final : d->packed;
+    if (gather_index >= 0) {
+        set_exchange_args(d->xc, -1, gather_index, hidden_out);
+        return linear_top1_offset(s, c.format, hidden, d->final_norm, c.norm_eps, d->output.w, d->output.scales, d->vocab_l, c.dim,
+                                  offset, d->part_tok, d->part_logit, dst, d->xc);
+    }
     if (c.fused) {
         KMLL_TRY(linear_top1_offset(s, c.format, hidden, d->final_norm, c.norm_eps, d->output.w, d->output.scales, d->vocab_l, c.dim,
                                     offset, d->part_tok, d->part_logit, dst));
@@ -227,14 +244,19 @@ static int output_top1(Decoder* d, cudaStream_t s, const float* hidden) {
 static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
     const kmll_decoder_config& c = d->cfg;
     const int q_len = d->n_heads_l * c.head_dim, kv_len = d->n_kv_l * c.head_dim;
+    const bool peer = d->xc != nullptr;  // tensor parallel with the peer-memory exchange (no library collective in the step)
     int n = 0;
-    KMLL_TRY(decode_begin(s, d->embedding, c.vocab_size, c.dim, d->state, d->history, d->history_cap, d->hidden_a));
+    KMLL_TRY(decode_begin(s, d->embedding, c.vocab_size, c.dim, d->state, d->history, d->history_cap, d->hidden_a,
+                          peer ? d->xc_epoch : nullptr));
     ++n;
     float* hidden = d->hidden_a;
     float* other = d->hidden_b;
     const bool w4 = c.format == KMLL_FORMAT_W4G128;
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = d->layers[l];
+        // peer exchange: the hidden state of layers > 0 is still spread over the ranks' inboxes (exchange 2l-1);
+        // the QKV kernel sums it while staging and writes it to `hidden`
+        if (peer && l > 0) set_exchange_args(d->xc, -1, 2 * l - 1, hidden);
         if (w4) {
             KMLL_TRY(kmll_rmsnorm_linear_triple_w4g128(s, hidden, L.attention_norm, c.norm_eps, (const uint8_t*)L.wq.w,
                                                        (const uint16_t*)L.wq.scales, (const uint8_t*)L.wk.w, (const uint16_t*)L.wk.scales,
@@ -245,18 +267,21 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
                                                    (const int8_t*)L.wk.w, (const float*)L.wk.scales, (const int8_t*)L.wv.w,
                                                    (const float*)L.wv.scales, q_len, kv_len, c.dim, d->q, d->k, d->v));
         }
+        ++n;
         if (c.rotary_dim == c.head_dim) {
             // RoPE of q and of the new K row and the KV-cache write happen inside the attention kernel
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache));
-            --n;
+            ++n;
         } else {
             KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache));
             KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->attn_ws, d->attn));
+            n += 2;
         }
-        KMLL_TRY(row_parallel_residual(d, s, d->attn, L.wo, hidden, d->hidden_mid));
+        KMLL_TRY(row_parallel_residual(d, s, d->attn, L.wo, hidden, d->hidden_mid, peer ? 2 * l : -1));
+        if (peer) set_exchange_args(d->xc, -1, 2 * l, d->hidden_mid);
         if (w4) {
             KMLL_TRY(kmll_rmsnorm_silu_gate_up_w4g128(s, d->hidden_mid, L.ffn_norm, c.norm_eps, (const uint8_t*)L.w1.w,
                                                       (const uint16_t*)L.w1.scales, (const uint8_t*)L.w3.w, (const uint16_t*)L.w3.scales,
@@ -265,16 +290,22 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
             KMLL_TRY(kmll_rmsnorm_silu_gate_up_i8(s, d->hidden_mid, L.ffn_norm, c.norm_eps, (const int8_t*)L.w1.w, (const float*)L.w1.scales,
                                                   (const int8_t*)L.w3.w, (const float*)L.w3.scales, d->hidden_l, c.dim, d->act));
         }
-        KMLL_TRY(row_parallel_residual(d, s, d->act, L.w2, d->hidden_mid, other));
-        n += 6 + (c.tp_size > 1 ? 2 : 0);
+        KMLL_TRY(row_parallel_residual(d, s, d->act, L.w2, d->hidden_mid, other, peer ? 2 * l + 1 : -1));
+        n += 3 + ((c.tp_size > 1 && !peer) ? 2 : 0);
         float* t = hidden;
         hidden = other;
         other = t;
     }
-    KMLL_TRY(output_top1(d, s, hidden));
-    n += 2 + (c.tp_size > 1 ? 2 : 0);
-    KMLL_TRY(decode_end(s, d->packed_final, d->state));
-    ++n;
+    if (peer) {
+        KMLL_TRY(output_top1(d, s, hidden, 2 * c.n_layers - 1, hidden));
+        KMLL_TRY(decode_end_gather(s, d->xc, d->state, d->packed_final));
+        n += 3;
+    } else {
+        KMLL_TRY(output_top1(d, s, hidden));
+        n += 2 + (c.tp_size > 1 ? 2 : 0);
+        KMLL_TRY(decode_end(s, d->packed_final, d->state));
+        ++n;
+    }
     // keep the final hidden state where kmll_decoder_last_hidden finds it
     if (hidden != d->hidden_a) {
         KMLL_CUDA(cudaMemcpyAsync(d->hidden_a, hidden, sizeof(float) * c.dim, cudaMemcpyDeviceToDevice, s));
@@ -437,6 +468,57 @@ static int tensor_ref(Decoder* d, int layer, int tensor, TensorRef* out) {
 
 using namespace kmll;
 
+// Peer-memory exchange: every rank allocates one buffer (inboxes, flags, arg-max slots, counters), the ranks
+// swap CUDA IPC handles through an NCCL all-gather and map each other's buffers.  Needs batch-1 stream kernels
+// for every exchanged vector, at most 63 layers (exchange numbers stay below 127) and tp_size <= 8.
+static int setup_peer_exchange(Decoder* d) {
+    const kmll_decoder_config& c = d->cfg;
+    const int tp = c.tp_size;
+    if (tp > kMaxTp || 2 * c.n_layers > 126 || !c.fused) return KMLL_OK;  // stay on NCCL
+    NcclApi* api = nccl_api();
+    const size_t inbox_bytes = (size_t)2 * tp * c.dim * sizeof(uint2);
+    const size_t off_top = (inbox_bytes + 127) & ~(size_t)127;
+    const size_t top_bytes = ((size_t)2 * tp * 2 * sizeof(uint2) + 127) & ~(size_t)127;
+    const size_t off_local = off_top + top_bytes;  // epoch
+    const size_t total = off_local + 256;
+    KMLL_CUDA(cudaMalloc(&d->xc_local, total));
+    KMLL_CUDA(cudaMemset(d->xc_local, 0, total));
+    cudaIpcMemHandle_t mine;
+    KMLL_CUDA(cudaIpcGetMemHandle(&mine, d->xc_local));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+    unsigned char* handles_dev = nullptr;
+    KMLL_CUDA(cudaMalloc(&handles_dev, (size_t)tp * 64));
+    KMLL_CUDA(cudaMemcpy(handles_dev + (size_t)c.tp_rank * 64, &mine, 64, cudaMemcpyHostToDevice));
+    // (in-place all-gather: the send buffer is this rank's slot of the receive buffer; it also orders every
+    // rank's memset above before anybody's first push)
+    ncclResult_t r = api->AllGather(handles_dev + (size_t)c.tp_rank * 64, handles_dev, 64, ncclChar, d->comm, nullptr);
+    if (r != ncclSuccess) { cudaFree(handles_dev); return fail(KMLL_ERR_CUDA, "ncclAllGather (IPC handles) failed"); }
+    KMLL_CUDA(cudaStreamSynchronize(nullptr));
+    std::vector<cudaIpcMemHandle_t> handles(tp);
+    KMLL_CUDA(cudaMemcpy(handles.data(), handles_dev, (size_t)tp * 64, cudaMemcpyDeviceToHost));
+    cudaFree(handles_dev);
+    TpExchange h;
+    memset(&h, 0, sizeof(h));
+    h.tp = tp; h.rank = c.tp_rank; h.dim = c.dim;
+    for (int rnk = 0; rnk < tp; ++rnk) {
+        void* base = d->xc_local;
+        if (rnk != c.tp_rank) {
+            cudaError_t e = cudaIpcOpenMemHandle(&base, handles[rnk], cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaIpcOpenMemHandle (rank %d): %s", rnk, cudaGetErrorString(e));
+            d->xc_peer_base[rnk] = base;
+        }
+        unsigned char* b = static_cast<unsigned char*>(base);
+        h.inbox[rnk] = reinterpret_cast<uint2*>(b);
+        h.top_inbox[rnk] = reinterpret_cast<uint2*>(b + off_top);
+    }
+    unsigned char* lb = static_cast<unsigned char*>(d->xc_local);
+    h.epoch = reinterpret_cast<unsigned int*>(lb + off_local);
+    d->xc_epoch = h.epoch;
+    KMLL_TRY(dalloc(d, &d->xc, 1));
+    KMLL_CUDA(cudaMemcpy(d->xc, &h, sizeof(h), cudaMemcpyHostToDevice));
+    return KMLL_OK;
+}
+
 extern "C" {
 
 int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out) {
@@ -530,6 +612,9 @@ int kmll_decoder_destroy(kmll_decoder_t dec) {
         NcclApi* api = nccl_api();
         if (api && api->CommDestroy) api->CommDestroy(d->comm);
     }
+    for (int r = 0; r < kMaxTp; ++r)
+        if (d->xc_peer_base[r]) cudaIpcCloseMemHandle(d->xc_peer_base[r]);
+    if (d->xc_local) cudaFree(d->xc_local);
     for (void* p : d->allocs) cudaFree(p);
     if (d->pinned) cudaFreeHost(d->pinned);
     delete d;
@@ -677,7 +762,9 @@ int kmll_decoder_tp_init(kmll_decoder_t dec, const unsigned char id[128]) {
     memcpy(&nid, id, 128);
     ncclResult_t r = api->CommInitRank(&d->comm, d->cfg.tp_size, nid, d->cfg.tp_rank);
     if (r != ncclSuccess) return fail(KMLL_ERR_CUDA, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
-    return KMLL_OK;
+    const char* mode = std::getenv("KMLL_TP_EXCHANGE");  // "nccl" keeps the library collectives inside the decode step
+    if (mode != nullptr && strcmp(mode, "nccl") == 0) return KMLL_OK;
+    return setup_peer_exchange(d);
 }
 
 int kmll_decoder_prefill_token_loop(kmll_decoder_t dec, kmll_stream_t stream, const uint32_t* tokens, int n_tokens) {
