@@ -1,5 +1,6 @@
 """Tensor-parallel decode on 2 GPUs must generate the same greedy tokens as the single-GPU decoder
-(weights are quantized before sharding, so the shards are slices of the same tensors)."""
+(weights are quantized before sharding, so the shards are slices of the same tensors), both with the
+peer-memory exchange inside the decode step and with the NCCL collectives."""
 import os
 import socket
 
@@ -21,11 +22,13 @@ def _cfg(rt, fmt, rank, size):
                             norm_eps=1e-6, max_seq_len=48, format=fmt, tp_rank=rank, tp_size=size)
 
 
-def _worker(rank, world, port, fmt, out):
+def _worker(rank, world, port, fmt, exchange, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["KMLL_TP_EXCHANGE"] = exchange
     os.environ["MASTER_PORT"] = str(port)
+    import ctypes as C
     import torch.distributed as dist
-    from kmll_b200 import runtime as rt
+    from kmll_b200 import lib as klib, runtime as rt
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)  # plumbing only: carries the NCCL id
     try:
@@ -39,16 +42,19 @@ def _worker(rank, world, port, fmt, out):
         tokens, logits = dec.generate_greedy(8)
         dec.prefill(prompt, token_loop=True)
         tokens2, _ = dec.generate_greedy(8)
+        status = C.c_int(-1)
+        klib.check(klib.load().kmll_device_status(C.byref(status)))
         if rank == 0:
-            out.put((tokens.tolist(), logits.tolist(), tokens2.tolist()))
+            out.put((tokens.tolist(), logits.tolist(), tokens2.tolist(), status.value, dec.launches_per_step))
         dist.barrier()
         dec.close()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
 @pytest.mark.parametrize("fmt", [0, 1])
-def test_tp2_matches_single_gpu(cuda, fmt):
+def test_tp2_matches_single_gpu(cuda, fmt, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -62,13 +68,16 @@ def test_tp2_matches_single_gpu(cuda, fmt):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, fmt, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, fmt, exchange, out)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    tokens, logits, tokens2 = out.get(timeout=10)
+    tokens, logits, tokens2, status, launches = out.get(timeout=10)
+    assert status == 0  # no bounded wait gave up
+    # 2 layers of 5 launches + begin, lm_head, arg-max reduce, end; the NCCL form adds all-reduces, a gather and a merge
+    assert launches == 14 if exchange == "peer" else launches > 14
     assert tokens == ref_tokens.tolist()
     assert tokens2 == ref_tokens.tolist()
     assert np.max(np.abs(np.array(logits) - ref_logits)) <= 1e-3 * max(1.0, float(np.max(np.abs(ref_logits))))
