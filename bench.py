@@ -257,6 +257,28 @@ def run_ours(args):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
     launches = dec.launches_per_step * K
 
+    # ---- batch 16 (one GPU): 16 sequences in lockstep share every weight read.  The prefilled sequence is adopted
+    # into all 16 slots (identical prompts: throughput does not depend on the token values) -----------------------
+    batch16 = None
+    if world == 1 and not args.no_batch16:
+        B = 16
+        steps16 = max(4, min(K, 32))
+        dec.rewind(start_pos - W)
+        bd = rt.BatchDecoder(dec, B)
+        for slot in range(B):
+            bd.adopt(slot)
+        bd.enqueue_steps(3)
+        torch.cuda.synchronize()
+        e0.record()
+        bd.enqueue_steps(steps16)
+        e1.record()
+        torch.cuda.synchronize()
+        ms16 = e0.elapsed_time(e1) / steps16
+        batch16 = {"metric": "decode_tokens_per_s_batch16_mistral7b_arch_w4g128", "value": B * 1e3 / ms16, "unit": "tokens/s", "batch": B,
+                   "steps": steps16, "ms_per_step": ms16, "launches_per_step": bd.launches_per_step,
+                   "context_at_start": start_pos - W + 3}
+        bd.close()
+
     # ---- roofline of the dominant kernel: the fused RMSNorm + gate/up + SiLU streaming kernel, timed live over
     # the 32 layers' weights (1.9 GB of distinct weights per pass) on the launching stream ----------------
     roofline = None
@@ -318,6 +340,8 @@ def run_ours(args):
             "prefill_s": prefill_s, "context_at_start": start_pos}
     if roofline is not None:
         line["roofline"] = roofline
+    if batch16 is not None:
+        line["batch16"] = batch16
     if rank == 0 and world == 1 and not args.no_cpu:
         cb = cpu_sample(8, 1)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -336,6 +360,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-batch16", action="store_true", help="skip the batch-16 leg")
     ap.add_argument("--profile", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -128,6 +128,24 @@ int kmll_decoder_launches_per_step(kmll_decoder_t dec);
 size_t kmll_decoder_weight_bytes(kmll_decoder_t dec);
 size_t kmll_decoder_kv_bytes(kmll_decoder_t dec);
 
+/* ---- lockstep batch of sequences (new; kmll decodes one sequence at a time) -------------------------
+ * Up to 16 independent sequences at the same position are decoded together so that every weight is read
+ * once per step for all of them.  The batch shares the decoder's weights and owns its KV caches
+ * ([batch] x the decoder's cache size).  Each sequence is prefilled with the ordinary decoder and then
+ * adopted into a slot (its KV rows and pending token are copied); all sequences must be at the same
+ * position.  Single GPU, rotary_dim == head_dim.  The per-sequence results equal those of the
+ * single-sequence decoder up to the rounding of the batched linear kernel. */
+typedef void* kmll_batch_t;
+int kmll_batch_create(kmll_decoder_t dec, int batch, kmll_batch_t* out);
+int kmll_batch_destroy(kmll_batch_t batch);
+int kmll_batch_adopt(kmll_batch_t batch, kmll_stream_t stream, int slot);
+/* n_steps greedy tokens for every sequence: tokens_out / logits_out are [batch][n_steps]. */
+int kmll_batch_generate_greedy(kmll_batch_t batch, kmll_stream_t stream, int n_steps, uint32_t* tokens_out,
+                               float* logits_out);
+int kmll_batch_enqueue_steps(kmll_batch_t batch, kmll_stream_t stream, int n_steps);
+int kmll_batch_position(kmll_batch_t batch);
+int kmll_batch_launches_per_step(kmll_batch_t batch);
+
 #ifdef __cplusplus
 }
 #endif

@@ -83,6 +83,8 @@ struct DecodeAttnParams {
     float* k_cache_w;
     float* v_cache_w;
     unsigned long long* trace;  // timeline slot of this launch, or null
+    // batch of independent sequences in lockstep (blockIdx.z = sequence): element strides between sequences
+    size_t q_stride, new_stride, cache_stride, ws_stride, out_stride;
 };
 
 // Half-split RoPE of a head slice held 4 (or 2) consecutive dims per lane: the partner dim d +- HD/2 lives
@@ -130,7 +132,24 @@ __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" 
 // GQM bounds the query heads per KV head at compile time (4 or 8): the per-head register arrays and unrolled
 // loops are sized by it.
 template <int HD, int GQM>
-__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p_in) {
+    DecodeAttnParams p = p_in;
+    if (gridDim.z > 1) {  // sequence blockIdx.z of a batch: shift every per-sequence operand
+        const size_t b = blockIdx.z;
+        p.q += b * p.q_stride;
+        p.out += b * p.out_stride;
+        p.k_cache += b * p.cache_stride;
+        p.v_cache += b * p.cache_stride;
+        if (p.k_new != nullptr) {
+            p.k_new += b * p.new_stride;
+            p.v_new += b * p.new_stride;
+            p.k_cache_w += b * p.cache_stride;
+            p.v_cache_w += b * p.cache_stride;
+        }
+        p.part_acc += b * p.ws_stride;
+        p.part_ml += b * p.ws_stride;
+        p.counters += b * p.ws_stride;
+    }
     constexpr int EPL = HD / 32;        // elements per lane
     constexpr int V16 = HD / 4;         // 16-byte pieces per row
     constexpr int KP = HD + 16;         // padded K row: the score pass reads 16-byte pieces at stride KP conflict-free
@@ -151,15 +170,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     const bool fused = p.k_new != nullptr;
     const int s0 = split * p.chunk;
     int seq_len = 0, n = 0;
-    auto issue_tile = [&](int t0, int nt) {
+    // one commit group per K tile and per V tile (also when the tile does not exist, so the group count is uniform)
+    auto issue_k = [&](int t0) {
+        const int nt = min(kAttnTile, n - t0);
         const float* kg = p.k_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
-        const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
 #pragma unroll 2
         for (int i = tid; i < nt * V16; i += kAttnThreads) {
             const int r = i / V16, cidx = i - r * V16;
             cp_async16(Ks + r * KP + cidx * 4, kg + (size_t)r * kv_stride + cidx * 4);
         }
         cp_async_commit();
+    };
+    auto issue_v = [&](int t0) {
+        const int nt = min(kAttnTile, n - t0);
+        const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
 #pragma unroll 2
         for (int i = tid; i < nt * V16; i += kAttnThreads) {
             const int r = i / V16, cidx = i - r * V16;
@@ -171,7 +195,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
         n = min(s0 + p.chunk, seq_len) - s0;
         if (n > 0) {
-            issue_tile(0, min(kAttnTile, n));
+            issue_k(0);
+            issue_v(0);
             // rotation angles depend on the position only: one sine / cosine evaluation per pair and block, done
             // while the copies are in flight and before the query exists (the accurate sincosf is long code)
             if (tid < HD / 2) {
@@ -217,9 +242,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll 1
     for (int t0 = 0; t0 < n; t0 += kAttnTile) {
         const int nt = min(kAttnTile, n - t0);
-        __syncthreads();  // the previous tile has been consumed (first tile: qs / hstat are written)
-        if (!(fused && t0 == 0)) issue_tile(t0, nt);
-        cp_async_wait<1>();  // K has landed
+        __syncthreads();  // the previous V tile has been consumed (first tile: qs / hstat are written)
+        // Copies run one phase ahead of their use: the V tile of this iteration is requested as soon as the previous
+        // one has been consumed, the next K tile as soon as the scores below are done.  The first tile of the fused
+        // form was requested before the dependency wait.
+        if (t0 == 0) {
+            if (!fused) { issue_k(0); issue_v(0); }
+        } else {
+            issue_v(t0);
+        }
+        cp_async_wait<1>();  // K has landed (at most the V tile is still in flight)
         __syncthreads();
         const int newrow = newpos - t0;  // row of this tile that is the position being written
         const bool has_new = owns_new && newrow >= 0 && newrow < nt;
@@ -253,6 +285,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             }
         }
         __syncthreads();
+        issue_k(t0 + kAttnTile);  // the K tile is free: request the next one (an empty group after the last tile)
         // running softmax statistics: one warp per query head
         if (warp < gq) {
             const int h = warp;
@@ -267,7 +300,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             const float corr = expf(m_old - m);  // exp(-inf) = 0 on the first tile
             if (lane == 0) { hstat[h * 4] = m; hstat[h * 4 + 1] = l_old * corr + l; hstat[h * 4 + 2] = corr; }
         }
-        cp_async_wait<0>();  // V has landed
+        cp_async_wait<1>();  // V has landed (at most the next K tile is still in flight)
         __syncthreads();
         if (has_new) {
             if (warp == kAttnWarps - 1) {
@@ -521,7 +554,7 @@ static AttnPlan plan_decode_attention(int seq_cap) {
 int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_cache, const float* v_cache,
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
                             int head_dim, float* workspace, float* out, const float* k_new, const float* v_new,
-                            const float* freqs, float* k_cache_w, float* v_cache_w) {
+                            const float* freqs, float* k_cache_w, float* v_cache_w, int batch, size_t cache_stride) {
     const int gq = n_heads / n_kv_heads;
     AttnPlan pl = plan_decode_attention(seq_cap);
     DecodeAttnParams p;
@@ -534,7 +567,12 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
     p.out = out;
     p.k_new = k_new; p.v_new = v_new; p.freqs = freqs; p.k_cache_w = k_cache_w; p.v_cache_w = v_cache_w;
-    p.trace = trace_next_slot(200, n_kv_heads * pl.nsplit);
+    p.trace = batch > 1 ? nullptr : trace_next_slot(200, n_kv_heads * pl.nsplit);
+    // batch: q / out rows of n_heads*head_dim, new K/V rows of n_kv_heads*head_dim, one workspace per sequence
+    p.q_stride = p.out_stride = (size_t)n_heads * head_dim;
+    p.new_stride = (size_t)n_kv_heads * head_dim;
+    p.cache_stride = cache_stride;
+    p.ws_stride = decode_attention_workspace_floats(n_heads, head_dim, seq_cap);
     // K tile (padded rows), V tile, scores, statistics, query heads; the cross-warp reduction reuses the V tile
     // (kAttnWarps * gq <= kAttnTile rows because gq <= kMaxGq)
     const size_t smem = ((size_t)kAttnTile * (head_dim + 16) + (size_t)kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile +
@@ -543,7 +581,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     auto go = [&](auto kern) {
         // (the attribute is per kernel and per device; setting it again is cheap and keeps this re-entrant)
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        return launch(kern, dim3(n_kv_heads, pl.nsplit), dim3(kAttnThreads), smem, stream, true, p);
+        return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem, stream, true, p);
     };
     if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4>) : go(decode_attention_kernel<128, 8>);
     else e = gq <= 4 ? go(decode_attention_kernel<64, 4>) : go(decode_attention_kernel<64, 8>);

@@ -456,6 +456,78 @@ int decode_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim,
     return KMLL_OK;
 }
 
+__global__ void batch_begin_kernel(const uint16_t* __restrict__ table, int vocab, int dim, BatchState* state,
+                                   uint64_t* __restrict__ history, int history_cap, float* __restrict__ hidden) {
+    pdl_wait();
+    const int b = blockIdx.y;
+    const uint64_t packed = state->next_top[b];
+    uint32_t token = (uint32_t)(packed & 0xffffffffull);
+    if (token >= (uint32_t)vocab) token = (uint32_t)vocab - 1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < dim) hidden[(size_t)b * dim + i] = bf16_bits_to_f32(table[(size_t)token * dim + i]);
+    if (i == 0) {
+        const int step = state->step;
+        if (step < history_cap) history[(size_t)b * history_cap + step] = packed;
+        if (b == 0) state->seq_len = state->position + 1;
+    }
+}
+
+// one block per sequence: arg-max over its logits row with the tie rule of the packed arg-max (lower token wins)
+__global__ void batch_end_kernel(const float* __restrict__ logits, int vocab, BatchState* state) {
+    pdl_wait();
+    __shared__ float s_logit[32];
+    __shared__ uint32_t s_tok[32];
+    const int b = blockIdx.x;
+    const float* row = logits + (size_t)b * vocab;
+    float best = -INFINITY;
+    uint32_t tok = 0xffffffffu;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (tok == 0xffffffffu || top1_better(v, (uint32_t)i, best, tok)) { best = v; tok = (uint32_t)i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
+        if (ot != 0xffffffffu && (tok == 0xffffffffu || top1_better(ov, ot, best, tok))) { best = ov; tok = ot; }
+    }
+    if (lane == 0) { s_logit[warp] = best; s_tok[warp] = tok; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? s_logit[lane] : -INFINITY;
+        tok = lane < nw ? s_tok[lane] : 0xffffffffu;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const uint32_t ot = __shfl_xor_sync(0xffffffffu, tok, off);
+            if (ot != 0xffffffffu && (tok == 0xffffffffu || top1_better(ov, ot, best, tok))) { best = ov; tok = ot; }
+        }
+        if (lane == 0) {
+            state->next_top[b] = pack_top1(best, tok);
+            if (b == 0) {
+                state->position += 1;
+                state->step += 1;
+            }
+        }
+    }
+}
+
+int batch_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim, int batch, BatchState* state, uint64_t* history,
+                int history_cap, float* hidden) {
+    cudaError_t e = launch(batch_begin_kernel, dim3((dim + 255) / 256, batch), dim3(256), 0, stream, true, table, vocab, dim, state,
+                           history, history_cap, hidden);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "batch_begin: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int batch_end(cudaStream_t stream, const float* logits, int vocab, int batch, BatchState* state) {
+    cudaError_t e = launch(batch_end_kernel, dim3(batch), dim3(1024), 0, stream, true, logits, vocab, state);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "batch_end: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
 int decode_end(cudaStream_t stream, const uint64_t* packed, DecodeState* state) {
     cudaError_t e = launch(decode_end_kernel, dim3(1), dim3(32), 0, stream, true, packed, state);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "decode_end: %s", cudaGetErrorString(e));

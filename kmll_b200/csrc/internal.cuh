@@ -57,7 +57,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
                             int head_dim, float* workspace, float* out, const float* k_new = nullptr,
                             const float* v_new = nullptr, const float* freqs = nullptr, float* k_cache_w = nullptr,
-                            float* v_cache_w = nullptr);
+                            float* v_cache_w = nullptr, int batch = 1, size_t cache_stride = 0);
 size_t decode_attention_workspace_floats(int n_heads, int head_dim, int seq_cap);
 
 // elementwise.cu
@@ -74,6 +74,18 @@ int decode_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim,
 // state->next_top = *packed; position += 1; step += 1.
 int decode_end(cudaStream_t stream, const uint64_t* packed, DecodeState* state);
 
+// Lockstep batch of sequences: shared position, one pending token per sequence.
+constexpr int kMaxBatch = 16;
+struct BatchState {
+    int position, seq_len, step, pad;
+    uint64_t next_top[kMaxBatch];
+};
+// hidden[b] = embedding[next_top[b].token]; records the tokens into history[b][step]; seq_len = position + 1.
+int batch_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim, int batch, BatchState* state, uint64_t* history,
+                int history_cap, float* hidden);
+// packed[b] = arg-max of logits[b] (ties -> lower token); next_top[b] = packed[b]; position += 1; step += 1.
+int batch_end(cudaStream_t stream, const float* logits, int vocab, int batch, BatchState* state);
+
 // quantize.cu: bf16 bits -> f32 (exact)
 int widen_bf16(cudaStream_t stream, const uint16_t* src, size_t n, float* dst);
 
@@ -81,6 +93,12 @@ int widen_bf16(cudaStream_t stream, const uint16_t* src, size_t n, float* dst);
 int linear_top1_offset(cudaStream_t stream, int fmt, const float* x, const uint16_t* norm_w, float eps, const void* w,
                        const void* scales, int rows, int cols, uint32_t token_offset, uint32_t* partial_tokens,
                        float* partial_logits, uint64_t* packed_out, const TpExchange* xc = nullptr);
+// Batched fused linear forms for rows of x that are independent sequences (batch <= 16 per pass):
+// form 0 = RMSNorm + QKV (3 matrices, rows[0..2]), 1 = RMSNorm + gate/up + SiLU*up (2 matrices of rows[0]),
+// 2 = projection + residual, 3 = (RMSNorm +) projection.  Outputs are [batch, rows] row-major.
+int linear_batched_form(int form, cudaStream_t stream, int fmt, const float* x, int batch, const uint16_t* norm_w, float eps,
+                        const void* const* w, const void* const* scales, const int* rows, int cols, float* const* outs,
+                        const float* residual);
 // Deterministic merge of per-rank packed results: higher logit wins, ties -> lower token.
 int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out);
 

@@ -780,7 +780,11 @@ static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) 
     if (EPI == EPI_TOP1 || EPI == EPI_SILU) {
         // rows-per-block fixed at 32 tile rows so the partial count is a pure function of rows
         if (M <= 4) return launch_variant<FMT, 2, 1, EPI, 4>(stream, p, grid);
-        return fail(KMLL_ERR_UNSUPPORTED, "fused epilogue supports batch <= 4 per call");
+        if constexpr (EPI == EPI_SILU) {
+            if (M <= 8) return launch_variant<FMT, 2, 2, EPI, 2>(stream, p, grid);
+            return launch_variant<FMT, 2, 4, EPI, 1>(stream, p, grid);
+        }
+        return fail(KMLL_ERR_UNSUPPORTED, "the arg-max epilogue supports batch <= 4 per call");
     }
     if (M <= 4) {
         if (mt2) return launch_variant<FMT, 2, 1, EPI, 4>(stream, p, grid);
@@ -949,6 +953,38 @@ int decode_end_gather(cudaStream_t stream, const TpExchange* xc, DecodeState* st
     cudaError_t e = launch(decode_end_gather_kernel, dim3(1), dim3(32), 0, stream, true, xc, state, packed_final);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "decode_end_gather: %s", cudaGetErrorString(e));
     return KMLL_OK;
+}
+
+// ---- batched fused forms (rows of x = independent sequences), used by the lockstep batch decoder ------------
+template <int FMT>
+static int batched_forms(int form, cudaStream_t stream, const float* x, int batch, const uint16_t* norm_w, float eps,
+                         const void* const* w, const void* const* scales, const int* rows, int cols, float* const* outs,
+                         const float* residual) {
+    switch (form) {
+        case 0: {  // RMSNorm + QKV
+            MatArg m[3] = {{w[0], scales[0], rows[0], outs[0], nullptr}, {w[1], scales[1], rows[1], outs[1], nullptr},
+                           {w[2], scales[2], rows[2], outs[2], nullptr}};
+            return run_linear<FMT, EPI_STORE>("linear_qkv_batched_norm", stream, x, batch, cols, cols, norm_w, eps, m, 3, 0, nullptr, nullptr);
+        }
+        case 1: {  // RMSNorm + gate/up + SiLU*up
+            MatArg m[2] = {{w[0], scales[0], rows[0], outs[0], nullptr}, {w[1], scales[1], rows[0], nullptr, nullptr}};
+            return run_linear<FMT, EPI_SILU>("silu_gate_up_batched_norm", stream, x, batch, cols, cols, norm_w, eps, m, 2, 0, nullptr, nullptr);
+        }
+        case 2: {  // projection + residual
+            MatArg m = {w[0], scales[0], rows[0], outs[0], residual};
+            return run_linear<FMT, EPI_RESIDUAL>("linear_residual_batched", stream, x, batch, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+        }
+        default: {  // (RMSNorm +) projection
+            MatArg m = {w[0], scales[0], rows[0], outs[0], nullptr};
+            return run_linear<FMT, EPI_STORE>("linear_batched_norm", stream, x, batch, cols, cols, norm_w, eps, &m, 1, 0, nullptr, nullptr);
+        }
+    }
+}
+int linear_batched_form(int form, cudaStream_t stream, int fmt, const float* x, int batch, const uint16_t* norm_w, float eps,
+                        const void* const* w, const void* const* scales, const int* rows, int cols, float* const* outs,
+                        const float* residual) {
+    if (fmt == FMT_W4) return batched_forms<FMT_W4>(form, stream, x, batch, norm_w, eps, w, scales, rows, cols, outs, residual);
+    return batched_forms<FMT_I8>(form, stream, x, batch, norm_w, eps, w, scales, rows, cols, outs, residual);
 }
 
 int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out) {

@@ -95,6 +95,12 @@ __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
 __device__ inline void cp_async_stream16(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
 }
+__device__ inline void cp_async_stream16_to(uint32_t smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ inline void cp_async_word_to(uint32_t smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
 __device__ inline void cp_async_word(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
 }
@@ -402,12 +408,16 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
     unsigned char* ring = smem + p.off_ring + (size_t)tid * 16;  // plane stride = kSThreads * 16 bytes
     constexpr int kPlane = kSThreads * 16;
     // W4 group scales ride in a second, tiny ring: per (slot, 16-row block, row half) one 4-byte word per row
-    // (the aligned word that contains the binary16 scale), copied by the t == 0 lane of each row
+    // (the aligned word that contains the binary16 scale).  Lane (g, t) copies the word of row g of block t >> 1,
+    // half t & 1: one copy and one pointer per lane and tile.
     unsigned char* sring = smem + p.off_sring + warp * 32 + g * 4;
     constexpr int kSPlane = kSWarps * 32;
+    const bool scale_lane = FMT == FMT_W4 && t < 2 * MT;
+    const uint32_t ring_dst = smem_u32(ring);
+    const uint32_t sring_dst = smem_u32(sring) + (uint32_t)t * kSPlane;  // plane (t >> 1) * 2 + (t & 1) = t
     int l_unit = blockIdx.x, l_seg = j0;  // load cursor
     const unsigned char* lw[MT][2];   // this lane's 16 bytes of the cursor's segment, rows g and g+8
-    const unsigned short* ls[MT][2];  // W4: the group scales of the same rows
+    const unsigned short* ls_mine = nullptr;  // W4: the group scale this lane copies
     auto enter_unit = [&]() {         // row pointers of the cursor's unit (rows past the end re-read the last row)
         if (l_unit >= p.total_units || spu <= 0) return;
         int mi, row0;
@@ -419,29 +429,25 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
             const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);
             lw[mt][0] = m.w + (size_t)r0 * rowbytes + (size_t)j0 * 64 + t * 16;
             lw[mt][1] = m.w + (size_t)r1 * rowbytes + (size_t)j0 * 64 + t * 16;
-            if (FMT == FMT_W4) {
-                ls[mt][0] = reinterpret_cast<const unsigned short*>(m.scales) + (size_t)r0 * ngr + j0;
-                ls[mt][1] = reinterpret_cast<const unsigned short*>(m.scales) + (size_t)r1 * ngr + j0;
-            }
+            if (FMT == FMT_W4 && (t >> 1) == mt)
+                ls_mine = reinterpret_cast<const unsigned short*>(m.scales) + (size_t)((t & 1) ? r1 : r0) * ngr + j0;
         }
     };
     enter_unit();
     auto load_tile = [&](int slot) {
         if (l_unit < p.total_units && spu > 0) {
+            const uint32_t dst = ring_dst + (uint32_t)slot * (MT * 2 * kPlane);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                cp_async_stream16(ring + (size_t)((slot * MT + mt) * 2) * kPlane, lw[mt][0]);
-                cp_async_stream16(ring + (size_t)((slot * MT + mt) * 2 + 1) * kPlane, lw[mt][1]);
+                cp_async_stream16_to(dst + (mt * 2) * kPlane, lw[mt][0]);
+                cp_async_stream16_to(dst + (mt * 2 + 1) * kPlane, lw[mt][1]);
                 lw[mt][0] += 64;
                 lw[mt][1] += 64;
-                if (FMT == FMT_W4) {
-                    if (t == 0) {
-                        cp_async_word(sring + (size_t)((slot * MT + mt) * 2) * kSPlane, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ls[mt][0]) & ~(uintptr_t)3));
-                        cp_async_word(sring + (size_t)((slot * MT + mt) * 2 + 1) * kSPlane, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ls[mt][1]) & ~(uintptr_t)3));
-                    }
-                    ls[mt][0] += 1;
-                    ls[mt][1] += 1;
-                }
+            }
+            if (scale_lane) {
+                cp_async_word_to(sring_dst + (uint32_t)slot * (MT * 2 * kSPlane),
+                                 reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ls_mine) & ~(uintptr_t)3));
+                ls_mine += 1;
             }
             if (++l_seg == j1) {
                 l_seg = j0;

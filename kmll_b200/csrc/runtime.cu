@@ -468,6 +468,130 @@ static int tensor_ref(Decoder* d, int layer, int tensor, TensorRef* out) {
 
 using namespace kmll;
 
+// ---- lockstep batch of sequences ---------------------------------------------------------------------
+// Several independent sequences at the same position share every weight read: the activations of a step are
+// [batch, dim] rows through the batched linear kernel, attention runs per sequence (grid z) on per-sequence
+// KV caches.  kmll has no batched decode; the per-sequence math is that of the single-sequence step.
+struct BatchDecoder {
+    Decoder* d = nullptr;  // weights and configuration (not owned)
+    int batch = 0;
+    size_t cache_stride = 0;  // floats between two sequences' caches
+    std::vector<float*> key_cache, value_cache;  // per layer: [batch][max_seq * kv_len]
+    float *hidden_a = nullptr, *hidden_b = nullptr, *hidden_mid = nullptr, *q = nullptr, *k = nullptr, *v = nullptr;
+    float *attn = nullptr, *act = nullptr, *logits = nullptr, *attn_ws = nullptr;
+    BatchState* state = nullptr;
+    uint64_t* history = nullptr;  // [batch][history_cap]
+    int history_cap = 0;
+    int host_position = -1;
+    unsigned filled = 0;  // bit b: slot b holds a sequence
+    cudaGraphExec_t graph = nullptr;
+    cudaStream_t capture_stream = nullptr;
+    bool warmed = false;
+    int launches_per_step = 0;
+    std::vector<void*> allocs;
+};
+
+template <typename T>
+static int balloc(BatchDecoder* b, T** out, size_t count) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, count * sizeof(T) + 16);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaMalloc(%zu bytes): %s", count * sizeof(T), cudaGetErrorString(e));
+    b->allocs.push_back(p);
+    *out = static_cast<T*>(p);
+    return KMLL_OK;
+}
+
+static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
+    Decoder* d = b->d;
+    const kmll_decoder_config& c = d->cfg;
+    const int B = b->batch;
+    const int q_len = c.n_heads * c.head_dim, kv_len = c.n_kv_heads * c.head_dim;
+    int n = 0;
+    KMLL_TRY(batch_begin(s, d->embedding, c.vocab_size, c.dim, B, b->state, b->history, b->history_cap, b->hidden_a));
+    ++n;
+    float* hidden = b->hidden_a;
+    float* other = b->hidden_b;
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = d->layers[l];
+        {
+            const void* w[3] = {L.wq.w, L.wk.w, L.wv.w};
+            const void* sc[3] = {L.wq.scales, L.wk.scales, L.wv.scales};
+            const int rows[3] = {q_len, kv_len, kv_len};
+            float* outs[3] = {b->q, b->k, b->v};
+            KMLL_TRY(linear_batched_form(0, s, c.format, hidden, B, L.attention_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
+        }
+        KMLL_TRY(decode_attention_launch(s, b->q, b->key_cache[l], b->value_cache[l], &b->state->seq_len, 0, c.max_seq_len, c.n_heads,
+                                         c.n_kv_heads, c.head_dim, b->attn_ws, b->attn, b->k, b->v, d->freqs, b->key_cache[l],
+                                         b->value_cache[l], B, b->cache_stride));
+        {
+            const void* w[1] = {L.wo.w};
+            const void* sc[1] = {L.wo.scales};
+            const int rows[1] = {c.dim};
+            float* outs[1] = {b->hidden_mid};
+            KMLL_TRY(linear_batched_form(2, s, c.format, b->attn, B, nullptr, 0.f, w, sc, rows, q_len, outs, hidden));
+        }
+        {
+            const void* w[2] = {L.w1.w, L.w3.w};
+            const void* sc[2] = {L.w1.scales, L.w3.scales};
+            const int rows[1] = {c.hidden_dim};
+            float* outs[1] = {b->act};
+            KMLL_TRY(linear_batched_form(1, s, c.format, b->hidden_mid, B, L.ffn_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
+        }
+        {
+            const void* w[1] = {L.w2.w};
+            const void* sc[1] = {L.w2.scales};
+            const int rows[1] = {c.dim};
+            float* outs[1] = {other};
+            KMLL_TRY(linear_batched_form(2, s, c.format, b->act, B, nullptr, 0.f, w, sc, rows, c.hidden_dim, outs, b->hidden_mid));
+        }
+        n += 5;
+        float* t = hidden;
+        hidden = other;
+        other = t;
+    }
+    {
+        const void* w[1] = {d->output.w};
+        const void* sc[1] = {d->output.scales};
+        const int rows[1] = {c.vocab_size};
+        float* outs[1] = {b->logits};
+        KMLL_TRY(linear_batched_form(3, s, c.format, hidden, B, d->final_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
+    }
+    KMLL_TRY(batch_end(s, b->logits, c.vocab_size, B, b->state));
+    n += 2;
+    if (launches) *launches = n;
+    return KMLL_OK;
+}
+
+static int ensure_batch_graph(BatchDecoder* b, cudaStream_t s) {
+    if (b->graph != nullptr) return KMLL_OK;
+    if (!b->warmed) {
+        // one eager step (kernel attributes get set outside capture); the state is restored afterwards and the KV
+        // rows it wrote are rewritten by the real step at this position
+        BatchState saved;
+        KMLL_CUDA(cudaStreamSynchronize(s));
+        KMLL_CUDA(cudaMemcpy(&saved, b->state, sizeof(saved), cudaMemcpyDeviceToHost));
+        KMLL_TRY(enqueue_batch_step(b, s, &b->launches_per_step));
+        KMLL_CUDA(cudaStreamSynchronize(s));
+        KMLL_CUDA(cudaMemcpy(b->state, &saved, sizeof(saved), cudaMemcpyHostToDevice));
+        b->warmed = true;
+    }
+    cudaGraph_t g = nullptr;
+    if (b->capture_stream == nullptr) KMLL_CUDA(cudaStreamCreateWithFlags(&b->capture_stream, cudaStreamNonBlocking));
+    KMLL_CUDA(cudaStreamBeginCapture(b->capture_stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_batch_step(b, b->capture_stream, &b->launches_per_step);
+    cudaError_t e = cudaStreamEndCapture(b->capture_stream, &g);
+    if (rc != KMLL_OK) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&b->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+
 // Peer-memory exchange: every rank allocates one buffer (inboxes, flags, arg-max slots, counters), the ranks
 // swap CUDA IPC handles through an NCCL all-gather and map each other's buffers.  Needs batch-1 stream kernels
 // for every exchanged vector, at most 63 layers (exchange numbers stay below 127) and tp_size <= 8.
@@ -1003,5 +1127,148 @@ int kmll_decoder_last_hidden(kmll_decoder_t dec, kmll_stream_t stream, float* hi
 int kmll_decoder_launches_per_step(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->launches_per_step : 0; }
 size_t kmll_decoder_weight_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->weight_bytes : 0; }
 size_t kmll_decoder_kv_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->kv_bytes : 0; }
+
+int kmll_batch_destroy(kmll_batch_t batch) {
+    if (batch == nullptr) return KMLL_OK;
+    BatchDecoder* b = static_cast<BatchDecoder*>(batch);
+    if (b->graph) cudaGraphExecDestroy(b->graph);
+    if (b->capture_stream) cudaStreamDestroy(b->capture_stream);
+    for (void* p : b->allocs) cudaFree(p);
+    delete b;
+    return KMLL_OK;
+}
+
+int kmll_batch_create(kmll_decoder_t dec, int batch, kmll_batch_t* out) {
+    KMLL_REQUIRE_PTR(dec);
+    KMLL_REQUIRE_PTR(out);
+    Decoder* d = static_cast<Decoder*>(dec);
+    const kmll_decoder_config& c = d->cfg;
+    KMLL_REQUIRE(batch >= 1 && batch <= kMaxBatch, "batch %d outside 1..%d", batch, kMaxBatch);
+    if (c.tp_size != 1) return fail(KMLL_ERR_UNSUPPORTED, "batched decode is single-GPU");
+    if (c.rotary_dim != c.head_dim) return fail(KMLL_ERR_UNSUPPORTED, "batched decode needs rotary_dim == head_dim");
+    if ((c.head_dim != 64 && c.head_dim != 128) || c.n_heads / c.n_kv_heads > 8)
+        return fail(KMLL_ERR_UNSUPPORTED, "batched decode needs head_dim 64 or 128 and at most 8 query heads per KV head");
+    BatchDecoder* b = new BatchDecoder();
+    b->d = d;
+    b->batch = batch;
+    auto body = [&]() -> int {
+        const int q_len = c.n_heads * c.head_dim, kv_len = c.n_kv_heads * c.head_dim;
+        b->cache_stride = (size_t)c.max_seq_len * kv_len;
+        b->key_cache.resize(c.n_layers);
+        b->value_cache.resize(c.n_layers);
+        for (int l = 0; l < c.n_layers; ++l) {
+            KMLL_TRY(balloc(b, &b->key_cache[l], b->cache_stride * batch));
+            KMLL_TRY(balloc(b, &b->value_cache[l], b->cache_stride * batch));
+            KMLL_CUDA(cudaMemset(b->key_cache[l], 0, b->cache_stride * batch * sizeof(float)));
+            KMLL_CUDA(cudaMemset(b->value_cache[l], 0, b->cache_stride * batch * sizeof(float)));
+        }
+        KMLL_TRY(balloc(b, &b->hidden_a, (size_t)batch * c.dim));
+        KMLL_TRY(balloc(b, &b->hidden_b, (size_t)batch * c.dim));
+        KMLL_TRY(balloc(b, &b->hidden_mid, (size_t)batch * c.dim));
+        KMLL_TRY(balloc(b, &b->q, (size_t)batch * q_len));
+        KMLL_TRY(balloc(b, &b->attn, (size_t)batch * q_len));
+        KMLL_TRY(balloc(b, &b->k, (size_t)batch * kv_len));
+        KMLL_TRY(balloc(b, &b->v, (size_t)batch * kv_len));
+        KMLL_TRY(balloc(b, &b->act, (size_t)batch * c.hidden_dim));
+        KMLL_TRY(balloc(b, &b->logits, (size_t)batch * c.vocab_size));
+        const size_t ws = (decode_attention_workspace_floats(c.n_heads, c.head_dim, c.max_seq_len) + 3) & ~(size_t)3;
+        KMLL_TRY(balloc(b, &b->attn_ws, ws * batch));
+        KMLL_CUDA(cudaMemset(b->attn_ws, 0, ws * batch * sizeof(float)));
+        KMLL_TRY(balloc(b, &b->state, (size_t)1));
+        KMLL_CUDA(cudaMemset(b->state, 0, sizeof(BatchState)));
+        b->history_cap = c.max_seq_len;
+        KMLL_TRY(balloc(b, &b->history, (size_t)batch * b->history_cap));
+        return KMLL_OK;
+    };
+    const int rc = body();
+    if (rc != KMLL_OK) {
+        kmll_batch_destroy(b);
+        return rc;
+    }
+    *out = b;
+    return KMLL_OK;
+}
+
+int kmll_batch_adopt(kmll_batch_t batch, kmll_stream_t stream, int slot) {
+    KMLL_REQUIRE_PTR(batch);
+    BatchDecoder* b = static_cast<BatchDecoder*>(batch);
+    Decoder* d = b->d;
+    cudaStream_t s = as_stream(stream);
+    KMLL_REQUIRE(slot >= 0 && slot < b->batch, "slot %d outside 0..%d", slot, b->batch - 1);
+    if (!d->have_next) return fail(KMLL_ERR_STATE, "the decoder must be prefilled before its sequence can be adopted");
+    if (b->filled != 0 && d->host_position != b->host_position)
+        return fail(KMLL_ERR_STATE, "sequences of a batch advance in lockstep: slot at position %d, batch at %d", d->host_position,
+                    b->host_position);
+    const kmll_decoder_config& c = d->cfg;
+    const size_t kv_len = (size_t)c.n_kv_heads * c.head_dim;
+    const size_t bytes = (size_t)d->host_position * kv_len * sizeof(float);
+    for (int l = 0; l < c.n_layers; ++l) {
+        KMLL_CUDA(cudaMemcpyAsync(b->key_cache[l] + (size_t)slot * b->cache_stride, d->layers[l].key_cache, bytes, cudaMemcpyDeviceToDevice, s));
+        KMLL_CUDA(cudaMemcpyAsync(b->value_cache[l] + (size_t)slot * b->cache_stride, d->layers[l].value_cache, bytes, cudaMemcpyDeviceToDevice, s));
+    }
+    KMLL_CUDA(cudaMemcpyAsync(&b->state->next_top[slot], &d->state->next_top, sizeof(uint64_t), cudaMemcpyDeviceToDevice, s));
+    if (b->filled == 0) {
+        int head[4] = {d->host_position, d->host_position + 1, 0, 0};
+        KMLL_CUDA(cudaMemcpyAsync(b->state, head, sizeof(head), cudaMemcpyHostToDevice, s));
+        KMLL_CUDA(cudaStreamSynchronize(s));  // `head` lives on this stack frame
+        b->host_position = d->host_position;
+    }
+    b->filled |= 1u << slot;
+    return KMLL_OK;
+}
+
+int kmll_batch_enqueue_steps(kmll_batch_t batch, kmll_stream_t stream, int n_steps) {
+    KMLL_REQUIRE_PTR(batch);
+    BatchDecoder* b = static_cast<BatchDecoder*>(batch);
+    cudaStream_t s = as_stream(stream);
+    if (b->filled != (b->batch >= 32 ? 0xffffffffu : ((1u << b->batch) - 1u)))
+        return fail(KMLL_ERR_STATE, "every slot of the batch must hold a sequence (kmll_batch_adopt)");
+    KMLL_REQUIRE(n_steps >= 0, "generate: negative step count");
+    if (b->host_position + n_steps > b->d->cfg.max_seq_len)
+        return fail(KMLL_ERR_CAPACITY, "position %d exceeds max sequence length %d", b->host_position + n_steps, b->d->cfg.max_seq_len);
+    KMLL_TRY(ensure_batch_graph(b, s));
+    for (int i = 0; i < n_steps; ++i) {
+        KMLL_CUDA(cudaGraphLaunch(b->graph, s));
+        b->host_position += 1;
+    }
+    return KMLL_OK;
+}
+
+int kmll_batch_generate_greedy(kmll_batch_t batch, kmll_stream_t stream, int n_steps, uint32_t* tokens_out, float* logits_out) {
+    KMLL_REQUIRE_PTR(batch);
+    BatchDecoder* b = static_cast<BatchDecoder*>(batch);
+    cudaStream_t s = as_stream(stream);
+    KMLL_REQUIRE(n_steps >= 0 && n_steps <= b->history_cap, "generate: step count %d outside 0..%d", n_steps, b->history_cap);
+    if (n_steps == 0) return KMLL_OK;
+    // restart the history index, keep position and pending tokens
+    KMLL_CUDA(cudaStreamSynchronize(s));
+    int head[4];
+    KMLL_CUDA(cudaMemcpy(head, b->state, sizeof(head), cudaMemcpyDeviceToHost));
+    head[2] = 0;
+    KMLL_CUDA(cudaMemcpy(b->state, head, sizeof(head), cudaMemcpyHostToDevice));
+    KMLL_TRY(kmll_batch_enqueue_steps(batch, stream, n_steps));
+    std::vector<uint64_t> hist((size_t)b->batch * b->history_cap);
+    KMLL_CUDA(cudaMemcpyAsync(hist.data(), b->history, hist.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
+    KMLL_CUDA(cudaStreamSynchronize(s));
+    for (int q = 0; q < b->batch; ++q)
+        for (int i = 0; i < n_steps; ++i) {
+            const uint64_t h = hist[(size_t)q * b->history_cap + i];
+            if (tokens_out) tokens_out[(size_t)q * n_steps + i] = (uint32_t)(h & 0xffffffffull);
+            if (logits_out) {
+                const uint32_t bits = (uint32_t)(h >> 32);
+                memcpy(&logits_out[(size_t)q * n_steps + i], &bits, 4);
+            }
+        }
+    return KMLL_OK;
+}
+
+int kmll_batch_position(kmll_batch_t batch) {
+    if (batch == nullptr) return -1;
+    return static_cast<BatchDecoder*>(batch)->host_position;
+}
+int kmll_batch_launches_per_step(kmll_batch_t batch) {
+    if (batch == nullptr) return 0;
+    return static_cast<BatchDecoder*>(batch)->launches_per_step;
+}
 
 }  // extern "C"

@@ -27,7 +27,7 @@ class KmllError(RuntimeError):
 _SCALARS = {
     "int": C.c_int, "float": C.c_float, "size_t": C.c_size_t, "uint32_t": C.c_uint32, "uint64_t": C.c_uint64,
     "int32_t": C.c_int32, "int64_t": C.c_int64, "double": C.c_double, "kmll_stream_t": C.c_void_p,
-    "kmll_decoder_t": C.c_void_p,
+    "kmll_decoder_t": C.c_void_p, "kmll_batch_t": C.c_void_p,
 }
 
 

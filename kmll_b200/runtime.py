@@ -185,6 +185,50 @@ class Decoder:
         return int(self._lib.kmll_decoder_kv_bytes(self._h))
 
 
+class BatchDecoder:
+    """Lockstep batch of sequences decoded together (kmll_batch_*): shares a Decoder's weights, owns its KV caches.
+    Prefill each sequence with the decoder, then `adopt(slot)` it; all sequences must be at the same position."""
+
+    def __init__(self, decoder: Decoder, batch: int):
+        self._lib = decoder._lib
+        self.decoder = decoder
+        self.batch = batch
+        self._h = C.c_void_p()
+        check(self._lib.kmll_batch_create(decoder._h, batch, C.byref(self._h)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.kmll_batch_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def adopt(self, slot: int) -> None:
+        check(self._lib.kmll_batch_adopt(self._h, Decoder._stream(), slot))
+
+    def generate_greedy(self, n_steps: int):
+        """(tokens, logits), each [batch, n_steps]."""
+        tokens = np.zeros((self.batch, n_steps), dtype=np.uint32)
+        logits = np.zeros((self.batch, n_steps), dtype=np.float32)
+        check(self._lib.kmll_batch_generate_greedy(self._h, Decoder._stream(), n_steps, tokens.ctypes.data, logits.ctypes.data))
+        return tokens, logits
+
+    def enqueue_steps(self, n_steps: int) -> None:
+        check(self._lib.kmll_batch_enqueue_steps(self._h, Decoder._stream(), n_steps))
+
+    @property
+    def position(self) -> int:
+        return int(self._lib.kmll_batch_position(self._h))
+
+    @property
+    def launches_per_step(self) -> int:
+        return int(self._lib.kmll_batch_launches_per_step(self._h))
+
+
 def unpack_top1(packed: int):
     """unpack_packed_top_logit (crates/inference/src/model.rs:11808-11812)."""
     token = packed & 0xFFFFFFFF
@@ -192,4 +236,4 @@ def unpack_top1(packed: int):
     return int(token), float(logit)
 
 
-__all__ = ["Decoder", "DecoderConfig", "KmllError", "FORMAT_RS_I8", "FORMAT_W4G128", "unpack_top1"]
+__all__ = ["Decoder", "BatchDecoder", "DecoderConfig", "KmllError", "FORMAT_RS_I8", "FORMAT_W4G128", "unpack_top1"]
