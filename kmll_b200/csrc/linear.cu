@@ -65,6 +65,7 @@ struct LinearParams {
     const TpExchange* xc;  // tensor-parallel exchange of the next launch (set_exchange_args), or null
     int push_index, gather_index;
     float* x_out;
+    int ldw, lds;  // weight row stride in bytes / W4 scales per row when K is a column slice; 0 = the K of this call
 };
 
 constexpr int kWarps = 8;
@@ -654,16 +655,18 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     sp.partial_tokens = lp.partial_tokens;
     sp.partial_logits = lp.partial_logits;
     sp.xc = lp.xc; sp.push_index = lp.push_index; sp.gather_index = lp.gather_index; sp.x_out = lp.x_out;
+    sp.ldw = lp.ldw > 0 ? lp.ldw : (FMT == FMT_W4 ? lp.K / 2 : lp.K);
+    sp.lds = lp.lds > 0 ? lp.lds : lp.K / 128;
     const int K = lp.K, M = lp.M;
     // digit rows: 16-byte reads of two rows (lanes g, g+1) must fall into different banks
     sp.xs_pitch = K + (FMT == FMT_W4 ? 16 : 64);
     auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
     const size_t xs_bytes = up128((size_t)4 * M * sp.xs_pitch + 16);  // digit rows + 16 zero bytes (absent MMA columns)
-    const size_t red_bytes = up128((size_t)kRedBufs * (kSWarps + 2) * ROWS * M * sizeof(float));  // partials + epilogue operands
+    const size_t red_bytes = up128((size_t)red_bufs(NT) * (kSWarps + 2) * ROWS * M * sizeof(float));  // partials + epilogue operands
     const size_t bars_bytes = 128;
     const size_t misc_bytes = 1024;
-    const size_t ring_bytes = (size_t)8 * 2 * kSThreads * 16;  // 8 tile halves in flight per lane (128 KB)
-    const size_t sring_bytes = FMT == FMT_W4 ? (size_t)8 * 2 * kSWarps * 32 : 0;  // scale words of the tiles in flight
+    const size_t ring_bytes = (size_t)ring_halves(NT) * 2 * kSThreads * 16;  // tile halves in flight per lane (128 KB for batch 1)
+    const size_t sring_bytes = FMT == FMT_W4 ? (size_t)ring_halves(NT) * 2 * kSWarps * 32 : 0;  // scale words of the tiles in flight
     const size_t smem = xs_bytes + red_bytes + bars_bytes + misc_bytes + ring_bytes + sring_bytes;
     if (smem > 226 * 1024) return KMLL_OK;  // *launched stays false
     // the activation staging keeps x in registers (M*K <= 24576) and reads it with 16-byte loads
@@ -827,7 +830,7 @@ struct MatArg {
 template <int FMT, int EPI>
 static int run_linear(const char* name, cudaStream_t stream, const float* x, int M, int K, int ldx,
                       const uint16_t* norm_w, float eps, const MatArg* mats, int nmat, int ldo_override,
-                      uint32_t* partial_tokens, float* partial_logits, int* top1_count = nullptr) {
+                      uint32_t* partial_tokens, float* partial_logits, int* top1_count = nullptr, int ldw = 0, int lds = 0) {
     const ExchangeArgs xa = g_exchange_args;
     g_exchange_args = ExchangeArgs();
     if (xa.xc != nullptr && M != 1) return fail(KMLL_ERR_UNSUPPORTED, "%s: the peer-memory exchange needs batch 1", name);
@@ -877,33 +880,59 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
                         FMT == FMT_W4 ? 128 : 64);
         }
     }
-    for (int m0 = 0; m0 < M; m0 += 16) {
-        LinearParams p;
-        memset(&p, 0, sizeof(p));
-        p.x = x + (size_t)m0 * ldx;
-        p.M = (M - m0) < 16 ? (M - m0) : 16;
-        p.K = K;
-        p.ldx = ldx;
-        p.norm_w = norm_w;
-        p.eps = eps;
-        p.nmat = nmat;
-        for (int i = 0; i < nmat; ++i) {
-            const int ldo = ldo_override > 0 ? ldo_override : mats[i].rows;
-            p.mat[i].w = reinterpret_cast<const uint8_t*>(mats[i].w);
-            p.mat[i].scales = mats[i].scales;
-            p.mat[i].rows = mats[i].rows;
-            p.mat[i].ldo = ldo;
-            p.mat[i].out = mats[i].out ? mats[i].out + (size_t)m0 * ldo : nullptr;
-            p.mat[i].residual = mats[i].residual ? mats[i].residual + (size_t)m0 * ldo : nullptr;
+    // Batches above one row: the streaming kernel takes up to 4 rows of x per pass when its shared-memory plan fits
+    // (digit rows of 4 rows of x + partial sums + the weight ring: in_dim <= 5376); a single projection without
+    // RMSNorm prologue whose in_dim is larger is cut into column slices of 4096 whose results accumulate through
+    // the +residual epilogue (out = out + W[:, slice] x[slice]).  Everything else goes to the tiled kernel, 16 rows
+    // per pass.
+    constexpr int kStreamBatchRows = 4, kStreamBatchMaxK = 5376, kSlice = 4096;
+    int mstep = 16, kslice = K;
+    if (M > 1 && EPI != EPI_TOP1 && stream_kernel_enabled()) {
+        if (K <= kStreamBatchMaxK) {
+            mstep = kStreamBatchRows;
+        } else if (nmat == 1 && norm_w == nullptr && (EPI == EPI_STORE || EPI == EPI_RESIDUAL)) {
+            mstep = kStreamBatchRows;
+            kslice = kSlice;
         }
-        p.partial_tokens = partial_tokens;
-        p.partial_logits = partial_logits;
-        p.xc = xa.xc;
-        p.push_index = xa.xc ? xa.push_index : -1;
-        p.gather_index = xa.xc ? xa.gather_index : -1;
-        p.x_out = xa.x_out;
-        int rc = launch_linear<FMT, EPI>(stream, p, top1_count);
-        if (rc != KMLL_OK) return rc;
+    }
+    for (int m0 = 0; m0 < M; m0 += mstep) {
+        for (int k0 = 0; k0 < K; k0 += kslice) {
+            LinearParams p;
+            memset(&p, 0, sizeof(p));
+            p.x = x + (size_t)m0 * ldx + k0;
+            p.M = (M - m0) < mstep ? (M - m0) : mstep;
+            p.K = (K - k0) < kslice ? (K - k0) : kslice;
+            p.ldx = ldx;
+            p.norm_w = norm_w;
+            p.eps = eps;
+            p.nmat = nmat;
+            p.ldw = ldw > 0 ? ldw : (FMT == FMT_W4 ? K / 2 : K);
+            p.lds = lds > 0 ? lds : K / 128;
+            for (int i = 0; i < nmat; ++i) {
+                const int ldo = ldo_override > 0 ? ldo_override : mats[i].rows;
+                p.mat[i].w = reinterpret_cast<const uint8_t*>(mats[i].w) + (FMT == FMT_W4 ? k0 / 2 : k0);
+                p.mat[i].scales = FMT == FMT_W4 ? static_cast<const void*>(reinterpret_cast<const uint16_t*>(mats[i].scales) + k0 / 128)
+                                                : mats[i].scales;
+                p.mat[i].rows = mats[i].rows;
+                p.mat[i].ldo = ldo;
+                p.mat[i].out = mats[i].out ? mats[i].out + (size_t)m0 * ldo : nullptr;
+                p.mat[i].residual = mats[i].residual ? mats[i].residual + (size_t)m0 * ldo : nullptr;
+                if (k0 > 0) p.mat[i].residual = p.mat[i].out;  // later slices accumulate onto the first one's result
+            }
+            p.partial_tokens = partial_tokens;
+            p.partial_logits = partial_logits;
+            p.xc = xa.xc;
+            p.push_index = xa.xc ? xa.push_index : -1;
+            p.gather_index = xa.xc ? xa.gather_index : -1;
+            p.x_out = xa.x_out;
+            int rc;
+            if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+                rc = k0 == 0 ? launch_linear<FMT, EPI>(stream, p, top1_count) : launch_linear<FMT, EPI_RESIDUAL>(stream, p, top1_count);
+            } else {
+                rc = launch_linear<FMT, EPI>(stream, p, top1_count);
+            }
+            if (rc != KMLL_OK) return rc;
+        }
     }
     return KMLL_OK;
 }

@@ -41,6 +41,7 @@ struct StreamParams {
     int unit_start[4];
     int total_units;
     int xs_pitch;   // bytes per staged digit row of the activations
+    int ldw, lds;   // bytes per weight row and (W4) scales per weight row: larger than K implies when K is a column slice
     int off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
     uint32_t* partial_tokens;
     float* partial_logits;
@@ -111,7 +112,11 @@ __device__ inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint
 }
 
 constexpr int kSBlock = kSThreads;
-constexpr int kRedBufs = 8;  // units whose partial sums may be pending at once
+// units whose partial sums may be pending at once, and weight tile halves in flight per lane: the batch-1 form
+// takes 8 and 8 (128 KB of weights in flight per SM); the batched form (NT = 2, up to 4 rows of x, whose digit rows
+// and partial sums need more shared memory) takes 4 and 6
+__host__ __device__ constexpr int red_bufs(int nt) { return nt == 1 ? 8 : 4; }
+__host__ __device__ constexpr int ring_halves(int nt) { return nt == 1 ? 8 : 6; }
 
 __device__ inline void consumer_bar_sync() { __syncthreads(); }
 
@@ -365,7 +370,8 @@ template <int FMT, int MT, int NT, int EPI>
 __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamParams p) {
     constexpr int ROWS = 16 * MT;                       // weight rows per unit tile
     constexpr int RU = (EPI == EPI_SILU) ? 16 : ROWS;   // output rows per unit
-    constexpr int kDepth = 8 / MT;  // weight tiles in flight per lane: 256 B x 512 threads = 128 KB per SM
+    constexpr int kDepth = ring_halves(NT) / MT;  // weight tiles in flight per lane
+    constexpr int kRedBufs = red_bufs(NT);
     extern __shared__ __align__(128) unsigned char smem[];
 
     trace_stamp(p.trace, 0);
@@ -378,7 +384,8 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
     const int j0 = (warp * nseg) / kSWarps, j1 = ((warp + 1) * nseg) / kSWarps;  // this warp's K slice
     const int spu = j1 - j0;         // tiles per unit for this warp
     const int xs_pitch = p.xs_pitch;
-    const int ngr = K >> 7;  // W4 groups per row
+    const int ngr = p.lds;  // W4: binary16 scales per weight row (= groups of the whole row; K may be a column slice)
+    const int ldw = p.ldw;  // bytes per weight row
 
     int8_t* xs = reinterpret_cast<int8_t*>(smem);                       // [4*M][xs_pitch] digit rows
     float* red = reinterpret_cast<float*>(smem + p.off_red);            // [kRedBufs][kSWarps + 2][ROWS][M]
@@ -427,8 +434,8 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
             const LinearMat& m = (EPI == EPI_SILU) ? p.mat[mt] : p.mat[mi];
             const int base = (EPI == EPI_SILU) ? row0 : row0 + mt * 16;
             const int r0 = min(base + g, m.rows - 1), r1 = min(base + g + 8, m.rows - 1);
-            lw[mt][0] = m.w + (size_t)r0 * rowbytes + (size_t)j0 * 64 + t * 16;
-            lw[mt][1] = m.w + (size_t)r1 * rowbytes + (size_t)j0 * 64 + t * 16;
+            lw[mt][0] = m.w + (size_t)r0 * ldw + (size_t)j0 * 64 + t * 16;
+            lw[mt][1] = m.w + (size_t)r1 * ldw + (size_t)j0 * 64 + t * 16;
             if (FMT == FMT_W4 && (t >> 1) == mt)
                 ls_mine = reinterpret_cast<const unsigned short*>(m.scales) + (size_t)((t & 1) ? r1 : r0) * ngr + j0;
         }
