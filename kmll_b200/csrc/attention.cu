@@ -538,13 +538,21 @@ struct AttnPlan {
 
 // Split plan: a pure function of the sequence capacity, so a CUDA graph captured for a given
 // max_seq_len stays valid while the device-side sequence length grows.
-static AttnPlan plan_decode_attention(int seq_cap) {
+static AttnPlan plan_decode_attention(int seq_cap, int kv_heads_times_batch = 0) {
     AttnPlan pl;
     int nsplit = (seq_cap + 63) / 64;
     if (nsplit > 64) nsplit = 64;
+    // A batch of sequences already fills the GPU along the batch axis: aim at about two waves of blocks (2 x 296
+    // resident) with longer slices per block instead of many waves of one-tile blocks, each of which would pay the
+    // full latency chain of a block.
+    if (kv_heads_times_batch > 0) {
+        int cap = 592 / kv_heads_times_batch;
+        if (cap < 1) cap = 1;
+        if (nsplit > cap) nsplit = cap;
+    }
     if (nsplit < 1) nsplit = 1;
     int chunk = (seq_cap + nsplit - 1) / nsplit;
-    chunk = (chunk + 3) & ~3;
+    chunk = kv_heads_times_batch > 0 ? ((chunk + 63) & ~63) : ((chunk + 3) & ~3);
     pl.chunk = chunk;
     pl.nsplit = (seq_cap + chunk - 1) / chunk;
     if (pl.nsplit < 1) pl.nsplit = 1;
@@ -556,7 +564,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
                             int head_dim, float* workspace, float* out, const float* k_new, const float* v_new,
                             const float* freqs, float* k_cache_w, float* v_cache_w, int batch, size_t cache_stride) {
     const int gq = n_heads / n_kv_heads;
-    AttnPlan pl = plan_decode_attention(seq_cap);
+    AttnPlan pl = plan_decode_attention(seq_cap, batch > 1 ? n_kv_heads * batch : 0);
     DecodeAttnParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
     p.seq_len_ptr = seq_len_ptr; p.seq_len = seq_len;
@@ -572,7 +580,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.q_stride = p.out_stride = (size_t)n_heads * head_dim;
     p.new_stride = (size_t)n_kv_heads * head_dim;
     p.cache_stride = cache_stride;
-    p.ws_stride = decode_attention_workspace_floats(n_heads, head_dim, seq_cap);
+    p.ws_stride = (decode_attention_workspace_floats(n_heads, head_dim, seq_cap) + 3) & ~(size_t)3;  // keeps 16-byte alignment
     // K tile (padded rows), V tile, scores, statistics, query heads; the cross-warp reduction reuses the V tile
     // (kAttnWarps * gq <= kAttnTile rows because gq <= kMaxGq)
     const size_t smem = ((size_t)kAttnTile * (head_dim + 16) + (size_t)kAttnTile * head_dim + (size_t)kMaxGq * kAttnTile +

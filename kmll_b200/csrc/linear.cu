@@ -882,10 +882,10 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
     }
     // Batches above one row: the streaming kernel takes up to 4 rows of x per pass when its shared-memory plan fits
     // (digit rows of 4 rows of x + partial sums + the weight ring: in_dim <= 5376); a single projection without
-    // RMSNorm prologue whose in_dim is larger is cut into column slices of 4096 whose results accumulate through
+    // RMSNorm prologue whose in_dim is larger is cut into column slices of 5376 whose results accumulate through
     // the +residual epilogue (out = out + W[:, slice] x[slice]).  Everything else goes to the tiled kernel, 16 rows
     // per pass.
-    constexpr int kStreamBatchRows = 4, kStreamBatchMaxK = 5376, kSlice = 4096;
+    constexpr int kStreamBatchRows = 4, kStreamBatchMaxK = 5376, kSlice = 5376;
     int mstep = 16, kslice = K;
     if (M > 1 && EPI != EPI_TOP1 && stream_kernel_enabled()) {
         if (K <= kStreamBatchMaxK) {
