@@ -208,8 +208,10 @@ __device__ __noinline__ void gather_exchange(const TpExchange* xcp, int gather_i
     if (!good) atomicCAS(&g_device_status, 0, 2);
 }
 
-template <int FMT, bool SINGLE>
-__device__ inline float stage_activations(const StreamParams& p, int8_t* xs, float* misc) {
+// `after_loads` runs once the loads of x have been issued and before anything waits for them (the caller
+// issues the second half of its first weight copies there, so they queue behind x instead of ahead of it).
+template <int FMT, bool SINGLE, typename AfterLoads>
+__device__ inline float stage_activations(const StreamParams& p, int8_t* xs, float* misc, AfterLoads after_loads) {
     constexpr int NM = SINGLE ? 1 : 4;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int M = SINGLE ? 1 : p.M, K = p.K;
@@ -239,6 +241,7 @@ __device__ inline float stage_activations(const StreamParams& p, int8_t* xs, flo
             v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
         }
     }
+    after_loads();
     float ss[NM], mx[NM];
 #pragma unroll
     for (int mm = 0; mm < NM; ++mm) ss[mm] = mx[mm] = 0.0f;
@@ -464,13 +467,19 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
         }
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, also when nothing was left to copy
     };
+    // weights do not depend on the previous kernel: half of the ring is requested before the dependency wait, the
+    // other half right behind the loads of x (so x is not queued behind 128 KB of weights)
+    constexpr int kEarly = (kDepth + 1) / 2;
 #pragma unroll 1
-    for (int d = 0; d < kDepth; ++d) load_tile(d);  // weights do not depend on the previous kernel
+    for (int d = 0; d < kEarly; ++d) load_tile(d);
 
     // ---- stage the activations once -----------------------------------------------------------------
     pdl_wait();
     trace_stamp(p.trace, 1);
-    const float inv_xscale = stage_activations<FMT, kSingle>(p, xs, misc);
+    const float inv_xscale = stage_activations<FMT, kSingle>(p, xs, misc, [&]() {
+#pragma unroll 1
+        for (int d = kEarly; d < kDepth; ++d) load_tile(d);
+    });
     trace_stamp(p.trace, 2);
 
     // this lane's B columns: column g of each n-tile; a batch row owns 4 consecutive columns.  A lane whose
