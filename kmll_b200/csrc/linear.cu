@@ -26,6 +26,7 @@
 //     deterministic run to run.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "internal.cuh"
 
@@ -616,6 +617,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
 }  // namespace kmll
 
 #include "linear_stream.cuh"
+#include "linear_umma.cuh"
 
 namespace kmll {
 
@@ -801,6 +803,77 @@ static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) 
     return launch_variant<FMT, 1, 4, EPI, 2>(stream, p, grid);
 }
 
+// ---- tcgen05 path for batches of RS-I8 rows -----------------------------------------------------------
+// Digit scratch of the batched tensor-core path: [64 rows][kUmmaMaxK] bytes + 16 scales, allocated once per device on
+// the first batched call (the operators themselves never allocate per call).  Calls that overlap on one device from
+// different streams would share it; the decoder and the tests issue them on one stream.
+constexpr int kUmmaMaxK = 65536;
+struct UmmaScratch { uint8_t* digits = nullptr; float* inv_xscale = nullptr; };
+static int umma_scratch(UmmaScratch* out) {
+    static std::mutex mu;
+    static UmmaScratch per_device[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(KMLL_ERR_CUDA, "linear_batched: cudaGetDevice failed");
+    std::lock_guard<std::mutex> lock(mu);
+    if (per_device[dev].digits == nullptr) {
+        void* ptr = nullptr;
+        e = cudaMalloc(&ptr, (size_t)kUmmaN * kUmmaMaxK + 256);
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_batched: scratch allocation failed: %s", cudaGetErrorString(e));
+        per_device[dev].digits = static_cast<uint8_t*>(ptr);
+        per_device[dev].inv_xscale = reinterpret_cast<float*>(per_device[dev].digits + (size_t)kUmmaN * kUmmaMaxK);
+    }
+    *out = per_device[dev];
+    return KMLL_OK;
+}
+static bool umma_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("KMLL_UMMA");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+// y[m, :] (+= residual) = dequant(W_i) x[m, :] for every matrix i and up to 16 rows of x per pass
+static int run_umma_i8(cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps,
+                       const void* const* w, const void* const* scales, const int* rows, float* const* outs,
+                       const float* const* residuals, const int* ldos, int nmat) {
+    UmmaScratch sc;
+    {
+        const int rc = umma_scratch(&sc);
+        if (rc != KMLL_OK) return rc;
+    }
+    static thread_local bool configured = false;
+    const size_t smem = (size_t)kUmmaStages * (kUmmaABytes + kUmmaBBytes) + (2 * kUmmaStages + 1) * 8 + 64;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(linear_umma_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    for (int m0 = 0; m0 < M; m0 += kUmmaBatch) {
+        const int mb = (M - m0) < kUmmaBatch ? (M - m0) : kUmmaBatch;
+        cudaError_t e = launch(digitize_rows_kernel, dim3(mb), dim3(1024), 0, stream, true, x + (size_t)m0 * ldx, ldx, K, norm_w, eps,
+                               sc.digits, sc.inv_xscale);
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "digitize_rows: %s", cudaGetErrorString(e));
+        for (int i = 0; i < nmat; ++i) {
+            UmmaParams up;
+            up.w = static_cast<const int8_t*>(w[i]);
+            up.row_scales = static_cast<const float*>(scales[i]);
+            up.rows = rows[i];
+            up.K = K;
+            up.ldw = K;
+            up.digits = sc.digits;
+            up.inv_xscale = sc.inv_xscale;
+            up.batch = mb;
+            up.out = outs[i] + (size_t)m0 * ldos[i];
+            up.residual = residuals[i] ? residuals[i] + (size_t)m0 * ldos[i] : nullptr;
+            up.ldo = ldos[i];
+            e = launch(linear_umma_i8_kernel, dim3((rows[i] + kUmmaRows - 1) / kUmmaRows), dim3(kUmmaThreads), smem, stream, true, up);
+            if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_umma_i8: %s", cudaGetErrorString(e));
+        }
+    }
+    return KMLL_OK;
+}
+
 static bool fast_shape(int fmt, int K) { return fmt == FMT_W4 ? (K % 128 == 0) : (K % 64 == 0); }
 
 
@@ -878,6 +951,23 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
         } else {
             return fail(KMLL_ERR_UNSUPPORTED, "%s: in_dim=%d needs a multiple of %d and 16-byte aligned weights", name, K,
                         FMT == FMT_W4 ? 128 : 64);
+        }
+    }
+    // RS-I8 batches of 5 or more rows: the tcgen05 kernel (weights as the M side of the MMA, 16 rows of x per pass)
+    if constexpr (FMT == FMT_I8 && (EPI == EPI_STORE || EPI == EPI_RESIDUAL)) {
+        if (M > 4 && K % kUmmaKT == 0 && K <= kUmmaMaxK && ldw == 0 && (ldx & 3) == 0 && aligned16(x) &&
+            (norm_w == nullptr || (reinterpret_cast<uintptr_t>(norm_w) & 7u) == 0) && umma_enabled()) {
+            const void* w_[3];
+            const void* s_[3];
+            int rows_[3], ldos_[3];
+            float* outs_[3];
+            const float* res_[3];
+            for (int i = 0; i < nmat; ++i) {
+                w_[i] = mats[i].w; s_[i] = mats[i].scales; rows_[i] = mats[i].rows; outs_[i] = mats[i].out;
+                res_[i] = EPI == EPI_RESIDUAL ? mats[i].residual : nullptr;
+                ldos_[i] = ldo_override > 0 ? ldo_override : mats[i].rows;
+            }
+            return run_umma_i8(stream, x, M, K, ldx, norm_w, eps, w_, s_, rows_, outs_, res_, ldos_, nmat);
         }
     }
     // Batches above one row: the streaming kernel takes up to 4 rows of x per pass when its shared-memory plan fits

@@ -80,6 +80,7 @@ __device__ inline unsigned long long global_timer_ns() {
 // Bounded wait; false = timed out (the caller raises the status word and unwinds).  There is no
 // blocking hardware barrier anywhere in the kernel, so a time-out in one warp can never leave
 // another warp waiting forever.
+template <bool BACKOFF = true>
 __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
@@ -87,7 +88,7 @@ __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
-            __nanosleep(64);  // leave the issue slots to the warps that share the scheduler
+            if (BACKOFF) __nanosleep(64);  // leave the issue slots to the warps that share the scheduler
         }
         if (global_timer_ns() - t0 > kWaitLimitNs) return false;
     }
