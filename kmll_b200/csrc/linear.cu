@@ -867,6 +867,7 @@ static int run_umma_i8(cudaStream_t stream, const float* x, int M, int K, int ld
             up.out = outs[i] + (size_t)m0 * ldos[i];
             up.residual = residuals[i] ? residuals[i] + (size_t)m0 * ldos[i] : nullptr;
             up.ldo = ldos[i];
+            up.trace = trace_next_slot(300, (rows[i] + kUmmaRows - 1) / kUmmaRows);
             e = launch(linear_umma_i8_kernel, dim3((rows[i] + kUmmaRows - 1) / kUmmaRows), dim3(kUmmaThreads), smem, stream, true, up);
             if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_umma_i8: %s", cudaGetErrorString(e));
         }

@@ -14,11 +14,14 @@
 // the whole K loop live in 64 columns of tensor memory and are read once (tcgen05.ld) by the four warps
 // for the epilogue: combine the digit columns, row scale, 2^-sh, optional residual.
 //
-// Pipeline: kUmmaStages stages of (16 KB weights + 8 KB digits).  Four warps copy (each thread's copies arrive on
-// the stage's `full` mbarrier when they land), one thread of a fifth warp waits for `full`, issues the four MMAs of
-// the stage and commits them to the stage's `empty` mbarrier, which releases the stage for refilling; no block-wide
-// barrier inside the loop.  Every mbarrier wait is bounded (mbar_wait); on time-out the block raises the
-// device status word and leaves after freeing its tensor memory.
+// Pipeline: kUmmaStages stages of one k-tile each (128 weight rows x 256 bytes + 64 digit rows x 256 bytes; core
+// matrices 144 bytes apart so that a warp's 16-byte copies spread over all shared-memory banks).  Eight warps copy;
+// a copied k-tile is reported on the stage's `full` mbarrier kUmmaLag tiles later (cp.async.wait_group, then a plain
+// arrive).  One thread of a ninth warp waits for `full`, issues the proxy fence and the eight MMAs of the stage and
+// commits them to the stage's `empty` mbarrier, which releases the stage for refilling; no block-wide barrier inside
+// the loop.  Measured and rejected: an arrive-on-completion copy barrier (cp.async.mbarrier.arrive) and a proxy fence
+// in every copying thread - both serialise a thread's copies tile by tile.  Every mbarrier wait is bounded
+// (mbar_wait); on time-out the block raises the device status word and leaves after freeing its tensor memory.
 #pragma once
 
 namespace kmll {
@@ -29,10 +32,13 @@ constexpr int kUmmaN = 4 * kUmmaBatch;  // digit columns = MMA N
 constexpr int kUmmaKT = 256;      // bytes of K per stage (8 MMAs of K = 32)
 constexpr int kUmmaStages = 4;
 constexpr int kUmmaLag = 2;       // a copied k-tile is reported to the MMA thread this many k-tiles later
-constexpr int kUmmaABytes = kUmmaRows * kUmmaKT;  // 16 KB
-constexpr int kUmmaBBytes = kUmmaN * kUmmaKT;     // 8 KB
+constexpr int kUmmaABytes = (kUmmaRows / 8) * (kUmmaKT / 16) * (128 + 16);  // weight tile incl. padding
+constexpr int kUmmaBBytes = (kUmmaN / 8) * (kUmmaKT / 16) * (128 + 16);     // digit tile incl. padding
 constexpr int kUmmaLoaders = 256;  // copying threads (8 warps)
-constexpr int kUmmaSbo = (kUmmaKT / 16) * 128;  // bytes between groups of 8 rows: the core matrices of one group lie side by side
+constexpr int kUmmaLbo = 128 + 16;  // bytes between core matrices that are neighbours along K: 16 bytes of padding
+                                    // spread a warp's 16-byte copies over all shared-memory banks (with 128 the 16
+                                    // chunks of a row would all fall on the same four banks)
+constexpr int kUmmaSbo = (kUmmaKT / 16) * kUmmaLbo;  // bytes between groups of 8 rows
 constexpr int kUmmaThreads = kUmmaLoaders + 32;  // + the warp whose lane 0 issues the MMAs
 
 struct UmmaParams {
@@ -45,6 +51,8 @@ struct UmmaParams {
     float* out;               // [batch, ldo]
     const float* residual;    // [batch, ldo] or null
     int ldo;
+    unsigned long long* trace;  // timeline slot of this launch, or null (stamps: 0 entry, 1 tensor memory ready,
+                                // 2 first k-tile landed, 3 last MMA issued, 4 block done, 5 copies issued)
 };
 
 // ---- activations -> byte digits (optionally RMSNorm first), one block per row of x -------------------
@@ -148,6 +156,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
     uint64_t* empty = full + kUmmaStages;                                                                    // its MMAs completed
     uint64_t* all_done = empty + kUmmaStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
+    trace_stamp(p.trace, 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row0 = blockIdx.x * kUmmaRows;
     const int KT = p.K / kUmmaKT;
@@ -166,13 +175,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t smem_base = smem_u32(usmem);
+    trace_stamp(p.trace, 1);
     constexpr uint32_t kIdesc = umma_idesc_s8u8(kUmmaRows, kUmmaN);
 
     pdl_wait();  // the digits come from the previous kernel
     bool ok = true;
     if (warp < kUmmaLoaders / 32) {
         // ---- loader warps: thread t moves 16-byte chunk t % kChunks of rows t / kChunks + kPass * i of every k-tile.  Destination:
-        // core matrix (row / 8, chunk) at (row / 8) * kUmmaSbo + chunk * 128, row (row % 8) of it at + (row % 8) * 16.
+        // core matrix (row / 8, chunk) at (row / 8) * kUmmaSbo + chunk * kUmmaLbo, row (row % 8) of it at + (row % 8) * 16.
         constexpr int kChunks = kUmmaKT / 16, kPass = kUmmaLoaders / kChunks;  // 16-byte chunks per row, rows per pass
         const int chunk = tid % kChunks, rsub = tid / kChunks;
 #pragma unroll 1
@@ -186,27 +196,27 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
             for (int i = 0; i < kUmmaRows / kPass; ++i) {
                 const int r = rsub + kPass * i;
                 const int row = min(row0 + r, p.rows - 1);
-                cp_async16_ca(a_dst + (uint32_t)((r >> 3) * kUmmaSbo + chunk * 128 + (r & 7) * 16), p.w + (size_t)row * p.ldw + koff);
+                cp_async16_ca(a_dst + (uint32_t)((r >> 3) * kUmmaSbo + chunk * kUmmaLbo + (r & 7) * 16), p.w + (size_t)row * p.ldw + koff);
             }
 #pragma unroll
             for (int i = 0; i < (kUmmaN + kPass - 1) / kPass; ++i) {
                 const int r = rsub + kPass * i;
                 if (r >= kUmmaN) break;
                 const int drow = min(r, 4 * p.batch - 1);  // columns of absent batch rows repeat a valid one and are ignored
-                cp_async16_ca(b_dst + (uint32_t)((r >> 3) * kUmmaSbo + chunk * 128 + (r & 7) * 16), p.digits + (size_t)drow * p.K + koff);
+                cp_async16_ca(b_dst + (uint32_t)((r >> 3) * kUmmaSbo + chunk * kUmmaLbo + (r & 7) * 16), p.digits + (size_t)drow * p.K + koff);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
-            // k-tile kt - kUmmaLag has landed (for this thread): make it visible to the tensor core's proxy and report it.
+            // k-tile kt - kUmmaLag has landed (for this thread): report it.  A proxy fence here, in every copying thread, was
+            // measured to wait for ALL of the thread's copies in flight and so to serialise the tiles.
             // (An arrive-on-completion copy barrier was measured to serialise a warp's copies tile by tile.)
             if (kt >= kUmmaLag) {
                 asm volatile("cp.async.wait_group %0;" ::"n"(kUmmaLag) : "memory");
-                fence_proxy_async_smem();
-                mbar_arrive(&full[(kt - kUmmaLag) % kUmmaStages]);
+                mbar_arrive(&full[(kt - kUmmaLag) % kUmmaStages]);  // (the MMA thread issues the proxy fence)
             }
         }
+        trace_stamp(p.trace, 5);
         // drain: the last kUmmaLag k-tiles
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        fence_proxy_async_smem();
         if (ok)
             for (int kt = (KT > kUmmaLag ? KT - kUmmaLag : 0); kt < KT; ++kt) mbar_arrive(&full[kt % kUmmaStages]);
     } else if (lane == 0) {
@@ -215,19 +225,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
         for (int kt = 0; kt < KT; ++kt) {
             const int stage = kt % kUmmaStages, use = kt / kUmmaStages;
             if (!mbar_wait<false>(&full[stage], (uint32_t)use & 1u)) { ok = false; break; }
+            if (kt == 0 && p.trace != nullptr) trace_stamp_latest(p.trace, 2);
             fence_proxy_async_smem();  // the copies went through the generic proxy; the tensor core reads through the async proxy
             tcgen05_fence_after();
             const uint32_t a_addr = smem_base + (uint32_t)stage * (kUmmaABytes + kUmmaBBytes);
             const uint32_t b_addr = a_addr + kUmmaABytes;
 #pragma unroll
             for (int ks = 0; ks < kUmmaKT / 32; ++ks) {
-                const uint64_t da = umma_smem_desc(a_addr + ks * 256, 128, kUmmaSbo);
-                const uint64_t db = umma_smem_desc(b_addr + ks * 256, 128, kUmmaSbo);
+                const uint64_t da = umma_smem_desc(a_addr + ks * 2 * kUmmaLbo, kUmmaLbo, kUmmaSbo);
+                const uint64_t db = umma_smem_desc(b_addr + ks * 2 * kUmmaLbo, kUmmaLbo, kUmmaSbo);
                 umma_mma_i8(tmem_base, da, db, kIdesc, (kt > 0 || ks > 0) ? 1u : 0u);
             }
             umma_commit(&empty[stage]);  // arrives when the MMAs issued so far have completed: the stage may be refilled
         }
         if (ok) umma_commit(all_done);
+        if (p.trace != nullptr) trace_stamp_latest(p.trace, 3);
     }
     // ---- epilogue (warps 0..3; warp w reads tensor-memory lanes 32 w .. 32 w + 31)
     if (warp < 4) {
@@ -258,6 +270,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
     }
     tcgen05_fence_before();
     __syncthreads();
+    trace_stamp(p.trace, 4);
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kUmmaN) : "memory");
     if (!ok) atomicCAS(&g_device_status, 0, 1);
 }
