@@ -191,7 +191,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
             if (use > 0 && !mbar_wait<false>(&empty[stage], (uint32_t)(use - 1) & 1u)) { ok = false; break; }
             const uint32_t a_dst = smem_base + (uint32_t)stage * (kUmmaABytes + kUmmaBBytes);
             const uint32_t b_dst = a_dst + kUmmaABytes;
-            const size_t koff = (size_t)kt * kUmmaKT + (size_t)chunk * 16;
+            // Blocks walk K from staggered starting points (integer accumulation does not depend on the order): with
+            // every block on the same k-tile at the same time, all rows' addresses would agree modulo the row pitch
+            // and crowd onto a few memory channels.
+            const int kt_eff = (kt + (int)blockIdx.x * 5) % KT;
+            const size_t koff = (size_t)kt_eff * kUmmaKT + (size_t)chunk * 16;
 #pragma unroll
             for (int i = 0; i < kUmmaRows / kPass; ++i) {
                 const int r = rsub + kPass * i;
