@@ -808,7 +808,8 @@ static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) 
 // the first batched call (the operators themselves never allocate per call).  Calls that overlap on one device from
 // different streams would share it; the decoder and the tests issue them on one stream.
 constexpr int kUmmaMaxK = 65536;
-struct UmmaScratch { uint8_t* digits = nullptr; float* inv_xscale = nullptr; };
+constexpr int kUmmaSplitTiles = 74, kUmmaMaxSplit = 4;  // split-K only for row counts up to 74 * 128
+struct UmmaScratch { uint8_t* digits = nullptr; float* inv_xscale = nullptr; float* partial = nullptr; unsigned int* counters = nullptr; };
 static int umma_scratch(UmmaScratch* out) {
     static std::mutex mu;
     static UmmaScratch per_device[64];
@@ -818,10 +819,16 @@ static int umma_scratch(UmmaScratch* out) {
     std::lock_guard<std::mutex> lock(mu);
     if (per_device[dev].digits == nullptr) {
         void* ptr = nullptr;
-        e = cudaMalloc(&ptr, (size_t)kUmmaN * kUmmaMaxK + 256);
+        const size_t digit_bytes = (size_t)kUmmaN * kUmmaMaxK;
+        const size_t partial_bytes = (size_t)kUmmaSplitTiles * kUmmaMaxSplit * kUmmaBatch * kUmmaRows * sizeof(float);
+        e = cudaMalloc(&ptr, digit_bytes + 256 + partial_bytes + 1024);
         if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_batched: scratch allocation failed: %s", cudaGetErrorString(e));
         per_device[dev].digits = static_cast<uint8_t*>(ptr);
-        per_device[dev].inv_xscale = reinterpret_cast<float*>(per_device[dev].digits + (size_t)kUmmaN * kUmmaMaxK);
+        per_device[dev].inv_xscale = reinterpret_cast<float*>(per_device[dev].digits + digit_bytes);
+        per_device[dev].partial = reinterpret_cast<float*>(per_device[dev].digits + digit_bytes + 256);
+        per_device[dev].counters = reinterpret_cast<unsigned int*>(per_device[dev].digits + digit_bytes + 256 + partial_bytes);
+        e = cudaMemset(per_device[dev].counters, 0, 1024);
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_batched: scratch initialisation failed: %s", cudaGetErrorString(e));
     }
     *out = per_device[dev];
     return KMLL_OK;
@@ -867,8 +874,20 @@ static int run_umma_i8(cudaStream_t stream, const float* x, int M, int K, int ld
             up.out = outs[i] + (size_t)m0 * ldos[i];
             up.residual = residuals[i] ? residuals[i] + (size_t)m0 * ldos[i] : nullptr;
             up.ldo = ldos[i];
-            up.trace = trace_next_slot(300, (rows[i] + kUmmaRows - 1) / kUmmaRows);
-            e = launch(linear_umma_i8_kernel, dim3((rows[i] + kUmmaRows - 1) / kUmmaRows), dim3(kUmmaThreads), smem, stream, true, up);
+            // few row tiles: split K over up to 4 blocks per tile (at least 4 k-tiles each) so that more SMs stream
+            const int tiles = (rows[i] + kUmmaRows - 1) / kUmmaRows;
+            int ksplit = 1;
+            if (tiles <= kUmmaSplitTiles) {
+                ksplit = 148 / tiles;
+                if (ksplit > kUmmaMaxSplit) ksplit = kUmmaMaxSplit;
+                const int by_k = (K / kUmmaKT) / 4;
+                if (ksplit > by_k) ksplit = by_k;
+                if (ksplit < 1) ksplit = 1;
+            }
+            up.partial = sc.partial;
+            up.counters = sc.counters;
+            up.trace = trace_next_slot(300, tiles * ksplit);
+            e = launch(linear_umma_i8_kernel, dim3(tiles, ksplit), dim3(kUmmaThreads), smem, stream, true, up);
             if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_umma_i8: %s", cudaGetErrorString(e));
         }
     }

@@ -51,6 +51,8 @@ struct UmmaParams {
     float* out;               // [batch, ldo]
     const float* residual;    // [batch, ldo] or null
     int ldo;
+    float* partial;           // split-K: [row tiles][gridDim.y][kUmmaBatch][kUmmaRows] digit-combined partial sums
+    unsigned int* counters;   // split-K: [row tiles] arrivals, zero between launches
     unsigned long long* trace;  // timeline slot of this launch, or null (stamps: 0 entry, 1 tensor memory ready,
                                 // 2 first k-tile landed, 3 last MMA issued, 4 block done, 5 copies issued)
 };
@@ -159,7 +161,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
     trace_stamp(p.trace, 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row0 = blockIdx.x * kUmmaRows;
-    const int KT = p.K / kUmmaKT;
+    // split-K: blockIdx.y takes k-tiles [kt0, kt0 + KT) of the row; the blocks of a row tile meet in the epilogue
+    const int kt_all = p.K / kUmmaKT;
+    const int kt_per = (kt_all + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int kt0 = (int)blockIdx.y * kt_per;
+    const int KT = max(0, min(kt_per, kt_all - kt0));
 
     if (tid == 0) {
         for (int s = 0; s < kUmmaStages; ++s) { mbar_init(&full[s], kUmmaLoaders); mbar_init(&empty[s], 1); }
@@ -194,7 +200,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
             // Blocks walk K from staggered starting points (integer accumulation does not depend on the order): with
             // every block on the same k-tile at the same time, all rows' addresses would agree modulo the row pitch
             // and crowd onto a few memory channels.
-            const int kt_eff = (kt + (int)blockIdx.x * 5) % KT;
+            const int kt_eff = kt0 + (kt + (int)blockIdx.x * 5) % KT;
             const size_t koff = (size_t)kt_eff * kUmmaKT + (size_t)chunk * 16;
 #pragma unroll
             for (int i = 0; i < kUmmaRows / kPass; ++i) {
@@ -246,30 +252,69 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
         if (p.trace != nullptr) trace_stamp_latest(p.trace, 3);
     }
     // ---- epilogue (warps 0..3; warp w reads tensor-memory lanes 32 w .. 32 w + 31)
+    __shared__ bool is_last;
+    const bool split = gridDim.y > 1;
     if (warp < 4) {
         if (ok && KT > 0 && !mbar_wait<false>(all_done, 0u)) ok = false;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         tcgen05_fence_after();
         if (ok) {
-            const int row = row0 + warp * 32 + lane;
+            const int rl = warp * 32 + lane;  // row inside the tile
+            const int row = row0 + rl;
             const float rs = row < p.rows ? p.row_scales[row] : 0.0f;
+            float* part = split ? p.partial + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * kUmmaBatch * kUmmaRows : nullptr;
 #pragma unroll
             for (int c0 = 0; c0 < kUmmaN; c0 += 16) {
                 uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (KT > 0) {
+                    tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) r[q] = 0u;
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int b = c0 / 4 + j;
-                    if (b < p.batch && row < p.rows) {
-                        const int u0 = (int)r[4 * j], u1 = (int)r[4 * j + 1], top = (int)r[4 * j + 2], ones = (int)r[4 * j + 3];
-                        float v = ((float)u0 + 256.0f * (float)u1 + 65536.0f * (float)(top - 64 * ones)) * p.inv_xscale[b] * rs;
+                    const int u0 = (int)r[4 * j], u1 = (int)r[4 * j + 1], top = (int)r[4 * j + 2], ones = (int)r[4 * j + 3];
+                    const float comb = (float)u0 + 256.0f * (float)u1 + 65536.0f * (float)(top - 64 * ones);
+                    if (split) {
+                        part[b * kUmmaRows + rl] = comb;  // scales and residual are applied after the merge
+                    } else if (b < p.batch && row < p.rows) {
+                        float v = comb * p.inv_xscale[b] * rs;
                         const size_t o = (size_t)b * p.ldo + row;
                         if (p.residual != nullptr) v = p.residual[o] + v;
                         p.out[o] = v;
                     }
                 }
             }
+        }
+    }
+    if (split) {
+        // the block that delivers last adds the partial sums of the row tile in blockIdx.y order and finishes the rows
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int prev = atomicAdd(&p.counters[blockIdx.x], 1u);
+            is_last = prev == gridDim.y - 1;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            const float* base = p.partial + (size_t)blockIdx.x * gridDim.y * kUmmaBatch * kUmmaRows;
+            for (int idx = tid; idx < p.batch * kUmmaRows; idx += kUmmaThreads) {
+                const int b = idx / kUmmaRows, rl = idx - b * kUmmaRows;
+                const int row = row0 + rl;
+                if (row < p.rows) {
+                    float acc = 0.0f;
+                    for (int z = 0; z < (int)gridDim.y; ++z) acc += __ldcg(base + ((size_t)z * kUmmaBatch + b) * kUmmaRows + rl);
+                    float v = acc * p.inv_xscale[b] * p.row_scales[row];
+                    const size_t o = (size_t)b * p.ldo + row;
+                    if (p.residual != nullptr) v = p.residual[o] + v;
+                    p.out[o] = v;
+                }
+            }
+            if (tid == 0) p.counters[blockIdx.x] = 0u;  // ready for the next launch
         }
     }
     tcgen05_fence_before();

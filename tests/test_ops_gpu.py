@@ -273,6 +273,21 @@ def test_linear_batched_vs_oracle(cuda, fmt, batch):
     assert_close(host(ops.linear_batched(dev(x), w, batch, cols, rows)), ref, cols, f"batched {fmt} {batch}")
 
 
+@pytest.mark.parametrize("batch", [9, 33])
+def test_linear_batched_i8_split_k(cuda, batch):
+    """Few row tiles and a long K: the tensor-core kernel splits K over several blocks per row tile and the block that
+    arrives last merges the partial sums; two calls in a row check that the arrival counters are left at zero."""
+    rng = np.random.default_rng(700 + batch)
+    rows, cols = 700, 4096
+    x = rng.normal(0, 1, (batch, cols)).astype(F)
+    _, q, sc, w = i8_weight(rng, rows, cols)
+    ref = oracle.rs_i8_linear_batched(x, q, sc)
+    first = host(ops.linear_batched(dev(x), w, batch, cols, rows))
+    second = host(ops.linear_batched(dev(x), w, batch, cols, rows))
+    assert_close(first, ref, cols, f"split-k i8 {batch}")
+    assert np.array_equal(first, second)
+
+
 def test_linear_batched_large_k_chunks_and_qkv(cuda):
     rng = np.random.default_rng(9)
     batch, cols = 16, 4096  # 16 rows x 4096 forces several K chunks
