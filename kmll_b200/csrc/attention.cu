@@ -382,6 +382,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     float* f_s = Ks + 2 * GQM * 64;      // [gq][nsplit] weights, then [gq] denominators after them
     float* l_s = f_s + GQM * 64;
     const int ns = nactive;  // only these splits wrote partials
+    // the first round of partial accumulators (splits w, w+8, w+16, w+24) is requested before the statistics are even
+    // loaded, so that both L2 round trips overlap (only where the registers allow it: 4 heads x 4 floats per lane)
+    constexpr bool kHoist = (GQM == 4 && EPL == 4);
+    float4 early[kHoist ? 4 : 1][kHoist ? GQM : 1];
+    if (kHoist) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sp = warp + kAttnWarps * i;
+#pragma unroll
+            for (int h = 0; h < GQM; ++h) {
+                early[kHoist ? i : 0][kHoist ? h : 0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (h < gq && sp < ns)
+                    early[kHoist ? i : 0][kHoist ? h : 0] = __ldcg(reinterpret_cast<const float4*>(
+                        p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + sp) * HD + lane * EPL));
+            }
+        }
+    }
 #pragma unroll 1
     for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
         const int h = idx / (ns * 2), r = idx - h * ns * 2;
@@ -405,8 +422,24 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     for (int h = 0; h < GQM; ++h)
 #pragma unroll
         for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
+    if (kHoist) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sp = warp + kAttnWarps * i;
+#pragma unroll
+            for (int h = 0; h < GQM; ++h)
+                if (h < gq && sp < ns) {
+                    const float4 t4 = early[kHoist ? i : 0][kHoist ? h : 0];
+                    const float f = f_s[h * ns + sp];
+                    acc[h][0] = fmaf(t4.x, f, acc[h][0]);
+                    acc[h][1] = fmaf(t4.y, f, acc[h][1]);
+                    acc[h][EPL - 2] = fmaf(t4.z, f, acc[h][EPL - 2]);
+                    acc[h][EPL - 1] = fmaf(t4.w, f, acc[h][EPL - 1]);
+                }
+        }
+    }
 #pragma unroll(GQM == 4 ? 4 : 2)
-    for (int s = warp; s < ns; s += kAttnWarps) {
+    for (int s = warp + (kHoist ? 4 * kAttnWarps : 0); s < ns; s += kAttnWarps) {
 #pragma unroll
         for (int h = 0; h < GQM; ++h)
             if (h < gq) {
