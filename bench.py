@@ -92,65 +92,99 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of kmll's CPU path (rowwise_scaled.rs:108-126 applied to W4-G128) timed on the
-# host cores over a bounded sample of the same workload.
+# host cores over whole decode steps of the same workload (all 32 layers and the lm_head, context 2048+).
 # ---------------------------------------------------------------------------------------------------
-def cpu_sample(steps: int, warmup: int):
-    import numpy as np
+def cpu_threads(requested: int) -> int:
+    """Threads for the CPU arm: an explicit request, else every core this process may run on (a launcher may have
+    set OMP_NUM_THREADS=1 for its ranks; the CPU arm is one process and takes the whole host)."""
+    if requested > 0:
+        return requested
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
+
+class CpuModel:
+    """Mistral-7B-architecture decoder with W4-G128 weights on the host, built from the oracle's C functions
+    (kmll's operator order, crates/inference/src/model.rs:10102-10300).  Weight bytes are random: throughput does
+    not depend on their values."""
+
+    def __init__(self, ctx: int):
+        import numpy as np
+
+        import oracle
+        self.np, self.o = np, oracle
+        rng = np.random.default_rng(SEED)
+        self.dim, self.q, self.kv, self.hid, self.vocab, self.hd, self.layers_n = 4096, 4096, 1024, 14336, 32000, 128, 32
+        block = rng.integers(0, 256, 1 << 22, dtype=np.uint8)  # 4 MiB of random nibble pairs, tiled into every tensor
+        fblock = rng.normal(0, 1, 1 << 20).astype(np.float32)
+
+        def tiled(src, n, dtype):
+            out = np.empty(n, dtype=dtype)
+            full = n // src.size
+            if full:
+                out[:full * src.size].reshape(full, src.size)[:] = src
+            out[full * src.size:] = src[:n - full * src.size]
+            return out
+
+        def qw(rows, cols):
+            return (tiled(block, rows * cols // 2, np.uint8).reshape(rows, cols // 2),
+                    tiled(block[:1 << 16].astype(np.uint16) % 0x800 + 0x1C00, rows * (cols // 128), np.uint16).reshape(rows, cols // 128))
+
+        def kv():
+            return tiled(fblock, ctx * 8 * self.hd, np.float32).reshape(ctx, 8, self.hd)
+
+        self.layers = [{"wq": qw(self.q, self.dim), "wk": qw(self.kv, self.dim), "wv": qw(self.kv, self.dim), "wo": qw(self.dim, self.q),
+                        "w1": qw(self.hid, self.dim), "w3": qw(self.hid, self.dim), "w2": qw(self.dim, self.hid), "k": kv(), "v": kv()}
+                       for _ in range(self.layers_n)]
+        self.head = qw(self.vocab, self.dim)
+        self.gamma = oracle.bf16_from_f32(np.ones(self.dim, dtype=np.float32))
+        self.freqs = oracle.rope_frequencies(1e6, self.hd)
+        self.embedding = oracle.bf16_from_f32(rng.normal(0, 0.02, (1024, self.dim)).astype(np.float32))
+
+    def step(self, token: int, pos: int) -> int:
+        o = self.o
+        h = o.embedding(self.embedding, token % 1024)
+        for L in self.layers:
+            n = o.rmsnorm(h, self.gamma, 1e-5)
+            qv, kvv, vv = o.w4_matvec(*L["wq"], n), o.w4_matvec(*L["wk"], n), o.w4_matvec(*L["wv"], n)
+            qr = o.apply_rope(qv, self.freqs, pos, self.hd)
+            L["k"][pos] = o.apply_rope(kvv, self.freqs, pos, self.hd).reshape(8, self.hd)
+            L["v"][pos] = vv.reshape(8, self.hd)
+            a = o.single_query_attention(qr, L["k"], L["v"], pos + 1, 32, 8, self.hd)
+            h2 = o.add(h, o.w4_matvec(*L["wo"], a))
+            n2 = o.rmsnorm(h2, self.gamma, 1e-5)
+            act = o.silu_mul(o.w4_matvec(*L["w1"], n2), o.w4_matvec(*L["w3"], n2))
+            h = o.add(h2, o.w4_matvec(*L["w2"], act))
+        return o.unpack_top1(o.top1_packed(o.w4_matvec(*self.head, o.rmsnorm(h, self.gamma, 1e-5))))[0]
+
+
+def cpu_sample(steps: int, warmup: int, threads: int, budget_s: float):
+    """Whole decode steps on the host.  The number of timed steps is cut so that the run stays near budget_s."""
     import oracle
+    oracle.set_threads(threads)
     cores = oracle.max_threads()
-    rng = np.random.default_rng(SEED)
-    dim, q, kv, hid, vocab, hd, ctx = 4096, 4096, 1024, 14336, 32000, 128, PROMPT_LEN
-
-    def qw(rows, cols):
-        return (rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8), rng.integers(0x1C00, 0x2400, (rows, cols // 128)).astype(np.uint16))
-
-    layer = {"wq": qw(q, dim), "wk": qw(kv, dim), "wv": qw(kv, dim), "wo": qw(dim, q), "w1": qw(hid, dim), "w3": qw(hid, dim),
-             "w2": qw(dim, hid)}
-    head = qw(vocab, dim)
-    gamma = oracle.bf16_from_f32(np.ones(dim, dtype=np.float32))
-    kc = rng.normal(0, 1, (ctx + 1, 8, hd)).astype(np.float32)
-    vc = rng.normal(0, 1, (ctx + 1, 8, hd)).astype(np.float32)
-    freqs = oracle.rope_frequencies(1e6, hd)
-    x = rng.normal(0, 1, dim).astype(np.float32)
-
-    def one_layer(h):
-        n = oracle.rmsnorm(h, gamma, 1e-5)
-        qv, kvv, vv = oracle.w4_matvec(*layer["wq"], n), oracle.w4_matvec(*layer["wk"], n), oracle.w4_matvec(*layer["wv"], n)
-        qr = oracle.apply_rope(qv, freqs, ctx, hd)
-        kc[ctx] = oracle.apply_rope(kvv, freqs, ctx, hd).reshape(8, hd)
-        vc[ctx] = vv.reshape(8, hd)
-        a = oracle.single_query_attention(qr, kc, vc, ctx + 1, 32, 8, hd)
-        h2 = oracle.add(h, oracle.w4_matvec(*layer["wo"], a))
-        n2 = oracle.rmsnorm(h2, gamma, 1e-5)
-        act = oracle.silu_mul(oracle.w4_matvec(*layer["w1"], n2), oracle.w4_matvec(*layer["w3"], n2))
-        return oracle.add(h2, oracle.w4_matvec(*layer["w2"], act))
-
-    def one_head(h):
-        return oracle.top1_packed(oracle.w4_matvec(*head, oracle.rmsnorm(h, gamma, 1e-5)))
-
-    for _ in range(max(1, warmup)):
-        one_layer(x)
+    model = CpuModel(PROMPT_LEN + warmup + steps + 2)
+    pos, token = PROMPT_LEN, 1
     t0 = time.perf_counter()
-    one_layer(x)
-    probe = time.perf_counter() - t0
-    target = max(4, min(256, int(12.0 / max(probe, 1e-3))))  # about 12 s of CPU work
+    token = model.step(token, pos)
+    pos += 1
+    first = time.perf_counter() - t0
+    for _ in range(max(0, min(warmup - 1, int(budget_s / 4 / max(first, 1e-3))))):
+        token = model.step(token, pos)
+        pos += 1
+    run = max(1, min(steps, int(budget_s / max(first, 1e-3))))
     t0 = time.perf_counter()
-    reps = 0
-    while reps < max(steps, target):
-        one_layer(x)
-        reps += 1
-    t_layer = (time.perf_counter() - t0) / reps
-    one_head(x)
-    t0 = time.perf_counter()
-    hreps = max(1, min(steps, 4))
-    for _ in range(hreps):
-        one_head(x)
-    t_head = (time.perf_counter() - t0) / hreps
-    t_token = 32 * t_layer + t_head
-    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"1 of 32 decoder layers (W4-G128 matvecs, RMSNorm, RoPE, attention over {ctx + 1} positions, SwiGLU) x{reps} "
-                      f"and the lm_head arg-max x{hreps}, extrapolated to 32 layers; oracle C code, OpenMP over rows",
+    for _ in range(run):
+        token = model.step(token, pos)
+        pos += 1
+    seconds = time.perf_counter() - t0
+    t_token = seconds / run
+    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": cores, "kind": "port", "steps_run": run, "seconds_measured": seconds,
+            "extrapolated": False,
+            "sample": f"{run} whole decode steps (32 layers of W4-G128 matvecs, RMSNorm, RoPE, attention over {PROMPT_LEN}+ positions, SwiGLU, "
+                      f"and the lm_head arg-max) in {seconds:.1f} s; oracle C code, OpenMP over rows, {cores} threads",
             "ms_per_token": t_token * 1e3}
 
 
@@ -158,10 +192,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 16))
-    cb = cpu_sample(steps, max(1, min(args.warmup, 2)))
+    cb = cpu_sample(args.steps, args.warmup, cpu_threads(args.cpu_threads), 40.0)
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": cb["ms_per_token"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "steps_run": cb["steps_run"], "warmup": args.warmup, "ms_per_step": cb["ms_per_token"], "seconds_measured": cb["seconds_measured"],
+            "extrapolated": False, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int4 weights x f32 activations, f32 accumulate (CPU)", "data": "synthetic",
             "config": workload_config(args.gpus),
             "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -174,6 +208,29 @@ def workload_config(n_gpus):
                         "f32 KV cache, full causal attention (window 4096 never truncates)",
             "layers": 32, "dim": 4096, "heads": "32q/8kv x128", "hidden": 14336, "vocab": 32000, "prompt_len": PROMPT_LEN,
             "parallelism": f"tp{n_gpus}", "l2_policy": "inputs larger than L2 (3.67 GB of weights per step vs 126 MB L2)"}
+
+
+def device_status() -> int:
+    """0 unless a bounded wait inside a kernel gave up (1) or a tensor-parallel peer did not deliver in time (2)."""
+    import ctypes as C
+
+    from kmll_b200 import lib as klib
+    status = C.c_int(-1)
+    klib.check(klib.load().kmll_device_status(C.byref(status)))
+    return int(status.value)
+
+
+def same_greedy_run(tokens, logits, ref_tokens, ref_logits, rel_tol=1e-3):
+    """(ok, step of a near-tie or None).  Two greedy runs of the same model agree when their tokens are identical, or
+    differ for the first time at a step where both chosen logits lie within rel_tol of each other (a near-tie: either
+    token is a faithful arg-max; later steps then legitimately diverge)."""
+    for i, (a, b) in enumerate(zip(tokens, ref_tokens)):
+        la, lb = float(logits[i]), float(ref_logits[i])
+        if int(a) != int(b):
+            return abs(la - lb) <= rel_tol * max(1.0, abs(lb)), i
+        if abs(la - lb) > rel_tol * max(1.0, abs(lb)):
+            return False, i
+    return True, None
 
 
 def run_ours(args):
@@ -241,21 +298,29 @@ def run_ours(args):
         torch.cuda.profiler.stop()
     clocks = sampler.stop()
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
+    # what the loop generated: entry i = (token, logit) consumed by step i since the prefill
+    dev_tokens, dev_logits = dec.history(0, W + K)
 
     # ---- end to end through the public per-token API: token from host memory, packed result back ----
+    first_packed = (int(dev_logits[:1].view(np.uint32)[0]) << 32) | int(dev_tokens[0])
     dec.rewind(start_pos - W)
+    dec.set_pending(first_packed)
     packed = dec.next_top()
+    host_tokens = []
     for _ in range(W):
+        host_tokens.append(packed & 0xFFFFFFFF)
         packed = dec.step_host(packed & 0xFFFFFFFF)
     barrier()
-    t0 = time.perf_counter()
     e0.record()
     for _ in range(K):
+        host_tokens.append(packed & 0xFFFFFFFF)
         packed = dec.step_host(packed & 0xFFFFFFFF)
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
     launches = dec.launches_per_step * K
+    check = {"device_status": device_status(), "first_tokens": [int(t) for t in dev_tokens[W:W + 8]],
+             "host_loop_tokens_match_device_loop": [int(t) for t in dev_tokens] == [int(t) for t in host_tokens]}
 
     # ---- batch 16 (one GPU): 16 sequences in lockstep share every weight read.  The prefilled sequence is adopted
     # into all 16 slots (identical prompts: throughput does not depend on the token values) -----------------------
@@ -264,10 +329,12 @@ def run_ours(args):
         B = 16
         steps16 = max(4, min(K, 32))
         dec.rewind(start_pos - W)
+        dec.set_pending(first_packed)
         bd = rt.BatchDecoder(dec, B)
         for slot in range(B):
             bd.adopt(slot)
-        bd.enqueue_steps(3)
+        t16, l16 = bd.generate_greedy(3)  # warm-up steps, also a check: every slot holds the batch-1 sequence
+        check["batch16_tokens_match_batch1"] = all(same_greedy_run(t16[slot], l16[slot], dev_tokens[:3], dev_logits[:3])[0] for slot in range(B))
         torch.cuda.synchronize()
         e0.record()
         bd.enqueue_steps(steps16)
@@ -343,14 +410,33 @@ def run_ours(args):
     if batch16 is not None:
         line["batch16"] = batch16
     if rank == 0 and world == 1 and not args.no_cpu:
-        cb = cpu_sample(8, 1)
+        cb = cpu_sample(8, 1, cpu_threads(args.cpu_threads), 12.0)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    # ---- tensor parallel: rank 0 decodes the same prompt once more on a single-GPU decoder (same seed, so the same
+    # quantized tensors; untimed) and the generated tokens must agree -----------------------------------------
+    if world > 1:
+        statuses = [None] * world
+        dist.all_gather_object(statuses, check["device_status"])
+        check["device_status"] = max(statuses)
+        if rank == 0:
+            ref = rt.Decoder(rt.DecoderConfig.mistral_7b(max_seq_len=max_seq, format=rt.FORMAT_W4G128))
+            ref.init_random(SEED, 0.02, False)
+            ref.prefill(prompt)
+            ref_tokens, ref_logits = ref.generate_greedy(W + K)
+            ref.close()
+            same, where = same_greedy_run(dev_tokens, dev_logits, ref_tokens, ref_logits)
+            check["tokens_match_tp1"] = same
+            check["near_tie_at_step"] = where
+    line["check"] = check
+    ok = check["device_status"] == 0 and check["host_loop_tokens_match_device_loop"] and check.get("tokens_match_tp1", True)
     if rank == 0:
         print(json.dumps(line))
     dec.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("bench: the generated tokens failed their check (see \"check\" in the line above)")
 
 
 def main():
@@ -360,6 +446,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-threads", type=int, default=0, help="threads of the CPU arm (default: every core of the host)")
     ap.add_argument("--no-batch16", action="store_true", help="skip the batch-16 leg")
     ap.add_argument("--profile", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()

@@ -62,7 +62,10 @@ int kmll_compiled_arch(void);
  * blocks*6 64-bit words in it, and thread 0 of each block writes the device clock (%globaltimer, ns)
  * at six points: 0 entry, 1 dependency wait passed, 2 inputs staged, 3 main loop done, 4 block done,
  * 5 unused.  Launches recorded into a CUDA graph keep their slots across replays.  Attach a null
- * buffer to stop.  kernel_id: 100 + 10*format + epilogue for the linear kernel, 200 for attention. */
+ * buffer to stop.  The decoders of kmll_b200_runtime.h capture their per-token graph again after every
+ * attach or detach, so their replays never write to a detached buffer; a graph the CALLER captured while a
+ * buffer was attached keeps writing to it, so that buffer must outlive the graph.
+ * kernel_id: 100 + 10*format + epilogue for the linear kernel, 200 for attention. */
 int kmll_trace_attach(void* device_buffer, size_t bytes);
 int kmll_trace_launches(int* kernel_ids, int* blocks, size_t* offset_words, int max_launches, int* count_out);
 

@@ -108,6 +108,10 @@ int kmll_decoder_generate_greedy(kmll_decoder_t dec, kmll_stream_t stream, int n
                                  uint32_t* tokens_out, float* logits_out);
 /* The same steps without waiting and without reading anything back (timing loops). */
 int kmll_decoder_enqueue_steps(kmll_decoder_t dec, kmll_stream_t stream, int n_steps);
+/* The device keeps the packed (logit, token) of every step since the last prefill / rewind / generate_greedy:
+ * packed_out[i] = entry first + i (the token step first + i consumed).  Lets a timing loop built on
+ * kmll_decoder_enqueue_steps check afterwards what it generated.  Synchronises the stream. */
+int kmll_decoder_history(kmll_decoder_t dec, kmll_stream_t stream, int first, int count, uint64_t* packed_out);
 /* One step the way kmll's host loop does it: the token comes from host memory, the packed
  * (logit, token) result is copied back and the stream is synchronised
  * (crates/inference/src/model.rs:10655).  *packed_out = (f32 bits << 32) | next token. */
@@ -119,6 +123,9 @@ int kmll_decoder_next_top(kmll_decoder_t dec, kmll_stream_t stream, uint64_t* pa
 /* Truncate the sequence to `position` tokens (<= current position); the pending token is kept.  Used to
  * replay the same positions again (timing legs, speculative roll-back). */
 int kmll_decoder_rewind(kmll_decoder_t dec, kmll_stream_t stream, int position);
+/* Replace the pending token (packed (f32 bits << 32) | token) that the next step will consume; with kmll_decoder_rewind
+ * this replays a recorded continuation from an earlier position. */
+int kmll_decoder_set_pending(kmll_decoder_t dec, kmll_stream_t stream, uint64_t packed);
 /* Number of tokens in the sequence (= next position). */
 int kmll_decoder_position(kmll_decoder_t dec);
 /* Final hidden state of the last forward [dim] to host (parity checks); synchronises. */

@@ -135,6 +135,10 @@ __device__ inline void pdl_wait() {
 // and every replay overwrites the same words.  With no buffer attached the kernels get a null pointer.
 constexpr int kTraceStamps = 6;
 unsigned long long* trace_next_slot(int kernel_id, int blocks);  // host side; null when tracing is off
+// Bumped by every kmll_trace_attach.  A CUDA graph bakes the slot pointers of the launches it captured, so whoever
+// caches a graph records the generation at capture and captures again when it has changed (otherwise replays would
+// keep stamping a buffer the caller has detached, and possibly freed).
+unsigned long long trace_generation();
 __device__ inline void trace_stamp(unsigned long long* base, int stamp) {
     if (base != nullptr && threadIdx.x == 0) {
         unsigned long long t;
@@ -154,8 +158,10 @@ __device__ inline void trace_stamp_latest(unsigned long long* base, int stamp) {
 
 inline cudaStream_t as_stream(kmll_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
-// Launch helper: optional programmatic dependent launch attribute.
+// Launch helper: optional programmatic dependent launch attribute.  Every launch through it is counted per host
+// thread, so a caller can report how many kernels an operator sequence really issued.
 bool pdl_enabled();
+unsigned long long& launch_counter();
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                           cudaStream_t stream, bool pdl, Args&&... args) {
@@ -171,6 +177,7 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
+    ++launch_counter();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -37,6 +37,11 @@ bool pdl_enabled() {
 }
 
 
+unsigned long long& launch_counter() {
+    static thread_local unsigned long long n = 0;
+    return n;
+}
+
 namespace {
 struct TraceLaunch { int kernel_id; int blocks; size_t offset_words; };
 struct TraceState {
@@ -44,8 +49,14 @@ struct TraceState {
     unsigned long long* buf = nullptr;
     size_t capacity_words = 0, next_word = 0;
     std::vector<TraceLaunch> launches;
+    unsigned long long generation = 0;
 } g_trace;
 }  // namespace
+
+unsigned long long trace_generation() {
+    std::lock_guard<std::mutex> lock(g_trace.mu);
+    return g_trace.generation;
+}
 
 unsigned long long* trace_next_slot(int kernel_id, int blocks) {
     std::lock_guard<std::mutex> lock(g_trace.mu);
@@ -71,6 +82,7 @@ int kmll_trace_attach(void* device_buffer, size_t bytes) {
     kmll::g_trace.capacity_words = device_buffer ? bytes / sizeof(unsigned long long) : 0;
     kmll::g_trace.next_word = 0;
     kmll::g_trace.launches.clear();
+    ++kmll::g_trace.generation;  // cached CUDA graphs hold slot pointers of the previous buffer: they are captured again
     return KMLL_OK;
 }
 

@@ -33,10 +33,19 @@ struct TpExchange {  // lives in device memory; entry d of each table is rank d'
     uint2* top_inbox[kMaxTp];  // [2][tp][2] words (logit bits, number), (token, number): each rank's arg-max
     unsigned int* epoch;       // local: decode steps started (decode_begin increments it)
 };
-__device__ inline uint4 ld_volatile_u4(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+// An exchange word is ONE 64-bit scalar: low half = value bits, high half = exchange number.  It is written with a
+// single 64-bit store and read as 64-bit elements, and a naturally aligned 64-bit scalar access is single-copy
+// atomic, so a reader can never see the number of one store with the value of another.  (A 2 x 32-bit vector
+// access would be two scalar accesses to the memory model, with no such promise.)
+__device__ inline void st_exchange_word(uint2* slot, uint32_t value_bits, uint32_t number) {
+    const unsigned long long w = ((unsigned long long)number << 32) | (unsigned long long)value_bits;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+}
+// two neighbouring exchange words with one 16-byte request; each 64-bit element is atomic on its own
+__device__ inline uint4 ld_exchange_pair(const uint4* p) {
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
 }
 __device__ inline unsigned long long device_clock_ns() {
     unsigned long long t;

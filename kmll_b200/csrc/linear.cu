@@ -578,8 +578,8 @@ __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const fl
                 const unsigned int epoch = *xc.epoch * 128u + kTopExchangeIndex + 1u;
                 const size_t slot = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * 2;
                 for (int dst = 0; dst < xc.tp; ++dst) {
-                    xc.top_inbox[dst][slot] = make_uint2((uint32_t)(packed >> 32), epoch);
-                    xc.top_inbox[dst][slot + 1] = make_uint2((uint32_t)(packed & 0xffffffffull), epoch);
+                    st_exchange_word(xc.top_inbox[dst] + slot, (uint32_t)(packed >> 32), epoch);
+                    st_exchange_word(xc.top_inbox[dst] + slot + 1, (uint32_t)(packed & 0xffffffffull), epoch);
                 }
             }
         }
@@ -600,7 +600,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
     for (int r = 0; r < xc.tp; ++r) {
         uint4 q;
         for (;;) {
-            q = ld_volatile_u4(box + r);
+            q = ld_exchange_pair(box + r);
             if (q.y == epoch && q.w == epoch) break;
             if (device_clock_ns() - t0 > kPeerWaitLimitNs) { atomicCAS(&g_device_status, 0, 2); break; }
         }
@@ -701,13 +701,11 @@ static int launch_stream_variant(cudaStream_t stream, const LinearParams& lp, bo
     sp.trace = trace_next_slot(100 + FMT * 10 + EPI, grid);
 
     auto kern = linear_stream_kernel<FMT, MT, NT, EPI>;
-    static thread_local bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
-        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    cudaError_t e = launch(kern, dim3(grid), dim3(kSBlock), smem, stream, true, sp);
+    // (the attribute is per kernel and per DEVICE: a thread that moves to another GPU must set it there too, so it is
+    // set on every launch; the call is cheap and not a stream operation)
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    e = launch(kern, dim3(grid), dim3(kSBlock), smem, stream, true, sp);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear stream launch: %s", cudaGetErrorString(e));
     *launched = true;
     return KMLL_OK;
@@ -731,13 +729,9 @@ static int launch_variant(cudaStream_t stream, LinearParams& p, int grid) {
     if (kc_max < unit) kc_max = unit;
     p.kc = p.K < kc_max ? p.K : kc_max;
     const size_t smem = linear_smem_bytes(FMT, p.M, p.kc, MT, NT);
-    static thread_local bool configured = false;  // one flag per template instantiation
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
-        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    cudaError_t e = launch(kern, dim3(grid), dim3(kThreads), smem, stream, true, p);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));  // per device: every launch
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    e = launch(kern, dim3(grid), dim3(kThreads), smem, stream, true, p);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear launch: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }
@@ -849,12 +843,10 @@ static int run_umma_i8(cudaStream_t stream, const float* x, int M, int K, int ld
         const int rc = umma_scratch(&sc);
         if (rc != KMLL_OK) return rc;
     }
-    static thread_local bool configured = false;
     const size_t smem = (size_t)kUmmaStages * (kUmmaABytes + kUmmaBBytes) + (2 * kUmmaStages + 1) * 8 + 64;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_umma_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = cudaFuncSetAttribute(linear_umma_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  // per device
         if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured = true;
     }
     for (int m0 = 0; m0 < M; m0 += kUmmaBatch) {
         const int mb = (M - m0) < kUmmaBatch ? (M - m0) : kUmmaBatch;
@@ -1051,8 +1043,10 @@ template <int FMT>
 static int run_top1(const char* name, cudaStream_t stream, const float* x, const uint16_t* norm_w, float eps,
                     const void* w, const void* scales, int rows, int cols, uint32_t* partial_tokens,
                     float* partial_logits, uint64_t* packed_out, uint32_t token_offset = 0, const TpExchange* xc = nullptr) {
-    if (partial_tokens == nullptr || partial_logits == nullptr || packed_out == nullptr)
+    if (partial_tokens == nullptr || partial_logits == nullptr || packed_out == nullptr) {
+        set_exchange_args(nullptr, -1, -1, nullptr);
         return fail(KMLL_ERR_NULL, "%s: null partial/packed buffer", name);
+    }
     MatArg m = {w, scales, rows, nullptr, nullptr};
     int count = 0;
     int rc = run_linear<FMT, EPI_TOP1>(name, stream, x, 1, cols, cols, norm_w, eps, &m, 1, 0, partial_tokens, partial_logits, &count);
@@ -1136,8 +1130,22 @@ int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, ui
 
 using namespace kmll;
 
+// An entry point that returns before run_linear has consumed the exchange arguments must not leave them armed
+// for an unrelated later call of the same thread.
+#define KMLL_REQUIRE_PTR_DISARM(p)                                                          \
+    do {                                                                                    \
+        if ((p) == nullptr) {                                                               \
+            set_exchange_args(nullptr, -1, -1, nullptr);                                    \
+            return ::kmll::fail(KMLL_ERR_NULL, "%s: null pointer %s", __func__, #p);        \
+        }                                                                                   \
+    } while (0)
+
 extern "C" {
 
+// Upper bound of the partial (token, logit) pairs a fused lm_head arg-max writes for `rows` vocabulary rows: one per
+// 32-row block.  The streaming kernel writes one per thread block (at most the number of multiprocessors), never
+// more than this bound.  kmll's own plan has one partial per 4 rows (ops/inference.rs:254-260); callers size
+// their buffers through this function on both sides, so only the bound is part of the contract.
 int kmll_linear_top1_partial_count(int rows) { return rows <= 0 ? 0 : (rows + 31) / 32; }
 
 int kmll_device_status(int* status_out) {
@@ -1181,14 +1189,14 @@ int kmll_linear_triple_w4g128(kmll_stream_t s, const float* x, const uint8_t* wq
 int kmll_rmsnorm_linear_triple_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* wq,
                                   const float* sq, const int8_t* wk, const float* sk, const int8_t* wv, const float* sv,
                                   int q_rows, int kv_rows, int cols, float* q, float* k, float* v) {
-    KMLL_REQUIRE_PTR(nw);
+    KMLL_REQUIRE_PTR_DISARM(nw);
     MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
     return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 3, 0, nullptr, nullptr);
 }
 int kmll_rmsnorm_linear_triple_w4g128(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const uint8_t* wq,
                                       const uint16_t* sq, const uint8_t* wk, const uint16_t* sk, const uint8_t* wv,
                                       const uint16_t* sv, int q_rows, int kv_rows, int cols, float* q, float* k, float* v) {
-    KMLL_REQUIRE_PTR(nw);
+    KMLL_REQUIRE_PTR_DISARM(nw);
     MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
     return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 3, 0, nullptr, nullptr);
 }
@@ -1205,14 +1213,14 @@ int kmll_silu_gate_up_w4g128(kmll_stream_t s, const float* x, const uint8_t* wg,
 }
 int kmll_rmsnorm_silu_gate_up_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* wg,
                                  const float* sg, const int8_t* wu, const float* su, int rows, int cols, float* out) {
-    KMLL_REQUIRE_PTR(nw);
+    KMLL_REQUIRE_PTR_DISARM(nw);
     MatArg m[2] = {{wg, sg, rows, out, nullptr}, {wu, su, rows, nullptr, nullptr}};
     return run_linear<FMT_I8, EPI_SILU>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 2, 0, nullptr, nullptr);
 }
 int kmll_rmsnorm_silu_gate_up_w4g128(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const uint8_t* wg,
                                      const uint16_t* sg, const uint8_t* wu, const uint16_t* su, int rows, int cols,
                                      float* out) {
-    KMLL_REQUIRE_PTR(nw);
+    KMLL_REQUIRE_PTR_DISARM(nw);
     MatArg m[2] = {{wg, sg, rows, out, nullptr}, {wu, su, rows, nullptr, nullptr}};
     return run_linear<FMT_W4, EPI_SILU>(__func__, as_stream(s), x, 1, cols, cols, nw, eps, m, 2, 0, nullptr, nullptr);
 }
@@ -1227,12 +1235,12 @@ int kmll_linear_top1_w4g128(kmll_stream_t s, const float* x, const uint8_t* pack
 }
 int kmll_rmsnorm_linear_top1_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* w,
                                 const float* scales, int rows, int cols, uint32_t* pt, float* pl, uint64_t* packed_out) {
-    KMLL_REQUIRE_PTR(nw);
+    KMLL_REQUIRE_PTR_DISARM(nw);
     return run_top1<FMT_I8>(__func__, as_stream(s), x, nw, eps, w, scales, rows, cols, pt, pl, packed_out);
 }
 int kmll_rmsnorm_linear_top1_w4g128(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const uint8_t* packed,
                                     const uint16_t* gs, int rows, int cols, uint32_t* pt, float* pl, uint64_t* packed_out) {
-    KMLL_REQUIRE_PTR(nw);
+    KMLL_REQUIRE_PTR_DISARM(nw);
     return run_top1<FMT_W4>(__func__, as_stream(s), x, nw, eps, packed, gs, rows, cols, pt, pl, packed_out);
 }
 

@@ -57,9 +57,6 @@ __device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_gen
 __device__ inline void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ inline void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 __device__ inline void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -105,11 +102,6 @@ __device__ inline void cp_async_word_to(uint32_t smem_dst, const void* gmem_src)
 }
 __device__ inline void cp_async_word(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ inline void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
 }
 
 constexpr int kSBlock = kSThreads;
@@ -185,7 +177,7 @@ __device__ __noinline__ void gather_exchange(const TpExchange* xcp, int gather_i
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int i = i0 + u * kSThreads;
-                    q[u] = ld_volatile_u4(gb + (size_t)r * npair + (i < npair ? i : i0));
+                    q[u] = ld_exchange_pair(gb + (size_t)r * npair + (i < npair ? i : i0));
                     all = all && q[u].y == epoch && q[u].w == epoch;
                 }
                 if (all) break;
@@ -697,7 +689,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                             const TpExchange& xc = *p.xc;
                             const unsigned int epoch = *xc.epoch * 128u + (unsigned int)p.push_index + 1u;
                             const size_t slot = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * xc.dim + row;
-                            for (int dst = 0; dst < xc.tp; ++dst) xc.inbox[dst][slot] = make_uint2(__float_as_uint(v), epoch);
+                            for (int dst = 0; dst < xc.tp; ++dst) st_exchange_word(xc.inbox[dst] + slot, __float_as_uint(v), epoch);
                         } else {
                             om.out[(size_t)m * om.ldo + row] = v;
                         }

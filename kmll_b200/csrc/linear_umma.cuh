@@ -258,6 +258,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_i8_kernel(const U
         if (ok && KT > 0 && !mbar_wait<false>(all_done, 0u)) ok = false;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         tcgen05_fence_after();
+        ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective: all lanes or none
         if (ok) {
             const int rl = warp * 32 + lane;  // row inside the tile
             const int row = row0 + rl;

@@ -102,6 +102,7 @@ struct Decoder {
     bool have_next = false;
     bool warmed = false;
     cudaGraphExec_t graph = nullptr;
+    unsigned long long graph_trace_generation = 0;  // trace_generation() when `graph` was captured
     cudaStream_t capture_stream = nullptr;  // the caller's stream may be the legacy default stream, which cannot capture
     ncclComm_t comm = nullptr;
     // peer-memory exchange (tensor parallel decode step); null = NCCL collectives
@@ -369,7 +370,14 @@ static int write_state(Decoder* d, cudaStream_t s, int position, int step, uint6
 }
 
 static int ensure_graph(Decoder* d, cudaStream_t s) {
+    // a timeline buffer was attached or detached since the capture: the graph holds stale slot pointers
+    if (d->graph != nullptr && d->graph_trace_generation != trace_generation()) {
+        KMLL_CUDA(cudaStreamSynchronize(s));
+        cudaGraphExecDestroy(d->graph);
+        d->graph = nullptr;
+    }
     if (d->graph != nullptr) return KMLL_OK;
+    d->graph_trace_generation = trace_generation();
     if (!d->warmed) {
         // one eager step so that every kernel has its attributes set before capture; the state is
         // restored afterwards and the KV row it wrote is rewritten by the real step at this position
@@ -485,6 +493,7 @@ struct BatchDecoder {
     int host_position = -1;
     unsigned filled = 0;  // bit b: slot b holds a sequence
     cudaGraphExec_t graph = nullptr;
+    unsigned long long graph_trace_generation = 0;
     cudaStream_t capture_stream = nullptr;
     bool warmed = false;
     int launches_per_step = 0;
@@ -506,9 +515,8 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
     const kmll_decoder_config& c = d->cfg;
     const int B = b->batch;
     const int q_len = c.n_heads * c.head_dim, kv_len = c.n_kv_heads * c.head_dim;
-    int n = 0;
+    const unsigned long long launches_before = launch_counter();  // the batched linear forms issue several kernels each
     KMLL_TRY(batch_begin(s, d->embedding, c.vocab_size, c.dim, B, b->state, b->history, b->history_cap, b->hidden_a));
-    ++n;
     float* hidden = b->hidden_a;
     float* other = b->hidden_b;
     for (int l = 0; l < c.n_layers; ++l) {
@@ -544,7 +552,6 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
             float* outs[1] = {other};
             KMLL_TRY(linear_batched_form(2, s, c.format, b->act, B, nullptr, 0.f, w, sc, rows, c.hidden_dim, outs, b->hidden_mid));
         }
-        n += 5;
         float* t = hidden;
         hidden = other;
         other = t;
@@ -557,13 +564,18 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
         KMLL_TRY(linear_batched_form(3, s, c.format, hidden, B, d->final_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
     }
     KMLL_TRY(batch_end(s, b->logits, c.vocab_size, B, b->state));
-    n += 2;
-    if (launches) *launches = n;
+    if (launches) *launches = (int)(launch_counter() - launches_before);
     return KMLL_OK;
 }
 
 static int ensure_batch_graph(BatchDecoder* b, cudaStream_t s) {
+    if (b->graph != nullptr && b->graph_trace_generation != trace_generation()) {
+        KMLL_CUDA(cudaStreamSynchronize(s));
+        cudaGraphExecDestroy(b->graph);
+        b->graph = nullptr;
+    }
     if (b->graph != nullptr) return KMLL_OK;
+    b->graph_trace_generation = trace_generation();
     if (!b->warmed) {
         // one eager step (kernel attributes get set outside capture); the state is restored afterwards and the KV
         // rows it wrote are rewritten by the real step at this position
@@ -1056,6 +1068,19 @@ int kmll_decoder_generate_greedy(kmll_decoder_t dec, kmll_stream_t stream, int n
     return KMLL_OK;
 }
 
+int kmll_decoder_history(kmll_decoder_t dec, kmll_stream_t stream, int first, int count, uint64_t* packed_out) {
+    KMLL_REQUIRE_PTR(dec);
+    KMLL_REQUIRE_PTR(packed_out);
+    Decoder* d = static_cast<Decoder*>(dec);
+    cudaStream_t s = as_stream(stream);
+    KMLL_REQUIRE(first >= 0 && count >= 0 && first + count <= d->history_cap, "history: entries %d..%d outside 0..%d", first, first + count,
+                 d->history_cap);
+    if (count == 0) return KMLL_OK;
+    KMLL_CUDA(cudaMemcpyAsync(packed_out, d->history + first, sizeof(uint64_t) * (size_t)count, cudaMemcpyDeviceToHost, s));
+    KMLL_CUDA(cudaStreamSynchronize(s));
+    return KMLL_OK;
+}
+
 int kmll_decoder_step_host(kmll_decoder_t dec, kmll_stream_t stream, uint32_t token, uint64_t* packed_out) {
     KMLL_REQUIRE_PTR(dec);
     KMLL_REQUIRE_PTR(packed_out);
@@ -1109,6 +1134,19 @@ int kmll_decoder_rewind(kmll_decoder_t dec, kmll_stream_t stream, int position) 
     KMLL_TRY(write_state(d, s, position, 0, packed));
     KMLL_CUDA(cudaStreamSynchronize(s));
     d->host_position = position;
+    return KMLL_OK;
+}
+
+int kmll_decoder_set_pending(kmll_decoder_t dec, kmll_stream_t stream, uint64_t packed) {
+    KMLL_REQUIRE_PTR(dec);
+    Decoder* d = static_cast<Decoder*>(dec);
+    cudaStream_t s = as_stream(stream);
+    if (!d->have_next) return fail(KMLL_ERR_STATE, "runtime must be prefilled before a pending token can be set");
+    KMLL_REQUIRE((uint32_t)(packed & 0xffffffffull) < (uint32_t)d->cfg.vocab_size, "set_pending: token %u out of range",
+                 (uint32_t)(packed & 0xffffffffull));
+    KMLL_CUDA(cudaStreamSynchronize(s));
+    KMLL_TRY(write_state(d, s, d->host_position, 0, packed));
+    KMLL_CUDA(cudaStreamSynchronize(s));
     return KMLL_OK;
 }
 

@@ -150,6 +150,12 @@ class Decoder:
     def enqueue_steps(self, n_steps: int) -> None:
         check(self._lib.kmll_decoder_enqueue_steps(self._h, self._stream(), n_steps))
 
+    def history(self, first: int, count: int):
+        """(tokens, logits) of the steps first .. first + count - 1 run since the last prefill / rewind."""
+        packed = np.zeros(count, dtype=np.uint64)
+        check(self._lib.kmll_decoder_history(self._h, self._stream(), first, count, packed.ctypes.data))
+        return (packed & 0xFFFFFFFF).astype(np.uint32), (packed >> np.uint64(32)).astype(np.uint32).view(np.float32)
+
     def step_host(self, token: int) -> int:
         out = C.c_uint64()
         check(self._lib.kmll_decoder_step_host(self._h, self._stream(), token, C.byref(out)))
@@ -157,6 +163,9 @@ class Decoder:
 
     def rewind(self, position: int) -> None:
         check(self._lib.kmll_decoder_rewind(self._h, self._stream(), position))
+
+    def set_pending(self, packed: int) -> None:
+        check(self._lib.kmll_decoder_set_pending(self._h, self._stream(), C.c_uint64(packed)))
 
     def next_top(self) -> int:
         out = C.c_uint64()

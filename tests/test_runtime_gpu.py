@@ -151,3 +151,33 @@ def test_qwen2_shape_slice(cuda):
     rng = np.random.default_rng(2)
     check_against_oracle(dec, cfg, rng.integers(0, cfg.vocab_size, 12), 4, batched_prefill=True)
     dec.close()
+
+
+def test_timeline_attach_and_detach_recapture_the_step_graph(cuda):
+    """The per-token CUDA graph bakes the timeline slots of its launches: after the buffer is detached the decoder must
+    capture the graph again, so replays leave the (possibly freed) buffer alone; attaching later must trace again."""
+    import ctypes as C
+    from kmll_b200 import lib as klib
+    L = klib.load()
+    cfg = tiny(rt.FORMAT_W4G128)
+    dec = make(cfg, seed=7)
+    prompt = np.array([5, 17, 300, 2])
+    dec.prefill(prompt)
+    ref_tokens, _ = dec.generate_greedy(6)  # graph captured with no buffer attached
+    buf = torch.zeros(1 << 16, dtype=torch.int64, device="cuda")
+    count = C.c_int(0)
+    klib.check(L.kmll_trace_attach(C.c_void_p(buf.data_ptr()), buf.numel() * 8))
+    dec.prefill(prompt)
+    tokens, _ = dec.generate_greedy(6)
+    torch.cuda.synchronize()
+    klib.check(L.kmll_trace_launches(None, None, None, 0, C.byref(count)))
+    assert count.value > 0 and int(torch.count_nonzero(buf)) > 0, "attaching after the first capture must trace the step"
+    assert tokens.tolist() == ref_tokens.tolist()
+    klib.check(L.kmll_trace_attach(None, 0))
+    buf.zero_()
+    dec.prefill(prompt)
+    tokens, _ = dec.generate_greedy(6)
+    torch.cuda.synchronize()
+    assert int(torch.count_nonzero(buf)) == 0, "a detached buffer must not be written by later replays"
+    assert tokens.tolist() == ref_tokens.tolist()
+    dec.close()

@@ -1,6 +1,7 @@
-"""Tensor-parallel decode on 2 GPUs must generate the same greedy tokens as the single-GPU decoder
+"""Tensor-parallel decode on 2, 4 and 8 GPUs must generate the same greedy tokens as the single-GPU decoder
 (weights are quantized before sharding, so the shards are slices of the same tensors), both with the
-peer-memory exchange inside the decode step and with the NCCL collectives."""
+peer-memory exchange inside the decode step and with the NCCL collectives.  The model has the head geometry of
+the Mistral-7B architecture (32 query / 8 KV heads), so 8 ranks own one KV head each."""
 import os
 import socket
 
@@ -18,7 +19,7 @@ def _free_port():
 
 
 def _cfg(rt, fmt, rank, size):
-    return rt.DecoderConfig(n_layers=2, dim=256, n_heads=4, n_kv_heads=2, head_dim=64, hidden_dim=512, vocab_size=640, rope_theta=1e6,
+    return rt.DecoderConfig(n_layers=2, dim=1024, n_heads=32, n_kv_heads=8, head_dim=64, hidden_dim=2048, vocab_size=1024, rope_theta=1e6,
                             norm_eps=1e-6, max_seq_len=48, format=fmt, tp_rank=rank, tp_size=size)
 
 
@@ -52,11 +53,12 @@ def _worker(rank, world, port, fmt, exchange, out):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("exchange", ["peer", "nccl"])
 @pytest.mark.parametrize("fmt", [0, 1])
-def test_tp2_matches_single_gpu(cuda, fmt, exchange):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+def test_tp_matches_single_gpu(cuda, fmt, exchange, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     from kmll_b200 import runtime as rt
     single = rt.Decoder(_cfg(rt, fmt, 0, 1))
@@ -68,7 +70,7 @@ def test_tp2_matches_single_gpu(cuda, fmt, exchange):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, fmt, exchange, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, exchange, out)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

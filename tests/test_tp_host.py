@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import oracle
-from kmll_b200 import tp
+import tp_rules as tp
 
 F = np.float32
 
