@@ -175,6 +175,43 @@ int kmll_rmsnorm_linear_top1_i8(kmll_stream_t stream, const float* x,
                                 const float* scales, int rows, int cols, uint32_t* partial_tokens,
                                 float* partial_logits, uint64_t* packed_out);
 
+/* ------------------------------------------------------------------------------------------
+ * W4-G128 in the PREPARED layout (load-time re-ordering of the same 4-bit values and binary16 scales; no
+ * counterpart in kmll, whose int8 weights are used as stored).  The prepared bytes are what the batch-1 kernels
+ * stream: records of 32 rows x one 128-column group, 2112 bytes each (2048 bytes of nibbles in tensor-core
+ * fragment order + 32 scales), two row blocks sharing every byte so that one logic operation per register
+ * separates them.  The canonical arrays stay the interchange format and the dequantization contract
+ * (kmll_dequant_w4g128); a prepared buffer is derived from them and holds exactly the same values.
+ *   kmll_w4g128_prepare        rows r of a matrix: record u holds rows 32u..32u+15 and 32u+16..32u+31
+ *   kmll_w4g128_prepare_pair   gate and up matrices of a gated MLP: record u holds gate rows 16u..16u+15 and the
+ *                              same rows of up, so SiLU(gate) * up meets inside one thread
+ * The operators below equal their canonical-layout namesakes (same arithmetic contract: exact integer products,
+ * activations rounded to 2^-29 of the largest element, f32 accumulation over the 128-column groups);
+ * norm_weight_bf16 may be null (no RMSNorm prologue), residual may be null.  Batch 1.
+ * ---------------------------------------------------------------------------------------- */
+size_t kmll_w4g128_prepared_bytes(int rows, int cols);
+size_t kmll_w4g128_prepared_pair_bytes(int rows, int cols);
+int kmll_w4g128_prepare(kmll_stream_t stream, const uint8_t* packed, const uint16_t* gscales_f16, int rows, int cols,
+                        uint8_t* prepared);
+int kmll_w4g128_prepare_pair(kmll_stream_t stream, const uint8_t* gate_packed, const uint16_t* gate_gscales_f16,
+                             const uint8_t* up_packed, const uint16_t* up_gscales_f16, int rows, int cols,
+                             uint8_t* prepared);
+/* y = [residual +] dequant(W) . [rmsnorm](x) — CudaLinearWeight::launch_linear, crates/inference/src/ops/inference.rs:205-252 */
+int kmll_linear_w4p(kmll_stream_t stream, const float* x, const uint16_t* norm_weight_bf16, float eps,
+                    const uint8_t* prepared, const float* residual, int rows, int cols, float* y);
+/* Q, K, V in one launch — matvec_triple, crates/inference/src/kernels/inference.rs:629-739 */
+int kmll_linear_triple_w4p(kmll_stream_t stream, const float* x, const uint16_t* norm_weight_bf16, float eps,
+                           const uint8_t* prepared_q, const uint8_t* prepared_k, const uint8_t* prepared_v, int q_rows,
+                           int kv_rows, int cols, float* q, float* k, float* v);
+/* silu(gate . x) * (up . x) — matvec_silu_gate_up, crates/inference/src/kernels/inference.rs:535-626 */
+int kmll_silu_gate_up_w4p(kmll_stream_t stream, const float* x, const uint16_t* norm_weight_bf16, float eps,
+                          const uint8_t* prepared_pair, int rows, int cols, float* out);
+/* lm_head + arg-max — linear_top1_i8_scaled, crates/inference/src/ops/inference.rs:454-560.  Calls of this entry
+ * point that overlap on one GPU share an arrival counter and must not run concurrently. */
+int kmll_linear_top1_w4p(kmll_stream_t stream, const float* x, const uint16_t* norm_weight_bf16, float eps,
+                         const uint8_t* prepared, int rows, int cols, uint32_t* partial_tokens, float* partial_logits,
+                         uint64_t* packed_out);
+
 /* y[batch, out] = x[batch, in] . dequant(W)^T — linear_batched_i8_scaled,
  * crates/inference/src/ops/matmul.rs:423-463 (gemm_f32_i8_scaled_tiled_kernel).  x and y are
  * row-major prefixes of possibly larger buffers, as in kmll. */

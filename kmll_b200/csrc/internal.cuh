@@ -28,9 +28,13 @@ struct DecodeState {
 // push exchange k+2 only after it consumed k+1, which every rank pushed after consuming k.
 constexpr int kMaxTp = 8;
 struct TpExchange {  // lives in device memory; entry d of each table is rank d's buffer as mapped into this process
-    int tp, rank, dim, pad;
+    int tp, rank, dim;
+    int mult;                  // exchange numbers are step * mult + index + 1 (index < mult)
+    int top_index;             // index of the arg-max hand-over within a step (mult - 1)
+    int local_dim;
     uint2* inbox[kMaxTp];      // [2][tp][dim] words (value bits, exchange number)
     uint2* top_inbox[kMaxTp];  // [2][tp][2] words (logit bits, number), (token, number): each rank's arg-max
+    uint2* local_box;          // [local_dim] words: a vector handed from one phase of the chained kernel to the next on this GPU
     unsigned int* epoch;       // local: decode steps started (decode_begin increments it)
 };
 // An exchange word is ONE 64-bit scalar: low half = value bits, high half = exchange number.  It is written with a
@@ -53,6 +57,59 @@ __device__ inline unsigned long long device_clock_ns() {
     return t;
 }
 constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;  // a peer that is 2 s late is given up on
+// ---- chained streaming kernel over prepared W4-G128 records (linear_chain.cuh) -----------------------------
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_TOP1 = 3 };
+constexpr int kCRecBytes = 2112;   // one prepared record: 32 rows x 128 columns of nibbles + 32 binary16 scales
+constexpr int kCRows = 32;         // weight rows per unit
+constexpr int kCDepth = 4;         // records in flight per warp (8 KB; 128 KB per block)
+constexpr int kCRedBufs = 8;       // units whose partial sums may be pending at once
+constexpr int kCMaxPhases = 4;
+
+enum { CHAIN_IN_PLAIN = 0, CHAIN_IN_INBOX = 1, CHAIN_IN_LOCAL = 2 };
+enum { CHAIN_OUT_PLAIN = 0, CHAIN_OUT_INBOX = 1, CHAIN_OUT_LOCAL = 2 };
+
+struct ChainPhase {
+    const uint8_t* w[3];      // prepared records of up to three matrices; the units of a matrix are consecutive
+    float* out[3];            // plain outputs (unused when the output is pushed)
+    int out_rows[3];          // valid output rows per matrix (gate/up: rows of the gate matrix)
+    int unit_start[4];        // first unit of each matrix; [3] = total
+    int total_units;
+    int K, ngroups;
+    int epi;                  // EPI_STORE / EPI_RESIDUAL / EPI_SILU / EPI_TOP1
+    int in_kind, in_index;    // CHAIN_IN_*: plain pointer, rank-ordered sum of inbox exchange in_index, local buffer
+    int out_kind, out_index;  // CHAIN_OUT_*
+    int residual_index;       // EPI_RESIDUAL: >= 0 takes the residual from the rank-ordered sum of that inbox exchange
+    int add_residual;         // 0 on tensor-parallel ranks above 0 (rank 0's partial vector carries the residual)
+    const float* x;           // plain input
+    float* x_out;             // gathered input: block 0 also stores the summed vector here (may be null)
+    const uint16_t* norm_w;   // fused RMSNorm weight or null
+    float eps;
+    const float* residual;    // plain residual
+};
+
+struct ChainParams {
+    ChainPhase phase[kCMaxPhases];
+    int n_phases;
+    int off_corr, off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
+    int xs_pitch;             // bytes per digit row (>= max K + 16)
+    const TpExchange* xc;     // exchange tables (also on one GPU, where tp == 1 and the inbox is local) or null
+    // lm_head arg-max (EPI_TOP1): per-block partials, merged by the block that finishes last
+    uint32_t* partial_tokens;
+    float* partial_logits;
+    uint64_t* packed_out;
+    unsigned int* top1_counter;  // zero between launches
+    uint32_t token_offset;
+    DecodeState* state;       // not null: the merging block also advances the decode state (single GPU)
+    int push_top;             // 1: the merging block hands this rank's arg-max to every rank (tensor parallel)
+    unsigned long long* trace;
+};
+
+// Plans the shared memory of a chain and launches it (every phase: K % 128 == 0, K <= 24576, 16-byte aligned inputs).
+int launch_chain(cudaStream_t stream, ChainParams& cp);
+size_t w4_prepared_bytes(int rows, int cols, int pair);
+int w4_prepare(cudaStream_t stream, const uint8_t* pa, const uint16_t* sa, const uint8_t* pb, const uint16_t* sb, int rows, int cols,
+               uint8_t* out);
+
 // Arguments for the NEXT linear launch of this thread (consumed and cleared by it): push the output as exchange
 // `push_index` instead of storing it, and / or take the input vector from exchange `gather_index` (writing the
 // summed vector to x_out as well).  -1 = off.

@@ -39,7 +39,6 @@ __device__ int g_device_status = 0;
 namespace kmll {
 
 enum { FMT_I8 = 0, FMT_W4 = 1 };
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_TOP1 = 3 };
 
 struct LinearMat {
     const uint8_t* w;       // int8 values [rows, K] or packed nibbles [rows, K/2]
@@ -537,7 +536,6 @@ __global__ void __launch_bounds__(1024) linear_i8_rowwarp_top1_kernel(const floa
 
 // Second stage of the fused arg-max: one block reduces the per-block partials
 // (argmax_pairs_f32_packed_kernel, crates/inference/src/kernels/inference.rs:1812-1878).
-constexpr unsigned int kTopExchangeIndex = 127;  // exchange number of the arg-max hand-over within a step
 __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const float* __restrict__ logits, int count,
                                    uint32_t token_offset, uint64_t* __restrict__ packed_out, const TpExchange* xcp) {
     pdl_wait();
@@ -575,7 +573,7 @@ __global__ void top1_reduce_kernel(const uint32_t* __restrict__ tokens, const fl
             packed_out[0] = packed;
             if (xcp != nullptr) {  // tensor parallel: hand this rank's result to every rank (two 8-byte words)
                 const TpExchange& xc = *xcp;
-                const unsigned int epoch = *xc.epoch * 128u + kTopExchangeIndex + 1u;
+                const unsigned int epoch = *xc.epoch * (unsigned int)xc.mult + (unsigned int)xc.top_index + 1u;
                 const size_t slot = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * 2;
                 for (int dst = 0; dst < xc.tp; ++dst) {
                     st_exchange_word(xc.top_inbox[dst] + slot, (uint32_t)(packed >> 32), epoch);
@@ -592,7 +590,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
     pdl_wait();
     if (threadIdx.x != 0) return;
     const TpExchange& xc = *xcp;
-    const unsigned int epoch = *xc.epoch * 128u + kTopExchangeIndex + 1u;
+    const unsigned int epoch = *xc.epoch * (unsigned int)xc.mult + (unsigned int)xc.top_index + 1u;
     const uint4* box = reinterpret_cast<const uint4*>(xc.top_inbox[xc.rank]) + (size_t)(epoch & 1u) * xc.tp;
     const unsigned long long t0 = device_clock_ns();
     float best = -INFINITY;
@@ -618,6 +616,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
 
 #include "linear_stream.cuh"
 #include "linear_umma.cuh"
+#include "linear_chain.cuh"
 
 namespace kmll {
 
@@ -884,6 +883,104 @@ static int run_umma_i8(cudaStream_t stream, const float* x, int M, int K, int ld
         }
     }
     return KMLL_OK;
+}
+
+// ---- chained kernel over prepared W4-G128 records ---------------------------------------------------------------
+__device__ unsigned int g_chain_top1_counter = 0;  // arrival counter of operator-level arg-max calls (left at zero by every launch)
+
+size_t w4_prepared_bytes(int rows, int cols, int pair) {
+    if (rows <= 0 || cols <= 0 || cols % 128 != 0) return 0;
+    const size_t units = pair ? ((size_t)rows + 15) / 16 : ((size_t)rows + 31) / 32;
+    return units * (size_t)(cols / 128) * kCRecBytes;
+}
+
+int w4_prepare(cudaStream_t stream, const uint8_t* pa, const uint16_t* sa, const uint8_t* pb, const uint16_t* sb, int rows, int cols,
+               uint8_t* out) {
+    const int pair = pb != nullptr;
+    const size_t words = w4_prepared_bytes(rows, cols, pair) / 4;
+    if (words == 0) return fail(KMLL_ERR_SHAPE, "w4g128_prepare: rows=%d cols=%d (cols must be a positive multiple of 128)", rows, cols);
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return fail(KMLL_ERR_UNSUPPORTED, "w4g128_prepare: the output must be 16-byte aligned");
+    const size_t blocks = (words + 255) / 256;
+    if (blocks > 0x7fffffffull) return fail(KMLL_ERR_CAPACITY, "w4g128_prepare: matrix too large");
+    w4_prepare_kernel<<<(unsigned)blocks, 256, 0, stream>>>(pa, sa, pb, sb, rows, cols, pair, words, reinterpret_cast<uint32_t*>(out));
+    return check_launch("w4g128_prepare");
+}
+
+int launch_chain(cudaStream_t stream, ChainParams& cp) {
+    if (cp.n_phases < 1 || cp.n_phases > kCMaxPhases) return fail(KMLL_ERR_SHAPE, "chain: %d phases", cp.n_phases);
+    int kmax = 0, units_max = 0;
+    for (int i = 0; i < cp.n_phases; ++i) {
+        ChainPhase& ph = cp.phase[i];
+        if (ph.K <= 0 || ph.K % 128 != 0) return fail(KMLL_ERR_SHAPE, "chain: in_dim %d must be a positive multiple of 128", ph.K);
+        if ((size_t)ph.K > (size_t)kStageBlocks * 8 * kSThreads) return fail(KMLL_ERR_CAPACITY, "chain: in_dim %d beyond %d", ph.K, kStageBlocks * 8 * kSThreads);
+        if (ph.in_kind == CHAIN_IN_PLAIN && (ph.x == nullptr || (reinterpret_cast<uintptr_t>(ph.x) & 15u) != 0))
+            return fail(KMLL_ERR_UNSUPPORTED, "chain: the input vector must be 16-byte aligned");
+        if (ph.norm_w != nullptr && (reinterpret_cast<uintptr_t>(ph.norm_w) & 15u) != 0)
+            return fail(KMLL_ERR_UNSUPPORTED, "chain: the norm weight must be 16-byte aligned");
+        if ((ph.in_kind != CHAIN_IN_PLAIN || ph.out_kind != CHAIN_OUT_PLAIN || ph.residual_index >= 0) && cp.xc == nullptr)
+            return fail(KMLL_ERR_STATE, "chain: a phase uses exchange words but no exchange tables were given");
+        ph.ngroups = ph.K / 128;
+        if (ph.total_units <= 0) return fail(KMLL_ERR_SHAPE, "chain: a phase has no rows");
+        for (int m = 0; m < 3; ++m)
+            if (ph.unit_start[m] < ph.total_units && (ph.w[m] == nullptr || (reinterpret_cast<uintptr_t>(ph.w[m]) & 15u) != 0))
+                return fail(KMLL_ERR_UNSUPPORTED, "chain: prepared weights must be 16-byte aligned");
+        if (ph.K > kmax) kmax = ph.K;
+        if (ph.total_units > units_max) units_max = ph.total_units;
+    }
+    auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
+    cp.xs_pitch = kmax + 16;
+    const size_t xs_bytes = up128((size_t)4 * cp.xs_pitch + 32);
+    const size_t corr_bytes = up128((size_t)(kmax / 128) * 16);
+    const size_t red_bytes = up128((size_t)kCRedBufs * (kSWarps + 2) * kCRows * sizeof(float));
+    const size_t bars_bytes = 128, misc_bytes = 1024;
+    const size_t ring_bytes = (size_t)kCDepth * 4 * kCPlane;
+    const size_t sring_bytes = (size_t)kSWarps * kCDepth * 64;
+    cp.off_corr = (int)xs_bytes;
+    cp.off_red = cp.off_corr + (int)corr_bytes;
+    cp.off_bars = cp.off_red + (int)red_bytes;
+    cp.off_misc = cp.off_bars + (int)bars_bytes;
+    cp.off_ring = cp.off_misc + (int)misc_bytes;
+    cp.off_sring = cp.off_ring + (int)ring_bytes;
+    const size_t smem = (size_t)cp.off_sring + sring_bytes;
+    if (smem > 224 * 1024) return fail(KMLL_ERR_CAPACITY, "chain: in_dim %d needs %zu bytes of shared memory", kmax, smem);
+    // every block must be resident at once (blocks of one launch wait for each other's words): one block per
+    // multiprocessor at most
+    const int grid = units_max < num_sms() ? units_max : num_sms();
+    cp.trace = trace_next_slot(400, grid);
+    // (the kernel also has a little static shared memory, so the dynamic limit is set to what this launch needs)
+    cudaError_t e = cudaFuncSetAttribute(linear_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu bytes): %s", smem, cudaGetErrorString(e));
+    e = launch(linear_chain_kernel, dim3(grid), dim3(kSBlock), smem, stream, true, cp);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear chain launch: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+// one phase over up to three prepared matrices with plain input and output
+static void chain_plain_phase(ChainPhase& ph, int epi, const float* x, const uint16_t* norm_w, float eps, int K, const uint8_t* const* w,
+                              const int* rows, float* const* outs, int nmat, const float* residual) {
+    memset(&ph, 0, sizeof(ph));
+    ph.epi = epi;
+    ph.K = K;
+    ph.x = x;
+    ph.norm_w = norm_w;
+    ph.eps = eps;
+    ph.in_kind = CHAIN_IN_PLAIN;
+    ph.out_kind = CHAIN_OUT_PLAIN;
+    ph.residual = residual;
+    ph.residual_index = -1;
+    ph.add_residual = residual != nullptr;
+    int units = 0;
+    for (int m = 0; m < 3; ++m) {
+        ph.unit_start[m] = units;
+        if (m < nmat) {
+            ph.w[m] = w[m];
+            ph.out[m] = outs ? outs[m] : nullptr;
+            ph.out_rows[m] = rows[m];
+            units += epi == EPI_SILU ? (rows[m] + 15) / 16 : (rows[m] + 31) / 32;
+        }
+    }
+    ph.unit_start[3] = units;
+    ph.total_units = units;
 }
 
 static bool fast_shape(int fmt, int K) { return fmt == FMT_W4 ? (K % 128 == 0) : (K % 64 == 0); }
@@ -1242,6 +1339,70 @@ int kmll_rmsnorm_linear_top1_w4g128(kmll_stream_t s, const float* x, const uint1
                                     const uint16_t* gs, int rows, int cols, uint32_t* pt, float* pl, uint64_t* packed_out) {
     KMLL_REQUIRE_PTR_DISARM(nw);
     return run_top1<FMT_W4>(__func__, as_stream(s), x, nw, eps, packed, gs, rows, cols, pt, pl, packed_out);
+}
+
+size_t kmll_w4g128_prepared_bytes(int rows, int cols) { return w4_prepared_bytes(rows, cols, 0); }
+size_t kmll_w4g128_prepared_pair_bytes(int rows, int cols) { return w4_prepared_bytes(rows, cols, 1); }
+int kmll_w4g128_prepare(kmll_stream_t s, const uint8_t* packed, const uint16_t* gscales, int rows, int cols, uint8_t* prepared) {
+    KMLL_REQUIRE_PTR(packed); KMLL_REQUIRE_PTR(gscales); KMLL_REQUIRE_PTR(prepared);
+    return w4_prepare(as_stream(s), packed, gscales, nullptr, nullptr, rows, cols, prepared);
+}
+int kmll_w4g128_prepare_pair(kmll_stream_t s, const uint8_t* gate_packed, const uint16_t* gate_gscales, const uint8_t* up_packed,
+                             const uint16_t* up_gscales, int rows, int cols, uint8_t* prepared) {
+    KMLL_REQUIRE_PTR(gate_packed); KMLL_REQUIRE_PTR(gate_gscales); KMLL_REQUIRE_PTR(up_packed); KMLL_REQUIRE_PTR(up_gscales);
+    KMLL_REQUIRE_PTR(prepared);
+    return w4_prepare(as_stream(s), gate_packed, gate_gscales, up_packed, up_gscales, rows, cols, prepared);
+}
+int kmll_linear_w4p(kmll_stream_t s, const float* x, const uint16_t* norm_w, float eps, const uint8_t* prepared, const float* residual,
+                    int rows, int cols, float* y) {
+    KMLL_REQUIRE_PTR(x); KMLL_REQUIRE_PTR(prepared); KMLL_REQUIRE_PTR(y);
+    KMLL_REQUIRE(rows > 0 && cols > 0, "%s: rows=%d cols=%d must be positive", __func__, rows, cols);
+    ChainParams cp;
+    memset(&cp, 0, sizeof(cp));
+    cp.n_phases = 1;
+    chain_plain_phase(cp.phase[0], residual ? EPI_RESIDUAL : EPI_STORE, x, norm_w, eps, cols, &prepared, &rows, &y, 1, residual);
+    return launch_chain(as_stream(s), cp);
+}
+int kmll_linear_triple_w4p(kmll_stream_t s, const float* x, const uint16_t* norm_w, float eps, const uint8_t* pq, const uint8_t* pk,
+                           const uint8_t* pv, int q_rows, int kv_rows, int cols, float* q, float* k, float* v) {
+    KMLL_REQUIRE_PTR(x); KMLL_REQUIRE_PTR(pq); KMLL_REQUIRE_PTR(pk); KMLL_REQUIRE_PTR(pv); KMLL_REQUIRE_PTR(q); KMLL_REQUIRE_PTR(k);
+    KMLL_REQUIRE_PTR(v);
+    KMLL_REQUIRE(q_rows > 0 && kv_rows > 0 && cols > 0, "%s: sizes must be positive", __func__);
+    const uint8_t* w[3] = {pq, pk, pv};
+    const int rows[3] = {q_rows, kv_rows, kv_rows};
+    float* outs[3] = {q, k, v};
+    ChainParams cp;
+    memset(&cp, 0, sizeof(cp));
+    cp.n_phases = 1;
+    chain_plain_phase(cp.phase[0], EPI_STORE, x, norm_w, eps, cols, w, rows, outs, 3, nullptr);
+    return launch_chain(as_stream(s), cp);
+}
+int kmll_silu_gate_up_w4p(kmll_stream_t s, const float* x, const uint16_t* norm_w, float eps, const uint8_t* prepared_pair, int rows,
+                          int cols, float* out) {
+    KMLL_REQUIRE_PTR(x); KMLL_REQUIRE_PTR(prepared_pair); KMLL_REQUIRE_PTR(out);
+    KMLL_REQUIRE(rows > 0 && cols > 0, "%s: rows=%d cols=%d must be positive", __func__, rows, cols);
+    ChainParams cp;
+    memset(&cp, 0, sizeof(cp));
+    cp.n_phases = 1;
+    chain_plain_phase(cp.phase[0], EPI_SILU, x, norm_w, eps, cols, &prepared_pair, &rows, &out, 1, nullptr);
+    return launch_chain(as_stream(s), cp);
+}
+int kmll_linear_top1_w4p(kmll_stream_t s, const float* x, const uint16_t* norm_w, float eps, const uint8_t* prepared, int rows, int cols,
+                         uint32_t* pt, float* pl, uint64_t* packed_out) {
+    KMLL_REQUIRE_PTR(x); KMLL_REQUIRE_PTR(prepared); KMLL_REQUIRE_PTR(pt); KMLL_REQUIRE_PTR(pl); KMLL_REQUIRE_PTR(packed_out);
+    KMLL_REQUIRE(rows > 0 && cols > 0, "%s: rows=%d cols=%d must be positive", __func__, rows, cols);
+    ChainParams cp;
+    memset(&cp, 0, sizeof(cp));
+    cp.n_phases = 1;
+    chain_plain_phase(cp.phase[0], EPI_TOP1, x, norm_w, eps, cols, &prepared, &rows, nullptr, 1, nullptr);
+    cp.partial_tokens = pt;
+    cp.partial_logits = pl;
+    cp.packed_out = packed_out;
+    void* counter = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&counter, g_chain_top1_counter);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", __func__, cudaGetErrorString(e));
+    cp.top1_counter = static_cast<unsigned int*>(counter);
+    return launch_chain(as_stream(s), cp);
 }
 
 int kmll_linear_batched_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, int batch, int in_dim,

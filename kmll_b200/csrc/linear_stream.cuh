@@ -160,7 +160,7 @@ __device__ inline void transpose_bytes3(uint32_t a, uint32_t b, uint32_t c, uint
 __device__ __noinline__ void gather_exchange(const TpExchange* xcp, int gather_index, int K, float* x_out, float2* xf) {
     const int tid = threadIdx.x;
     const TpExchange& xc = *xcp;
-    const unsigned int epoch = *xc.epoch * 128u + (unsigned int)gather_index + 1u;
+    const unsigned int epoch = *xc.epoch * (unsigned int)xc.mult + (unsigned int)gather_index + 1u;
     const int tp = xc.tp, npair = K >> 1;  // a 16-byte load = two (value, number) words
     const uint4* gb = reinterpret_cast<const uint4*>(xc.inbox[xc.rank]) + (size_t)(epoch & 1u) * tp * npair;
     const unsigned long long t0 = device_clock_ns();
@@ -687,7 +687,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_stream_kernel(const StreamP
                             // tensor-parallel exchange: (value, exchange number) goes to every rank's inbox in one
                             // 8-byte peer store
                             const TpExchange& xc = *p.xc;
-                            const unsigned int epoch = *xc.epoch * 128u + (unsigned int)p.push_index + 1u;
+                            const unsigned int epoch = *xc.epoch * (unsigned int)xc.mult + (unsigned int)p.push_index + 1u;
                             const size_t slot = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * xc.dim + row;
                             for (int dst = 0; dst < xc.tp; ++dst) st_exchange_word(xc.inbox[dst] + slot, __float_as_uint(v), epoch);
                         } else {

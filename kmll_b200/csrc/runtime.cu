@@ -63,12 +63,14 @@ struct QWeight {
     void* w = nullptr;       // int8 values or packed nibbles
     void* scales = nullptr;  // float[rows] or half[rows, cols/128]
     int rows = 0, cols = 0;  // local (sharded) shape
+    uint8_t* prep = nullptr;  // W4-G128: the same values in the prepared layout the batch-1 kernels stream
 };
 
 struct Layer {
     uint16_t* attention_norm = nullptr;
     uint16_t* ffn_norm = nullptr;
     QWeight wq, wk, wv, wo, w1, w3, w2;
+    uint8_t* w13_prep = nullptr;  // W4-G128: gate (w1) and up (w3) interleaved in the prepared layout
     float* key_cache = nullptr;
     float* value_cache = nullptr;
 };
@@ -114,6 +116,10 @@ struct Decoder {
     size_t weight_bytes = 0, kv_bytes = 0;
     int launches_per_step = 0;
     bool weights_set = false;
+    // chained decode step (W4-G128, fused): prepared weights, exchange words also on a single GPU
+    bool chain = false;            // the decode step runs linear_chain_kernel
+    bool prepared_valid = false;   // the prepared buffers match the canonical tensors
+    unsigned int* top1_counter = nullptr;
 };
 
 template <typename T>
@@ -316,6 +322,184 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
     return KMLL_OK;
 }
 
+
+// ---- chained decode step (W4-G128) ---------------------------------------------------------------------
+// Per layer two launches: the attention kernel, then ONE chained kernel that runs the output projection + residual,
+// RMSNorm + gate/up + SiLU, the down projection + residual and RMSNorm + the NEXT layer's Q/K/V (after the last
+// layer: the final RMSNorm + lm_head arg-max and the end of the step).  Inside the chain the vectors travel as
+// exchange words (internal.cuh); under tensor parallelism the row-parallel projections push theirs to every rank.
+static bool chain_supported(const Decoder* d) {
+    const kmll_decoder_config& c = d->cfg;
+    if (c.format != KMLL_FORMAT_W4G128 || !c.fused) return false;
+    if (2 * c.n_layers + 1 > 250) return false;
+    const char* v = std::getenv("KMLL_CHAIN");
+    return !(v != nullptr && v[0] == '0');
+}
+
+static int ensure_prepared(Decoder* d) {
+    if (!d->chain || d->prepared_valid) return KMLL_OK;
+    const kmll_decoder_config& c = d->cfg;
+    auto one = [&](QWeight& w) -> int {
+        if (w.prep == nullptr) KMLL_TRY(dalloc(d, &w.prep, w4_prepared_bytes(w.rows, w.cols, 0)));
+        return w4_prepare(nullptr, (const uint8_t*)w.w, (const uint16_t*)w.scales, nullptr, nullptr, w.rows, w.cols, w.prep);
+    };
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = d->layers[l];
+        KMLL_TRY(one(L.wq));
+        KMLL_TRY(one(L.wk));
+        KMLL_TRY(one(L.wv));
+        KMLL_TRY(one(L.wo));
+        KMLL_TRY(one(L.w2));
+        if (L.w13_prep == nullptr) KMLL_TRY(dalloc(d, &L.w13_prep, w4_prepared_bytes(L.w1.rows, L.w1.cols, 1)));
+        KMLL_TRY(w4_prepare(nullptr, (const uint8_t*)L.w1.w, (const uint16_t*)L.w1.scales, (const uint8_t*)L.w3.w, (const uint16_t*)L.w3.scales,
+                            L.w1.rows, L.w1.cols, L.w13_prep));
+    }
+    KMLL_TRY(one(d->output));
+    KMLL_CUDA(cudaDeviceSynchronize());
+    d->prepared_valid = true;
+    return KMLL_OK;
+}
+
+static void chain_phase_common(ChainPhase& ph, int epi, int K) {
+    memset(&ph, 0, sizeof(ph));
+    ph.epi = epi;
+    ph.K = K;
+    ph.residual_index = -1;
+}
+static void chain_phase_mats(ChainPhase& ph, const uint8_t* const* w, const int* rows, float* const* outs, int nmat) {
+    int units = 0;
+    for (int m = 0; m < 3; ++m) {
+        ph.unit_start[m] = units;
+        if (m < nmat) {
+            ph.w[m] = w[m];
+            ph.out[m] = outs ? outs[m] : nullptr;
+            ph.out_rows[m] = rows[m];
+            units += ph.epi == EPI_SILU ? (rows[m] + 15) / 16 : (rows[m] + 31) / 32;
+        }
+    }
+    ph.unit_start[3] = units;
+    ph.total_units = units;
+}
+
+static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
+    const kmll_decoder_config& c = d->cfg;
+    const int q_len = d->n_heads_l * c.head_dim, kv_len = d->n_kv_l * c.head_dim;
+    const unsigned long long before = launch_counter();
+    const bool tp = c.tp_size > 1;
+    KMLL_TRY(decode_begin(s, d->embedding, c.vocab_size, c.dim, d->state, d->history, d->history_cap, d->hidden_a, d->xc_epoch));
+    // Q/K/V of layer `l` from the vector `in` (plain pointer or exchange 2l - 1)
+    auto qkv_phase = [&](ChainPhase& ph, int l) {
+        Layer& L = d->layers[l];
+        chain_phase_common(ph, EPI_STORE, c.dim);
+        const uint8_t* w[3] = {L.wq.prep, L.wk.prep, L.wv.prep};
+        const int rows[3] = {q_len, kv_len, kv_len};
+        float* outs[3] = {d->q, d->k, d->v};
+        chain_phase_mats(ph, w, rows, outs, 3);
+        ph.norm_w = L.attention_norm;
+        ph.eps = c.norm_eps;
+        if (l == 0) {
+            ph.in_kind = CHAIN_IN_PLAIN;
+            ph.x = d->hidden_a;
+        } else {
+            ph.in_kind = CHAIN_IN_INBOX;
+            ph.in_index = 2 * l - 1;
+        }
+    };
+    {
+        ChainParams cp;
+        memset(&cp, 0, sizeof(cp));
+        cp.n_phases = 1;
+        cp.xc = d->xc;
+        qkv_phase(cp.phase[0], 0);
+        KMLL_TRY(launch_chain(s, cp));
+    }
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = d->layers[l];
+        if (c.rotary_dim == c.head_dim) {
+            KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache));
+        } else {
+            KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache));
+            KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn));
+        }
+        ChainParams cp;
+        memset(&cp, 0, sizeof(cp));
+        cp.n_phases = 4;
+        cp.xc = d->xc;
+        {   // output projection + residual -> exchange 2l
+            ChainPhase& ph = cp.phase[0];
+            chain_phase_common(ph, EPI_RESIDUAL, q_len);
+            const uint8_t* w[1] = {L.wo.prep};
+            const int rows[1] = {c.dim};
+            chain_phase_mats(ph, w, rows, nullptr, 1);
+            ph.in_kind = CHAIN_IN_PLAIN;
+            ph.x = d->attn;
+            ph.add_residual = c.tp_rank == 0;
+            if (l == 0) ph.residual = d->hidden_a;
+            else ph.residual_index = 2 * l - 1;
+            ph.out_kind = CHAIN_OUT_INBOX;
+            ph.out_index = 2 * l;
+        }
+        {   // RMSNorm + gate/up + SiLU -> local exchange l
+            ChainPhase& ph = cp.phase[1];
+            chain_phase_common(ph, EPI_SILU, c.dim);
+            const uint8_t* w[1] = {L.w13_prep};
+            const int rows[1] = {d->hidden_l};
+            chain_phase_mats(ph, w, rows, nullptr, 1);
+            ph.norm_w = L.ffn_norm;
+            ph.eps = c.norm_eps;
+            ph.in_kind = CHAIN_IN_INBOX;
+            ph.in_index = 2 * l;
+            ph.out_kind = CHAIN_OUT_LOCAL;
+            ph.out_index = l;
+        }
+        {   // down projection + residual -> exchange 2l + 1
+            ChainPhase& ph = cp.phase[2];
+            chain_phase_common(ph, EPI_RESIDUAL, d->hidden_l);
+            const uint8_t* w[1] = {L.w2.prep};
+            const int rows[1] = {c.dim};
+            chain_phase_mats(ph, w, rows, nullptr, 1);
+            ph.in_kind = CHAIN_IN_LOCAL;
+            ph.in_index = l;
+            ph.add_residual = c.tp_rank == 0;
+            ph.residual_index = 2 * l;
+            ph.out_kind = CHAIN_OUT_INBOX;
+            ph.out_index = 2 * l + 1;
+        }
+        if (l + 1 < c.n_layers) {
+            qkv_phase(cp.phase[3], l + 1);
+        } else {  // final RMSNorm + lm_head arg-max; the block that finishes last ends the step
+            ChainPhase& ph = cp.phase[3];
+            chain_phase_common(ph, EPI_TOP1, c.dim);
+            const uint8_t* w[1] = {d->output.prep};
+            const int rows[1] = {d->vocab_l};
+            chain_phase_mats(ph, w, rows, nullptr, 1);
+            ph.norm_w = d->final_norm;
+            ph.eps = c.norm_eps;
+            ph.in_kind = CHAIN_IN_INBOX;
+            ph.in_index = 2 * l + 1;
+            ph.x_out = d->hidden_a;  // where kmll_decoder_last_hidden finds the final hidden state
+            cp.partial_tokens = d->part_tok;
+            cp.partial_logits = d->part_logit;
+            cp.packed_out = tp ? d->packed : d->packed_final;
+            cp.top1_counter = d->top1_counter;
+            cp.token_offset = (uint32_t)(c.tp_rank * d->vocab_l);
+            cp.state = tp ? nullptr : d->state;
+            cp.push_top = tp ? 1 : 0;
+        }
+        KMLL_TRY(launch_chain(s, cp));
+    }
+    if (tp) KMLL_TRY(decode_end_gather(s, d->xc, d->state, d->packed_final));
+    if (launches) *launches = (int)(launch_counter() - before);
+    return KMLL_OK;
+}
+
+static int enqueue_step(Decoder* d, cudaStream_t s, int* launches) {
+    return d->chain ? enqueue_step_chain(d, s, launches) : enqueue_step_fused(d, s, launches);
+}
+
 // One decode step launched operator by operator with the position known on the host, in kmll's own
 // order (run_incremental_layer_token_into, crates/inference/src/model.rs:10102-10300).
 static int enqueue_step_unfused(Decoder* d, cudaStream_t s, uint32_t token, int position) {
@@ -376,6 +560,7 @@ static int ensure_graph(Decoder* d, cudaStream_t s) {
         cudaGraphExecDestroy(d->graph);
         d->graph = nullptr;
     }
+    KMLL_TRY(ensure_prepared(d));  // (never inside a capture: the capture below happens after this returned)
     if (d->graph != nullptr) return KMLL_OK;
     d->graph_trace_generation = trace_generation();
     if (!d->warmed) {
@@ -385,7 +570,7 @@ static int ensure_graph(Decoder* d, cudaStream_t s) {
         KMLL_CUDA(cudaStreamSynchronize(s));
         KMLL_CUDA(cudaMemcpy(&saved, d->state, sizeof(saved), cudaMemcpyDeviceToHost));
         if (d->host_position >= d->cfg.max_seq_len) return fail(KMLL_ERR_CAPACITY, "sequence is full");
-        KMLL_TRY(enqueue_step_fused(d, s, &d->launches_per_step));
+        KMLL_TRY(enqueue_step(d, s, &d->launches_per_step));
         KMLL_CUDA(cudaStreamSynchronize(s));
         KMLL_CUDA(cudaMemcpy(d->state, &saved, sizeof(saved), cudaMemcpyHostToDevice));
         d->warmed = true;
@@ -393,7 +578,7 @@ static int ensure_graph(Decoder* d, cudaStream_t s) {
     cudaGraph_t g = nullptr;
     if (d->capture_stream == nullptr) KMLL_CUDA(cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking));
     KMLL_CUDA(cudaStreamBeginCapture(d->capture_stream, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_step_fused(d, d->capture_stream, &d->launches_per_step);
+    int rc = enqueue_step(d, d->capture_stream, &d->launches_per_step);
     cudaError_t e = cudaStreamEndCapture(d->capture_stream, &g);
     if (rc != KMLL_OK) {
         if (g) cudaGraphDestroy(g);
@@ -604,38 +789,48 @@ static int ensure_batch_graph(BatchDecoder* b, cudaStream_t s) {
 }
 
 
-// Peer-memory exchange: every rank allocates one buffer (inboxes, flags, arg-max slots, counters), the ranks
-// swap CUDA IPC handles through an NCCL all-gather and map each other's buffers.  Needs batch-1 stream kernels
-// for every exchanged vector, at most 63 layers (exchange numbers stay below 127) and tp_size <= 8.
-static int setup_peer_exchange(Decoder* d) {
+// Exchange buffer of a decoder: inboxes [2][tp][dim], arg-max slots [2][tp][2], the local vector of the chained step
+// [hidden_l] and the step counter.  On one GPU it is plain device memory.  Under tensor parallelism every rank
+// allocates one, the ranks swap CUDA IPC handles through an NCCL all-gather and map each other's buffers; the
+// unchained path needs batch-1 stream kernels for every exchanged vector and at most 63 layers (its exchange numbers
+// stay below 127), the chained path at most 124 layers.
+static int setup_exchange(Decoder* d) {
     const kmll_decoder_config& c = d->cfg;
     const int tp = c.tp_size;
-    if (tp > kMaxTp || 2 * c.n_layers > 126 || !c.fused) return KMLL_OK;  // stay on NCCL
-    NcclApi* api = nccl_api();
+    if (tp > kMaxTp || !c.fused) return KMLL_OK;  // stay on NCCL
+    if (!d->chain && 2 * c.n_layers > 126) return KMLL_OK;
+    NcclApi* api = tp > 1 ? nccl_api() : nullptr;
     const size_t inbox_bytes = (size_t)2 * tp * c.dim * sizeof(uint2);
     const size_t off_top = (inbox_bytes + 127) & ~(size_t)127;
     const size_t top_bytes = ((size_t)2 * tp * 2 * sizeof(uint2) + 127) & ~(size_t)127;
-    const size_t off_local = off_top + top_bytes;  // epoch
+    const size_t off_box = off_top + top_bytes;
+    const size_t box_bytes = ((size_t)d->hidden_l * sizeof(uint2) + 127) & ~(size_t)127;
+    const size_t off_local = off_box + box_bytes;  // epoch
     const size_t total = off_local + 256;
     KMLL_CUDA(cudaMalloc(&d->xc_local, total));
     KMLL_CUDA(cudaMemset(d->xc_local, 0, total));
-    cudaIpcMemHandle_t mine;
-    KMLL_CUDA(cudaIpcGetMemHandle(&mine, d->xc_local));
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
-    unsigned char* handles_dev = nullptr;
-    KMLL_CUDA(cudaMalloc(&handles_dev, (size_t)tp * 64));
-    KMLL_CUDA(cudaMemcpy(handles_dev + (size_t)c.tp_rank * 64, &mine, 64, cudaMemcpyHostToDevice));
-    // (in-place all-gather: the send buffer is this rank's slot of the receive buffer; it also orders every
-    // rank's memset above before anybody's first push)
-    ncclResult_t r = api->AllGather(handles_dev + (size_t)c.tp_rank * 64, handles_dev, 64, ncclChar, d->comm, nullptr);
-    if (r != ncclSuccess) { cudaFree(handles_dev); return fail(KMLL_ERR_CUDA, "ncclAllGather (IPC handles) failed"); }
-    KMLL_CUDA(cudaStreamSynchronize(nullptr));
     std::vector<cudaIpcMemHandle_t> handles(tp);
-    KMLL_CUDA(cudaMemcpy(handles.data(), handles_dev, (size_t)tp * 64, cudaMemcpyDeviceToHost));
-    cudaFree(handles_dev);
+    if (tp > 1) {
+        cudaIpcMemHandle_t mine;
+        KMLL_CUDA(cudaIpcGetMemHandle(&mine, d->xc_local));
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+        unsigned char* handles_dev = nullptr;
+        KMLL_CUDA(cudaMalloc(&handles_dev, (size_t)tp * 64));
+        KMLL_CUDA(cudaMemcpy(handles_dev + (size_t)c.tp_rank * 64, &mine, 64, cudaMemcpyHostToDevice));
+        // (in-place all-gather: the send buffer is this rank's slot of the receive buffer; it also orders every
+        // rank's memset above before anybody's first push)
+        ncclResult_t r = api->AllGather(handles_dev + (size_t)c.tp_rank * 64, handles_dev, 64, ncclChar, d->comm, nullptr);
+        if (r != ncclSuccess) { cudaFree(handles_dev); return fail(KMLL_ERR_CUDA, "ncclAllGather (IPC handles) failed"); }
+        KMLL_CUDA(cudaStreamSynchronize(nullptr));
+        KMLL_CUDA(cudaMemcpy(handles.data(), handles_dev, (size_t)tp * 64, cudaMemcpyDeviceToHost));
+        cudaFree(handles_dev);
+    }
     TpExchange h;
     memset(&h, 0, sizeof(h));
     h.tp = tp; h.rank = c.tp_rank; h.dim = c.dim;
+    h.mult = d->chain ? 256 : 128;
+    h.top_index = h.mult - 1;
+    h.local_dim = d->hidden_l;
     for (int rnk = 0; rnk < tp; ++rnk) {
         void* base = d->xc_local;
         if (rnk != c.tp_rank) {
@@ -648,6 +843,7 @@ static int setup_peer_exchange(Decoder* d) {
         h.top_inbox[rnk] = reinterpret_cast<uint2*>(b + off_top);
     }
     unsigned char* lb = static_cast<unsigned char*>(d->xc_local);
+    h.local_box = reinterpret_cast<uint2*>(lb + off_box);
     h.epoch = reinterpret_cast<unsigned int*>(lb + off_local);
     d->xc_epoch = h.epoch;
     KMLL_TRY(dalloc(d, &d->xc, 1));
@@ -717,7 +913,8 @@ int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out) 
         const size_t ws = decode_attention_workspace_floats(d->n_heads_l, c.head_dim, c.max_seq_len);
         KMLL_TRY(dalloc(d, &d->attn_ws, ws));
         KMLL_CUDA(cudaMemset(d->attn_ws, 0, ws * sizeof(float)));
-        const int parts = kmll_linear_top1_partial_count(d->vocab_l);
+        // (the chained kernel writes one partial per block of its grid, which another phase may have sized)
+        const int parts = kmll_linear_top1_partial_count(d->vocab_l) + 1024;
         KMLL_TRY(dalloc(d, &d->part_tok, (size_t)parts));
         KMLL_TRY(dalloc(d, &d->part_logit, (size_t)parts));
         KMLL_TRY(dalloc(d, &d->packed, (size_t)2));
@@ -728,6 +925,12 @@ int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out) 
         KMLL_TRY(dalloc(d, &d->history, (size_t)d->history_cap));
         KMLL_CUDA(cudaMemset(d->state, 0, sizeof(DecodeState)));
         KMLL_CUDA(cudaMallocHost((void**)&d->pinned, 64 * sizeof(uint64_t)));
+        d->chain = chain_supported(d);
+        if (d->chain) {
+            KMLL_TRY(dalloc(d, &d->top1_counter, (size_t)4));
+            KMLL_CUDA(cudaMemset(d->top1_counter, 0, 16));
+            if (c.tp_size == 1) KMLL_TRY(setup_exchange(d));
+        }
         return KMLL_OK;
     };
     rc = body();
@@ -828,6 +1031,7 @@ int kmll_decoder_init_random(kmll_decoder_t dec, uint64_t seed, float std, int t
     const int rc = body();
     cleanup();
     if (rc == KMLL_OK) d->weights_set = true;
+    d->prepared_valid = false;
     return rc;
 }
 
@@ -856,6 +1060,7 @@ int kmll_decoder_set_tensor(kmll_decoder_t dec, int layer, int tensor, const voi
     cudaFree(fw);
     cudaFree(fs);
     if (rc == KMLL_OK) d->weights_set = true;
+    d->prepared_valid = false;
     return rc;
 }
 
@@ -899,8 +1104,11 @@ int kmll_decoder_tp_init(kmll_decoder_t dec, const unsigned char id[128]) {
     ncclResult_t r = api->CommInitRank(&d->comm, d->cfg.tp_size, nid, d->cfg.tp_rank);
     if (r != ncclSuccess) return fail(KMLL_ERR_CUDA, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
     const char* mode = std::getenv("KMLL_TP_EXCHANGE");  // "nccl" keeps the library collectives inside the decode step
-    if (mode != nullptr && strcmp(mode, "nccl") == 0) return KMLL_OK;
-    return setup_peer_exchange(d);
+    if (mode != nullptr && strcmp(mode, "nccl") == 0) {
+        d->chain = false;  // the chained step hands its vectors over through exchange words only
+        return KMLL_OK;
+    }
+    return setup_exchange(d);
 }
 
 int kmll_decoder_prefill_token_loop(kmll_decoder_t dec, kmll_stream_t stream, const uint32_t* tokens, int n_tokens) {

@@ -110,7 +110,35 @@ class DeviceW4G128Matrix:
                                   self.rows, hi - lo)
 
 
-Weight = DeviceRowwiseScaledI8Matrix | DeviceW4G128Matrix
+@dataclass
+class DeviceW4PMatrix:
+    """W4-G128 weights in the prepared layout the batch-1 kernels stream (kmll_w4g128_prepare): records of 32 rows x one
+    128-column group in tensor-core fragment order.  `pair` = gate and up matrices of a gated MLP interleaved."""
+    prepared: torch.Tensor  # uint8
+    rows: int
+    cols: int
+    pair: bool = False
+    fmt = "w4p"
+
+    @staticmethod
+    def from_canonical(m: DeviceW4G128Matrix) -> "DeviceW4PMatrix":
+        n = int(load().kmll_w4g128_prepared_bytes(m.rows, m.cols))
+        out = torch.empty(n, dtype=torch.uint8, device=m.packed.device)
+        check(load().kmll_w4g128_prepare(_stream(), _p(m.packed), _p(m.gscales), m.rows, m.cols, _p(out)))
+        return DeviceW4PMatrix(out, m.rows, m.cols, False)
+
+    @staticmethod
+    def from_gate_up(gate: DeviceW4G128Matrix, up: DeviceW4G128Matrix) -> "DeviceW4PMatrix":
+        if gate.rows != up.rows or gate.cols != up.cols:
+            raise KmllError(-2, "gate and up matrices must have the same shape")
+        n = int(load().kmll_w4g128_prepared_pair_bytes(gate.rows, gate.cols))
+        out = torch.empty(n, dtype=torch.uint8, device=gate.packed.device)
+        check(load().kmll_w4g128_prepare_pair(_stream(), _p(gate.packed), _p(gate.gscales), _p(up.packed), _p(up.gscales), gate.rows,
+                                              gate.cols, _p(out)))
+        return DeviceW4PMatrix(out, gate.rows, gate.cols, True)
+
+
+Weight = DeviceRowwiseScaledI8Matrix | DeviceW4G128Matrix | DeviceW4PMatrix
 
 
 def _w(weight: Weight):
@@ -152,6 +180,9 @@ def linear(x: torch.Tensor, weight: Weight, out: torch.Tensor | None = None) -> 
     out = torch.empty(weight.rows, dtype=torch.float32, device=x.device) if out is None else out
     if out.numel() != weight.rows:
         raise KmllError(-2, "linear output shape mismatch")
+    if isinstance(weight, DeviceW4PMatrix):
+        check(load().kmll_linear_w4p(_stream(), _p(x), None, 0.0, _p(weight.prepared), None, weight.rows, weight.cols, _p(out)))
+        return out
     fmt, w, s = _w(weight)
     check(_fn("linear", fmt)(_stream(), _p(x), w, s, weight.rows, weight.cols, _p(out)))
     return out
@@ -162,6 +193,10 @@ def linear_residual(x, weight: Weight, residual, out=None):
     if x.numel() != weight.cols or residual.numel() != weight.rows:
         raise KmllError(-2, "linear residual shape mismatch")
     out = torch.empty(weight.rows, dtype=torch.float32, device=x.device) if out is None else out
+    if isinstance(weight, DeviceW4PMatrix):
+        check(load().kmll_linear_w4p(_stream(), _p(_f32(x, "input")), None, 0.0, _p(weight.prepared), _p(_f32(residual, "residual")),
+                                     weight.rows, weight.cols, _p(out)))
+        return out
     fmt, w, s = _w(weight)
     check(_fn("linear_residual", fmt)(_stream(), _p(_f32(x, "input")), w, s, _p(_f32(residual, "residual")), weight.rows, weight.cols, _p(out)))
     return out
@@ -175,6 +210,10 @@ def linear_triple(x, wq: Weight, wk: Weight, wv: Weight, norm_weight=None, eps: 
     q = torch.empty(wq.rows, dtype=torch.float32, device=x.device)
     k = torch.empty(wk.rows, dtype=torch.float32, device=x.device)
     v = torch.empty(wv.rows, dtype=torch.float32, device=x.device)
+    if fmt == "w4p":
+        check(load().kmll_linear_triple_w4p(_stream(), _p(_f32(x, "input")), _p(norm_weight), eps, _p(wq.prepared), _p(wk.prepared),
+                                            _p(wv.prepared), wq.rows, wk.rows, wq.cols, _p(q), _p(k), _p(v)))
+        return q, k, v
     (_, pq, sq), (_, pk, sk), (_, pv, sv) = _w(wq), _w(wk), _w(wv)
     if norm_weight is None:
         check(_fn("linear_triple", fmt)(_stream(), _p(_f32(x, "input")), pq, sq, pk, sk, pv, sv, wq.rows, wk.rows, wq.cols, _p(q), _p(k), _p(v)))
@@ -184,8 +223,16 @@ def linear_triple(x, wq: Weight, wk: Weight, wv: Weight, norm_weight=None, eps: 
     return q, k, v
 
 
-def silu_gate_up(x, w_gate: Weight, w_up: Weight, norm_weight=None, eps: float = 0.0, out=None):
-    """silu_gate_up_bf16 (ops/inference.rs:777-869) for quantized weights: silu(Wg.x) * (Wu.x)."""
+def silu_gate_up(x, w_gate: Weight, w_up: Weight | None, norm_weight=None, eps: float = 0.0, out=None):
+    """silu_gate_up_bf16 (ops/inference.rs:777-869) for quantized weights: silu(Wg.x) * (Wu.x).  A prepared gate/up pair
+    (DeviceW4PMatrix.from_gate_up) is passed as w_gate with w_up = None."""
+    if isinstance(w_gate, DeviceW4PMatrix):
+        if not w_gate.pair or w_up is not None or x.numel() != w_gate.cols:
+            raise KmllError(-2, "silu gate/up over prepared weights takes one gate/up pair")
+        out = torch.empty(w_gate.rows, dtype=torch.float32, device=x.device) if out is None else out
+        check(load().kmll_silu_gate_up_w4p(_stream(), _p(_f32(x, "input")), _p(norm_weight), eps, _p(w_gate.prepared), w_gate.rows,
+                                           w_gate.cols, _p(out)))
+        return out
     fmt = _same_fmt(w_gate, w_up)
     if w_gate.rows != w_up.rows or w_gate.cols != w_up.cols or x.numel() != w_gate.cols:
         raise KmllError(-2, "silu gate/up shape mismatch")
@@ -217,6 +264,10 @@ def linear_top1(x, weight: Weight, partial_tokens=None, partial_logits=None, pac
     packed_out = torch.zeros(1, dtype=torch.int64, device=dev) if packed_out is None else packed_out
     if partial_tokens.numel() < n or partial_logits.numel() < n:
         raise KmllError(-2, "linear top1 partial buffers too short")
+    if isinstance(weight, DeviceW4PMatrix):
+        check(load().kmll_linear_top1_w4p(_stream(), _p(_f32(x, "input")), _p(norm_weight), eps, _p(weight.prepared), weight.rows, weight.cols,
+                                          _p(partial_tokens), _p(partial_logits), _p(packed_out)))
+        return packed_out
     fmt, w, s = _w(weight)
     if norm_weight is None:
         check(_fn("linear_top1", fmt)(_stream(), _p(_f32(x, "input")), w, s, weight.rows, weight.cols, _p(partial_tokens), _p(partial_logits), _p(packed_out)))
