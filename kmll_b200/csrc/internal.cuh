@@ -35,6 +35,8 @@ struct TpExchange {  // lives in device memory; entry d of each table is rank d'
     uint2* inbox[kMaxTp];      // [2][tp][dim] words (value bits, exchange number)
     uint2* top_inbox[kMaxTp];  // [2][tp][2] words (logit bits, number), (token, number): each rank's arg-max
     uint2* local_box;          // [local_dim] words: a vector handed from one phase of the chained kernel to the next on this GPU
+    unsigned int* ready[kMaxTp];  // [mult] arrival hints of the inbox exchanges (chained kernel), one table per rank
+    unsigned int* ready_local;    // [mult] arrival hints of the local vector
     unsigned int* epoch;       // local: decode steps started (decode_begin increments it)
 };
 // An exchange word is ONE 64-bit scalar: low half = value bits, high half = exchange number.  It is written with a
@@ -77,6 +79,7 @@ struct ChainPhase {
     int K, ngroups;
     int epi;                  // EPI_STORE / EPI_RESIDUAL / EPI_SILU / EPI_TOP1
     int in_kind, in_index;    // CHAIN_IN_*: plain pointer, rank-ordered sum of inbox exchange in_index, local buffer
+    int in_units;             // gathered input produced by an earlier phase of the SAME launch: its units per rank (arrival hint); else 0
     int out_kind, out_index;  // CHAIN_OUT_*
     int residual_index;       // EPI_RESIDUAL: >= 0 takes the residual from the rank-ordered sum of that inbox exchange
     int add_residual;         // 0 on tensor-parallel ranks above 0 (rank 0's partial vector carries the residual)

@@ -946,7 +946,7 @@ int launch_chain(cudaStream_t stream, ChainParams& cp) {
     // every block must be resident at once (blocks of one launch wait for each other's words): one block per
     // multiprocessor at most
     const int grid = units_max < num_sms() ? units_max : num_sms();
-    cp.trace = trace_next_slot(400, grid);
+    cp.trace = trace_next_slot(400, 2 * grid);  // 12 stamps per block
     // (the kernel also has a little static shared memory, so the dynamic limit is set to what this launch needs)
     cudaError_t e = cudaFuncSetAttribute(linear_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu bytes): %s", smem, cudaGetErrorString(e));

@@ -53,9 +53,23 @@ __device__ inline bool ld_exchange_value(const uint2* slot, uint32_t number, uns
 
 __device__ inline uint32_t chain_epoch(const TpExchange& xc, int index) { return *xc.epoch * (uint32_t)xc.mult + (uint32_t)index + 1u; }
 
+// Arrival hint of an exchange: every finished unit adds one to a counter next to the consumer (a remote reduction for
+// the inbox of a tensor-parallel peer).  Counters only grow: after `step` decode steps an exchange fed by n units per
+// rank stands at step * tp * n.  The hint carries no data and orders nothing - the words themselves say whether they
+// are valid - it only keeps 148 blocks x 512 threads from hammering L2 with polls while the producers still work.
+__device__ inline void chain_signal(const TpExchange& xc, int kind, int index) {
+    if (kind == CHAIN_OUT_INBOX) {
+        for (int dst = 0; dst < xc.tp; ++dst)
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(xc.ready[dst] + index) : "memory");
+    } else {
+        asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(xc.ready_local + index) : "memory");
+    }
+}
+
 // Gathers the input vector of a phase from exchange words into shared memory as K floats (block 0 also stores it
-// to x_out).  kind = inbox: sum over the ranks' slots in rank order; kind = local: one slot.
-__device__ __noinline__ void chain_gather(const TpExchange* xcp, int kind, int index, int K, float* x_out, float2* xf) {
+// to x_out).  kind = inbox: sum over the ranks' slots in rank order; kind = local: one slot.  in_units > 0: thread 0
+// first sleeps on the arrival hint until that many units per rank have reported.
+__device__ __noinline__ void chain_gather(const TpExchange* xcp, int kind, int index, int in_units, int K, float* x_out, float2* xf) {
     const TpExchange& xc = *xcp;
     const uint32_t epoch = chain_epoch(xc, index);
     const int tid = threadIdx.x, npair = K >> 1;
@@ -65,32 +79,50 @@ __device__ __noinline__ void chain_gather(const TpExchange* xcp, int kind, int i
     const int stride = kind == CHAIN_IN_INBOX ? (xc.dim >> 1) : 0;
     const unsigned long long t0 = device_clock_ns();
     bool good = true;
+    if (in_units > 0) {
+        if (tid == 0) {
+            const unsigned int* hint = (kind == CHAIN_IN_INBOX ? xc.ready[xc.rank] : xc.ready_local) + index;
+            const unsigned int target = *xc.epoch * (unsigned int)(tp * in_units);
+            for (;;) {
+                unsigned int c;
+                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(hint) : "memory");
+                if ((int)(c - target) >= 0) break;
+                if (device_clock_ns() - t0 > kPeerWaitLimitNs) break;  // the word loads below report the failure
+                __nanosleep(100);
+            }
+        }
+        __syncthreads();
+    }
+    constexpr int kInFlight = 8;  // 16-byte loads in flight per thread
 #pragma unroll 1
-    for (int i0 = tid; i0 < npair; i0 += 4 * kSThreads) {
-        float2 sum[4];
+    for (int base = tid; base < npair; base += kInFlight * kSThreads) {
+        float2 sum[kInFlight];
 #pragma unroll 1
         for (int r = 0; r < tp; ++r) {
-            uint4 q[4];
+            const uint4* src = gb + (size_t)r * stride;
+            uint4 q[kInFlight];
             for (;;) {
                 bool all = true;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + u * kSThreads;
-                    q[u] = ld_exchange_pair(gb + (size_t)r * stride + (i < npair ? i : i0));
-                    all = all && q[u].y == epoch && q[u].w == epoch;
+                for (int u = 0; u < kInFlight; ++u) {
+                    const int i = base + u * kSThreads;
+                    q[u] = ld_exchange_pair(src + (i < npair ? i : base));
                 }
+#pragma unroll
+                for (int u = 0; u < kInFlight; ++u) all = all && q[u].y == epoch && q[u].w == epoch;
                 if (all) break;
                 if (device_clock_ns() - t0 > kPeerWaitLimitNs) { good = false; break; }
+                __nanosleep(40);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kInFlight; ++u) {
                 const float2 pv = make_float2(__uint_as_float(q[u].x), __uint_as_float(q[u].z));
                 sum[u] = (r == 0) ? pv : make_float2(sum[u].x + pv.x, sum[u].y + pv.y);
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * kSThreads;
+        for (int u = 0; u < kInFlight; ++u) {
+            const int i = base + u * kSThreads;
             if (i < npair) {
                 xf[i] = sum[u];
                 if (blockIdx.x == 0 && x_out != nullptr) reinterpret_cast<float2*>(x_out)[i] = sum[u];
@@ -122,7 +154,7 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
     uint4 nw[kStageBlocks];
     const float* src_base = ph.x;
     if (ph.in_kind != CHAIN_IN_PLAIN) {
-        chain_gather(xc, ph.in_kind, ph.in_index, K, ph.x_out, reinterpret_cast<float2*>(xs));
+        chain_gather(xc, ph.in_kind, ph.in_index, ph.in_units, K, ph.x_out, reinterpret_cast<float2*>(xs));
         __syncthreads();
         src_base = reinterpret_cast<const float*>(xs);
     }
@@ -251,9 +283,15 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
     return inv_xscale;
 }
 
+// timeline of the chained kernel: 12 stamps per block (two ordinary slots): 0 entry, 1 dependency wait passed,
+// 2 + 2 i input of phase i staged, 3 + 2 i units of phase i done (as seen by thread 0), 10 end
+__device__ inline void chain_stamp(unsigned long long* base, int stamp) {
+    if (base != nullptr && threadIdx.x == 0) base[(size_t)blockIdx.x * 2 * kTraceStamps + stamp] = global_timer_ns();
+}
+
 __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_constant__ ChainParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    trace_stamp(p.trace, 0);
+    chain_stamp(p.trace, 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
@@ -324,7 +362,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
     for (int d = 0; d < kCDepth; ++d) load_record(d);  // weights do not depend on the previous kernel
 
     pdl_wait();
-    trace_stamp(p.trace, 1);
+    chain_stamp(p.trace, 1);
 
     // this lane's B column g: digit rows d0, d1, d2, -, d3, ones, -, -; absent columns read 16 zero bytes with stride 0
     const int8_t* ones = xs + (size_t)4 * p.xs_pitch;
@@ -352,7 +390,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
         if ((int)blockIdx.x >= ph.total_units) continue;  // no unit of this phase for this block
         __syncthreads();  // every warp has finished the previous phase's records: the digit rows may be replaced
         const float inv_xscale = chain_stage(ph, p.xc, p.xs_pitch, xs, corr, misc);
-        if (c_phase == 0) trace_stamp(p.trace, 2);
+        chain_stamp(p.trace, 2 + 2 * c_phase);
         const float wA = w_lane * inv_xscale * 0.0625f, wB = w_lane * inv_xscale;
         const int epi = ph.epi;
 
@@ -491,12 +529,15 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&done[buf]);
+            if (lane == 0) {
+                if (ph.out_kind != CHAIN_OUT_PLAIN) chain_signal(*p.xc, ph.out_kind, ph.out_index);
+                mbar_arrive(&done[buf]);
+            }
         }
+        chain_stamp(p.trace, 3 + 2 * c_phase);
         if (!ok) break;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    trace_stamp(p.trace, 3);
     if (p.partial_tokens != nullptr) {
         // every warp finished some units: merge the 16 running bests (fixed order) into one partial per block; the
         // block that arrives last merges the blocks' partials (arg-max of kmll: higher logit, then lower token)
@@ -554,7 +595,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
             }
         }
     }
-    if (lane == 0) trace_stamp_latest(p.trace, 4);
+    chain_stamp(p.trace, 10);
     if (!ok) atomicCAS(&g_device_status, 0, 1);
 }
 

@@ -452,6 +452,7 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
             ph.eps = c.norm_eps;
             ph.in_kind = CHAIN_IN_INBOX;
             ph.in_index = 2 * l;
+            ph.in_units = cp.phase[0].total_units;
             ph.out_kind = CHAIN_OUT_LOCAL;
             ph.out_index = l;
         }
@@ -463,6 +464,7 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
             chain_phase_mats(ph, w, rows, nullptr, 1);
             ph.in_kind = CHAIN_IN_LOCAL;
             ph.in_index = l;
+            ph.in_units = cp.phase[1].total_units;
             ph.add_residual = c.tp_rank == 0;
             ph.residual_index = 2 * l;
             ph.out_kind = CHAIN_OUT_INBOX;
@@ -489,6 +491,7 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
             cp.state = tp ? nullptr : d->state;
             cp.push_top = tp ? 1 : 0;
         }
+        cp.phase[3].in_units = cp.phase[2].total_units;  // its input comes from the down projection of this launch
         KMLL_TRY(launch_chain(s, cp));
     }
     if (tp) KMLL_TRY(decode_end_gather(s, d->xc, d->state, d->packed_final));
@@ -805,7 +808,8 @@ static int setup_exchange(Decoder* d) {
     const size_t top_bytes = ((size_t)2 * tp * 2 * sizeof(uint2) + 127) & ~(size_t)127;
     const size_t off_box = off_top + top_bytes;
     const size_t box_bytes = ((size_t)d->hidden_l * sizeof(uint2) + 127) & ~(size_t)127;
-    const size_t off_local = off_box + box_bytes;  // epoch
+    const size_t off_ready = off_box + box_bytes;  // arrival hints: inbox exchanges, then the local vector (256 each)
+    const size_t off_local = off_ready + 2 * 256 * sizeof(unsigned int);  // epoch
     const size_t total = off_local + 256;
     KMLL_CUDA(cudaMalloc(&d->xc_local, total));
     KMLL_CUDA(cudaMemset(d->xc_local, 0, total));
@@ -841,9 +845,11 @@ static int setup_exchange(Decoder* d) {
         unsigned char* b = static_cast<unsigned char*>(base);
         h.inbox[rnk] = reinterpret_cast<uint2*>(b);
         h.top_inbox[rnk] = reinterpret_cast<uint2*>(b + off_top);
+        h.ready[rnk] = reinterpret_cast<unsigned int*>(b + off_ready);
     }
     unsigned char* lb = static_cast<unsigned char*>(d->xc_local);
     h.local_box = reinterpret_cast<uint2*>(lb + off_box);
+    h.ready_local = reinterpret_cast<unsigned int*>(lb + off_ready) + 256;
     h.epoch = reinterpret_cast<unsigned int*>(lb + off_local);
     d->xc_epoch = h.epoch;
     KMLL_TRY(dalloc(d, &d->xc, 1));
