@@ -912,7 +912,7 @@ int launch_chain(cudaStream_t stream, ChainParams& cp) {
     for (int i = 0; i < cp.n_phases; ++i) {
         ChainPhase& ph = cp.phase[i];
         if (ph.K <= 0 || ph.K % 128 != 0) return fail(KMLL_ERR_SHAPE, "chain: in_dim %d must be a positive multiple of 128", ph.K);
-        if ((size_t)ph.K > (size_t)kStageBlocks * 8 * kSThreads) return fail(KMLL_ERR_CAPACITY, "chain: in_dim %d beyond %d", ph.K, kStageBlocks * 8 * kSThreads);
+        if ((size_t)ph.K > (size_t)kCStageBlocks * 8 * kSThreads) return fail(KMLL_ERR_CAPACITY, "chain: in_dim %d beyond %d", ph.K, kCStageBlocks * 8 * kSThreads);
         if (ph.in_kind == CHAIN_IN_PLAIN && (ph.x == nullptr || (reinterpret_cast<uintptr_t>(ph.x) & 15u) != 0))
             return fail(KMLL_ERR_UNSUPPORTED, "chain: the input vector must be 16-byte aligned");
         if (ph.norm_w != nullptr && (reinterpret_cast<uintptr_t>(ph.norm_w) & 15u) != 0)

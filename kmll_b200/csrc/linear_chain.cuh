@@ -132,6 +132,12 @@ __device__ __noinline__ void chain_gather(const TpExchange* xcp, int kind, int i
     if (!good) atomicCAS(&g_device_status, 0, 2);
 }
 
+// timeline of the chained kernel: 12 stamps per block (two ordinary slots): 0 entry, 1 dependency wait passed,
+// 2 + 2 i input of phase i staged, 3 + 2 i units of phase i done (as seen by thread 0), 10 end
+__device__ inline void chain_stamp(unsigned long long* base, int stamp) {
+    if (base != nullptr && threadIdx.x == 0) base[(size_t)blockIdx.x * 2 * kTraceStamps + stamp] = global_timer_ns();
+}
+
 // rows[r] = byte r of (a, b, c, d), r = 0..3
 __device__ inline void transpose_bytes4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&rows)[4]) {
     const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
@@ -145,13 +151,14 @@ __device__ inline void transpose_bytes4(uint32_t a, uint32_t b, uint32_t c, uint
 // Stages the K activations of a phase as four digit rows d0..d3 of (x * 2^sh + 2^30) in natural column order, plus
 // the per-group correction words of the low-nibble rows (see the file comment): corr[4 g + t] for lane position t.
 // Returns 2^-sh.
-__device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange* xc, int xs_pitch, int8_t* xs, int* corr, float* misc) {
+constexpr int kCStageBlocks = 4;  // 8-element blocks of the input a thread holds in registers while it is staged: K <= 16384
+__device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange* xc, int xs_pitch, int8_t* xs, int* corr, float* misc,
+                                          unsigned long long* dbg) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = ph.K;
     const int nblk = K >> 3;
     const bool norm = ph.norm_w != nullptr;
-    float v[kStageBlocks][8];
-    uint4 nw[kStageBlocks];
+    float v[kCStageBlocks][8];
     const float* src_base = ph.x;
     if (ph.in_kind != CHAIN_IN_PLAIN) {
         chain_gather(xc, ph.in_kind, ph.in_index, ph.in_units, K, ph.x_out, reinterpret_cast<float2*>(xs));
@@ -159,25 +166,26 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
         src_base = reinterpret_cast<const float*>(xs);
     }
 #pragma unroll
-    for (int j = 0; j < kStageBlocks; ++j) {
+    for (int j = 0; j < kCStageBlocks; ++j) {
         if (j * kSThreads + warp * 32 < nblk) {
             const int blk = j * kSThreads + tid;
             const int k = (blk < nblk ? blk : 0) << 3;
             const float4* src = reinterpret_cast<const float4*>(src_base + k);
             const float4 a = src[0], b = src[1];
-            if (norm) nw[j] = *reinterpret_cast<const uint4*>(ph.norm_w + k);
             v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
             v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
         }
     }
+    chain_stamp(dbg, 4);
     float ss = 0.0f, mx = 0.0f;
 #pragma unroll
-    for (int j = 0; j < kStageBlocks; ++j) {
+    for (int j = 0; j < kCStageBlocks; ++j) {
         if (j * kSThreads + warp * 32 < nblk) {
             const bool active = j * kSThreads + tid < nblk;
             float s_ = 0.0f, m_ = 0.0f;
             if (norm) {
-                const uint32_t ww[4] = {nw[j].x, nw[j].y, nw[j].z, nw[j].w};
+                const uint4 nwj = *reinterpret_cast<const uint4*>(ph.norm_w + (active ? (j * kSThreads + tid) << 3 : 0));
+                const uint32_t ww[4] = {nwj.x, nwj.y, nwj.z, nwj.w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     s_ += v[j][2 * q] * v[j][2 * q] + v[j][2 * q + 1] * v[j][2 * q + 1];
@@ -195,6 +203,7 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
     mx = warp_max(mx);
     if (lane == 0) { misc[warp * 2] = ss; misc[warp * 2 + 1] = mx; }
     __syncthreads();  // (also: every thread has read its floats from the digit area before digits overwrite it)
+    chain_stamp(dbg, 5);
     float inv, amax;
     {
         float s_ = misc[(lane & 15) * 2], m_ = misc[(lane & 15) * 2 + 1];
@@ -218,7 +227,7 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
         inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
 #pragma unroll 1
-    for (int j = 0; j < kStageBlocks; ++j) {
+    for (int j = 0; j < kCStageBlocks; ++j) {
         const int wbase = j * kSThreads + warp * 32;
         if (wbase >= nblk) break;
         const int blk = wbase + lane;
@@ -227,14 +236,14 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
         float u[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) u[q] = v[0][q];
-        const uint32_t ww[4] = {nw[0].x, nw[0].y, nw[0].z, nw[0].w};
 #pragma unroll
-        for (int jj = 0; jj + 1 < kStageBlocks; ++jj) {
+        for (int jj = 0; jj + 1 < kCStageBlocks; ++jj) {
 #pragma unroll
             for (int q = 0; q < 8; ++q) v[jj][q] = v[jj + 1][q];
-            nw[jj] = nw[jj + 1];
         }
         if (norm) {
+            const uint4 nwj = *reinterpret_cast<const uint4*>(ph.norm_w + k);  // (read before: a cache hit)
+            const uint32_t ww[4] = {nwj.x, nwj.y, nwj.z, nwj.w};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
                 u[2 * q] = u[2 * q] * inv * __uint_as_float(ww[q] << 16);
@@ -251,42 +260,27 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
 #pragma unroll
             for (int r = 0; r < 4; ++r) *reinterpret_cast<uint2*>(xs + (size_t)r * xs_pitch + k) = make_uint2(r0[r], r1[r]);
         }
+        // per-group sums of the digit bytes -> correction words of the low-nibble rows: a group is the 16 blocks of a
+        // half warp
+        int sdig[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            unsigned int a = active ? __dp4a(r0[r], 0x01010101u, __dp4a(r1[r], 0x01010101u, 0u)) : 0u;
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+            sdig[r] = (int)a;
+        }
+        if ((lane & 15) == 0 && active) {
+            *reinterpret_cast<int4*>(corr + 4 * (k >> 7)) = make_int4(8 * (sdig[0] + 256 * sdig[1]), 8 * sdig[2], 8 * (sdig[3] - 64 * 128), 0);
+        }
     }
     // constants behind the digit rows: 16 bytes of ones, then 16 bytes of zeros (absent MMA columns); in this order the
     // broadcast reads of either fall on banks the digit row read by the same quarter warp does not use
     if (tid < 4) reinterpret_cast<uint32_t*>(xs + (size_t)4 * xs_pitch)[tid] = 0x01010101u;
     else if (tid < 8) reinterpret_cast<uint32_t*>(xs + (size_t)4 * xs_pitch)[tid] = 0u;
     __syncthreads();
-    // per-group sums of the digit bytes -> correction words of the low-nibble rows
-    for (int g = tid; g < ph.ngroups; g += kSThreads) {
-        int s[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const uint4* row = reinterpret_cast<const uint4*>(xs + (size_t)r * xs_pitch + g * 128);
-            unsigned int a = 0;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const uint4 w4 = row[q];
-                a = __dp4a(w4.x, 0x01010101u, a);
-                a = __dp4a(w4.y, 0x01010101u, a);
-                a = __dp4a(w4.z, 0x01010101u, a);
-                a = __dp4a(w4.w, 0x01010101u, a);
-            }
-            s[r] = (int)a;
-        }
-        corr[4 * g + 0] = 8 * (s[0] + 256 * s[1]);
-        corr[4 * g + 1] = 8 * s[2];
-        corr[4 * g + 2] = 8 * (s[3] - 64 * 128);
-        corr[4 * g + 3] = 0;
-    }
-    __syncthreads();
+    chain_stamp(dbg, 7);
     return inv_xscale;
-}
-
-// timeline of the chained kernel: 12 stamps per block (two ordinary slots): 0 entry, 1 dependency wait passed,
-// 2 + 2 i input of phase i staged, 3 + 2 i units of phase i done (as seen by thread 0), 10 end
-__device__ inline void chain_stamp(unsigned long long* base, int stamp) {
-    if (base != nullptr && threadIdx.x == 0) base[(size_t)blockIdx.x * 2 * kTraceStamps + stamp] = global_timer_ns();
 }
 
 __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_constant__ ChainParams p) {
@@ -389,7 +383,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
         const int spu = j1 - j0;
         if ((int)blockIdx.x >= ph.total_units) continue;  // no unit of this phase for this block
         __syncthreads();  // every warp has finished the previous phase's records: the digit rows may be replaced
-        const float inv_xscale = chain_stage(ph, p.xc, p.xs_pitch, xs, corr, misc);
+        const float inv_xscale = chain_stage(ph, p.xc, p.xs_pitch, xs, corr, misc, p.n_phases == 1 ? p.trace : nullptr);
         chain_stamp(p.trace, 2 + 2 * c_phase);
         const float wA = w_lane * inv_xscale * 0.0625f, wB = w_lane * inv_xscale;
         const int epi = ph.epi;

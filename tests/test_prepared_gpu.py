@@ -70,7 +70,7 @@ def test_prepare_matches_its_definition(cuda, rows, cols):
     assert np.array_equal(host(pp.prepared), prepare_ref(packed, gs, rows, cols, packed2, gs2))
 
 
-@pytest.mark.parametrize("rows,cols", [(4096, 4096), (1024, 4096), (4096, 14336), (1000, 256), (17, 128), (896, 896), (33, 18944), (4864, 896)])
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (1024, 4096), (4096, 14336), (1000, 256), (17, 128), (896, 896), (4864, 896), (33, 16384)])
 def test_linear_prepared_vs_oracle(cuda, rows, cols):
     rng = np.random.default_rng(rows * 7 + cols)
     _, packed, gs, w = w4_weight(rng, rows, cols)
