@@ -47,6 +47,25 @@ __device__ inline void st_exchange_word(uint2* slot, uint32_t value_bits, uint32
     const unsigned long long w = ((unsigned long long)number << 32) | (unsigned long long)value_bits;
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
 }
+// The chained kernel publishes its words with a 64-bit MAX reduction instead of a store.  Exchange numbers only grow,
+// so the new word (number in the high half) is larger than whatever the slot held and the maximum IS the new word;
+// but a reduction is carried out at the L2 cache (or at the peer over NVLink) right away, whereas a relaxed store may
+// linger in the multiprocessor's write path for microseconds before anybody can see it (measured: ~3.5 us behind a
+// reduction issued after it).  Device scope for words that never leave this GPU.
+__device__ inline void push_exchange_word(uint2* slot, uint32_t value_bits, uint32_t number, bool sys) {
+    const unsigned long long w = ((unsigned long long)number << 32) | (unsigned long long)value_bits;
+    if (sys) asm volatile("red.relaxed.sys.global.max.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+    else asm volatile("red.relaxed.gpu.global.max.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+}
+// Polling loads of the chained kernel: plain loads that bypass L1 (.cg), not strong ones.  The words live in this GPU's
+// memory, whose point of coherence is the L2 cache, so an L1-bypassing load returns what L2 holds; the number inside
+// the word says whether it is the awaited one, and a stale word is simply read again.  Strong loads (relaxed / volatile)
+// were measured to complete one after the other within a thread (eight of them: 3.5-4.4 us), plain ones overlap.
+__device__ inline uint4 ld_exchange_pair_gpu(const uint4* p) {
+    unsigned long long a, b;
+    asm volatile("ld.global.cg.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
+}
 // two neighbouring exchange words with one 16-byte request; each 64-bit element is atomic on its own
 __device__ inline uint4 ld_exchange_pair(const uint4* p) {
     unsigned long long a, b;
@@ -96,6 +115,7 @@ struct ChainParams {
     int off_corr, off_red, off_bars, off_misc, off_ring, off_sring;  // shared-memory offsets in bytes
     int xs_pitch;             // bytes per digit row (>= max K + 16)
     const TpExchange* xc;     // exchange tables (also on one GPU, where tp == 1 and the inbox is local) or null
+    TpExchange xcv;           // their contents, by value (launch_chain copies them): the kernel chases no pointer to find them
     // lm_head arg-max (EPI_TOP1): per-block partials, merged by the block that finishes last
     uint32_t* partial_tokens;
     float* partial_logits;

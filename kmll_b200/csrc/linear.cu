@@ -927,6 +927,11 @@ int launch_chain(cudaStream_t stream, ChainParams& cp) {
         if (ph.K > kmax) kmax = ph.K;
         if (ph.total_units > units_max) units_max = ph.total_units;
     }
+    if (cp.xc != nullptr) {
+        // the tables live in device memory (they are also what the other kernels of a tensor-parallel step read); the chain
+        // gets a copy by value.  (host copy kept by the caller: see ChainParams::xcv)
+        if (cp.xcv.epoch == nullptr) return fail(KMLL_ERR_STATE, "chain: the exchange tables were not copied into the launch parameters");
+    }
     auto up128 = [](size_t v) { return (v + 127) & ~(size_t)127; };
     cp.xs_pitch = kmax + 16;
     const size_t xs_bytes = up128((size_t)4 * cp.xs_pitch + 32);
@@ -946,7 +951,7 @@ int launch_chain(cudaStream_t stream, ChainParams& cp) {
     // every block must be resident at once (blocks of one launch wait for each other's words): one block per
     // multiprocessor at most
     const int grid = units_max < num_sms() ? units_max : num_sms();
-    cp.trace = trace_next_slot(400, 2 * grid);  // 12 stamps per block
+    cp.trace = trace_next_slot(400, 4 * grid);  // 24 stamps per block
     // (the kernel also has a little static shared memory, so the dynamic limit is set to what this launch needs)
     cudaError_t e = cudaFuncSetAttribute(linear_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu bytes): %s", smem, cudaGetErrorString(e));

@@ -34,12 +34,13 @@
 namespace kmll {
 
 constexpr int kCPlane = kSThreads * 16;
+constexpr int kCEarly = 0;  // records of a later phase a warp may have in flight before that phase's input has been requested
 
 // one exchange word; waits (bounded) until it carries `number`
 __device__ inline bool ld_exchange_value(const uint2* slot, uint32_t number, unsigned long long t0, float* value) {
     for (;;) {
         unsigned long long w;
-        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
+        asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
         if ((uint32_t)(w >> 32) == number) {
             *value = __uint_as_float((uint32_t)w);
             return true;
@@ -51,7 +52,7 @@ __device__ inline bool ld_exchange_value(const uint2* slot, uint32_t number, uns
     }
 }
 
-__device__ inline uint32_t chain_epoch(const TpExchange& xc, int index) { return *xc.epoch * (uint32_t)xc.mult + (uint32_t)index + 1u; }
+__device__ inline uint32_t chain_epoch(const TpExchange& xc, uint32_t step, int index) { return step * (uint32_t)xc.mult + (uint32_t)index + 1u; }
 
 // Arrival hint of an exchange: every finished unit adds one to a counter next to the consumer (a remote reduction for
 // the inbox of a tensor-parallel peer).  Counters only grow: after `step` decode steps an exchange fed by n units per
@@ -66,76 +67,12 @@ __device__ inline void chain_signal(const TpExchange& xc, int kind, int index) {
     }
 }
 
-// Gathers the input vector of a phase from exchange words into shared memory as K floats (block 0 also stores it
-// to x_out).  kind = inbox: sum over the ranks' slots in rank order; kind = local: one slot.  in_units > 0: thread 0
-// first sleeps on the arrival hint until that many units per rank have reported.
-__device__ __noinline__ void chain_gather(const TpExchange* xcp, int kind, int index, int in_units, int K, float* x_out, float2* xf) {
-    const TpExchange& xc = *xcp;
-    const uint32_t epoch = chain_epoch(xc, index);
-    const int tid = threadIdx.x, npair = K >> 1;
-    const int tp = kind == CHAIN_IN_INBOX ? xc.tp : 1;
-    const uint4* gb = kind == CHAIN_IN_INBOX ? reinterpret_cast<const uint4*>(xc.inbox[xc.rank]) + (size_t)(index & 1) * tp * (xc.dim >> 1)
-                                            : reinterpret_cast<const uint4*>(xc.local_box);
-    const int stride = kind == CHAIN_IN_INBOX ? (xc.dim >> 1) : 0;
-    const unsigned long long t0 = device_clock_ns();
-    bool good = true;
-    if (in_units > 0) {
-        if (tid == 0) {
-            const unsigned int* hint = (kind == CHAIN_IN_INBOX ? xc.ready[xc.rank] : xc.ready_local) + index;
-            const unsigned int target = *xc.epoch * (unsigned int)(tp * in_units);
-            for (;;) {
-                unsigned int c;
-                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(hint) : "memory");
-                if ((int)(c - target) >= 0) break;
-                if (device_clock_ns() - t0 > kPeerWaitLimitNs) break;  // the word loads below report the failure
-                __nanosleep(100);
-            }
-        }
-        __syncthreads();
-    }
-    constexpr int kInFlight = 8;  // 16-byte loads in flight per thread
-#pragma unroll 1
-    for (int base = tid; base < npair; base += kInFlight * kSThreads) {
-        float2 sum[kInFlight];
-#pragma unroll 1
-        for (int r = 0; r < tp; ++r) {
-            const uint4* src = gb + (size_t)r * stride;
-            uint4 q[kInFlight];
-            for (;;) {
-                bool all = true;
-#pragma unroll
-                for (int u = 0; u < kInFlight; ++u) {
-                    const int i = base + u * kSThreads;
-                    q[u] = ld_exchange_pair(src + (i < npair ? i : base));
-                }
-#pragma unroll
-                for (int u = 0; u < kInFlight; ++u) all = all && q[u].y == epoch && q[u].w == epoch;
-                if (all) break;
-                if (device_clock_ns() - t0 > kPeerWaitLimitNs) { good = false; break; }
-                __nanosleep(40);
-            }
-#pragma unroll
-            for (int u = 0; u < kInFlight; ++u) {
-                const float2 pv = make_float2(__uint_as_float(q[u].x), __uint_as_float(q[u].z));
-                sum[u] = (r == 0) ? pv : make_float2(sum[u].x + pv.x, sum[u].y + pv.y);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-            const int i = base + u * kSThreads;
-            if (i < npair) {
-                xf[i] = sum[u];
-                if (blockIdx.x == 0 && x_out != nullptr) reinterpret_cast<float2*>(x_out)[i] = sum[u];
-            }
-        }
-    }
-    if (!good) atomicCAS(&g_device_status, 0, 2);
-}
-
-// timeline of the chained kernel: 12 stamps per block (two ordinary slots): 0 entry, 1 dependency wait passed,
-// 2 + 2 i input of phase i staged, 3 + 2 i units of phase i done (as seen by thread 0), 10 end
+// timeline of the chained kernel: 24 stamps per block (four ordinary slots): 0 entry, 1 dependency wait passed,
+// phase i at 2 + 5 i: arrival hint seen, input words loaded, statistics reduced, digits staged, units done (as seen by
+// thread 0); 22 end
+constexpr int kChainStamps = 4 * kTraceStamps;
 __device__ inline void chain_stamp(unsigned long long* base, int stamp) {
-    if (base != nullptr && threadIdx.x == 0) base[(size_t)blockIdx.x * 2 * kTraceStamps + stamp] = global_timer_ns();
+    if (base != nullptr && threadIdx.x == 0) base[(size_t)blockIdx.x * kChainStamps + stamp] = global_timer_ns();
 }
 
 // rows[r] = byte r of (a, b, c, d), r = 0..3
@@ -150,33 +87,116 @@ __device__ inline void transpose_bytes4(uint32_t a, uint32_t b, uint32_t c, uint
 
 // Stages the K activations of a phase as four digit rows d0..d3 of (x * 2^sh + 2^30) in natural column order, plus
 // the per-group correction words of the low-nibble rows (see the file comment): corr[4 g + t] for lane position t.
-// Returns 2^-sh.
+// The input comes from a plain vector or straight out of exchange words (rank-ordered sum of the inbox slots, or the
+// local vector): thread 0 first sleeps on the arrival hint, then every thread loads the words of its own blocks
+// into registers and checks their numbers (bounded retries), so the vector never takes a detour through shared
+// memory.  Block 0 also stores a gathered vector to x_out.  Returns 2^-sh.
 constexpr int kCStageBlocks = 4;  // 8-element blocks of the input a thread holds in registers while it is staged: K <= 16384
-__device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange* xc, int xs_pitch, int8_t* xs, int* corr, float* misc,
-                                          unsigned long long* dbg) {
+template <typename AfterLoads>
+__device__ __forceinline__ float chain_stage(const ChainPhase& ph, const TpExchange& xc, uint32_t step, int xs_pitch, int8_t* xs, int* corr,
+                                             float* misc, unsigned long long* dbg, AfterLoads after_loads) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = ph.K;
     const int nblk = K >> 3;
     const bool norm = ph.norm_w != nullptr;
     float v[kCStageBlocks][8];
-    const float* src_base = ph.x;
-    if (ph.in_kind != CHAIN_IN_PLAIN) {
-        chain_gather(xc, ph.in_kind, ph.in_index, ph.in_units, K, ph.x_out, reinterpret_cast<float2*>(xs));
-        __syncthreads();
-        src_base = reinterpret_cast<const float*>(xs);
-    }
+    if (ph.in_kind == CHAIN_IN_PLAIN) {
 #pragma unroll
-    for (int j = 0; j < kCStageBlocks; ++j) {
-        if (j * kSThreads + warp * 32 < nblk) {
-            const int blk = j * kSThreads + tid;
-            const int k = (blk < nblk ? blk : 0) << 3;
-            const float4* src = reinterpret_cast<const float4*>(src_base + k);
-            const float4 a = src[0], b = src[1];
-            v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
-            v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+        for (int j = 0; j < kCStageBlocks; ++j) {
+            if (j * kSThreads + warp * 32 < nblk) {
+                const int blk = j * kSThreads + tid;
+                const float4* src = reinterpret_cast<const float4*>(ph.x + ((blk < nblk ? blk : 0) << 3));
+                const float4 a = src[0], b = src[1];
+                v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+                v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+            }
+        }
+    } else {
+        const bool inbox = ph.in_kind == CHAIN_IN_INBOX;
+        const uint32_t epoch = chain_epoch(xc, step, ph.in_index);
+        const int tp = inbox ? xc.tp : 1;
+        const uint4* gb = inbox ? reinterpret_cast<const uint4*>(xc.inbox[xc.rank]) + (size_t)(ph.in_index & 1) * tp * (xc.dim >> 1)
+                                : reinterpret_cast<const uint4*>(xc.local_box);
+        const int stride = inbox ? (xc.dim >> 1) : 0;
+        const unsigned long long t0 = device_clock_ns();
+        bool good = true;
+        bool topped = false;
+        // the last pair of blocks this warp loads: the held-back weight copies are requested right behind its loads
+        int last_half = 0;
+#pragma unroll
+        for (int half = 1; half < kCStageBlocks / 2; ++half)
+            if ((2 * half) * kSThreads + warp * 32 < nblk) last_half = half;
+        if (ph.in_units > 0) {
+            if (tid == 0) {
+                const unsigned int* hint = (inbox ? xc.ready[xc.rank] : xc.ready_local) + ph.in_index;
+                const unsigned int target = step * (unsigned int)(tp * ph.in_units);
+                for (;;) {
+                    unsigned int c;
+                    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(hint) : "memory");
+                    if ((int)(c - target) >= 0) break;
+                    if (device_clock_ns() - t0 > kPeerWaitLimitNs) break;  // the word loads below report the failure
+                    __nanosleep(64);
+                }
+            }
+            __syncthreads();
+        }
+        chain_stamp(dbg, 0);
+        // two blocks (eight 16-byte loads) of a rank at a time
+#pragma unroll
+        for (int half = 0; half < kCStageBlocks / 2; ++half) {
+            if ((2 * half) * kSThreads + warp * 32 < nblk) {
+#pragma unroll 1
+                for (int r = 0; r < tp; ++r) {
+                    const uint4* src = gb + (size_t)r * stride;
+                    uint4 q[2][4];
+                    for (;;) {
+                        bool all = true;
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) {
+                            const int blk = (2 * half + jj) * kSThreads + tid;
+                            const uint4* bp = src + (size_t)(blk < nblk ? blk : 0) * 4;
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) q[jj][m] = ld_exchange_pair_gpu(bp + m);
+                        }
+                        if (!topped && half == last_half && r == tp - 1) {
+                            after_loads();
+                            topped = true;
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) all = all && q[jj][m].y == epoch && q[jj][m].w == epoch;
+                        if (all) break;
+                        if (device_clock_ns() - t0 > kPeerWaitLimitNs) { good = false; break; }
+                        __nanosleep(32);
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            const float a = __uint_as_float(q[jj][m].x), b = __uint_as_float(q[jj][m].z);
+                            v[2 * half + jj][2 * m] = r == 0 ? a : v[2 * half + jj][2 * m] + a;
+                            v[2 * half + jj][2 * m + 1] = r == 0 ? b : v[2 * half + jj][2 * m + 1] + b;
+                        }
+                }
+            }
+        }
+        if (!good) atomicCAS(&g_device_status, 0, 2);
+        if (!topped) after_loads();
+        if (blockIdx.x == 0 && ph.x_out != nullptr) {
+#pragma unroll
+            for (int j = 0; j < kCStageBlocks; ++j) {
+                const int blk = j * kSThreads + tid;
+                if (blk < nblk) {
+                    float4* dst = reinterpret_cast<float4*>(ph.x_out + (blk << 3));
+                    dst[0] = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+                    dst[1] = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+                }
+            }
         }
     }
-    chain_stamp(dbg, 4);
+    if (ph.in_kind == CHAIN_IN_PLAIN) after_loads();  // the input has been requested: weight copies held back for it may go now
+    chain_stamp(dbg, 1);
     float ss = 0.0f, mx = 0.0f;
 #pragma unroll
     for (int j = 0; j < kCStageBlocks; ++j) {
@@ -202,8 +222,7 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
     ss = warp_sum(ss);
     mx = warp_max(mx);
     if (lane == 0) { misc[warp * 2] = ss; misc[warp * 2 + 1] = mx; }
-    __syncthreads();  // (also: every thread has read its floats from the digit area before digits overwrite it)
-    chain_stamp(dbg, 5);
+    __syncthreads();  // (also: every warp is past the previous phase's records, so the digit rows may be replaced)
     float inv, amax;
     {
         float s_ = misc[(lane & 15) * 2], m_ = misc[(lane & 15) * 2 + 1];
@@ -215,6 +234,7 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
         inv = norm ? 1.0f / sqrtf(s_ / (float)K + ph.eps) : 1.0f;
         amax = m_ * inv;
     }
+    chain_stamp(dbg, 2);
     // power-of-two scale: |x * 2^sh| < 2^29 for every element (margin for the few ulps by which the product
     // recomputed below may exceed the maximum found above).  A non-finite maximum gives all-zero digits.
     float xscale = 0.0f, inv_xscale = 1.0f;
@@ -226,52 +246,51 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
         xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
         inv_xscale = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
-#pragma unroll 1
+#pragma unroll
     for (int j = 0; j < kCStageBlocks; ++j) {
         const int wbase = j * kSThreads + warp * 32;
-        if (wbase >= nblk) break;
-        const int blk = wbase + lane;
-        const bool active = blk < nblk;
-        const int k = (active ? blk : wbase) << 3;
-        float u[8];
+        if (wbase < nblk) {  // warp-uniform
+            const int blk = wbase + lane;
+            const bool active = blk < nblk;
+            const int k = (active ? blk : wbase) << 3;
+            float u[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) u[q] = v[0][q];
+            for (int q = 0; q < 8; ++q) u[q] = v[j][q];
+            if (norm) {
+                const uint4 nwj = *reinterpret_cast<const uint4*>(ph.norm_w + k);  // (read before: a cache hit)
+                const uint32_t ww[4] = {nwj.x, nwj.y, nwj.z, nwj.w};
 #pragma unroll
-        for (int jj = 0; jj + 1 < kCStageBlocks; ++jj) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) v[jj][q] = v[jj + 1][q];
-        }
-        if (norm) {
-            const uint4 nwj = *reinterpret_cast<const uint4*>(ph.norm_w + k);  // (read before: a cache hit)
-            const uint32_t ww[4] = {nwj.x, nwj.y, nwj.z, nwj.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
-                u[2 * q] = u[2 * q] * inv * __uint_as_float(ww[q] << 16);
-                u[2 * q + 1] = u[2 * q + 1] * inv * __uint_as_float(ww[q] & 0xffff0000u);
+                for (int q = 0; q < 4; ++q) {  // kmll's order: x * inv * w
+                    u[2 * q] = u[2 * q] * inv * __uint_as_float(ww[q] << 16);
+                    u[2 * q + 1] = u[2 * q + 1] * inv * __uint_as_float(ww[q] & 0xffff0000u);
+                }
             }
-        }
-        uint32_t d[8];
+            uint32_t d[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) d[q] = (uint32_t)(__float2int_rn(u[q] * xscale) + 0x40000000);
-        uint32_t r0[4], r1[4];
-        transpose_bytes4(d[0], d[1], d[2], d[3], r0);
-        transpose_bytes4(d[4], d[5], d[6], d[7], r1);
-        if (active) {
+            for (int q = 0; q < 8; ++q) d[q] = (uint32_t)(__float2int_rn(u[q] * xscale) + 0x40000000);
+            uint32_t r0[4], r1[4];
+            transpose_bytes4(d[0], d[1], d[2], d[3], r0);
+            transpose_bytes4(d[4], d[5], d[6], d[7], r1);
+            if (active) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r) *reinterpret_cast<uint2*>(xs + (size_t)r * xs_pitch + k) = make_uint2(r0[r], r1[r]);
-        }
-        // per-group sums of the digit bytes -> correction words of the low-nibble rows: a group is the 16 blocks of a
-        // half warp
-        int sdig[4];
+                for (int r = 0; r < 4; ++r) *reinterpret_cast<uint2*>(xs + (size_t)r * xs_pitch + k) = make_uint2(r0[r], r1[r]);
+            }
+            // per-group sums of the digit bytes -> correction words of the low-nibble rows: a group is the 16 blocks of
+            // a half warp; the four sums travel as two packed pairs (each sum < 2^16)
+            uint32_t s01 = 0u, s23 = 0u;
+            if (active) {
+                s01 = __dp4a(r0[0], 0x01010101u, __dp4a(r1[0], 0x01010101u, 0u)) | (__dp4a(r0[1], 0x01010101u, __dp4a(r1[1], 0x01010101u, 0u)) << 16);
+                s23 = __dp4a(r0[2], 0x01010101u, __dp4a(r1[2], 0x01010101u, 0u)) | (__dp4a(r0[3], 0x01010101u, __dp4a(r1[3], 0x01010101u, 0u)) << 16);
+            }
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            unsigned int a = active ? __dp4a(r0[r], 0x01010101u, __dp4a(r1[r], 0x01010101u, 0u)) : 0u;
-#pragma unroll
-            for (int off = 1; off < 16; off <<= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-            sdig[r] = (int)a;
-        }
-        if ((lane & 15) == 0 && active) {
-            *reinterpret_cast<int4*>(corr + 4 * (k >> 7)) = make_int4(8 * (sdig[0] + 256 * sdig[1]), 8 * sdig[2], 8 * (sdig[3] - 64 * 128), 0);
+            for (int off = 1; off < 16; off <<= 1) {
+                s01 += __shfl_xor_sync(0xffffffffu, s01, off);
+                s23 += __shfl_xor_sync(0xffffffffu, s23, off);
+            }
+            if ((lane & 15) == 0 && active) {
+                const int s0 = (int)(s01 & 0xffffu), s1 = (int)(s01 >> 16), s2 = (int)(s23 & 0xffffu), s3 = (int)(s23 >> 16);
+                *reinterpret_cast<int4*>(corr + 4 * (k >> 7)) = make_int4(8 * (s0 + 256 * s1), 8 * s2, 8 * (s3 - 64 * 128), 0);
+            }
         }
     }
     // constants behind the digit rows: 16 bytes of ones, then 16 bytes of zeros (absent MMA columns); in this order the
@@ -279,7 +298,7 @@ __device__ __noinline__ float chain_stage(const ChainPhase& ph, const TpExchange
     if (tid < 4) reinterpret_cast<uint32_t*>(xs + (size_t)4 * xs_pitch)[tid] = 0x01010101u;
     else if (tid < 8) reinterpret_cast<uint32_t*>(xs + (size_t)4 * xs_pitch)[tid] = 0u;
     __syncthreads();
-    chain_stamp(dbg, 7);
+    chain_stamp(dbg, 3);
     return inv_xscale;
 }
 
@@ -338,25 +357,45 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
     };
     l_unit = blockIdx.x;
     l_enter();
+    // Records of a LATER phase than the one being consumed are held back (beyond kCEarly per warp): a multiprocessor
+    // gets its load responses back in request order, so the loads of the next phase's input vector - the critical
+    // path of a phase change - would wait behind every weight read from HBM that was requested before them (measured:
+    // 3.5 us with the ring full, against 1 us for the same loads alone).  The slots held back are requested right
+    // behind those loads (top_up).
+    int c_phase_now = 0, ahead = 0, held = 0;
+    bool hold_all = false;
+    auto issue_record = [&](int slot) {
+        const uint32_t dst = ring_dst + (uint32_t)slot * (4 * kCPlane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cp_async_stream16_to(dst + i * kCPlane, l_src + i * 512);
+        if (lane < 4) cp_async_stream16_to(sring_dst + (uint32_t)slot * 64, l_src + 2048);
+        if (l_phase != c_phase_now) ++ahead;
+        l_src += kCRecBytes;
+        if (--l_left == 0) {
+            l_unit += gridDim.x;
+            l_enter();
+        }
+    };
     auto load_record = [&](int slot) {
         if (l_phase < p.n_phases) {
-            const uint32_t dst = ring_dst + (uint32_t)slot * (4 * kCPlane);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) cp_async_stream16_to(dst + i * kCPlane, l_src + i * 512);
-            if (lane < 4) cp_async_stream16_to(sring_dst + (uint32_t)slot * 64, l_src + 2048);
-            l_src += kCRecBytes;
-            if (--l_left == 0) {
-                l_unit += gridDim.x;
-                l_enter();
-            }
+            if (hold_all || (l_phase != c_phase_now && ahead >= kCEarly)) ++held;  // its slot stays empty until top_up
+            else issue_record(slot);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per slot, also when nothing was left to copy
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per slot, also when nothing was copied
     };
+    // weights do not depend on the previous kernel: half of the ring is requested before the dependency wait, the other
+    // half right behind the loads of the first phase's input (so that those do not wait behind 128 KB of weights)
 #pragma unroll 1
-    for (int d = 0; d < kCDepth; ++d) load_record(d);  // weights do not depend on the previous kernel
+    for (int d = 0; d < kCDepth; ++d) {
+        hold_all = d >= kCDepth / 2;
+        load_record(d);
+    }
+    hold_all = false;
 
     pdl_wait();
     chain_stamp(p.trace, 1);
+    // number of the running decode step (written by the kernel that began the step, at least one launch ago)
+    const uint32_t step = p.xc != nullptr ? *p.xcv.epoch : 0u;
 
     // this lane's B column g: digit rows d0, d1, d2, -, d3, ones, -, -; absent columns read 16 zero bytes with stride 0
     const int8_t* ones = xs + (size_t)4 * p.xs_pitch;
@@ -374,6 +413,15 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
     uint32_t best_token = 0xffffffffu;
     bool ok = true;
     int it = 0, slot = 0;
+    auto top_up = [&]() {  // the `held` most recently consumed slots are empty: fill them, oldest first
+        while (held > 0) {
+            int sl = slot - held;
+            if (sl < 0) sl += kCDepth;
+            if (l_phase < p.n_phases) issue_record(sl);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            --held;
+        }
+    };
 
 #pragma unroll 1
     for (int c_phase = 0; c_phase < p.n_phases; ++c_phase) {
@@ -382,9 +430,9 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
         warp_slice(ph.ngroups, j0, j1);
         const int spu = j1 - j0;
         if ((int)blockIdx.x >= ph.total_units) continue;  // no unit of this phase for this block
-        __syncthreads();  // every warp has finished the previous phase's records: the digit rows may be replaced
-        const float inv_xscale = chain_stage(ph, p.xc, p.xs_pitch, xs, corr, misc, p.n_phases == 1 ? p.trace : nullptr);
-        chain_stamp(p.trace, 2 + 2 * c_phase);
+        c_phase_now = c_phase;
+        ahead = 0;
+        const float inv_xscale = chain_stage(ph, p.xcv, step, p.xs_pitch, xs, corr, misc, p.trace != nullptr ? p.trace + 2 + 5 * c_phase : nullptr, top_up);
         const float wA = w_lane * inv_xscale * 0.0625f, wB = w_lane * inv_xscale;
         const int epi = ph.epi;
 
@@ -403,8 +451,8 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
                 const int row = row0 + lane;
                 if (row < ph.out_rows[mi]) {
                     if (ph.residual_index >= 0) {
-                        const TpExchange& xc = *p.xc;
-                        const uint32_t epoch = chain_epoch(xc, ph.residual_index);
+                        const TpExchange& xc = p.xcv;
+                        const uint32_t epoch = chain_epoch(xc, step, ph.residual_index);
                         const uint2* box = xc.inbox[xc.rank] + (size_t)(ph.residual_index & 1) * xc.tp * xc.dim + row;
                         const unsigned long long t0 = device_clock_ns();
                         for (int r = 0; r < xc.tp; ++r) {
@@ -511,24 +559,24 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
                     if (ph.out_kind == CHAIN_OUT_PLAIN) {
                         ph.out[mi][row] = v;
                     } else {
-                        const TpExchange& xc = *p.xc;
-                        const uint32_t epoch = chain_epoch(xc, ph.out_index);
+                        const TpExchange& xc = p.xcv;
+                        const uint32_t epoch = chain_epoch(xc, step, ph.out_index);
                         if (ph.out_kind == CHAIN_OUT_INBOX) {
                             const size_t s = ((size_t)(ph.out_index & 1) * xc.tp + xc.rank) * xc.dim + row;
-                            for (int dst = 0; dst < xc.tp; ++dst) st_exchange_word(xc.inbox[dst] + s, __float_as_uint(v), epoch);
+                            for (int dst = 0; dst < xc.tp; ++dst) push_exchange_word(xc.inbox[dst] + s, __float_as_uint(v), epoch, xc.tp > 1);
                         } else {
-                            st_exchange_word(xc.local_box + row, __float_as_uint(v), epoch);
+                            push_exchange_word(xc.local_box + row, __float_as_uint(v), epoch, false);
                         }
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) {
-                if (ph.out_kind != CHAIN_OUT_PLAIN) chain_signal(*p.xc, ph.out_kind, ph.out_index);
+                if (ph.out_kind != CHAIN_OUT_PLAIN) chain_signal(p.xcv, ph.out_kind, ph.out_index);
                 mbar_arrive(&done[buf]);
             }
         }
-        chain_stamp(p.trace, 3 + 2 * c_phase);
+        chain_stamp(p.trace, 2 + 5 * c_phase + 4);
         if (!ok) break;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -578,8 +626,8 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
                     p.state->step += 1;
                 }
                 if (p.push_top) {  // tensor parallel: hand this rank's result to every rank (two exchange words)
-                    const TpExchange& xc = *p.xc;
-                    const uint32_t epoch = *xc.epoch * (uint32_t)xc.mult + (uint32_t)xc.top_index + 1u;
+                    const TpExchange& xc = p.xcv;
+                    const uint32_t epoch = step * (uint32_t)xc.mult + (uint32_t)xc.top_index + 1u;
                     const size_t s = ((size_t)(epoch & 1u) * xc.tp + xc.rank) * 2;
                     for (int dst = 0; dst < xc.tp; ++dst) {
                         st_exchange_word(xc.top_inbox[dst] + s, (uint32_t)(packed >> 32), epoch);
@@ -589,7 +637,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
             }
         }
     }
-    chain_stamp(p.trace, 10);
+    chain_stamp(p.trace, 22);
     if (!ok) atomicCAS(&g_device_status, 0, 1);
 }
 

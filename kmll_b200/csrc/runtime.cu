@@ -109,6 +109,7 @@ struct Decoder {
     ncclComm_t comm = nullptr;
     // peer-memory exchange (tensor parallel decode step); null = NCCL collectives
     TpExchange* xc = nullptr;          // device copy of the tables
+    TpExchange xc_host;                // the same tables on the host (the chained kernel takes them by value)
     void* xc_local = nullptr;          // this rank's exchange buffer (shared with the peers through CUDA IPC)
     unsigned int* xc_epoch = nullptr;  // inside xc_local
     void* xc_peer_base[kMaxTp] = {};   // peers' buffers as mapped here (null for the own rank)
@@ -118,6 +119,8 @@ struct Decoder {
     bool weights_set = false;
     // chained decode step (W4-G128, fused): prepared weights, exchange words also on a single GPU
     bool chain = false;            // the decode step runs linear_chain_kernel
+    bool chain_split = true;       // ... one launch per projection (default) instead of one launch per layer (KMLL_CHAIN=layer)
+    bool chain_words = false;      // one GPU, one launch per projection: still hand the vectors over as exchange words (KMLL_CHAIN=words)
     bool prepared_valid = false;   // the prepared buffers match the canonical tensors
     unsigned int* top1_counter = nullptr;
 };
@@ -410,6 +413,7 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
         memset(&cp, 0, sizeof(cp));
         cp.n_phases = 1;
         cp.xc = d->xc;
+        if (d->xc != nullptr) cp.xcv = d->xc_host;
         qkv_phase(cp.phase[0], 0);
         KMLL_TRY(launch_chain(s, cp));
     }
@@ -428,6 +432,7 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
         memset(&cp, 0, sizeof(cp));
         cp.n_phases = 4;
         cp.xc = d->xc;
+        if (d->xc != nullptr) cp.xcv = d->xc_host;
         {   // output projection + residual -> exchange 2l
             ChainPhase& ph = cp.phase[0];
             chain_phase_common(ph, EPI_RESIDUAL, q_len);
@@ -492,10 +497,46 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
             cp.push_top = tp ? 1 : 0;
         }
         cp.phase[3].in_units = cp.phase[2].total_units;  // its input comes from the down projection of this launch
-        KMLL_TRY(launch_chain(s, cp));
+        if (d->chain_split && !tp && !d->chain_words) {
+            // one GPU, one launch per projection: the vectors go through plain buffers (the grid dependency of consecutive
+            // launches orders them), exactly like kmll's own operator sequence
+            float* hidden = (l & 1) ? d->hidden_b : d->hidden_a;   // input of this layer
+            float* other = (l & 1) ? d->hidden_a : d->hidden_b;    // its output
+            ChainPhase& wo = cp.phase[0];
+            wo.residual = hidden; wo.residual_index = -1; wo.out_kind = CHAIN_OUT_PLAIN; wo.out[0] = d->hidden_mid;
+            ChainPhase& gu = cp.phase[1];
+            gu.in_kind = CHAIN_IN_PLAIN; gu.x = d->hidden_mid; gu.out_kind = CHAIN_OUT_PLAIN; gu.out[0] = d->act;
+            ChainPhase& w2 = cp.phase[2];
+            w2.in_kind = CHAIN_IN_PLAIN; w2.x = d->act; w2.residual = d->hidden_mid; w2.residual_index = -1;
+            w2.out_kind = CHAIN_OUT_PLAIN; w2.out[0] = other;
+            ChainPhase& nx = cp.phase[3];
+            nx.in_kind = CHAIN_IN_PLAIN; nx.x = other; nx.x_out = nullptr;
+        }
+        if (d->chain_split) {
+            // one launch per phase: the grid dependency of consecutive launches hands the vectors over (the words are
+            // complete when a launch starts, so no arrival hint is needed); same kernel, same arithmetic
+            for (int i = 0; i < 4; ++i) {
+                ChainParams one = cp;
+                one.n_phases = 1;
+                one.phase[0] = cp.phase[i];
+                one.phase[0].in_units = 0;
+                if (i != 3) {
+                    one.partial_tokens = nullptr;
+                    one.state = nullptr;
+                    one.push_top = 0;
+                }
+                KMLL_TRY(launch_chain(s, one));
+            }
+        } else {
+            KMLL_TRY(launch_chain(s, cp));
+        }
     }
     if (tp) KMLL_TRY(decode_end_gather(s, d->xc, d->state, d->packed_final));
     if (launches) *launches = (int)(launch_counter() - before);
+    if (d->chain_split && !tp && !d->chain_words && (c.n_layers & 1)) {  // keep the final hidden state where kmll_decoder_last_hidden finds it
+        KMLL_CUDA(cudaMemcpyAsync(d->hidden_a, d->hidden_b, sizeof(float) * c.dim, cudaMemcpyDeviceToDevice, s));
+        if (launches) *launches += 1;
+    }
     return KMLL_OK;
 }
 
@@ -854,6 +895,7 @@ static int setup_exchange(Decoder* d) {
     d->xc_epoch = h.epoch;
     KMLL_TRY(dalloc(d, &d->xc, 1));
     KMLL_CUDA(cudaMemcpy(d->xc, &h, sizeof(h), cudaMemcpyHostToDevice));
+    d->xc_host = h;
     return KMLL_OK;
 }
 
@@ -932,6 +974,11 @@ int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out) 
         KMLL_CUDA(cudaMemset(d->state, 0, sizeof(DecodeState)));
         KMLL_CUDA(cudaMallocHost((void**)&d->pinned, 64 * sizeof(uint64_t)));
         d->chain = chain_supported(d);
+        {
+            const char* v = std::getenv("KMLL_CHAIN");
+            d->chain_split = !(v != nullptr && strcmp(v, "layer") == 0);
+            d->chain_words = v != nullptr && strcmp(v, "words") == 0;
+        }
         if (d->chain) {
             KMLL_TRY(dalloc(d, &d->top1_counter, (size_t)4));
             KMLL_CUDA(cudaMemset(d->top1_counter, 0, 16));
