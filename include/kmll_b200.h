@@ -7,7 +7,8 @@
  *   - `stream` is a CUDA stream handle (cudaStream_t / CUstream); ops only enqueue work on it
  *     and never synchronise (kmll ops have the same contract, crates/inference/src/ops/inference.rs).
  *   - every pointer is a DEVICE pointer owned by the caller; nothing is allocated or freed by an
- *     operator call (buffers: crates/inference/src/model.rs:9339-9498 allocates scratch once).
+ *     operator call (buffers: crates/inference/src/model.rs:9339-9498 allocates scratch once); operators that
+ *     need scratch take a caller-owned workspace and say how large it must be.
  *   - the return value is 0 on success or a negative KMLL_ERR_* code.  Where kmll panics on a
  *     shape mismatch (`assert!`, `LayoutError`, crates/inference/src/layout.rs:569-666) the C ABI
  *     returns KMLL_ERR_SHAPE / KMLL_ERR_NULL instead; kmll_last_error() gives the message of the
@@ -214,21 +215,27 @@ int kmll_linear_top1_w4p(kmll_stream_t stream, const float* x, const uint16_t* n
 
 /* y[batch, out] = x[batch, in] . dequant(W)^T — linear_batched_i8_scaled,
  * crates/inference/src/ops/matmul.rs:423-463 (gemm_f32_i8_scaled_tiled_kernel).  x and y are
- * row-major prefixes of possibly larger buffers, as in kmll. */
+ * row-major prefixes of possibly larger buffers, as in kmll.
+ * `workspace` is caller-owned scratch of kmll_linear_batched_workspace_bytes(batch, in_dim) bytes (16-byte aligned),
+ * as kmll's runtime owns every scratch buffer (crates/inference/src/model.rs:9339-9498); with it, 5 or more rows
+ * run on the tensor cores (tcgen05, up to 256 rows of x per pass over the weights, exact f16 operand splitting: the
+ * result carries f32 accuracy).  It may be null: the call then streams the weights once per 4 rows of x.  Calls
+ * that share a workspace must not overlap. */
+size_t kmll_linear_batched_workspace_bytes(int batch, int in_dim);
 int kmll_linear_batched_i8(kmll_stream_t stream, const float* x, const int8_t* w,
-                           const float* scales, int batch, int in_dim, int out_dim, float* y);
+                           const float* scales, int batch, int in_dim, int out_dim, void* workspace, float* y);
 int kmll_linear_batched_w4g128(kmll_stream_t stream, const float* x, const uint8_t* packed,
                                const uint16_t* gscales_f16, int batch, int in_dim, int out_dim,
-                               float* y);
+                               void* workspace, float* y);
 /* linear_qkv_batched_i8_scaled, crates/inference/src/ops/matmul.rs:465-510 */
 int kmll_linear_qkv_batched_i8(kmll_stream_t stream, const float* x, const int8_t* wq,
                                const float* sq, const int8_t* wk, const float* sk,
                                const int8_t* wv, const float* sv, int batch, int in_dim,
-                               int q_dim, int kv_dim, float* q, float* k, float* v);
+                               int q_dim, int kv_dim, void* workspace, float* q, float* k, float* v);
 int kmll_linear_qkv_batched_w4g128(kmll_stream_t stream, const float* x, const uint8_t* wq,
                                    const uint16_t* sq, const uint8_t* wk, const uint16_t* sk,
                                    const uint8_t* wv, const uint16_t* sv, int batch, int in_dim,
-                                   int q_dim, int kv_dim, float* q, float* k, float* v);
+                                   int q_dim, int kv_dim, void* workspace, float* q, float* k, float* v);
 
 /* ------------------------------------------------------------------------------------------
  * Row reductions and elementwise ops

@@ -27,6 +27,12 @@ int check_launch(const char* what);
         if (!(cond)) return ::kmll::fail(KMLL_ERR_SHAPE, __VA_ARGS__);        \
     } while (0)
 
+#define KMLL_TRY_RC(expr)                 \
+    do {                                  \
+        const int rc__ = (expr);          \
+        if (rc__ != KMLL_OK) return rc__; \
+    } while (0)
+
 // ---- bf16 bit patterns (kmll stores norm weights / embeddings as raw bf16 bits) ------------
 __host__ __device__ inline float bf16_bits_to_f32(uint16_t bits) {
 #ifdef __CUDA_ARCH__

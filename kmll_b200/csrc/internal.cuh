@@ -185,9 +185,12 @@ int linear_top1_offset(cudaStream_t stream, int fmt, const float* x, const uint1
 // Batched fused linear forms for rows of x that are independent sequences (batch <= 16 per pass):
 // form 0 = RMSNorm + QKV (3 matrices, rows[0..2]), 1 = RMSNorm + gate/up + SiLU*up (2 matrices of rows[0]),
 // 2 = projection + residual, 3 = (RMSNorm +) projection.  Outputs are [batch, rows] row-major.
+// `workspace` (linear_batched_workspace_bytes(batch, cols) bytes) enables the tensor-core path for 5 or more rows; form 1
+// then also needs two [batch, rows] scratch matrices for the gate and up projections.
 int linear_batched_form(int form, cudaStream_t stream, int fmt, const float* x, int batch, const uint16_t* norm_w, float eps,
                         const void* const* w, const void* const* scales, const int* rows, int cols, float* const* outs,
-                        const float* residual);
+                        const float* residual, void* workspace = nullptr, float* gate_tmp = nullptr, float* up_tmp = nullptr);
+size_t linear_batched_workspace_bytes(int batch, int in_dim);
 // Deterministic merge of per-rank packed results: higher logit wins, ties -> lower token.
 int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out);
 

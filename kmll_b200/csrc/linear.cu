@@ -615,8 +615,8 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
 }  // namespace kmll
 
 #include "linear_stream.cuh"
-#include "linear_umma.cuh"
 #include "linear_chain.cuh"
+#include "linear_gemm.cuh"
 
 namespace kmll {
 
@@ -796,95 +796,6 @@ static int launch_linear(cudaStream_t stream, LinearParams& p, int* top1_count) 
     return launch_variant<FMT, 1, 4, EPI, 2>(stream, p, grid);
 }
 
-// ---- tcgen05 path for batches of RS-I8 rows -----------------------------------------------------------
-// Digit scratch of the batched tensor-core path: [64 rows][kUmmaMaxK] bytes + 16 scales, allocated once per device on
-// the first batched call (the operators themselves never allocate per call).  Calls that overlap on one device from
-// different streams would share it; the decoder and the tests issue them on one stream.
-constexpr int kUmmaMaxK = 65536;
-constexpr int kUmmaSplitTiles = 74, kUmmaMaxSplit = 4;  // split-K only for row counts up to 74 * 128
-struct UmmaScratch { uint8_t* digits = nullptr; float* inv_xscale = nullptr; float* partial = nullptr; unsigned int* counters = nullptr; };
-static int umma_scratch(UmmaScratch* out) {
-    static std::mutex mu;
-    static UmmaScratch per_device[64];
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(KMLL_ERR_CUDA, "linear_batched: cudaGetDevice failed");
-    std::lock_guard<std::mutex> lock(mu);
-    if (per_device[dev].digits == nullptr) {
-        void* ptr = nullptr;
-        const size_t digit_bytes = (size_t)kUmmaN * kUmmaMaxK;
-        const size_t partial_bytes = (size_t)kUmmaSplitTiles * kUmmaMaxSplit * kUmmaBatch * kUmmaRows * sizeof(float);
-        e = cudaMalloc(&ptr, digit_bytes + 256 + partial_bytes + 1024);
-        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_batched: scratch allocation failed: %s", cudaGetErrorString(e));
-        per_device[dev].digits = static_cast<uint8_t*>(ptr);
-        per_device[dev].inv_xscale = reinterpret_cast<float*>(per_device[dev].digits + digit_bytes);
-        per_device[dev].partial = reinterpret_cast<float*>(per_device[dev].digits + digit_bytes + 256);
-        per_device[dev].counters = reinterpret_cast<unsigned int*>(per_device[dev].digits + digit_bytes + 256 + partial_bytes);
-        e = cudaMemset(per_device[dev].counters, 0, 1024);
-        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_batched: scratch initialisation failed: %s", cudaGetErrorString(e));
-    }
-    *out = per_device[dev];
-    return KMLL_OK;
-}
-static bool umma_enabled() {
-    static const bool on = [] {
-        const char* v = std::getenv("KMLL_UMMA");
-        return !(v != nullptr && v[0] == '0');
-    }();
-    return on;
-}
-// y[m, :] (+= residual) = dequant(W_i) x[m, :] for every matrix i and up to 16 rows of x per pass
-static int run_umma_i8(cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps,
-                       const void* const* w, const void* const* scales, const int* rows, float* const* outs,
-                       const float* const* residuals, const int* ldos, int nmat) {
-    UmmaScratch sc;
-    {
-        const int rc = umma_scratch(&sc);
-        if (rc != KMLL_OK) return rc;
-    }
-    const size_t smem = (size_t)kUmmaStages * (kUmmaABytes + kUmmaBBytes) + (2 * kUmmaStages + 1) * 8 + 64;
-    {
-        cudaError_t e = cudaFuncSetAttribute(linear_umma_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  // per device
-        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    }
-    for (int m0 = 0; m0 < M; m0 += kUmmaBatch) {
-        const int mb = (M - m0) < kUmmaBatch ? (M - m0) : kUmmaBatch;
-        cudaError_t e = launch(digitize_rows_kernel, dim3(mb), dim3(1024), 0, stream, true, x + (size_t)m0 * ldx, ldx, K, norm_w, eps,
-                               sc.digits, sc.inv_xscale);
-        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "digitize_rows: %s", cudaGetErrorString(e));
-        for (int i = 0; i < nmat; ++i) {
-            UmmaParams up;
-            up.w = static_cast<const int8_t*>(w[i]);
-            up.row_scales = static_cast<const float*>(scales[i]);
-            up.rows = rows[i];
-            up.K = K;
-            up.ldw = K;
-            up.digits = sc.digits;
-            up.inv_xscale = sc.inv_xscale;
-            up.batch = mb;
-            up.out = outs[i] + (size_t)m0 * ldos[i];
-            up.residual = residuals[i] ? residuals[i] + (size_t)m0 * ldos[i] : nullptr;
-            up.ldo = ldos[i];
-            // few row tiles: split K over up to 4 blocks per tile (at least 4 k-tiles each) so that more SMs stream
-            const int tiles = (rows[i] + kUmmaRows - 1) / kUmmaRows;
-            int ksplit = 1;
-            if (tiles <= kUmmaSplitTiles) {
-                ksplit = 148 / tiles;
-                if (ksplit > kUmmaMaxSplit) ksplit = kUmmaMaxSplit;
-                const int by_k = (K / kUmmaKT) / 4;
-                if (ksplit > by_k) ksplit = by_k;
-                if (ksplit < 1) ksplit = 1;
-            }
-            up.partial = sc.partial;
-            up.counters = sc.counters;
-            up.trace = trace_next_slot(300, tiles * ksplit);
-            e = launch(linear_umma_i8_kernel, dim3(tiles, ksplit), dim3(kUmmaThreads), smem, stream, true, up);
-            if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_umma_i8: %s", cudaGetErrorString(e));
-        }
-    }
-    return KMLL_OK;
-}
-
 // ---- chained kernel over prepared W4-G128 records ---------------------------------------------------------------
 __device__ unsigned int g_chain_top1_counter = 0;  // arrival counter of operator-level arg-max calls (left at zero by every launch)
 
@@ -988,6 +899,128 @@ static void chain_plain_phase(ChainPhase& ph, int epi, const float* x, const uin
     ph.total_units = units;
 }
 
+// ---- tcgen05 GEMM path (linear_gemm.cuh) ------------------------------------------------------------------------
+struct GemmPlan {
+    int n_block, x_blocks, row_tiles, ksplit, stages;
+    size_t smem;
+    size_t off_lo, off_inv, off_partial, off_counters, total;  // workspace layout in bytes
+};
+static bool gemm_plan(int fmt, int M, int K, int rows, GemmPlan* out) {
+    if (M < 5 || K % kGKT != 0 || (fmt == FMT_W4 && K % 128 != 0) || rows <= 0) return false;
+    GemmPlan pl;
+    pl.x_blocks = (M + kGMaxN - 1) / kGMaxN;
+    pl.n_block = (((M + pl.x_blocks - 1) / pl.x_blocks) + 15) & ~15;
+    pl.row_tiles = (rows + kGRows - 1) / kGRows;
+    const int tiles = pl.row_tiles * pl.x_blocks, kt_all = K / kGKT;
+    pl.ksplit = 1;
+    if (tiles < 148 && pl.n_block <= 64) {  // few tiles (batches of sequences): split K so that every multiprocessor streams
+        pl.ksplit = 148 / tiles;
+        if (pl.ksplit > kGMaxSplit) pl.ksplit = kGMaxSplit;
+        if (pl.ksplit > kt_all / 8) pl.ksplit = kt_all / 8;
+        if (pl.ksplit < 1) pl.ksplit = 1;
+    }
+    const size_t raw = fmt == FMT_W4 ? 4096 : 8192;
+    const size_t stage = (size_t)(fmt == FMT_W4 ? 2 : 1) * kGRows * 128 + (size_t)2 * pl.n_block * 128 + raw;
+    pl.stages = (int)((220 * 1024 - 2048) / stage);
+    if (pl.stages > 4) pl.stages = 4;
+    if (pl.stages < 2) return false;
+    pl.smem = (size_t)pl.stages * stage + (3 * pl.stages + 1) * 8 + 16 + 1024;  // + slack for the 1024-byte alignment
+    auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    pl.off_lo = up256((size_t)M * K * 2);
+    pl.off_inv = pl.off_lo + up256((size_t)M * K * 2);
+    pl.off_partial = pl.off_inv + up256((size_t)M * 4);
+    // the layout depends on (M, K) only, so one workspace serves matrices of any height: split-K keeps tiles * splits
+    // at or below 148 partial tiles; 16384 arrival counters
+    if (tiles > 16384) return false;
+    pl.off_counters = pl.off_partial + (pl.n_block <= 64 ? up256((size_t)148 * pl.n_block * kGRows * 4) : 0);
+    pl.total = pl.off_counters + 16384 * 4;
+    *out = pl;
+    return true;
+}
+
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                     CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
+            return (TensorMapEncodeFn) nullptr;
+        return reinterpret_cast<TensorMapEncodeFn>(sym);
+    }();
+    return fn;
+}
+// 2-D row-major tensor [rows, inner] of `elem` bytes, box = [box_rows, box_inner]
+static int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                       uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (enc == nullptr) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    (void)elem;
+    const CUresult r = enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return KMLL_OK;
+}
+
+static bool gemm_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("KMLL_GEMM");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+
+// y[m, :] (+= residual) = dequant(W_i) x[m, :] for every matrix i; x is split into f16 planes once for all of them
+template <int FMT>
+static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps, const void* const* w,
+                    const void* const* scales, const int* rows, float* const* outs, const float* const* residuals, const int* ldos, int nmat,
+                    void* workspace) {
+    int max_rows = 0;
+    for (int i = 0; i < nmat; ++i) max_rows = rows[i] > max_rows ? rows[i] : max_rows;
+    GemmPlan big;
+    if (!gemm_plan(FMT, M, K, max_rows, &big)) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: shape not supported by the tensor-core path");
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    __half* x_hi = reinterpret_cast<__half*>(ws);
+    __half* x_lo = reinterpret_cast<__half*>(ws + big.off_lo);
+    float* inv = reinterpret_cast<float*>(ws + big.off_inv);
+    float* partial = reinterpret_cast<float*>(ws + big.off_partial);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(ws + big.off_counters);
+    const int n_counters = 16384;
+    cudaError_t e = launch(split_rows_kernel, dim3(M), dim3(512), 0, stream, true, x, ldx, K, norm_w, eps, x_hi, x_lo, inv, counters, n_counters);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "split_rows: %s", cudaGetErrorString(e));
+    auto kern = linear_gemm_kernel<FMT>;
+    for (int i = 0; i < nmat; ++i) {
+        GemmPlan pl;
+        if (!gemm_plan(FMT, M, K, rows[i], &pl)) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: shape not supported by the tensor-core path");
+        CUtensorMap map_w, map_hi, map_lo;
+        if (FMT == FMT_W4) KMLL_TRY_RC(make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[i], (uint64_t)K / 2, (uint64_t)rows[i], (uint64_t)K / 2, 32, kGRows, CU_TENSOR_MAP_SWIZZLE_NONE));
+        else KMLL_TRY_RC(make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[i], (uint64_t)K, (uint64_t)rows[i], (uint64_t)K, 64, kGRows, CU_TENSOR_MAP_SWIZZLE_NONE));
+        KMLL_TRY_RC(make_map_2d(&map_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_hi, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kGKT, (uint32_t)pl.n_block, CU_TENSOR_MAP_SWIZZLE_128B));
+        KMLL_TRY_RC(make_map_2d(&map_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_lo, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kGKT, (uint32_t)pl.n_block, CU_TENSOR_MAP_SWIZZLE_128B));
+        GemmParams gp;
+        memset(&gp, 0, sizeof(gp));
+        gp.fmt = FMT; gp.rows = rows[i]; gp.K = K; gp.M = M;
+        gp.n_block = pl.n_block; gp.stages = pl.stages;
+        gp.scales = scales[i];
+        gp.inv_xscale = inv;
+        gp.out = outs[i];
+        gp.residual = residuals[i];
+        gp.ldo = ldos[i];
+        gp.partial = partial;
+        gp.counters = counters;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", pl.smem, cudaGetErrorString(e));
+        e = launch(kern, dim3(pl.row_tiles, pl.x_blocks, pl.ksplit), dim3(kGThreads), pl.smem, stream, true, gp, map_w, map_hi, map_lo);
+        if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_gemm: %s", cudaGetErrorString(e));
+    }
+    return KMLL_OK;
+}
+
 static bool fast_shape(int fmt, int K) { return fmt == FMT_W4 ? (K % 128 == 0) : (K % 64 == 0); }
 
 
@@ -1017,7 +1050,8 @@ struct MatArg {
 template <int FMT, int EPI>
 static int run_linear(const char* name, cudaStream_t stream, const float* x, int M, int K, int ldx,
                       const uint16_t* norm_w, float eps, const MatArg* mats, int nmat, int ldo_override,
-                      uint32_t* partial_tokens, float* partial_logits, int* top1_count = nullptr, int ldw = 0, int lds = 0) {
+                      uint32_t* partial_tokens, float* partial_logits, int* top1_count = nullptr, int ldw = 0, int lds = 0,
+                      void* workspace = nullptr) {
     const ExchangeArgs xa = g_exchange_args;
     g_exchange_args = ExchangeArgs();
     if (xa.xc != nullptr && M != 1) return fail(KMLL_ERR_UNSUPPORTED, "%s: the peer-memory exchange needs batch 1", name);
@@ -1067,10 +1101,14 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
                         FMT == FMT_W4 ? 128 : 64);
         }
     }
-    // RS-I8 batches of 5 or more rows: the tcgen05 kernel (weights as the M side of the MMA, 16 rows of x per pass)
-    if constexpr (FMT == FMT_I8 && (EPI == EPI_STORE || EPI == EPI_RESIDUAL)) {
-        if (M > 4 && K % kUmmaKT == 0 && K <= kUmmaMaxK && ldw == 0 && (ldx & 3) == 0 && aligned16(x) &&
-            (norm_w == nullptr || (reinterpret_cast<uintptr_t>(norm_w) & 7u) == 0) && umma_enabled()) {
+    // 5 or more rows of x and a caller-owned workspace: the tcgen05 kernel (linear_gemm.cuh), up to 256 rows of x per pass
+    // over the weights
+    if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+        GemmPlan pl;
+        bool ok = workspace != nullptr && gemm_enabled() && ldw == 0 && (ldx & 3) == 0 && aligned16(x) && aligned16(workspace) &&
+                  (norm_w == nullptr || (reinterpret_cast<uintptr_t>(norm_w) & 7u) == 0);
+        for (int i = 0; i < nmat && ok; ++i) ok = aligned16(mats[i].w) && gemm_plan(FMT, M, K, mats[i].rows, &pl);
+        if (ok) {
             const void* w_[3];
             const void* s_[3];
             int rows_[3], ldos_[3];
@@ -1081,7 +1119,7 @@ static int run_linear(const char* name, cudaStream_t stream, const float* x, int
                 res_[i] = EPI == EPI_RESIDUAL ? mats[i].residual : nullptr;
                 ldos_[i] = ldo_override > 0 ? ldo_override : mats[i].rows;
             }
-            return run_umma_i8(stream, x, M, K, ldx, norm_w, eps, w_, s_, rows_, outs_, res_, ldos_, nmat);
+            return run_gemm<FMT>(stream, x, M, K, ldx, norm_w, eps, w_, s_, rows_, outs_, res_, ldos_, nmat, workspace);
         }
     }
     // Batches above one row: the streaming kernel takes up to 4 rows of x per pass when its shared-memory plan fits
@@ -1194,32 +1232,52 @@ int decode_end_gather(cudaStream_t stream, const TpExchange* xc, DecodeState* st
 template <int FMT>
 static int batched_forms(int form, cudaStream_t stream, const float* x, int batch, const uint16_t* norm_w, float eps,
                          const void* const* w, const void* const* scales, const int* rows, int cols, float* const* outs,
-                         const float* residual) {
+                         const float* residual, void* workspace, float* gate_tmp, float* up_tmp) {
     switch (form) {
         case 0: {  // RMSNorm + QKV
             MatArg m[3] = {{w[0], scales[0], rows[0], outs[0], nullptr}, {w[1], scales[1], rows[1], outs[1], nullptr},
                            {w[2], scales[2], rows[2], outs[2], nullptr}};
-            return run_linear<FMT, EPI_STORE>("linear_qkv_batched_norm", stream, x, batch, cols, cols, norm_w, eps, m, 3, 0, nullptr, nullptr);
+            return run_linear<FMT, EPI_STORE>("linear_qkv_batched_norm", stream, x, batch, cols, cols, norm_w, eps, m, 3, 0, nullptr, nullptr,
+                                              nullptr, 0, 0, workspace);
         }
         case 1: {  // RMSNorm + gate/up + SiLU*up
+            GemmPlan pl;
+            if (workspace != nullptr && gate_tmp != nullptr && up_tmp != nullptr && gemm_enabled() && gemm_plan(FMT, batch, cols, rows[0], &pl)) {
+                // tensor-core path: gate and up as two plain projections over the same f16 planes of x, then SiLU(gate) * up
+                MatArg m[2] = {{w[0], scales[0], rows[0], gate_tmp, nullptr}, {w[1], scales[1], rows[0], up_tmp, nullptr}};
+                const int rc = run_linear<FMT, EPI_STORE>("silu_gate_up_batched_norm", stream, x, batch, cols, cols, norm_w, eps, m, 2, 0, nullptr,
+                                                          nullptr, nullptr, 0, 0, workspace);
+                if (rc != KMLL_OK) return rc;
+                return kmll_silu_mul_prefix(stream, gate_tmp, up_tmp, (size_t)batch * rows[0], outs[0]);
+            }
             MatArg m[2] = {{w[0], scales[0], rows[0], outs[0], nullptr}, {w[1], scales[1], rows[0], nullptr, nullptr}};
             return run_linear<FMT, EPI_SILU>("silu_gate_up_batched_norm", stream, x, batch, cols, cols, norm_w, eps, m, 2, 0, nullptr, nullptr);
         }
         case 2: {  // projection + residual
             MatArg m = {w[0], scales[0], rows[0], outs[0], residual};
-            return run_linear<FMT, EPI_RESIDUAL>("linear_residual_batched", stream, x, batch, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+            return run_linear<FMT, EPI_RESIDUAL>("linear_residual_batched", stream, x, batch, cols, cols, nullptr, 0.f, &m, 1, 0, nullptr, nullptr,
+                                                 nullptr, 0, 0, workspace);
         }
         default: {  // (RMSNorm +) projection
             MatArg m = {w[0], scales[0], rows[0], outs[0], nullptr};
-            return run_linear<FMT, EPI_STORE>("linear_batched_norm", stream, x, batch, cols, cols, norm_w, eps, &m, 1, 0, nullptr, nullptr);
+            return run_linear<FMT, EPI_STORE>("linear_batched_norm", stream, x, batch, cols, cols, norm_w, eps, &m, 1, 0, nullptr, nullptr,
+                                              nullptr, 0, 0, workspace);
         }
     }
 }
 int linear_batched_form(int form, cudaStream_t stream, int fmt, const float* x, int batch, const uint16_t* norm_w, float eps,
                         const void* const* w, const void* const* scales, const int* rows, int cols, float* const* outs,
-                        const float* residual) {
-    if (fmt == FMT_W4) return batched_forms<FMT_W4>(form, stream, x, batch, norm_w, eps, w, scales, rows, cols, outs, residual);
-    return batched_forms<FMT_I8>(form, stream, x, batch, norm_w, eps, w, scales, rows, cols, outs, residual);
+                        const float* residual, void* workspace, float* gate_tmp, float* up_tmp) {
+    if (fmt == FMT_W4)
+        return batched_forms<FMT_W4>(form, stream, x, batch, norm_w, eps, w, scales, rows, cols, outs, residual, workspace, gate_tmp, up_tmp);
+    return batched_forms<FMT_I8>(form, stream, x, batch, norm_w, eps, w, scales, rows, cols, outs, residual, workspace, gate_tmp, up_tmp);
+}
+size_t linear_batched_workspace_bytes(int batch, int in_dim) {
+    GemmPlan pl;
+    if (!gemm_plan(FMT_W4, batch, in_dim - in_dim % 128, 128, &pl) || in_dim % 64 != 0) {
+        if (!gemm_plan(FMT_I8, batch, in_dim, 128, &pl)) return 0;
+    }
+    return pl.total;
 }
 
 int merge_packed_top1(cudaStream_t stream, const uint64_t* packed_all, int n, uint64_t* packed_out) {
@@ -1410,27 +1468,35 @@ int kmll_linear_top1_w4p(kmll_stream_t s, const float* x, const uint16_t* norm_w
     return launch_chain(as_stream(s), cp);
 }
 
+size_t kmll_linear_batched_workspace_bytes(int batch, int in_dim) {
+    if (batch <= 0 || in_dim <= 0) return 0;
+    return linear_batched_workspace_bytes(batch, in_dim);
+}
 int kmll_linear_batched_i8(kmll_stream_t s, const float* x, const int8_t* w, const float* scales, int batch, int in_dim,
-                           int out_dim, float* y) {
+                           int out_dim, void* workspace, float* y) {
     MatArg m = {w, scales, out_dim, y, nullptr};
-    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, &m, 1, 0, nullptr, nullptr, nullptr, 0,
+                                         0, workspace);
 }
 int kmll_linear_batched_w4g128(kmll_stream_t s, const float* x, const uint8_t* packed, const uint16_t* gs, int batch,
-                               int in_dim, int out_dim, float* y) {
+                               int in_dim, int out_dim, void* workspace, float* y) {
     MatArg m = {packed, gs, out_dim, y, nullptr};
-    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, &m, 1, 0, nullptr, nullptr);
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, &m, 1, 0, nullptr, nullptr, nullptr, 0,
+                                         0, workspace);
 }
 int kmll_linear_qkv_batched_i8(kmll_stream_t s, const float* x, const int8_t* wq, const float* sq, const int8_t* wk,
                                const float* sk, const int8_t* wv, const float* sv, int batch, int in_dim, int q_dim,
-                               int kv_dim, float* q, float* k, float* v) {
+                               int kv_dim, void* workspace, float* q, float* k, float* v) {
     MatArg m[3] = {{wq, sq, q_dim, q, nullptr}, {wk, sk, kv_dim, k, nullptr}, {wv, sv, kv_dim, v, nullptr}};
-    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, m, 3, 0, nullptr, nullptr, nullptr, 0, 0,
+                                         workspace);
 }
 int kmll_linear_qkv_batched_w4g128(kmll_stream_t s, const float* x, const uint8_t* wq, const uint16_t* sq, const uint8_t* wk,
                                    const uint16_t* sk, const uint8_t* wv, const uint16_t* sv, int batch, int in_dim,
-                                   int q_dim, int kv_dim, float* q, float* k, float* v) {
+                                   int q_dim, int kv_dim, void* workspace, float* q, float* k, float* v) {
     MatArg m[3] = {{wq, sq, q_dim, q, nullptr}, {wk, sk, kv_dim, k, nullptr}, {wv, sv, kv_dim, v, nullptr}};
-    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, batch, in_dim, in_dim, nullptr, 0.f, m, 3, 0, nullptr, nullptr, nullptr, 0, 0,
+                                         workspace);
 }
 
 }  // extern "C"

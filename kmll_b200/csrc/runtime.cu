@@ -198,10 +198,10 @@ static int op_linear_residual(Decoder* d, cudaStream_t s, const float* x, const 
         return kmll_linear_residual_w4g128(s, x, (const uint8_t*)w.w, (const uint16_t*)w.scales, res, w.rows, w.cols, y);
     return kmll_linear_residual_i8(s, x, (const int8_t*)w.w, (const float*)w.scales, res, w.rows, w.cols, y);
 }
-static int op_linear_batched(Decoder* d, cudaStream_t s, const float* x, const QWeight& w, int batch, float* y) {
+static int op_linear_batched(Decoder* d, cudaStream_t s, const float* x, const QWeight& w, int batch, void* workspace, float* y) {
     if (d->cfg.format == KMLL_FORMAT_W4G128)
-        return kmll_linear_batched_w4g128(s, x, (const uint8_t*)w.w, (const uint16_t*)w.scales, batch, w.cols, w.rows, y);
-    return kmll_linear_batched_i8(s, x, (const int8_t*)w.w, (const float*)w.scales, batch, w.cols, w.rows, y);
+        return kmll_linear_batched_w4g128(s, x, (const uint8_t*)w.w, (const uint16_t*)w.scales, batch, w.cols, w.rows, workspace, y);
+    return kmll_linear_batched_i8(s, x, (const int8_t*)w.w, (const float*)w.scales, batch, w.cols, w.rows, workspace, y);
 }
 
 // Row-parallel projection followed by the residual add; under tensor parallelism rank 0 adds the
@@ -716,6 +716,8 @@ struct BatchDecoder {
     std::vector<float*> key_cache, value_cache;  // per layer: [batch][max_seq * kv_len]
     float *hidden_a = nullptr, *hidden_b = nullptr, *hidden_mid = nullptr, *q = nullptr, *k = nullptr, *v = nullptr;
     float *attn = nullptr, *act = nullptr, *logits = nullptr, *attn_ws = nullptr;
+    float *gate = nullptr, *up = nullptr;  // [batch, hidden] scratch of the tensor-core gate/up path
+    void* linear_ws = nullptr;             // scratch of the batched linears (f16 planes of the activations)
     BatchState* state = nullptr;
     uint64_t* history = nullptr;  // [batch][history_cap]
     int history_cap = 0;
@@ -755,7 +757,7 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
             const void* sc[3] = {L.wq.scales, L.wk.scales, L.wv.scales};
             const int rows[3] = {q_len, kv_len, kv_len};
             float* outs[3] = {b->q, b->k, b->v};
-            KMLL_TRY(linear_batched_form(0, s, c.format, hidden, B, L.attention_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
+            KMLL_TRY(linear_batched_form(0, s, c.format, hidden, B, L.attention_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr, b->linear_ws));
         }
         KMLL_TRY(decode_attention_launch(s, b->q, b->key_cache[l], b->value_cache[l], &b->state->seq_len, 0, c.max_seq_len, c.n_heads,
                                          c.n_kv_heads, c.head_dim, b->attn_ws, b->attn, b->k, b->v, d->freqs, b->key_cache[l],
@@ -765,21 +767,22 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
             const void* sc[1] = {L.wo.scales};
             const int rows[1] = {c.dim};
             float* outs[1] = {b->hidden_mid};
-            KMLL_TRY(linear_batched_form(2, s, c.format, b->attn, B, nullptr, 0.f, w, sc, rows, q_len, outs, hidden));
+            KMLL_TRY(linear_batched_form(2, s, c.format, b->attn, B, nullptr, 0.f, w, sc, rows, q_len, outs, hidden, b->linear_ws));
         }
         {
             const void* w[2] = {L.w1.w, L.w3.w};
             const void* sc[2] = {L.w1.scales, L.w3.scales};
             const int rows[1] = {c.hidden_dim};
             float* outs[1] = {b->act};
-            KMLL_TRY(linear_batched_form(1, s, c.format, b->hidden_mid, B, L.ffn_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
+            KMLL_TRY(linear_batched_form(1, s, c.format, b->hidden_mid, B, L.ffn_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr, b->linear_ws, b->gate,
+                                         b->up));
         }
         {
             const void* w[1] = {L.w2.w};
             const void* sc[1] = {L.w2.scales};
             const int rows[1] = {c.dim};
             float* outs[1] = {other};
-            KMLL_TRY(linear_batched_form(2, s, c.format, b->act, B, nullptr, 0.f, w, sc, rows, c.hidden_dim, outs, b->hidden_mid));
+            KMLL_TRY(linear_batched_form(2, s, c.format, b->act, B, nullptr, 0.f, w, sc, rows, c.hidden_dim, outs, b->hidden_mid, b->linear_ws));
         }
         float* t = hidden;
         hidden = other;
@@ -790,7 +793,7 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
         const void* sc[1] = {d->output.scales};
         const int rows[1] = {c.vocab_size};
         float* outs[1] = {b->logits};
-        KMLL_TRY(linear_batched_form(3, s, c.format, hidden, B, d->final_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr));
+        KMLL_TRY(linear_batched_form(3, s, c.format, hidden, B, d->final_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr, b->linear_ws));
     }
     KMLL_TRY(batch_end(s, b->logits, c.vocab_size, B, b->state));
     if (launches) *launches = (int)(launch_counter() - launches_before);
@@ -1228,6 +1231,12 @@ int kmll_decoder_prefill(kmll_decoder_t dec, kmll_stream_t stream, const uint32_
         float* tokf = nullptr;
         KMLL_TRY(talloc(&tokf, (size_t)n));
         dtok = (uint32_t*)tokf;
+        // scratch of the batched linears (f16 planes of the activations), sized for the widest input
+        float* wsf = nullptr;
+        const int widest = d->hidden_l > c.dim ? (d->hidden_l > q_len ? d->hidden_l : q_len) : (c.dim > q_len ? c.dim : q_len);
+        const size_t ws_bytes = kmll_linear_batched_workspace_bytes(n, widest);
+        if (ws_bytes > 0) KMLL_TRY(talloc(&wsf, ws_bytes / sizeof(float) + 64));
+        void* ws = wsf;
         KMLL_CUDA(cudaMemcpyAsync(dtok, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s));
         KMLL_TRY(kmll_embedding_tokens(s, d->embedding, c.vocab_size, c.dim, dtok, n, xb));
         const bool w4 = c.format == KMLL_FORMAT_W4G128;
@@ -1238,24 +1247,24 @@ int kmll_decoder_prefill(kmll_decoder_t dec, kmll_stream_t stream, const uint32_
             if (w4) {
                 KMLL_TRY(kmll_linear_qkv_batched_w4g128(s, nb, (const uint8_t*)L.wq.w, (const uint16_t*)L.wq.scales, (const uint8_t*)L.wk.w,
                                                         (const uint16_t*)L.wk.scales, (const uint8_t*)L.wv.w, (const uint16_t*)L.wv.scales, n,
-                                                        c.dim, q_len, kv_len, qb, kb, vb));
+                                                        c.dim, q_len, kv_len, ws, qb, kb, vb));
             } else {
                 KMLL_TRY(kmll_linear_qkv_batched_i8(s, nb, (const int8_t*)L.wq.w, (const float*)L.wq.scales, (const int8_t*)L.wk.w,
                                                     (const float*)L.wk.scales, (const int8_t*)L.wv.w, (const float*)L.wv.scales, n, c.dim,
-                                                    q_len, kv_len, qb, kb, vb));
+                                                    q_len, kv_len, ws, qb, kb, vb));
             }
             KMLL_TRY(prepare_prefill_offset(s, qb, kb, vb, d->freqs, c.rotary_dim / 2, n, q_len, kv_len, c.head_dim, 0, qrb, L.key_cache,
                                             L.value_cache));
             KMLL_TRY(kmll_prefill_causal_attention(s, qrb, L.key_cache, L.value_cache, n, c.max_seq_len, d->n_heads_l, d->n_kv_l, c.head_dim, ab));
-            KMLL_TRY(op_linear_batched(d, s, ab, L.wo, n, ob));
+            KMLL_TRY(op_linear_batched(d, s, ab, L.wo, n, ws, ob));
             KMLL_TRY(tp_allreduce(d, s, ob, (size_t)n * c.dim));
             KMLL_TRY(kmll_add_prefix(s, xb, ob, (size_t)n * c.dim, x2b));
             // run_ffn_batched_i8_from_hidden_into, crates/inference/src/model.rs:11326-11421
             KMLL_TRY(kmll_rmsnorm_batched(s, x2b, L.ffn_norm, n, c.dim, c.norm_eps, nb));
-            KMLL_TRY(op_linear_batched(d, s, nb, L.w1, n, gb));
-            KMLL_TRY(op_linear_batched(d, s, nb, L.w3, n, ub));
+            KMLL_TRY(op_linear_batched(d, s, nb, L.w1, n, ws, gb));
+            KMLL_TRY(op_linear_batched(d, s, nb, L.w3, n, ws, ub));
             KMLL_TRY(kmll_silu_mul_prefix(s, gb, ub, (size_t)n * d->hidden_l, actb));
-            KMLL_TRY(op_linear_batched(d, s, actb, L.w2, n, ob));
+            KMLL_TRY(op_linear_batched(d, s, actb, L.w2, n, ws, ob));
             KMLL_TRY(tp_allreduce(d, s, ob, (size_t)n * c.dim));
             KMLL_TRY(kmll_add_prefix(s, x2b, ob, (size_t)n * c.dim, xb));
         }
@@ -1469,6 +1478,17 @@ int kmll_batch_create(kmll_decoder_t dec, int batch, kmll_batch_t* out) {
         KMLL_TRY(balloc(b, &b->k, (size_t)batch * kv_len));
         KMLL_TRY(balloc(b, &b->v, (size_t)batch * kv_len));
         KMLL_TRY(balloc(b, &b->act, (size_t)batch * c.hidden_dim));
+        KMLL_TRY(balloc(b, &b->gate, (size_t)batch * c.hidden_dim));
+        KMLL_TRY(balloc(b, &b->up, (size_t)batch * c.hidden_dim));
+        {
+            const int widest = c.hidden_dim > c.dim ? (c.hidden_dim > q_len ? c.hidden_dim : q_len) : (c.dim > q_len ? c.dim : q_len);
+            const size_t ws_bytes = linear_batched_workspace_bytes(batch, widest);
+            if (ws_bytes > 0) {
+                unsigned char* p = nullptr;
+                KMLL_TRY(balloc(b, &p, ws_bytes));
+                b->linear_ws = p;
+            }
+        }
         KMLL_TRY(balloc(b, &b->logits, (size_t)batch * c.vocab_size));
         const size_t ws = (decode_attention_workspace_floats(c.n_heads, c.head_dim, c.max_seq_len) + 3) & ~(size_t)3;
         KMLL_TRY(balloc(b, &b->attn_ws, ws * batch));

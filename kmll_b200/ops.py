@@ -285,7 +285,13 @@ def unpack_top1(packed: int) -> tuple[int, float]:
     return token, logit
 
 
-def linear_batched(x, weight: Weight, batch: int, input_dim: int, output_dim: int, out=None):
+def linear_batched_workspace(batch: int, input_dim: int, device="cuda"):
+    """Caller-owned scratch of the batched linears (None when the shape needs none)."""
+    n = int(load().kmll_linear_batched_workspace_bytes(batch, input_dim))
+    return torch.empty(n, dtype=torch.uint8, device=device) if n > 0 else None
+
+
+def linear_batched(x, weight: Weight, batch: int, input_dim: int, output_dim: int, out=None, workspace=None):
     """linear_batched_i8_scaled (ops/matmul.rs:423-463): x is a row-major prefix [batch, input_dim]."""
     if weight.rows != output_dim or weight.cols != input_dim:
         raise KmllError(-2, "batched linear weight shape mismatch")
@@ -297,11 +303,12 @@ def linear_batched(x, weight: Weight, batch: int, input_dim: int, output_dim: in
     if batch == 0:
         return out
     fmt, w, s = _w(weight)
-    check(_fn("linear_batched", fmt)(_stream(), _p(_f32(x, "input")), w, s, batch, input_dim, output_dim, _p(out)))
+    ws = linear_batched_workspace(batch, input_dim, x.device) if workspace is None else workspace
+    check(_fn("linear_batched", fmt)(_stream(), _p(_f32(x, "input")), w, s, batch, input_dim, output_dim, _p(ws), _p(out)))
     return out
 
 
-def linear_qkv_batched(x, wq: Weight, wk: Weight, wv: Weight, batch: int, input_dim: int):
+def linear_qkv_batched(x, wq: Weight, wk: Weight, wv: Weight, batch: int, input_dim: int, workspace=None):
     """linear_qkv_batched_i8_scaled (ops/matmul.rs:465-510)."""
     fmt = _same_fmt(wq, wk, wv)
     if not (wq.cols == wk.cols == wv.cols == input_dim) or wk.rows != wv.rows:
@@ -312,8 +319,9 @@ def linear_qkv_batched(x, wq: Weight, wk: Weight, wv: Weight, batch: int, input_
     k = torch.empty((batch, wk.rows), dtype=torch.float32, device=x.device)
     v = torch.empty((batch, wv.rows), dtype=torch.float32, device=x.device)
     (_, pq, sq), (_, pk, sk), (_, pv, sv) = _w(wq), _w(wk), _w(wv)
+    ws = linear_batched_workspace(batch, input_dim, x.device) if workspace is None else workspace
     check(_fn("linear_qkv_batched", fmt)(_stream(), _p(_f32(x, "input")), pq, sq, pk, sk, pv, sv, batch, input_dim, wq.rows, wk.rows,
-                                         _p(q), _p(k), _p(v)))
+                                         _p(ws), _p(q), _p(k), _p(v)))
     return q, k, v
 
 

@@ -1,0 +1,74 @@
+"""Batched quantized linear on the tensor cores (tcgen05, caller-owned workspace) against the CPU oracle: the shapes of
+the quantized GEMM sweep (M = 64, 256; (N, K) = (3584, 3584), (18944, 3584), (3584, 18944), a slice of (152064, 3584)),
+prefill shapes of the Mistral-7B architecture, ragged sizes, both weight formats.  Same bounds as every other linear:
+kmll's max_abs <= 1e-4 sqrt(K) (src/main.rs:4306) and 1e-4 relative to the largest output."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from kmll_b200 import ops
+from test_ops_gpu import F, assert_close, dev, host, i8_weight, w4_weight
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(5, 300, 512), (16, 4096, 4096), (33, 700, 4096), (64, 3584, 3584), (256, 3584, 3584), (64, 18944, 3584),
+          (256, 3584, 18944), (64, 4736, 3584), (300, 1000, 256), (2048, 1024, 4096), (128, 4096, 14336)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_w4_vs_oracle(cuda, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    _, packed, gs, w = w4_weight(rng, n, k)
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    x[0, :] *= F(1e-3)  # rows of very different magnitude: the scale is per row
+    x[m - 1, :] *= F(1e3)
+    ref = oracle.w4_linear_batched(x, packed, gs)
+    ws = ops.linear_batched_workspace(m, k)
+    assert ws is not None
+    got = host(ops.linear_batched(dev(x), w, m, k, n, workspace=ws))
+    for row in (0, m // 2, m - 1):
+        assert_close(got[row], ref[row], k, f"w4 gemm {m}x{n}x{k} row {row}")
+    scale = np.maximum(np.max(np.abs(ref), axis=1, keepdims=True), 1e-30)
+    assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES[:5] + [(64, 1000, 896), (2048, 1024, 4096)])
+def test_gemm_i8_vs_oracle(cuda, m, n, k):
+    rng = np.random.default_rng(m + n + k + 1)
+    _, q, sc, w = i8_weight(rng, n, k)
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    ref = oracle.rs_i8_linear_batched(x, q, sc)
+    got = host(ops.linear_batched(dev(x), w, m, k, n))
+    scale = np.maximum(np.max(np.abs(ref), axis=1, keepdims=True), 1e-30)
+    assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4
+    assert float(np.max(np.abs(got - ref))) <= 1e-4 * np.sqrt(k)
+
+
+def test_gemm_qkv_and_is_deterministic(cuda):
+    rng = np.random.default_rng(9)
+    m, k = 96, 4096
+    mats = [w4_weight(rng, rows, k) for rows in (4096, 1024, 1024)]
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    xd = dev(x)
+    q, kk, v = ops.linear_qkv_batched(xd, mats[0][3], mats[1][3], mats[2][3], m, k)
+    for got, (_, packed, gs, _) in zip((q, kk, v), mats):
+        ref = oracle.w4_linear_batched(x, packed, gs)
+        assert float(np.max(np.abs(host(got) - ref))) <= 1e-4 * np.sqrt(k)
+    q2, _, _ = ops.linear_qkv_batched(xd, mats[0][3], mats[1][3], mats[2][3], m, k)
+    assert torch.equal(q, q2)
+
+
+def test_gemm_without_workspace_still_works(cuda):
+    """No workspace: the call falls back to passes of the streaming kernel (4 rows of x each) and gives the same result."""
+    rng = np.random.default_rng(10)
+    m, n, k = 9, 256, 512
+    _, packed, gs, w = w4_weight(rng, n, k)
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    ref = oracle.w4_linear_batched(x, packed, gs)
+    from kmll_b200.lib import check, load
+    out = torch.empty((m, n), device="cuda")
+    xd = dev(x)
+    check(load().kmll_linear_batched_w4g128(torch.cuda.current_stream().cuda_stream, xd.data_ptr(), w.packed.data_ptr(), w.gscales.data_ptr(), m, k,
+                                            n, None, out.data_ptr()))
+    assert float(np.max(np.abs(host(out) - ref))) <= 1e-4 * np.sqrt(k)
