@@ -919,15 +919,17 @@ static bool gemm_plan(int fmt, int M, int K, int rows, GemmPlan* out) {
         if (pl.ksplit > kt_all / 8) pl.ksplit = kt_all / 8;
         if (pl.ksplit < 1) pl.ksplit = 1;
     }
+    // (raw weight tiles with 128-byte rows in a ring of their own - 4 k-tiles of W4, 2 of RS-I8 per TMA box - were measured
+    // and brought nothing: the small-batch shapes are bound by the per-k-tile hand-offs, not by the row pieces TMA moves)
     const size_t raw = fmt == FMT_W4 ? 4096 : 8192;
     const size_t stage = (size_t)(fmt == FMT_W4 ? 2 : 1) * kGRows * 128 + (size_t)2 * pl.n_block * 128 + raw;
     pl.stages = (int)((220 * 1024 - 2048) / stage);
-    if (pl.stages > 4) pl.stages = 4;
+    if (pl.stages > 8) pl.stages = 8;
     if (pl.stages < 2) return false;
     pl.smem = (size_t)pl.stages * stage + (3 * pl.stages + 1) * 8 + 16 + 1024;  // + slack for the 1024-byte alignment
     auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
-    pl.off_lo = up256((size_t)M * K * 2);
-    pl.off_inv = pl.off_lo + up256((size_t)M * K * 2);
+    pl.off_lo = (size_t)M * K * 2;  // the two f16 planes of x are contiguous: one 3-D tensor [2, M, K]
+    pl.off_inv = up256(pl.off_lo * 2);
     pl.off_partial = pl.off_inv + up256((size_t)M * 4);
     // the layout depends on (M, K) only, so one workspace serves matrices of any height: split-K keeps tiles * splits
     // at or below 148 partial tiles; 16384 arrival counters
@@ -991,17 +993,27 @@ static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, 
     float* partial = reinterpret_cast<float*>(ws + big.off_partial);
     unsigned int* counters = reinterpret_cast<unsigned int*>(ws + big.off_counters);
     const int n_counters = 16384;
-    cudaError_t e = launch(split_rows_kernel, dim3(M), dim3(512), 0, stream, true, x, ldx, K, norm_w, eps, x_hi, x_lo, inv, counters, n_counters);
+    cudaError_t e = launch(split_rows_kernel, dim3(M), dim3(512), 0, stream, true, x, ldx, K, norm_w, eps, x_hi, x_lo, inv, counters, n_counters,
+                           FMT == FMT_W4 ? 1 : 0);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "split_rows: %s", cudaGetErrorString(e));
     auto kern = linear_gemm_kernel<FMT>;
     for (int i = 0; i < nmat; ++i) {
         GemmPlan pl;
         if (!gemm_plan(FMT, M, K, rows[i], &pl)) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: shape not supported by the tensor-core path");
-        CUtensorMap map_w, map_hi, map_lo;
+        CUtensorMap map_w, map_x;
         if (FMT == FMT_W4) KMLL_TRY_RC(make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[i], (uint64_t)K / 2, (uint64_t)rows[i], (uint64_t)K / 2, 32, kGRows, CU_TENSOR_MAP_SWIZZLE_NONE));
         else KMLL_TRY_RC(make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[i], (uint64_t)K, (uint64_t)rows[i], (uint64_t)K, 64, kGRows, CU_TENSOR_MAP_SWIZZLE_NONE));
-        KMLL_TRY_RC(make_map_2d(&map_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_hi, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kGKT, (uint32_t)pl.n_block, CU_TENSOR_MAP_SWIZZLE_128B));
-        KMLL_TRY_RC(make_map_2d(&map_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_lo, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kGKT, (uint32_t)pl.n_block, CU_TENSOR_MAP_SWIZZLE_128B));
+        {   // both f16 planes of x as one 3-D tensor [2, M, K]; box = [2, n_block, 64 columns], 128-byte swizzle
+            TensorMapEncodeFn enc = tensor_map_encoder();
+            if (enc == nullptr) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+            const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, 2};
+            const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)M * K * 2};
+            const cuuint32_t box[3] = {kGKT, (cuuint32_t)pl.n_block, 2};
+            const cuuint32_t estr[3] = {1, 1, 1};
+            const CUresult r = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, x_hi, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled (activations) failed (%d)", (int)r);
+        }
         GemmParams gp;
         memset(&gp, 0, sizeof(gp));
         gp.fmt = FMT; gp.rows = rows[i]; gp.K = K; gp.M = M;
@@ -1015,7 +1027,7 @@ static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, 
         gp.counters = counters;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
         if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", pl.smem, cudaGetErrorString(e));
-        e = launch(kern, dim3(pl.row_tiles, pl.x_blocks, pl.ksplit), dim3(kGThreads), pl.smem, stream, true, gp, map_w, map_hi, map_lo);
+        e = launch(kern, dim3(pl.row_tiles, pl.x_blocks, pl.ksplit), dim3(kGThreads), pl.smem, stream, true, gp, map_w, map_x);
         if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_gemm: %s", cudaGetErrorString(e));
     }
     return KMLL_OK;

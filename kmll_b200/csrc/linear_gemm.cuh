@@ -39,7 +39,7 @@ constexpr int kGRows = 128;        // weight rows per block = MMA M
 constexpr int kGMaxN = 256;        // rows of x per block = MMA N (multiple of 16)
 constexpr int kGKT = 64;           // columns per k-tile (one 128-byte swizzle atom of f16)
 constexpr int kGDequantWarps = 8;
-constexpr int kGThreads = (2 + kGDequantWarps) * 32;  // warp 0: TMA, warp 1: MMA, warps 2..9: dequantize + epilogue
+constexpr int kGThreads = (3 + kGDequantWarps) * 32;  // warp 0: TMA of x, warp 1: MMA, warps 2..9: dequantize + epilogue, warp 10: TMA of the weights
 constexpr int kGMaxSplit = 8;
 
 struct GemmParams {
@@ -61,7 +61,7 @@ struct GemmParams {
 // also clears the split-K counters.
 __global__ void __launch_bounds__(512) split_rows_kernel(const float* __restrict__ x, int ldx, int K, const uint16_t* __restrict__ norm_w,
                                                          float eps, __half* __restrict__ x_hi, __half* __restrict__ x_lo,
-                                                         float* __restrict__ inv_xscale, unsigned int* counters, int n_counters) {
+                                                         float* __restrict__ inv_xscale, unsigned int* counters, int n_counters, int permute) {
     __shared__ float scratch[40];
     pdl_wait();
     const int m = blockIdx.x;
@@ -93,23 +93,37 @@ __global__ void __launch_bounds__(512) split_rows_kernel(const float* __restrict
         xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
         inv_scale = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
-    uint2* hi = reinterpret_cast<uint2*>(x_hi + (size_t)m * K);
-    uint2* lo = reinterpret_cast<uint2*>(x_lo + (size_t)m * K);
-    for (int k4 = threadIdx.x; k4 < K / 4; k4 += blockDim.x) {
-        float4 v = xr[k4];
+    // eight columns per thread and step.  permute != 0 (W4-G128): inside every group of eight columns the planes hold the
+    // columns in the order 0 4 1 5 2 6 3 7 - the order in which the weight expansion of linear_gemm_kernel produces the
+    // nibbles of a word; a contraction does not care in which order its terms are summed as long as both operands agree
+    uint4* hi = reinterpret_cast<uint4*>(x_hi + (size_t)m * K);
+    uint4* lo = reinterpret_cast<uint4*>(x_lo + (size_t)m * K);
+    const uint4* nw8 = reinterpret_cast<const uint4*>(norm_w);
+    for (int k8 = threadIdx.x; k8 < K / 8; k8 += blockDim.x) {
+        const float4 a = xr[2 * k8], b = xr[2 * k8 + 1];
+        float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         if (norm_w) {
-            const uint2 w = nw[k4];
-            v.x = v.x * inv * __uint_as_float(w.x << 16);
-            v.y = v.y * inv * __uint_as_float(w.x & 0xffff0000u);
-            v.z = v.z * inv * __uint_as_float(w.y << 16);
-            v.w = v.w * inv * __uint_as_float(w.y & 0xffff0000u);
+            const uint4 w = nw8[k8];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                v[2 * q] = v[2 * q] * inv * __uint_as_float(ww[q] << 16);
+                v[2 * q + 1] = v[2 * q + 1] * inv * __uint_as_float(ww[q] & 0xffff0000u);
+            }
         }
-        v.x *= xscale; v.y *= xscale; v.z *= xscale; v.w *= xscale;
-        const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
-        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-        const __half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
-        hi[k4] = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-        lo[k4] = make_uint2(*reinterpret_cast<const uint32_t*>(&l0), *reinterpret_cast<const uint32_t*>(&l1));
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i0 = permute ? q : 2 * q, i1 = permute ? q + 4 : 2 * q + 1;
+            const float v0 = v[i0] * xscale, v1 = v[i1] * xscale;
+            const __half2 hh = __floats2half2_rn(v0, v1);
+            const float2 hf = __half22float2(hh);
+            const __half2 ll = __floats2half2_rn(v0 - hf.x, v1 - hf.y);
+            h[q] = *reinterpret_cast<const uint32_t*>(&hh);
+            l[q] = *reinterpret_cast<const uint32_t*>(&ll);
+        }
+        hi[k8] = make_uint4(h[0], h[1], h[2], h[3]);
+        lo[k8] = make_uint4(l[0], l[1], l[2], l[3]);
     }
     if (threadIdx.x == 0) inv_xscale[m] = inv_scale;
 }
@@ -147,10 +161,16 @@ __device__ inline void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, in
                  : "memory");
 }
 
+// 3-D tiled TMA load (inner, row, plane)
+__device__ inline void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_w,
-                                                                  const __grid_constant__ CUtensorMap map_xhi,
-                                                                  const __grid_constant__ CUtensorMap map_xlo) {
+                                                                  const __grid_constant__ CUtensorMap map_x) {
     constexpr bool W4 = FMT == FMT_W4;
     constexpr int kRawBytes = W4 ? kGRows * 32 : kGRows * 64;  // raw weight tile
     constexpr int kABytes = kGRows * 128;                      // one f16 operand plane of the weights
@@ -179,7 +199,7 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
     constexpr uint32_t kTmemCols = W4 ? 512u : 256u;
 
     if (tid == 0) {
-        for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&a_ready[s], kGDequantWarps * 32); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 2); mbar_init(&a_ready[s], kGDequantWarps); mbar_init(&empty[s], 1); }
         mbar_init(all_done, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -193,23 +213,33 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t smem_base = smem_u32(gsmem);
     const uint32_t idesc = gemm_idesc_f16(kGRows, n_block);
+    // Up to 128 rows of x per block: the x_hi and x_lo tiles lie back to back in shared memory, so ONE MMA with N = 2 n_block
+    // multiplies the weight plane by both (columns [0, n) and [n, 2 n) of the accumulator, added in the epilogue).  An MMA
+    // costs about the same for N = 16 as for N = 64, so fewer, wider MMAs is what small batches need.
+    const bool fused_n = 2 * n_block <= kGMaxN;
+    const uint32_t idesc2 = gemm_idesc_f16(kGRows, 2 * n_block);
 
     pdl_wait();  // the f16 planes of x come from the previous kernel
     bool ok = true;
-    if (warp == 0) {
-        // ---- TMA producer
+    if (warp == 0 || warp == 10) {
+        // ---- TMA producers: issuing a tensor copy occupies the issuing thread for a good fraction of a microsecond, so the
+        // two copies of a k-tile come from two warps: warp 0 brings both f16 planes of x with one 3-D box, warp 10 the raw
+        // weight tile.  Each registers its bytes on the stage's barrier (two arrivals).
         if (lane == 0) {
 #pragma unroll 1
             for (int kt = 0; kt < KT; ++kt) {
                 const int stage = kt % stages, use = kt / stages;
                 if (use > 0 && !mbar_wait<false>(&empty[stage], (uint32_t)(use - 1) & 1u)) { ok = false; break; }
                 const uint32_t st = smem_base + (uint32_t)stage * stage_bytes;
-                const uint32_t b_hi = st + (W4 ? 2 : 1) * kABytes, b_lo = b_hi + b_bytes, raw = b_lo + b_bytes;
-                mbar_arrive_expect_tx(&full[stage], (uint32_t)(kRawBytes + 2 * b_bytes));
+                const uint32_t b_hi = st + (W4 ? 2 : 1) * kABytes, raw = b_hi + 2 * b_bytes;
                 const int k = (kt0 + kt) * kGKT;
-                tma_load_2d(raw, &map_w, W4 ? k / 2 : k, row0, &full[stage]);
-                tma_load_2d(b_hi, &map_xhi, k, m0, &full[stage]);
-                tma_load_2d(b_lo, &map_xlo, k, m0, &full[stage]);
+                if (warp == 0) {
+                    mbar_arrive_expect_tx(&full[stage], (uint32_t)(2 * b_bytes));
+                    tma_load_3d(b_hi, &map_x, k, m0, 0, &full[stage]);
+                } else {
+                    mbar_arrive_expect_tx(&full[stage], (uint32_t)kRawBytes);
+                    tma_load_2d(raw, &map_w, W4 ? k / 2 : k, row0, &full[stage]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -227,15 +257,19 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
                 for (int ks = 0; ks < kGKT / 16; ++ks) {
                     const uint32_t first = (kt > 0 || ks > 0) ? 1u : 0u;
                     const uint64_t da = gemm_smem_desc(a_hi + ks * 32), dbh = gemm_smem_desc(b_hi + ks * 32), dbl = gemm_smem_desc(b_lo + ks * 32);
-                    gemm_mma_f16(tmem_base, da, dbh, idesc, first);
-                    gemm_mma_f16(tmem_base, da, dbl, idesc, 1u);
+                    if (fused_n) {
+                        gemm_mma_f16(tmem_base, da, dbh, idesc2, first);
+                    } else {
+                        gemm_mma_f16(tmem_base, da, dbh, idesc, first);
+                        gemm_mma_f16(tmem_base, da, dbl, idesc, 1u);
+                    }
                     if (W4) gemm_mma_f16(tmem_base + 256u, gemm_smem_desc(a_lo + ks * 32), dbh, idesc, first);
                 }
                 umma_commit(&empty[stage]);
             }
             if (ok) umma_commit(all_done);
         }
-    } else {
+    } else if (warp < 2 + kGDequantWarps) {
         // ---- weight expansion: thread pair (row, half) turns 32 columns of one raw row into f16 in the swizzled tile
         const int dt = tid - 64;               // 0..255
         const int r = dt >> 1, h = dt & 1;     // tile row, which half of the 64 columns
@@ -245,28 +279,36 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
 #pragma unroll 1
         for (int kt = 0; kt < KT; ++kt) {
             const int stage = kt % stages, use = kt / stages;
-            if (!mbar_wait<true>(&full[stage], (uint32_t)use & 1u)) { ok = false; break; }
+            if (!mbar_wait<false>(&full[stage], (uint32_t)use & 1u)) { ok = false; break; }
             unsigned char* st = gsmem + (size_t)stage * stage_bytes;
             unsigned char* a_hi = st;
             unsigned char* a_lo = st + kABytes;
             const unsigned char* raw = st + (W4 ? 2 : 1) * kABytes + 2 * b_bytes;
             if (W4) {
                 const int grp = ((kt0 + kt) * kGKT) >> 7;
-                const float sf = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short*>(p.scales)[(size_t)grow * (p.K >> 7) + grp]));
+                const __half sh = __ushort_as_half(reinterpret_cast<const unsigned short*>(p.scales)[(size_t)grow * (p.K >> 7) + grp]);
                 const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 32 + h * 16);  // 32 nibbles = columns 32 h .. 32 h + 31
                 const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                const __half2 s2 = __half2half2(sh);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // 8 columns -> one 16-byte chunk of each plane
+                for (int c = 0; c < 4; ++c) {  // one word = 8 columns -> one 16-byte chunk of each plane, columns in the order 0 4 1 5 2 6 3 7
+                    // nibbles -> exact binary16 values q = n - 8 without a conversion instruction: 0x6400 | n is 1024 + n,
+                    // 0x6400 | (n << 4) is 1024 + 16 n
+                    const uint32_t kMagic = 0x64006400u, kSubLo = 0x64086408u /* 1032 */, kMulHi = 0x2c002c00u /* 1/16 */, kAddHi = 0xd480d480u /* -72 */;
+                    const uint32_t w0 = ww[c], w8 = ww[c] >> 8;
+                    uint32_t qa = lop3_and_or(w0, 0x000f000fu, kMagic), qb = lop3_and_or(w0, 0x00f000f0u, kMagic);
+                    uint32_t qc = lop3_and_or(w8, 0x000f000fu, kMagic), qd = lop3_and_or(w8, 0x00f000f0u, kMagic);
+                    __half2 q2[4];
+                    q2[0] = __hsub2(*reinterpret_cast<__half2*>(&qa), *reinterpret_cast<const __half2*>(&kSubLo));                                            // (n0, n4)
+                    q2[1] = __hfma2(*reinterpret_cast<__half2*>(&qb), *reinterpret_cast<const __half2*>(&kMulHi), *reinterpret_cast<const __half2*>(&kAddHi));  // (n1, n5)
+                    q2[2] = __hsub2(*reinterpret_cast<__half2*>(&qc), *reinterpret_cast<const __half2*>(&kSubLo));                                            // (n2, n6)
+                    q2[3] = __hfma2(*reinterpret_cast<__half2*>(&qd), *reinterpret_cast<const __half2*>(&kMulHi), *reinterpret_cast<const __half2*>(&kAddHi));  // (n3, n7)
                     uint32_t hi2[4], lo2[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const uint32_t n0 = (ww[c] >> (8 * e)) & 15u, n1 = (ww[c] >> (8 * e + 4)) & 15u;
-                        // (float)(n - 8) without a conversion: 2^23 + n as a float, minus 2^23 + 8
-                        const float v0 = (__uint_as_float(0x4b000000u | n0) - 8388616.0f) * sf;
-                        const float v1 = (__uint_as_float(0x4b000000u | n1) - 8388616.0f) * sf;
-                        const __half2 hh = __floats2half2_rn(v0, v1);
-                        const float2 hf = __half22float2(hh);
-                        const __half2 ll = __floats2half2_rn((v0 - hf.x) * 2048.0f, (v1 - hf.y) * 2048.0f);
+                        const __half2 hh = __hmul2(q2[e], s2);                          // w_hi = f16(q s)
+                        const __half2 rr = __hfma2(q2[e], s2, __hneg2(hh));             // q s - w_hi, exact (a multiple of 2^-24 below half an ulp of w_hi)
+                        const __half2 ll = __hmul2(rr, __float2half2_rn(2048.0f));      // w_lo = (q s - w_hi) 2^11
                         hi2[e] = *reinterpret_cast<const uint32_t*>(&hh);
                         lo2[e] = *reinterpret_cast<const uint32_t*>(&ll);
                     }
@@ -296,13 +338,14 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
                 }
             }
             fence_proxy_async_smem();  // the tensor core reads these tiles through the async proxy
-            mbar_arrive(&a_ready[stage]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_ready[stage]);  // one arrival per warp
         }
     }
 
     // ---- epilogue: warps 2..9; warp w reads tensor-memory lanes 32 (w % 4) .., warps w and w + 4 share the columns
     const bool split = gridDim.z > 1;
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 2 + kGDequantWarps) {
         ok = __all_sync(0xffffffffu, ok);
         if (ok && KT > 0 && !mbar_wait<true>(all_done, 0u)) ok = false;
         ok = __all_sync(0xffffffffu, ok);
@@ -317,7 +360,7 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
             float* part = split ? p.partial + (((size_t)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z) * (size_t)n_block * kGRows : nullptr;
 #pragma unroll 1
             for (int c0 = half * ncols; c0 < (half + 1) * ncols; c0 += 8) {
-                uint32_t d1[8], d2[8];
+                uint32_t d1[8], d2[8], d3[8];
                 if (KT > 0) {
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
                     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -329,15 +372,21 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
                                      : "=r"(d2[0]), "=r"(d2[1]), "=r"(d2[2]), "=r"(d2[3]), "=r"(d2[4]), "=r"(d2[5]), "=r"(d2[6]), "=r"(d2[7])
                                      : "r"(taddr + 256u)
                                      : "memory");
+                    if (fused_n)  // the x_lo half of the wide accumulator
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                     : "=r"(d3[0]), "=r"(d3[1]), "=r"(d3[2]), "=r"(d3[3]), "=r"(d3[4]), "=r"(d3[5]), "=r"(d3[6]), "=r"(d3[7])
+                                     : "r"(taddr + (uint32_t)n_block)
+                                     : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) d1[j] = d2[j] = 0u;
+                    for (int j = 0; j < 8; ++j) d1[j] = d2[j] = d3[j] = 0u;
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int n = c0 + j, m = m0 + n;
                     float v = __uint_as_float(d1[j]);
+                    if (fused_n) v += __uint_as_float(d3[j]);
                     if (W4) v = fmaf(__uint_as_float(d2[j]), 1.0f / 2048.0f, v);
                     if (split) {
                         part[(size_t)n * kGRows + rl] = v;  // scales and residual are applied after the merge

@@ -27,10 +27,9 @@ def test_gemm_w4_vs_oracle(cuda, m, n, k):
     ws = ops.linear_batched_workspace(m, k)
     assert ws is not None
     got = host(ops.linear_batched(dev(x), w, m, k, n, workspace=ws))
-    for row in (0, m // 2, m - 1):
-        assert_close(got[row], ref[row], k, f"w4 gemm {m}x{n}x{k} row {row}")
+    assert_close(got[m // 2], ref[m // 2], k, f"w4 gemm {m}x{n}x{k} row {m // 2}")  # an unscaled row: kmll's absolute bound
     scale = np.maximum(np.max(np.abs(ref), axis=1, keepdims=True), 1e-30)
-    assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4
+    assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4  # every row, relative to its own largest output
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES[:5] + [(64, 1000, 896), (2048, 1024, 4096)])
