@@ -135,6 +135,35 @@ int kmll_decoder_launches_per_step(kmll_decoder_t dec);
 size_t kmll_decoder_weight_bytes(kmll_decoder_t dec);
 size_t kmll_decoder_kv_bytes(kmll_decoder_t dec);
 
+/* ---- on-disk archive of the quantized linear weights ---------------------------------------------------------
+ * The directory layout of kmll's quantization export, so an archive written by either side loads on the other:
+ *   manifest.json with "quantization": "row-symmetric-int8-with-f32-row-scales" (crates/inference/src/model.rs:9047-9053),
+ *   NNNN_<name>.i8 (raw int8, row-major) and NNNN_<name>.scales.f32 (little-endian f32) per tensor, where <name> has
+ *   every non-alphanumeric character replaced by '_' (crates/inference/src/rowwise_scaled.rs:141-157) and NNNN is the
+ *   tensor index: 0 = output.weight, 1 + layer * 7 + offset for wq, wk, wv, wo, w1, w3, w2
+ *   (crates/inference/src/model.rs:9082-9140, :9185-9187).
+ * W4-G128 archives (no counterpart in kmll) use the manifest value "group128-symmetric-int4-with-f16-group-scales" and
+ * the suffixes .w4 (packed nibbles) / .gscales.f16.  Host functions; `values` / `scales` are HOST pointers.
+ * Norm weights and embeddings are not part of kmll's archive (they stay in the checkpoint). */
+int kmll_archive_tensor_index(int layer, int offset); /* layer < 0: 0 (output.weight); exported_int8_layer_tensor_index */
+int kmll_archive_file_paths(const char* dir, int index, const char* name, int format, char* values_path, char* scales_path,
+                            size_t capacity);
+int kmll_archive_write_tensor(const char* dir, int index, const char* name, int format, int rows, int cols,
+                              const void* values, const void* scales);
+/* RowwiseScaledI8Matrix::read_exported (rowwise_scaled.rs:94-106): fails unless both files have exactly the bytes of
+ * a rows x cols tensor. */
+int kmll_archive_read_tensor(const char* dir, int index, const char* name, int format, int rows, int cols, void* values,
+                             void* scales);
+int kmll_archive_write_manifest(const char* dir, const kmll_decoder_config* config, const char* weights_path);
+/* validate_all_linear_int8_export_archive (crates/inference/src/model.rs:8984-9035): directory, manifest key, byte
+ * length of every expected file; with expected_weights_path also the manifest's weights_path. */
+int kmll_archive_validate(const char* dir, const kmll_decoder_config* config, const char* expected_weights_path);
+/* Write every linear tensor of a single-GPU decoder + the manifest / validate an archive and upload it (new_from_export,
+ * crates/inference/src/model.rs:6327-6384); `config` is the configuration the decoder was created with. */
+int kmll_decoder_export_archive(kmll_decoder_t dec, const kmll_decoder_config* config, const char* dir, const char* weights_path);
+int kmll_decoder_load_archive(kmll_decoder_t dec, const kmll_decoder_config* config, const char* dir,
+                              const char* expected_weights_path);
+
 /* ---- lockstep batch of sequences (new; kmll decodes one sequence at a time) -------------------------
  * Up to 16 independent sequences at the same position are decoded together so that every weight is read
  * once per step for all of them.  The batch shares the decoder's weights and owns its KV caches

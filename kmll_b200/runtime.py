@@ -135,6 +135,17 @@ class Decoder:
         sp = None if scales is None else np.ascontiguousarray(scales).ctypes.data
         check(self._lib.kmll_decoder_set_tensor(self._h, layer, tensor, values.ctypes.data, sp))
 
+    def export_archive(self, directory: str, weights_path: str = "") -> None:
+        """Write kmll's export directory (manifest.json + one values / scales file pair per linear tensor)."""
+        c = self.cfg._c()
+        check(self._lib.kmll_decoder_export_archive(self._h, C.byref(c), directory.encode(), weights_path.encode()))
+
+    def load_archive(self, directory: str, expected_weights_path: str | None = None) -> None:
+        """Validate an export directory and upload its linear tensors (MinistralAllLinearInt8Runtime::new_from_export)."""
+        c = self.cfg._c()
+        check(self._lib.kmll_decoder_load_archive(self._h, C.byref(c), directory.encode(),
+                                                  None if expected_weights_path is None else expected_weights_path.encode()))
+
     def prefill(self, tokens, token_loop: bool = False) -> None:
         t = np.ascontiguousarray(tokens, dtype=np.uint32)
         fn = self._lib.kmll_decoder_prefill_token_loop if token_loop else self._lib.kmll_decoder_prefill

@@ -181,3 +181,34 @@ def test_timeline_attach_and_detach_recapture_the_step_graph(cuda):
     assert int(torch.count_nonzero(buf)) == 0, "a detached buffer must not be written by later replays"
     assert tokens.tolist() == ref_tokens.tolist()
     dec.close()
+
+
+@pytest.mark.parametrize("fmt", [rt.FORMAT_RS_I8, rt.FORMAT_W4G128])
+def test_archive_round_trip_gives_the_same_model(cuda, fmt, tmp_path):
+    """Export a decoder's linear tensors in kmll's archive layout, load them into a fresh decoder (norms and embeddings
+    travel separately, as in kmll where they stay in the checkpoint): the tensors are bit-identical and the greedy
+    tokens equal the in-memory model's."""
+    cfg = tiny(fmt)
+    dec = make(cfg, seed=11)
+    prompt = np.array([7, 300, 12, 5, 99])
+    dec.prefill(prompt)
+    ref_tokens, ref_logits = dec.generate_greedy(8)
+    d = str(tmp_path / "export")
+    dec.export_archive(d, "/models/demo.safetensors")
+    fresh = rt.Decoder(cfg)
+    for layer in range(cfg.n_layers):
+        fresh.set_tensor(layer, rt.T_ATTENTION_NORM, dec.get_tensor(layer, rt.T_ATTENTION_NORM))
+        fresh.set_tensor(layer, rt.T_FFN_NORM, dec.get_tensor(layer, rt.T_FFN_NORM))
+    fresh.set_tensor(-1, rt.T_FINAL_NORM, dec.get_tensor(-1, rt.T_FINAL_NORM))
+    fresh.set_tensor(-1, rt.T_EMBEDDING, dec.get_tensor(-1, rt.T_EMBEDDING))
+    fresh.load_archive(d, "/models/demo.safetensors")
+    for layer, tensor in ((0, rt.T_WQ), (1, rt.T_W2), (-1, rt.T_OUTPUT)):
+        a, b = dec.get_tensor(layer, tensor), fresh.get_tensor(layer, tensor)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1].view(np.uint8), b[1].view(np.uint8))
+    fresh.prefill(prompt)
+    tokens, logits = fresh.generate_greedy(8)
+    assert np.array_equal(tokens, ref_tokens) and np.array_equal(logits, ref_logits)
+    with pytest.raises(KmllError):
+        fresh.load_archive(d, "/models/another.safetensors")
+    dec.close()
+    fresh.close()
