@@ -32,6 +32,7 @@ struct TpExchange {  // lives in device memory; entry d of each table is rank d'
     int mult;                  // exchange numbers are step * mult + index + 1 (index < mult)
     int top_index;             // index of the arg-max hand-over within a step (mult - 1)
     int local_dim;
+    int push_mode;             // how the chained kernel publishes words to the ranks: 1 = max-reduction, 2 = plain store
     uint2* inbox[kMaxTp];      // [2][tp][dim] words (value bits, exchange number)
     uint2* top_inbox[kMaxTp];  // [2][tp][2] words (logit bits, number), (token, number): each rank's arg-max
     uint2* local_box;          // [local_dim] words: a vector handed from one phase of the chained kernel to the next on this GPU
@@ -52,10 +53,11 @@ __device__ inline void st_exchange_word(uint2* slot, uint32_t value_bits, uint32
 // but a reduction is carried out at the L2 cache (or at the peer over NVLink) right away, whereas a relaxed store may
 // linger in the multiprocessor's write path for microseconds before anybody can see it (measured: ~3.5 us behind a
 // reduction issued after it).  Device scope for words that never leave this GPU.
-__device__ inline void push_exchange_word(uint2* slot, uint32_t value_bits, uint32_t number, bool sys) {
+__device__ inline void push_exchange_word(uint2* slot, uint32_t value_bits, uint32_t number, int mode) {
     const unsigned long long w = ((unsigned long long)number << 32) | (unsigned long long)value_bits;
-    if (sys) asm volatile("red.relaxed.sys.global.max.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
-    else asm volatile("red.relaxed.gpu.global.max.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+    if (mode == 1) asm volatile("red.relaxed.sys.global.max.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+    else if (mode == 0) asm volatile("red.relaxed.gpu.global.max.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+    else asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
 }
 // Polling loads of the chained kernel: plain loads that bypass L1 (.cg), not strong ones.  The words live in this GPU's
 // memory, whose point of coherence is the L2 cache, so an L1-bypassing load returns what L2 holds; the number inside

@@ -563,9 +563,9 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
                         const uint32_t epoch = chain_epoch(xc, step, ph.out_index);
                         if (ph.out_kind == CHAIN_OUT_INBOX) {
                             const size_t s = ((size_t)(ph.out_index & 1) * xc.tp + xc.rank) * xc.dim + row;
-                            for (int dst = 0; dst < xc.tp; ++dst) push_exchange_word(xc.inbox[dst] + s, __float_as_uint(v), epoch, xc.tp > 1);
+                            for (int dst = 0; dst < xc.tp; ++dst) push_exchange_word(xc.inbox[dst] + s, __float_as_uint(v), epoch, xc.tp > 1 ? xc.push_mode : 0);
                         } else {
-                            push_exchange_word(xc.local_box + row, __float_as_uint(v), epoch, false);
+                            push_exchange_word(xc.local_box + row, __float_as_uint(v), epoch, 0);
                         }
                     }
                 }

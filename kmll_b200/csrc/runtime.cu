@@ -336,7 +336,12 @@ static bool chain_supported(const Decoder* d) {
     if (c.format != KMLL_FORMAT_W4G128 || !c.fused) return false;
     if (2 * c.n_layers + 1 > 250) return false;
     const char* v = std::getenv("KMLL_CHAIN");
-    return !(v != nullptr && v[0] == '0');
+    if (v != nullptr && v[0] == '0') return false;
+    // Under tensor parallelism the kernels over the canonical layout are faster today (measured at 2 GPUs: 736 against
+    // 671 tokens/s): the prepared-layout kernel pays more per exchange than it gains in its main loop.  KMLL_CHAIN=tp
+    // selects it anyway.
+    if (c.tp_size > 1 && !(v != nullptr && strcmp(v, "tp") == 0)) return false;
+    return true;
 }
 
 static int ensure_prepared(Decoder* d) {
@@ -879,6 +884,10 @@ static int setup_exchange(Decoder* d) {
     h.mult = d->chain ? 256 : 128;
     h.top_index = h.mult - 1;
     h.local_dim = d->hidden_l;
+    {
+        const char* v = std::getenv("KMLL_PUSH");
+        h.push_mode = (v != nullptr && strcmp(v, "st") == 0) ? 2 : 1;
+    }
     for (int rnk = 0; rnk < tp; ++rnk) {
         void* base = d->xc_local;
         if (rnk != c.tp_rank) {

@@ -78,13 +78,9 @@ def test_tp_matches_single_gpu(cuda, fmt, exchange, world):
         assert p.exitcode == 0
     tokens, logits, tokens2, status, launches = out.get(timeout=10)
     assert status == 0  # no bounded wait gave up
-    # peer exchange: no collective kernels inside the step (RS-I8: 2 layers of 5 launches + begin, lm_head, arg-max
-    # reduce, end; W4-G128 on prepared weights: begin, first Q/K/V, per layer attention + 4 projections (the last one is
-    # the next layer's Q/K/V or the lm_head arg-max), end); the NCCL form adds all-reduces, a gather and a merge
-    if exchange == "peer":
-        assert launches == (13 if fmt == 1 else 14)
-    else:
-        assert launches > 14
+    # peer exchange: no collective kernels inside the step (2 layers of 5 launches + begin, lm_head, arg-max reduce, end);
+    # the NCCL form adds all-reduces, a gather and a merge
+    assert launches == 14 if exchange == "peer" else launches > 14
     assert tokens == ref_tokens.tolist()
     assert tokens2 == ref_tokens.tolist()
     assert np.max(np.abs(np.array(logits) - ref_logits)) <= 1e-3 * max(1.0, float(np.max(np.abs(ref_logits))))
