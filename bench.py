@@ -203,6 +203,65 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def cpu_operator_us(kind, **shape):
+    """Microseconds the CPU port of one micro-suite operator takes on every host core (the GEMM on a bounded slice of
+    its output rows, scaled by the rows left out: its cost is linear in them)."""
+    import numpy as np
+
+    import oracle
+    oracle.set_threads(cpu_threads(0))
+    rng = np.random.default_rng(0)
+
+    def timed(fn, min_s=0.3):
+        fn()
+        n, t0 = 0, time.perf_counter()
+        while n == 0 or time.perf_counter() - t0 < min_s:
+            fn()
+            n += 1
+        return (time.perf_counter() - t0) / n * 1e6
+
+    if kind == "chain4096":
+        rows = cols = 4096
+        x, r = rng.normal(0, 1, cols).astype(np.float32), rng.normal(0, 1, rows).astype(np.float32)
+        gamma = oracle.bf16_from_f32(rng.uniform(0.5, 1.5, rows).astype(np.float32))
+        w = rng.normal(0, 0.02, (rows, cols)).astype(np.float32)
+        if shape["fmt"] == "i8":
+            q, sc = oracle.rs_i8_quantize(oracle.bf16_from_f32(w))
+            return timed(lambda: oracle.rmsnorm(oracle.add(oracle.rs_i8_matvec(q, sc, x), r), gamma, 1e-6))
+        pk, gs = oracle.w4_quantize(w)
+        return timed(lambda: oracle.rmsnorm(oracle.add(oracle.w4_matvec(pk, gs, x), r), gamma, 1e-6))
+    if kind == "gemm_w4":
+        m, n, k = shape["m"], shape["n"], shape["k"]
+        n_s = int(min(n, max(64, 2e10 // (2 * m * k)) // 64 * 64))
+        pk = rng.integers(0, 256, (n_s, k // 2), dtype=np.uint8)
+        gs = np.full((n_s, k // 128), 0x2000, dtype=np.uint16)  # f16 bits of 2^-7; timing only
+        x = rng.normal(0, 1, (m, k)).astype(np.float32)
+        if m == 1:
+            return timed(lambda: oracle.w4_matvec(pk, gs, x[0])) * n / n_s
+        return timed(lambda: oracle.w4_linear_batched(x, pk, gs)) * n / n_s
+    B = shape["batch"]
+    if kind == "rmsnorm":
+        x, gamma = rng.normal(0, 1, (B, 4096)).astype(np.float32), oracle.bf16_from_f32(np.ones(4096, dtype=np.float32))
+        return timed(lambda: [oracle.rmsnorm(x[b], gamma, 1e-6) for b in range(B)])
+    if kind == "swiglu":
+        g, u = (rng.normal(0, 1, B * 11008).astype(np.float32) for _ in range(2))
+        return timed(lambda: oracle.silu_mul(g, u))
+    if kind == "rope":
+        x, f = rng.normal(0, 1, (B, 32 * 128)).astype(np.float32), oracle.rope_frequencies(1e6, 128)
+        return timed(lambda: [oracle.apply_rope(x[b], f, 1234 + b, 128) for b in range(B)])
+    if kind == "softmax":
+        x = rng.normal(0, 1, (B * 32, 4096)).astype(np.float32)
+        return timed(lambda: oracle.softmax_rows(x))
+    raise ValueError(kind)
+
+
+def run_suite(args):
+    """The operator suites of kmll_b200.microbench with the CPU port of each operator timed beside it."""
+    from kmll_b200 import microbench as mb
+    cpu = None if args.no_cpu else cpu_operator_us
+    {"chain4096": mb.suite_chain4096, "micro": mb.suite_micro, "gemm_sweep": mb.suite_gemm_sweep}[args.suite](args.suite_reps, cpu)
+
+
 def workload_config(n_gpus):
     return {"workload": "Mistral-7B-architecture decode, batch 1, W4-G128 weights (random-init seed 3), prompt 2048 random token ids, "
                         "f32 KV cache, full causal attention (window 4096 never truncates)",
@@ -346,26 +405,48 @@ def run_ours(args):
                    "context_at_start": start_pos - W + 3}
         bd.close()
 
-    # ---- roofline of the dominant kernel: the fused RMSNorm + gate/up + SiLU streaming kernel, timed live over
-    # the 32 layers' weights (1.9 GB of distinct weights per pass) on the launching stream ----------------
+    # ---- RS-I8 (the reference's own format) on the same architecture and prompt: 7.25 GB of weights per step ------
+    rs_i8 = None
+    if world == 1 and not args.no_rsi8:
+        steps8 = max(8, min(K, 64))
+        dec8 = rt.Decoder(rt.DecoderConfig.mistral_7b(max_seq_len=PROMPT_LEN + steps8 + 16, format=rt.FORMAT_RS_I8))
+        dec8.init_random(SEED, 0.02, False)
+        dec8.prefill(prompt)
+        dec8.enqueue_steps(3)
+        torch.cuda.synchronize()
+        e0.record()
+        dec8.enqueue_steps(steps8)
+        e1.record()
+        torch.cuda.synchronize()
+        ms8 = e0.elapsed_time(e1) / steps8
+        bytes8 = cfg.linear_elements() + 32 * 2 * (PROMPT_LEN + 3 + steps8 / 2) * 1024 * 4
+        rs_i8 = {"metric": "decode_tokens_per_s_batch1_mistral7b_arch_rs_i8", "value": 1e3 / ms8, "unit": "tokens/s", "steps": steps8,
+                 "ms_per_step": ms8, "launches_per_step": dec8.launches_per_step, "algorithmic_bytes_per_step": bytes8,
+                 "frac_of_peak": bytes8 / ms8 / 1e6 / peaks()[0]}
+        dec8.close()
+
+    # ---- roofline of the dominant kernel: the fused RMSNorm + gate/up + SiLU kernel over prepared-layout weights (the
+    # one the decode step above launches 32 times), timed live over 8 layers' worth of distinct weights (1.9 GB per
+    # pass) on the launching stream ----------------------------------------------------------------------
     roofline = None
     if world == 1:
         hid, dim = cfg.hidden_dim, cfg.dim
         n_mats = 8
-        mats = [(ops.DeviceW4G128Matrix(torch.randint(0, 256, (hid, dim // 2), dtype=torch.uint8, device="cuda"),
-                                        (torch.rand((hid, dim // 128), device="cuda") * 0.01 + 0.001).half(), hid, dim),
-                 ops.DeviceW4G128Matrix(torch.randint(0, 256, (hid, dim // 2), dtype=torch.uint8, device="cuda"),
-                                        (torch.rand((hid, dim // 128), device="cuda") * 0.01 + 0.001).half(), hid, dim)) for _ in range(n_mats)]
+
+        def canonical():
+            return ops.DeviceW4G128Matrix(torch.randint(0, 256, (hid, dim // 2), dtype=torch.uint8, device="cuda"),
+                                          (torch.rand((hid, dim // 128), device="cuda") * 0.01 + 0.001).half(), hid, dim)
+        mats = [ops.DeviceW4PMatrix.from_gate_up(canonical(), canonical()) for _ in range(n_mats)]
         x = torch.randn(dim, device="cuda")
         gamma = torch.ones(dim, dtype=torch.bfloat16, device="cuda")
         out = torch.empty(hid, device="cuda")
-        for g_, u_ in mats[:2]:
-            ops.silu_gate_up(x, g_, u_, norm_weight=gamma, eps=1e-5, out=out)
+        for pair in mats[:2]:
+            ops.silu_gate_up(x, pair, None, norm_weight=gamma, eps=1e-5, out=out)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            for g_, u_ in mats:
-                ops.silu_gate_up(x, g_, u_, norm_weight=gamma, eps=1e-5, out=out)
+            for pair in mats:
+                ops.silu_gate_up(x, pair, None, norm_weight=gamma, eps=1e-5, out=out)
         for _ in range(3):
             graph.replay()
         torch.cuda.synchronize()
@@ -383,10 +464,10 @@ def run_ours(args):
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tpath):
             with open(tpath) as f:
-                traffic = json.load(f).get("silu_gate_up_w4g128_bytes_per_launch")
-        roofline = {"bound": "hbm", "kernel": "linear_stream_kernel<W4, gate*up+SiLU> 2x[14336x4096]", "achieved": achieved, "peak": peak,
-                    "unit": "GB/s", "frac": achieved / peak, "of": peak_src, "traffic": traffic, "algorithmic_bytes_per_launch": alg_bytes,
-                    "us_per_launch": per_launch_us}
+                traffic = json.load(f).get("silu_gate_up_w4p_bytes_per_launch")
+        roofline = {"bound": "hbm", "kernel": "linear_chain_kernel, one phase: RMSNorm + gate/up pair records + SiLU, 2x[14336x4096] W4-G128 prepared",
+                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "of": peak_src, "traffic": traffic,
+                    "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": per_launch_us}
         del mats, graph
 
     tok_s = K / (dev_ms / 1e3)
@@ -397,7 +478,7 @@ def run_ours(args):
     peak, peak_src = peaks()
     line = {"metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "int4 weights, s8 x u8 tensor-core MMA on the byte digits of f32 activations (23-bit fixed point), s32/f32 accumulate",
+            "dtype": "int4 weights, s8 x u8 tensor-core MMA on four byte digits of the f32 activations (30-bit fixed point), s32 then f32 accumulate",
             "data": "synthetic", "config": workload_config(world), "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
                     "ms_per_step": e2e_ms / K, "api": "kmll_decoder_step_host (token from pinned host memory, packed result read back, stream sync)"},
@@ -409,6 +490,8 @@ def run_ours(args):
         line["roofline"] = roofline
     if batch16 is not None:
         line["batch16"] = batch16
+    if rs_i8 is not None:
+        line["rs_i8"] = rs_i8
     if rank == 0 and world == 1 and not args.no_cpu:
         cb = cpu_sample(8, 1, cpu_threads(args.cpu_threads), 12.0)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -448,11 +531,17 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-threads", type=int, default=0, help="threads of the CPU arm (default: every core of the host)")
     ap.add_argument("--no-batch16", action="store_true", help="skip the batch-16 leg")
+    ap.add_argument("--no-rsi8", action="store_true", help="skip the RS-I8 (the reference's own format) decode leg")
+    ap.add_argument("--suite", default="", choices=["", "chain4096", "micro", "gemm_sweep"],
+                    help="instead of the decode bench: one operator suite of kmll_b200.microbench, CPU port timed beside each line")
+    ap.add_argument("--suite-reps", type=int, default=20)
     ap.add_argument("--profile", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.suite:
+        run_suite(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

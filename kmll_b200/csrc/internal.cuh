@@ -74,12 +74,11 @@ __device__ inline uint4 ld_exchange_pair(const uint4* p) {
     asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
     return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
 }
-__device__ inline unsigned long long device_clock_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;  // a peer that is 2 s late is given up on
+// Deadline clock of the bounded waits: the multiprocessor's own cycle counter.  (The nanosecond %globaltimer is a
+// system-wide register whose read takes a good fraction of a microsecond - measured: a wait that read it once before
+// polling cost 0.4 us even when the awaited event was already there - so it is kept out of every wait.)
+__device__ inline unsigned long long wait_clock_ticks() { return (unsigned long long)clock64(); }
+constexpr unsigned long long kPeerWaitLimitTicks = 4000000000ull;  // a peer that is this late (2 to 4 s by the clock rate) is given up on
 // ---- chained streaming kernel over prepared W4-G128 records (linear_chain.cuh) -----------------------------
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_TOP1 = 3 };
 constexpr int kCRecBytes = 2112;   // one prepared record: 32 rows x 128 columns of nibbles + 32 binary16 scales

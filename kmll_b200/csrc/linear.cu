@@ -592,7 +592,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
     const TpExchange& xc = *xcp;
     const unsigned int epoch = *xc.epoch * (unsigned int)xc.mult + (unsigned int)xc.top_index + 1u;
     const uint4* box = reinterpret_cast<const uint4*>(xc.top_inbox[xc.rank]) + (size_t)(epoch & 1u) * xc.tp;
-    const unsigned long long t0 = device_clock_ns();
+    const unsigned long long t0 = wait_clock_ticks();
     float best = -INFINITY;
     uint32_t tok = 0xffffffffu;
     for (int r = 0; r < xc.tp; ++r) {
@@ -600,7 +600,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
         for (;;) {
             q = ld_exchange_pair(box + r);
             if (q.y == epoch && q.w == epoch) break;
-            if (device_clock_ns() - t0 > kPeerWaitLimitNs) { atomicCAS(&g_device_status, 0, 2); break; }
+            if (wait_clock_ticks() - t0 > kPeerWaitLimitTicks) { atomicCAS(&g_device_status, 0, 2); break; }
         }
         const float v = __uint_as_float(q.x);
         if (r == 0 || top1_better(v, q.z, best, tok)) { best = v; tok = q.z; }
@@ -617,6 +617,7 @@ __global__ void decode_end_gather_kernel(const TpExchange* xcp, DecodeState* sta
 #include "linear_stream.cuh"
 #include "linear_chain.cuh"
 #include "linear_gemm.cuh"
+#include "linear_gemm_small.cuh"
 
 namespace kmll {
 
@@ -934,7 +935,12 @@ static bool gemm_plan(int fmt, int M, int K, int rows, GemmPlan* out) {
     // the layout depends on (M, K) only, so one workspace serves matrices of any height: split-K keeps tiles * splits
     // at or below 148 partial tiles; 16384 arrival counters
     if (tiles > 16384) return false;
-    pl.off_counters = pl.off_partial + (pl.n_block <= 64 ? up256((size_t)148 * pl.n_block * kGRows * 4) : 0);
+    size_t partial_bytes = pl.n_block <= 64 ? (size_t)148 * pl.n_block * kGRows * 4 : 0;
+    if (M <= 32) {  // the small-batch kernel (linear_gemm_small.cuh) keeps up to kSMaxUnits partial tiles
+        const size_t small = (size_t)kBtMaxUnits * (M <= 16 ? 16 : 32) * 128 * 4;
+        partial_bytes = small > partial_bytes ? small : partial_bytes;
+    }
+    pl.off_counters = pl.off_partial + up256(partial_bytes);
     pl.total = pl.off_counters + 16384 * 4;
     *out = pl;
     return true;
@@ -955,7 +961,8 @@ static TensorMapEncodeFn tensor_map_encoder() {
 }
 // 2-D row-major tensor [rows, inner] of `elem` bytes, box = [box_rows, box_inner]
 static int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
-                       uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+                       uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle,
+                       CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
     TensorMapEncodeFn enc = tensor_map_encoder();
     if (enc == nullptr) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[2] = {inner, rows};
@@ -964,7 +971,7 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem, con
     const cuuint32_t estr[2] = {1, 1};
     (void)elem;
     const CUresult r = enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     return KMLL_OK;
 }
@@ -977,6 +984,89 @@ static bool gemm_enabled() {
     return on;
 }
 
+static bool gemm_small_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("KMLL_GEMM_SMALL");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+
+// Small batches of W4-G128 (linear_gemm_small.cuh): byte digits of x, then ONE persistent launch over the row tiles of
+// all matrices.  K is split so that the (row tile, split) units fill the 148 multiprocessors in whole rounds.
+static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps, const void* const* w,
+                          const void* const* scales, const int* rows, float* const* outs, const float* const* residuals, const int* ldos,
+                          int nmat, void* workspace, const GemmPlan& big) {
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    int8_t* digits = reinterpret_cast<int8_t*>(ws);
+    float* inv = reinterpret_cast<float*>(ws + big.off_inv);
+    float* partial = reinterpret_cast<float*>(ws + big.off_partial);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(ws + big.off_counters);
+    cudaError_t e = K <= 16384 ? launch(digit_rows_kernel<true>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384)
+                               : launch(digit_rows_kernel<false>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "digit_rows: %s", cudaGetErrorString(e));
+    const int nb = M <= 16 ? 16 : 32;
+    const size_t smem = nb == 16 ? SmallShape<16>::kSmemBytes : SmallShape<32>::kSmemBytes;
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (enc == nullptr) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap map_x, map_w[kBtMaxMats];
+    {   // digit planes as one 3-D tensor [4, M, K] of bytes; box = [4, nb, 128 columns], 128-byte swizzle
+        const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, 4};
+        const cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)M * K};
+        const cuuint32_t box[3] = {128, (cuuint32_t)nb, 4};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        const CUresult r = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, digits, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled (digits) failed (%d)", (int)r);
+    }
+    const int G = K / 128;
+    SmallParams sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.K = K; sp.M = M; sp.nmat = nmat;
+    int tiles = 0;
+    for (int i = 0; i < kBtMaxMats; ++i) {
+        const int src = i < nmat ? i : 0;  // unused tensor-map slots repeat the first matrix
+        KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K / 2, (uint64_t)rows[src], (uint64_t)K / 2, 64, 128,
+                                CU_TENSOR_MAP_SWIZZLE_NONE));
+        if (i >= nmat) continue;
+        sp.mat[i].scales = static_cast<const uint16_t*>(scales[i]);
+        sp.mat[i].out = outs[i];
+        sp.mat[i].residual = residuals[i];
+        sp.mat[i].rows = rows[i];
+        sp.mat[i].ldo = ldos[i];
+        sp.mat[i].tile_start = tiles;
+        tiles += (rows[i] + 127) / 128;
+    }
+    if (tiles > 16384) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: too many row tiles for the split-K counters");
+    int best = 1;
+    double best_eff = 0.0;
+    for (int ks = 1; ks <= kGMaxSplit; ++ks) {
+        if (ks > 1 && (G / ks < 4 || tiles * ks > kBtMaxUnits)) break;
+        const int units = tiles * ks, rounds = (units + 147) / 148;
+        const double eff = (double)units / (rounds * 148.0);
+        if (eff > best_eff + 0.02) { best_eff = eff; best = ks; }
+        if (best_eff >= 0.92) break;
+    }
+    sp.tiles = tiles;
+    sp.ksplit = best;
+    sp.units = tiles * best;
+    sp.inv_xscale = inv;
+    sp.partial = partial;
+    sp.counters = counters;
+    const int grid = sp.units < 148 ? sp.units : 148;
+    if (nb == 16) {
+        auto kern = linear_gemm_small_kernel<16>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
+    } else {
+        auto kern = linear_gemm_small_kernel<32>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
+    }
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_gemm_small (%zu bytes of shared memory): %s", smem, cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
 // y[m, :] (+= residual) = dequant(W_i) x[m, :] for every matrix i; x is split into f16 planes once for all of them
 template <int FMT>
 static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps, const void* const* w,
@@ -986,6 +1076,8 @@ static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, 
     for (int i = 0; i < nmat; ++i) max_rows = rows[i] > max_rows ? rows[i] : max_rows;
     GemmPlan big;
     if (!gemm_plan(FMT, M, K, max_rows, &big)) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: shape not supported by the tensor-core path");
+    if (FMT == FMT_W4 && M <= 32 && gemm_small_enabled())
+        return run_gemm_small(stream, x, M, K, ldx, norm_w, eps, w, scales, rows, outs, residuals, ldos, nmat, workspace, big);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     __half* x_hi = reinterpret_cast<__half*>(ws);
     __half* x_lo = reinterpret_cast<__half*>(ws + big.off_lo);

@@ -45,7 +45,7 @@ __device__ inline bool ld_exchange_value(const uint2* slot, uint32_t number, uns
             *value = __uint_as_float((uint32_t)w);
             return true;
         }
-        if (device_clock_ns() - t0 > kPeerWaitLimitNs) {
+        if (wait_clock_ticks() - t0 > kPeerWaitLimitTicks) {
             *value = 0.0f;
             return false;
         }
@@ -118,7 +118,7 @@ __device__ __forceinline__ float chain_stage(const ChainPhase& ph, const TpExcha
         const uint4* gb = inbox ? reinterpret_cast<const uint4*>(xc.inbox[xc.rank]) + (size_t)(ph.in_index & 1) * tp * (xc.dim >> 1)
                                 : reinterpret_cast<const uint4*>(xc.local_box);
         const int stride = inbox ? (xc.dim >> 1) : 0;
-        const unsigned long long t0 = device_clock_ns();
+        const unsigned long long t0 = wait_clock_ticks();
         bool good = true;
         bool topped = false;
         // the last pair of blocks this warp loads: the held-back weight copies are requested right behind its loads
@@ -134,7 +134,7 @@ __device__ __forceinline__ float chain_stage(const ChainPhase& ph, const TpExcha
                     unsigned int c;
                     asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(hint) : "memory");
                     if ((int)(c - target) >= 0) break;
-                    if (device_clock_ns() - t0 > kPeerWaitLimitNs) break;  // the word loads below report the failure
+                    if (wait_clock_ticks() - t0 > kPeerWaitLimitTicks) break;  // the word loads below report the failure
                     __nanosleep(64);
                 }
             }
@@ -167,7 +167,7 @@ __device__ __forceinline__ float chain_stage(const ChainPhase& ph, const TpExcha
 #pragma unroll
                             for (int m = 0; m < 4; ++m) all = all && q[jj][m].y == epoch && q[jj][m].w == epoch;
                         if (all) break;
-                        if (device_clock_ns() - t0 > kPeerWaitLimitNs) { good = false; break; }
+                        if (wait_clock_ticks() - t0 > kPeerWaitLimitTicks) { good = false; break; }
                         __nanosleep(32);
                     }
 #pragma unroll
@@ -454,7 +454,7 @@ __global__ void __launch_bounds__(kSBlock, 1) linear_chain_kernel(const __grid_c
                         const TpExchange& xc = p.xcv;
                         const uint32_t epoch = chain_epoch(xc, step, ph.residual_index);
                         const uint2* box = xc.inbox[xc.rank] + (size_t)(ph.residual_index & 1) * xc.tp * xc.dim + row;
-                        const unsigned long long t0 = device_clock_ns();
+                        const unsigned long long t0 = wait_clock_ticks();
                         for (int r = 0; r < xc.tp; ++r) {
                             float pv;
                             res_ok = ld_exchange_value(box + (size_t)r * xc.dim, epoch, t0, &pv) && res_ok;

@@ -274,11 +274,30 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
         const int dt = tid - 64;               // 0..255
         const int r = dt >> 1, h = dt & 1;     // tile row, which half of the 64 columns
         const int grow = min(row0 + r, p.rows - 1);
-        const float rs = 1.0f;
-        (void)rs;
+        // W4 group scales of this row, four groups (eight k-tiles) per 64-bit word: the word in use and the one after it are
+        // held in registers and the next is requested when a word is first used, so the load latency (most of a microsecond,
+        // as much as the whole expansion of several tiles) never sits between a tile landing and its planes being ready.
+        const int n_groups = p.K >> 7;
+        const unsigned short* srow = W4 ? reinterpret_cast<const unsigned short*>(p.scales) + (size_t)grow * n_groups : nullptr;
+        auto load_scales4 = [&](int word) -> uint2 {
+            uint32_t v[4] = {0u, 0u, 0u, 0u};
+            if (W4) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (4 * word + j < n_groups) v[j] = __ldg(srow + 4 * word + j);
+            }
+            return make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+        };
+        int word_cur = (kt0 * kGKT) >> 9;
+        uint2 sc_cur = load_scales4(word_cur), sc_next = load_scales4(word_cur + 1);
 #pragma unroll 1
         for (int kt = 0; kt < KT; ++kt) {
             const int stage = kt % stages, use = kt / stages;
+            if (W4 && (((kt0 + kt) * kGKT) >> 9) != word_cur) {
+                ++word_cur;
+                sc_cur = sc_next;
+                sc_next = load_scales4(word_cur + 1);
+            }
             if (!mbar_wait<false>(&full[stage], (uint32_t)use & 1u)) { ok = false; break; }
             unsigned char* st = gsmem + (size_t)stage * stage_bytes;
             unsigned char* a_hi = st;
@@ -286,7 +305,7 @@ __global__ void __launch_bounds__(kGThreads, 1) linear_gemm_kernel(const GemmPar
             const unsigned char* raw = st + (W4 ? 2 : 1) * kABytes + 2 * b_bytes;
             if (W4) {
                 const int grp = ((kt0 + kt) * kGKT) >> 7;
-                const __half sh = __ushort_as_half(reinterpret_cast<const unsigned short*>(p.scales)[(size_t)grow * (p.K >> 7) + grp]);
+                const __half sh = __ushort_as_half((unsigned short)(((grp & 2) ? sc_cur.y : sc_cur.x) >> ((grp & 1) * 16)));
                 const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 32 + h * 16);  // 32 nibbles = columns 32 h .. 32 h + 31
                 const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
                 const __half2 s2 = __half2half2(sh);

@@ -1,0 +1,525 @@
+// W4-G128 linear for small batches (5 to 32 rows of activations: batches of sequences decoding in lockstep), included
+// by linear.cu after linear_gemm.cuh.  Serves the same kmll operator as linear_gemm.cuh (linear_batched_i8_scaled,
+// crates/inference/src/ops/matmul.rs:423-463, over W4-G128 weights) where the work is a stream of weights, not a
+// contraction: the point is to keep every multiprocessor's share of the HBM stream in flight.
+//
+// Arithmetic.  Each row of x becomes a 30-bit fixed-point integer X = rint(x 2^sh) (2^sh puts the row maximum in
+// [2^28, 2^29)), written as four balanced base-256 digits d0..d3 in [-128, 127] (digit_rows_kernel).  The 4-bit weights
+// are used as the signed bytes q = nibble - 8.  For one group of 128 columns
+//   D_i[r, m] = sum_k q[r, k] d_i[m, k]          tcgen05.mma.kind::i8, s8 x s8 -> s32, exact
+//   y[m, r]  += scale[r, group] * sum_i 256^i D_i[r, m]
+// so the group scale is applied to an exact integer dot product after the MMA, in f32, as kmll's own kernel applies it
+// per group.  No second weight plane and no cross terms are needed.
+//
+// Pipeline.  One persistent block per multiprocessor walks its (row tile, k-split) units group by group; up to three
+// matrices that share x (q / k / v, gate / up) are one launch, their row tiles numbered through.  Every hand-off between
+// the roles below costs 0.1 to 0.2 us, the same order as the whole HBM share of a group (8 KB at 44 GB/s per
+// multiprocessor), so throughput is ring depth / loop latency, and each buffer has a ring of its own, sized by how long
+// its contents live:
+//   * raw weight tiles (128 rows x 64 bytes of nibbles, TMA by warp 8): 11 to 15 slots - they wait out the HBM latency;
+//   * digit planes of the same 128 columns (one 3-D TMA box, 128-byte swizzle, warp 4): 5 or 6 slots - L2 latency;
+//   * signed-byte weight tiles in the swizzled K-major layout the MMA reads (written by the eight expanding warps, seven
+//     integer instructions per word; the even and odd columns of a word come out as two runs, the digit planes are stored
+//     in that column order): 3 slots - they live from the expansion to the end of four MMAs;
+//   * accumulators in tensor memory: 8 (16 rows of x) or 4 (32 rows) buffers of 4 n_block columns.
+//   One thread of warp 0 waits for a stage's `a_ready` barrier (the expanding warps have by then also seen the digit planes
+//   land and the accumulator buffer read out), issues the four MMAs of the group (M = 128 weight rows, N = 4 n_block digit
+//   columns, K = 32 bytes each) and one commit on a ring of 16 `done` barriers; the producers, the expanding warps and the
+//   draining warps all derive what they wait for from that ring (the slot they want to refill was last used by the group
+//   `ring size` back).  Eight warps drain: tcgen05.ld of half the columns of the buffer, release it, integer -> f32
+//   without conversion instructions (the sums are below 2^22: add them to the bits of 1.5 * 2^23 and subtract that
+//   constant), combine the digits, one FMA with the group scale into f32 accumulators in registers.  After the last group
+//   of a unit they store the rows (or the split-K partial; the unit that arrives last adds the partials in split order).
+// Because an accumulator lives for one group only, the pipeline runs on across unit boundaries without draining.
+// Tensor maps cover this GPU's memory only; no multicast.  Every wait is bounded (mbar_wait); a time-out raises the device
+// status word, and the block frees its tensor memory and returns.  There is no blocking hardware barrier inside the loops.
+#pragma once
+
+namespace kmll {
+
+constexpr int kBtExpandWarps = 8;
+constexpr int kBtDrainWarps = 8;
+constexpr int kBtThreads = 20 * 32;  // roles by warp: see linear_gemm_small_kernel
+constexpr int kBtABytes = 128 * 128;  // expanded weight tile: 128 rows x 128 signed bytes
+constexpr int kBtRawBytes = 128 * 64;
+constexpr int kBtASlots = 3;
+constexpr int kBtDoneRing = 16;    // `done` barriers; a power of two above every ring size
+constexpr int kBtMaxUnits = 592;   // split-K partial tiles the workspace holds (four per multiprocessor)
+constexpr int kBtMaxMats = 3;
+
+struct SmallMat {
+    const uint16_t* scales;    // binary16 [rows, K / 128]
+    float* out;                // [M, ldo]
+    const float* residual;     // [M, ldo] or null
+    int rows, ldo;
+    int tile_start;            // first row tile of this matrix in the launch's numbering
+};
+
+struct SmallParams {
+    int K, M;
+    int nmat, tiles, ksplit, units;  // tiles = row tiles of all matrices; units = tiles * ksplit
+    SmallMat mat[kBtMaxMats];
+    const float* inv_xscale;   // [M] 2^-sh per row of x
+    float* partial;            // split-K: [tile][split][n_block][128]
+    unsigned int* counters;    // split-K: [tiles] arrivals, zero between launches
+};
+
+// One block per row of x: optional RMSNorm (kmll's order x * inv * w), power-of-two scale, four balanced byte digits.
+// digits = [4][M][K] signed bytes; inside every run of eight columns position p holds column {0,2,4,6,1,3,5,7}[p], the
+// order in which the weight expansion lays out the nibbles of a 32-bit word.  Block 0 also clears the split-K counters.
+// RESIDENT (K <= 16384): the row is read once and stays in registers between the statistics and the digits.
+__device__ inline void digits_of_eight(const float (&v)[8], float xscale, uint32_t (&d)[4][2]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[i][0] = d[i][1] = 0u;
+#pragma unroll
+    for (int pos = 0; pos < 8; ++pos) {
+        const int col = pos < 4 ? 2 * pos : 2 * (pos - 4) + 1;
+        int X = __float2int_rn(v[col] * xscale);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int di = i < 3 ? ((X + 128) & 255) - 128 : X;  // balanced digit; the top one is what is left (|.| <= 33)
+            X = (X - di) >> 8;
+            d[i][pos >> 2] |= (uint32_t)(di & 255) << (8 * (pos & 3));
+        }
+    }
+}
+template <bool RESIDENT>
+__global__ void __launch_bounds__(512) digit_rows_kernel(const float* __restrict__ x, int ldx, int K, int M, const uint16_t* __restrict__ norm_w,
+                                                         float eps, int8_t* __restrict__ digits, float* __restrict__ inv_xscale,
+                                                         unsigned int* counters, int n_counters) {
+    __shared__ float scratch[40];
+    pdl_wait();
+    pdl_launch_dependents();  // the kernel that follows starts bringing in its weights; it waits for this grid before it reads the digits
+    const int m = blockIdx.x;
+    if (m == 0)
+        for (int i = threadIdx.x; i < n_counters; i += blockDim.x) counters[i] = 0u;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * ldx);
+    const uint4* nw8 = reinterpret_cast<const uint4*>(norm_w);
+    constexpr int kPer = 4;  // runs of eight columns per thread when the row is resident: 512 * 4 * 8 = 16384 columns
+    float v[RESIDENT ? kPer : 1][8];
+    float ss = 0.0f, mx = 0.0f;
+    auto load8 = [&](int k8, float (&o)[8], float& ss_, float& mx_) {
+        const float4 a = xr[2 * k8], b = xr[2 * k8 + 1];
+        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) ss_ = fmaf(o[q], o[q], ss_);
+        if (norm_w) {  // largest |x w|; the factor 1 / rms follows once it is known (the margin below covers the rounding)
+            const uint4 w = nw8[k8];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                mx_ = fmaxf(mx_, fmaxf(fabsf(o[2 * q] * __uint_as_float(ww[q] << 16)), fabsf(o[2 * q + 1] * __uint_as_float(ww[q] & 0xffff0000u))));
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) mx_ = fmaxf(mx_, fabsf(o[q]));
+        }
+    };
+    if (RESIDENT) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int k8 = threadIdx.x + i * 512;
+            if (k8 < K / 8) load8(k8, v[RESIDENT ? i : 0], ss, mx);
+        }
+    } else {
+        for (int k8 = threadIdx.x; k8 < K / 8; k8 += 512) {
+            float t[8];
+            load8(k8, t, ss, mx);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    mx = block_max(mx, scratch);
+    const float inv = norm_w ? 1.0f / sqrtf(ss / (float)K + eps) : 1.0f;
+    const float amax = mx * inv * 1.00001f;
+    float xscale = 0.0f, inv_scale = 1.0f;
+    if (amax > 0.0f && amax < INFINITY) {
+        const int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;
+        int sh = 28 - e;  // the row maximum lands in [2^28, 2^29)
+        sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+        xscale = __uint_as_float((uint32_t)(sh + 127) << 23);
+        inv_scale = __uint_as_float((uint32_t)(127 - sh) << 23);
+    }
+    const size_t plane = (size_t)M * K;
+    int8_t* drow = digits + (size_t)m * K;
+    auto store8 = [&](int k8, const float (&o)[8]) {
+        float t[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) t[q] = o[q];
+        if (norm_w) {  // kmll's order: x * inv * w
+            const uint4 w = nw8[k8];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                t[2 * q] = t[2 * q] * inv * __uint_as_float(ww[q] << 16);
+                t[2 * q + 1] = t[2 * q + 1] * inv * __uint_as_float(ww[q] & 0xffff0000u);
+            }
+        }
+        uint32_t d[4][2];
+        digits_of_eight(t, xscale, d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) reinterpret_cast<uint2*>(drow + (size_t)i * plane)[k8] = make_uint2(d[i][0], d[i][1]);
+    };
+    if (RESIDENT) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int k8 = threadIdx.x + i * 512;
+            if (k8 < K / 8) store8(k8, v[RESIDENT ? i : 0]);
+        }
+    } else {
+        for (int k8 = threadIdx.x; k8 < K / 8; k8 += 512) {
+            float t[8], s2 = 0.0f, m2 = 0.0f;
+            load8(k8, t, s2, m2);
+            store8(k8, t);
+        }
+    }
+    if (threadIdx.x == 0) inv_xscale[m] = inv_scale;
+}
+
+// instruction descriptor of kind::i8: D = s32, A and B signed bytes, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__host__ __device__ constexpr uint32_t gemm_idesc_s8s8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ inline void gemm_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// four unsigned nibble bytes (0..15 each) -> four signed bytes nibble - 8, without a carry between the bytes
+__device__ inline uint32_t nibble_bytes_to_s8(uint32_t w, uint32_t shift) {
+    const uint32_t t = lop3_and_or(w >> shift, 0x0f0f0f0fu, 0x80808080u);
+    return (t - 0x08080808u) ^ 0x80808080u;
+}
+__device__ inline void tmem_ld8(uint32_t taddr, uint32_t (&d)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// Ring position with its phase bit, advanced without divisions.
+template <int N>
+struct RingPos {
+    int idx = 0;
+    uint32_t phase = 0;
+    bool wrapped = false;  // the ring has been used once: there is an earlier use to wait for
+    __device__ inline void next() {
+        if (++idx == N) { idx = 0; phase ^= 1u; wrapped = true; }
+    }
+};
+
+// Ring sizes and the shared-memory plan: [raw slots | digit slots | expanded slots | barriers]
+template <int NB>
+struct SmallShape {
+    static constexpr int kBBytes = 4 * NB * 128;           // the four digit planes of one group
+    static constexpr int kXSlots = NB == 16 ? 6 : 5;
+    static constexpr int kBufs = NB == 16 ? 8 : 4;         // accumulator buffers of 4 NB columns: 512 columns of tensor memory
+    static constexpr int kRawSlots = (224 * 1024 - 2048 - kBtASlots * kBtABytes - kXSlots * kBBytes) / kBtRawBytes;
+    static constexpr int kOffX = kRawSlots * kBtRawBytes;
+    static constexpr int kOffA = kOffX + kXSlots * kBBytes;
+    static constexpr int kOffBars = kOffA + kBtASlots * kBtABytes;
+    static constexpr int kNumBars = 2 * kRawSlots + kXSlots + kBtASlots + kBtDoneRing + kBufs + 1;
+    static constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;  // + slack for the 1024-byte alignment
+    static_assert(kRawSlots >= 8 && kRawSlots < kBtDoneRing && kXSlots < kBtDoneRing && kBufs < kBtDoneRing, "ring sizes");
+    static_assert(kOffX % 1024 == 0 && kOffA % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+};
+
+// The unit sequence of one block: units u = blockIdx.x, + gridDim.x, ...; unit = (row tile over all matrices, split);
+// every role walks it with its own copy of this cursor.
+struct UnitCursor {
+    int u, tile, z, g, g1;
+    __device__ inline bool start(const SmallParams& p, int first, int G) {
+        u = first;
+        return load(p, G);
+    }
+    __device__ inline bool load(const SmallParams& p, int G) {
+        if (u >= p.units) return false;
+        tile = u / p.ksplit;
+        z = u - tile * p.ksplit;
+        g = (int)(((long long)z * G) / p.ksplit);
+        g1 = (int)(((long long)(z + 1) * G) / p.ksplit);
+        return true;
+    }
+    // next group; false when the block's work is over
+    __device__ inline bool advance(const SmallParams& p, int G) {
+        if (++g < g1) return true;
+        u += gridDim.x;
+        return load(p, G);
+    }
+};
+
+// NB = rows of x per block (16 or 32): N = 4 NB digit columns per MMA.
+// Warp roles are placed by scheduler (warp % 4): the MMA warp shares its scheduler with the two TMA warps, which sleep on
+// barriers most of the time, and two drain warps; the expanding warps, which spin and compute, sit on the other three.
+//   warp 0: MMA     warp 4: TMA digits     warp 8: TMA weights     warps 1 2 3 5 6 7 9 10: expand     warp 11: idle
+//   warps 12..19: drain (tensor-memory lanes 32 (w % 4) .., warps 12..15 the lower half of the rows of x, 16..19 the upper)
+template <int NB>
+__global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const SmallParams p, const __grid_constant__ CUtensorMap map_w0,
+                                                                        const __grid_constant__ CUtensorMap map_w1,
+                                                                        const __grid_constant__ CUtensorMap map_w2,
+                                                                        const __grid_constant__ CUtensorMap map_x) {
+    using S = SmallShape<NB>;
+    constexpr int kBBytes = S::kBBytes;
+    constexpr int kN = 4 * NB;
+    constexpr int HB = NB / 2;  // rows of x per drain warp
+    constexpr uint32_t kTmemCols = 512;
+    extern __shared__ unsigned char ssmem_raw[];
+    unsigned char* ssmem = ssmem_raw + ((1024u - (smem_u32(ssmem_raw) & 1023u)) & 1023u);
+    uint64_t* raw_full = reinterpret_cast<uint64_t*>(ssmem + S::kOffBars);  // [kRawSlots] the raw weight tile has landed
+    uint64_t* raw_free = raw_full + S::kRawSlots;   // [kRawSlots] the expanding warps have read it
+    uint64_t* x_full = raw_free + S::kRawSlots;     // [kXSlots] the digit planes have landed
+    uint64_t* a_ready = x_full + S::kXSlots;        // [kBtASlots] the signed-byte tile is written and everything else the MMAs need is there
+    uint64_t* done = a_ready + kBtASlots;           // [kBtDoneRing] the MMAs of group number n (n % 16 here) have completed
+    uint64_t* tmem_free = done + kBtDoneRing;       // [kBufs] the drain warps have read the buffer
+    uint64_t* drain_bar = tmem_free + S::kBufs;     // meeting point of the drain warps (split-K hand-off)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+    uint32_t* last_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.K >> 7;  // groups = k-tiles
+
+    if (tid == 0) {
+        for (int s = 0; s < S::kRawSlots; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_free[s], kBtExpandWarps); }
+        for (int s = 0; s < S::kXSlots; ++s) mbar_init(&x_full[s], 1);
+        for (int s = 0; s < kBtASlots; ++s) mbar_init(&a_ready[s], kBtExpandWarps);
+        for (int s = 0; s < kBtDoneRing; ++s) mbar_init(&done[s], 1);
+        for (int b = 0; b < S::kBufs; ++b) mbar_init(&tmem_free[b], kBtDrainWarps);
+        mbar_init(drain_bar, kBtDrainWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t smem_base = smem_u32(ssmem);
+    bool ok = true;
+    // the `done` barrier and parity that report the completion of group number n of this block
+    auto done_wait = [&](int n) { return mbar_wait<false>(&done[n & (kBtDoneRing - 1)], (uint32_t)(n >> 4) & 1u); };
+    static_assert(kBtDoneRing == 16, "done_wait shifts by 4");
+    const bool expander = warp < 11 && (warp & 3) != 0;  // warps 1 2 3 5 6 7 9 10
+    UnitCursor cur;
+
+    if (warp == 8) {
+        // ---- TMA of the raw weight tiles.  The weights never change, so these copies start at once, whatever the previous
+        // kernel is still doing.
+        if (lane == 0 && cur.start(p, blockIdx.x, G)) {
+            RingPos<S::kRawSlots> rp;
+            do {
+                if (rp.wrapped && !mbar_wait<false>(&raw_free[rp.idx], rp.phase ^ 1u)) { ok = false; break; }
+                const int mi = (p.nmat > 2 && cur.tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && cur.tile >= p.mat[1].tile_start) ? 1 : 0;
+                const CUtensorMap* map = mi == 0 ? &map_w0 : mi == 1 ? &map_w1 : &map_w2;
+                mbar_arrive_expect_tx(&raw_full[rp.idx], (uint32_t)kBtRawBytes);
+                tma_load_2d(smem_base + (uint32_t)rp.idx * kBtRawBytes, map, cur.g * 64, (cur.tile - p.mat[mi].tile_start) * 128, &raw_full[rp.idx]);
+                rp.next();
+            } while (cur.advance(p, G));
+        }
+    } else if (warp == 4) {
+        // ---- TMA of the digit planes: they come from the previous kernel; a slot is free when the group that used it
+        // last (kXSlots back) has been multiplied
+        pdl_wait();
+        if (lane == 0 && cur.start(p, blockIdx.x, G)) {
+            RingPos<S::kXSlots> xp;
+            int it = 0;
+            do {
+                if (it >= S::kXSlots && !done_wait(it - S::kXSlots)) { ok = false; break; }
+                mbar_arrive_expect_tx(&x_full[xp.idx], (uint32_t)kBBytes);
+                tma_load_3d(smem_base + S::kOffX + (uint32_t)xp.idx * kBBytes, &map_x, cur.g * 128, 0, 0, &x_full[xp.idx]);
+                xp.next();
+                ++it;
+            } while (cur.advance(p, G));
+        }
+    } else if (warp == 0) {
+        // ---- MMA issuer: one wait, four MMAs and one commit per group
+        if (lane == 0 && cur.start(p, blockIdx.x, G)) {
+            constexpr uint32_t idesc = gemm_idesc_s8s8(128, kN);
+            const uint64_t desc_a0 = gemm_smem_desc(smem_base + S::kOffA), desc_b0 = gemm_smem_desc(smem_base + S::kOffX);
+            RingPos<kBtASlots> ap;
+            RingPos<S::kXSlots> xp;
+            RingPos<S::kBufs> bp;
+            int it = 0;
+            do {
+                if (!mbar_wait<false>(&a_ready[ap.idx], ap.phase)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint64_t da = desc_a0 + (uint64_t)((uint32_t)ap.idx * (kBtABytes >> 4));
+                const uint64_t db = desc_b0 + (uint64_t)((uint32_t)xp.idx * (kBBytes >> 4));
+                const uint32_t d = tmem_base + (uint32_t)(bp.idx * kN);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) gemm_mma_i8(d, da + 2 * ks, db + 2 * ks, idesc, ks > 0 ? 1u : 0u);
+                umma_commit(&done[it & (kBtDoneRing - 1)]);
+                ap.next(); xp.next(); bp.next();
+                ++it;
+            } while (cur.advance(p, G));
+        }
+    } else if (expander) {
+        // ---- weight expansion: thread (row r, half h) turns 32 raw bytes (64 columns) into 64 signed bytes = four 16-byte
+        // chunks of row r of the swizzled tile
+        const int e = warp - 1 - (warp > 4 ? 1 : 0) - (warp > 8 ? 1 : 0);  // 0..7
+        const int dt = e * 32 + lane;
+        const int r = dt >> 1, h = dt & 1;
+        if (cur.start(p, blockIdx.x, G)) {
+            RingPos<S::kRawSlots> rp;
+            RingPos<kBtASlots> ap;
+            RingPos<S::kXSlots> xp;
+            RingPos<S::kBufs> bp;
+            int it = 0;
+            do {
+                // the raw tile has landed; the expanded slot is free (its last user, kBtASlots groups back, has been multiplied)
+                if (!mbar_wait<false>(&raw_full[rp.idx], rp.phase) || (it >= kBtASlots && !done_wait(it - kBtASlots))) { ok = false; break; }
+                const unsigned char* raw = ssmem + (size_t)rp.idx * kBtRawBytes;
+                unsigned char* a = ssmem + S::kOffA + (size_t)ap.idx * kBtABytes;
+                const uint4 w0 = *reinterpret_cast<const uint4*>(raw + r * 64 + h * 32);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(raw + r * 64 + h * 32 + 16);
+                const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 o = make_uint4(nibble_bytes_to_s8(ww[2 * c], 0), nibble_bytes_to_s8(ww[2 * c], 4),
+                                               nibble_bytes_to_s8(ww[2 * c + 1], 0), nibble_bytes_to_s8(ww[2 * c + 1], 4));
+                    *reinterpret_cast<uint4*>(a + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = o;
+                }
+                fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_free[rp.idx]);
+                // everything else the MMAs of this group need: the digit planes, and the accumulator buffer read out
+                if (!mbar_wait<false>(&x_full[xp.idx], xp.phase) || (bp.wrapped && !mbar_wait<false>(&tmem_free[bp.idx], bp.phase ^ 1u))) {
+                    ok = false;
+                    break;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_ready[ap.idx]);
+                rp.next(); ap.next(); xp.next(); bp.next();
+                ++it;
+            } while (cur.advance(p, G));
+        }
+    } else if (warp >= 12) {
+        // ---- drain: warp w may read tensor-memory lanes 32 (w % 4) ..; lane = weight row inside the tile; this warp owns
+        // rows [m_lo, m_lo + HB) of x
+        const int q = warp & 3;
+        const int rl = q * 32 + lane;
+        const int m_lo = warp >= 16 ? HB : 0;
+        uint32_t drain_phase = 0;
+        pdl_wait();  // inv_xscale, the residual and the cleared counters come from earlier kernels
+        if (cur.start(p, blockIdx.x, G)) {
+            RingPos<S::kBufs> bp;
+            int it = 0;
+            bool more = true;
+            while (more && ok) {
+                const int tile = cur.tile, z = cur.z;
+                const int mi = (p.nmat > 2 && tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && tile >= p.mat[1].tile_start) ? 1 : 0;
+                const SmallMat& mt = p.mat[mi];
+                const int row = (tile - mt.tile_start) * 128 + rl;
+                const uint16_t* srow = mt.scales + (size_t)min(row, mt.rows - 1) * G;
+                float acc[HB];
+#pragma unroll
+                for (int m = 0; m < HB; ++m) acc[m] = 0.0f;
+                // group scales of this row, requested two groups ahead of their use
+                uint32_t s_next = __ldg(srow + cur.g), s_next2 = cur.g + 1 < cur.g1 ? __ldg(srow + cur.g + 1) : 0u;
+                bool same_unit = true;
+                while (same_unit) {
+                    const float sc = __half2float(__ushort_as_half((unsigned short)s_next));
+                    s_next = s_next2;
+                    s_next2 = cur.g + 2 < cur.g1 ? __ldg(srow + cur.g + 2) : 0u;
+                    if (!done_wait(it)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(bp.idx * kN + m_lo);
+#pragma unroll
+                    for (int m0 = 0; m0 < HB; m0 += 8) {
+                        uint32_t d0[8], d1[8], d2[8], d3[8];
+                        tmem_ld8(taddr + m0, d0);
+                        tmem_ld8(taddr + NB + m0, d1);
+                        tmem_ld8(taddr + 2 * NB + m0, d2);
+                        tmem_ld8(taddr + 3 * NB + m0, d3);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (m0 + 8 >= HB) {  // everything of this buffer is in registers: hand it back
+                            tcgen05_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&tmem_free[bp.idx]);
+                        }
+                        // |D_i| <= 128 * 8 * 128 = 2^17: the integer added to the bits of 1.5 * 2^23 is that float plus the integer
+                        const float kMagic = 12582912.0f;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float f0 = __uint_as_float(0x4b400000u + d0[j]) - kMagic, f1 = __uint_as_float(0x4b400000u + d1[j]) - kMagic;
+                            const float f2 = __uint_as_float(0x4b400000u + d2[j]) - kMagic, f3 = __uint_as_float(0x4b400000u + d3[j]) - kMagic;
+                            const float t = fmaf(fmaf(fmaf(f3, 256.0f, f2), 256.0f, f1), 256.0f, f0);
+                            acc[m0 + j] = fmaf(t, sc, acc[m0 + j]);
+                        }
+                    }
+                    bp.next();
+                    ++it;
+                    const int u_before = cur.u;
+                    more = cur.advance(p, G);
+                    same_unit = more && cur.u == u_before;
+                }
+                if (!ok) break;
+                // ---- the unit's rows are complete
+                if (p.ksplit == 1) {
+                    if (row < mt.rows) {
+#pragma unroll
+                        for (int m = 0; m < HB; ++m)
+                            if (m_lo + m < p.M) {
+                                float v = acc[m] * p.inv_xscale[m_lo + m];
+                                const size_t o = (size_t)(m_lo + m) * mt.ldo + row;
+                                if (mt.residual != nullptr) v = mt.residual[o] + v;
+                                mt.out[o] = v;
+                            }
+                    }
+                } else {
+                    float* part = p.partial + ((size_t)tile * p.ksplit + z) * (size_t)(NB * 128);
+#pragma unroll
+                    for (int m = 0; m < HB; ++m) part[(m_lo + m) * 128 + rl] = acc[m];
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(drain_bar);
+                    if (!mbar_wait<false>(drain_bar, drain_phase & 1u)) { ok = false; break; }
+                    ++drain_phase;
+                    if (warp == 12 && lane == 0) {
+                        const unsigned int prev = atomicAdd(&p.counters[tile], 1u);
+                        *last_flag = prev == (unsigned int)p.ksplit - 1u ? 1u : 0u;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(drain_bar);
+                    if (!mbar_wait<false>(drain_bar, drain_phase & 1u)) { ok = false; break; }
+                    ++drain_phase;
+                    if (*reinterpret_cast<volatile uint32_t*>(last_flag) != 0u) {
+                        // the last arrival of a tile adds the partials in split order; all loads of a split are issued together
+                        __threadfence();
+                        const float* base = p.partial + (size_t)tile * p.ksplit * (size_t)(NB * 128) + (size_t)m_lo * 128 + rl;
+                        float sum[HB];
+#pragma unroll
+                        for (int m = 0; m < HB; ++m) sum[m] = 0.0f;
+#pragma unroll 2
+                        for (int zz = 0; zz < p.ksplit; ++zz) {
+                            float t[HB];
+#pragma unroll
+                            for (int m = 0; m < HB; ++m) t[m] = __ldcg(base + (size_t)zz * (NB * 128) + m * 128);
+#pragma unroll
+                            for (int m = 0; m < HB; ++m) sum[m] += t[m];
+                        }
+                        if (row < mt.rows) {
+#pragma unroll
+                            for (int m = 0; m < HB; ++m)
+                                if (m_lo + m < p.M) {
+                                    float v = sum[m] * p.inv_xscale[m_lo + m];
+                                    const size_t o = (size_t)(m_lo + m) * mt.ldo + row;
+                                    if (mt.residual != nullptr) v = mt.residual[o] + v;
+                                    mt.out[o] = v;
+                                }
+                        }
+                        if (warp == 12 && lane == 0) p.counters[tile] = 0u;
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (!ok) atomicCAS(&g_device_status, 0, 1);
+}
+
+}  // namespace kmll

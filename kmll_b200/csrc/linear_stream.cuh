@@ -28,7 +28,7 @@ namespace kmll {
 
 constexpr int kSWarps = 16;
 constexpr int kSThreads = kSWarps * 32;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
+constexpr unsigned long long kWaitLimitTicks = 4000000000ull;  // every mbarrier wait gives up after this many cycles (2 to 4 s)
 
 
 struct StreamParams {
@@ -80,14 +80,14 @@ __device__ inline unsigned long long global_timer_ns() {
 template <bool BACKOFF = true>
 __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    const long long t0 = clock64();  // (not %globaltimer: reading that register costs a good fraction of a microsecond)
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
             if (BACKOFF) __nanosleep(64);  // leave the issue slots to the warps that share the scheduler
         }
-        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        if ((unsigned long long)(clock64() - t0) > kWaitLimitTicks) return false;
     }
 }
 // 16-byte asynchronous global->shared copy that bypasses L1 (weights are read once).
@@ -163,7 +163,7 @@ __device__ __noinline__ void gather_exchange(const TpExchange* xcp, int gather_i
     const unsigned int epoch = *xc.epoch * (unsigned int)xc.mult + (unsigned int)gather_index + 1u;
     const int tp = xc.tp, npair = K >> 1;  // a 16-byte load = two (value, number) words
     const uint4* gb = reinterpret_cast<const uint4*>(xc.inbox[xc.rank]) + (size_t)(epoch & 1u) * tp * npair;
-    const unsigned long long t0 = device_clock_ns();
+    const unsigned long long t0 = wait_clock_ticks();
     bool good = true;
 #pragma unroll 1
     for (int i0 = tid; i0 < npair; i0 += 4 * kSThreads) {
@@ -181,7 +181,7 @@ __device__ __noinline__ void gather_exchange(const TpExchange* xcp, int gather_i
                     all = all && q[u].y == epoch && q[u].w == epoch;
                 }
                 if (all) break;
-                if (device_clock_ns() - t0 > kPeerWaitLimitNs) { good = false; break; }
+                if (wait_clock_ticks() - t0 > kPeerWaitLimitTicks) { good = false; break; }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 
 import torch
 
@@ -45,7 +46,10 @@ def main():
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--mats", type=int, default=8)
     ap.add_argument("--reps", type=int, default=10)
-    ap.add_argument("--suite", default="", choices=["", "decode"], help="decode: every batch-1 operator shape of a Mistral-7B-architecture step")
+    ap.add_argument("--suite", default="", choices=["", "decode", "chain4096", "micro", "gemm_sweep"],
+                    help="decode: every batch-1 operator shape of a Mistral-7B-architecture step; chain4096: 4096x4096 matvec + residual + "
+                         "RMSNorm in both formats; micro: RMSNorm / SwiGLU / RoPE / row softmax over B in {1,16,64}, bf16; gemm_sweep: "
+                         "M in {1,16,64,256,2048} x four (N,K), W4-G128")
     ap.add_argument("--profile", action="store_true", help="bracket one graph replay with cudaProfilerStart/Stop")
     a = ap.parse_args()
     torch.cuda.set_device(0)
@@ -54,7 +58,141 @@ def main():
             a.op, a.rows, a.cols, a.mats = op, rows, cols, mats
             run_one(a)
         return
+    if a.suite == "chain4096":
+        return suite_chain4096(a.reps)
+    if a.suite == "micro":
+        return suite_micro(a.reps)
+    if a.suite == "gemm_sweep":
+        return suite_gemm_sweep(a.reps)
     run_one(a)
+
+
+def peak_hbm_gbs():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def time_graph(calls, reps):
+    """Average microseconds per call: the calls are captured once each in one CUDA graph, replayed `reps` times."""
+    for c in calls[:2]:
+        c()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for c in calls:
+            c()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
+
+
+def report(name, us, alg_bytes, extra=None, flops=None, cpu_us=None):
+    hbm, tf, src = peak_hbm_gbs()
+    line = {"op": name, "us": round(us, 2), "algorithmic_mb": round(alg_bytes / 1e6, 3), "gbs": round(alg_bytes / us / 1e3, 1),
+            "frac_hbm": round(alg_bytes / us / 1e3 / hbm, 3), "peak": src}
+    if flops is not None:
+        line["tflops"] = round(flops / us / 1e6, 1)
+        line["frac_tensor"] = round(flops / us / 1e6 / tf, 3)
+    if cpu_us is not None:
+        line["cpu_us"] = round(cpu_us, 1)
+        line["cpu_gbs"] = round(alg_bytes / cpu_us / 1e3, 2)
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def suite_chain4096(reps, cpu=None):
+    """y = dequant(W) x + r, h = RMSNorm(y): W 4096 x 4096 ~ N(0, 0.02) seed 0, x, r ~ N(0, 1), gamma ~ U(0.5, 1.5), eps 1e-6.
+    `cpu(kind, **shape)`, when given, returns the microseconds a CPU implementation of the same operator takes."""
+    rows = cols = 4096
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(cols, generator=gen, device="cuda")
+    r = torch.randn(rows, generator=gen, device="cuda")
+    gamma = (torch.rand(rows, generator=gen, device="cuda") + 0.5).to(torch.bfloat16)
+    y, h = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    for fmt in ("i8", "w4", "w4p"):
+        n = 24  # 24 distinct matrices: 200 to 400 MB, larger than L2
+        calls = []
+        for _ in range(n):
+            w32 = torch.randn((rows, cols), generator=gen, device="cuda") * 0.02
+            if fmt == "i8":
+                w = ops.DeviceRowwiseScaledI8Matrix.from_bf16_rows_symmetric(ops.f32_to_bf16(w32))
+            else:
+                w = ops.DeviceW4G128Matrix.from_f32_rows(w32)
+                if fmt == "w4p":
+                    w = ops.DeviceW4PMatrix.from_canonical(w)
+            calls.append(lambda w=w: (ops.linear_residual(x, w, r, out=y), ops.rmsnorm(y, gamma, 1e-6, out=h)))
+        us = time_graph(calls, reps)
+        alg = weight_bytes(fmt, rows, cols) + 4 * cols + 3 * 4 * rows + 2 * rows + 4 * rows
+        report(f"matvec+residual then rmsnorm 4096x4096 [{fmt}] (2 launches)", us, alg,
+               cpu_us=cpu("chain4096", fmt=fmt) if cpu else None)
+
+
+def suite_micro(reps, cpu=None):
+    """RMSNorm [B,4096], SwiGLU [B,11008], RoPE [B,32,128] theta 1e6 positions U[0,4096), row softmax [B*32,4096]; bf16, seed 1."""
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    for B in (1, 16, 64):
+        copies = max(2, int(300e6 // max(1, B * 32 * 4096 * 4)))  # distinct inputs so that together they exceed L2
+        copies = min(copies, 64)
+
+        def bf(*shape):
+            return [torch.randn(shape, generator=gen, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+
+        xs, outs = bf(B, 4096), bf(B, 4096)
+        gamma = (torch.rand(4096, generator=gen, device="cuda") + 0.5).to(torch.bfloat16)
+        us = time_graph([lambda i=i: ops.rmsnorm_batched_bf16(xs[i], gamma, B, 4096, 1e-6, out=outs[i]) for i in range(copies)], reps)
+        report(f"rmsnorm [{B},4096] bf16", us, B * 4096 * 4 + 2 * 4096, cpu_us=cpu("rmsnorm", batch=B) if cpu else None)
+        g, u, o = bf(B, 11008), bf(B, 11008), bf(B, 11008)
+        us = time_graph([lambda i=i: ops.silu_mul(g[i], u[i], out=o[i]) for i in range(copies)], reps)
+        report(f"swiglu [{B},11008] bf16", us, 3 * B * 11008 * 2, cpu_us=cpu("swiglu", batch=B) if cpu else None)
+        xr, orr = bf(B, 32, 128), bf(B, 32, 128)
+        freqs = torch.tensor([1.0 / (1e6 ** (2 * i / 128)) for i in range(64)], dtype=torch.float32, device="cuda")
+        pos = torch.randint(0, 4096, (B,), generator=gen, device="cuda", dtype=torch.int32)
+        us = time_graph([lambda i=i: ops.apply_rope_batched_bf16(xr[i], freqs, pos, out=orr[i]) for i in range(copies)], reps)
+        report(f"rope [{B},32,128] bf16", us, 2 * B * 32 * 128 * 2 + 4 * B, cpu_us=cpu("rope", batch=B) if cpu else None)
+        sm_copies = max(2, min(copies, int(300e6 // (B * 32 * 4096 * 4))))
+        sx = [torch.randn((B * 32, 4096), generator=gen, device="cuda").to(torch.bfloat16) for _ in range(sm_copies)]
+        so = [torch.empty_like(t) for t in sx]
+        us = time_graph([lambda i=i: ops.softmax_rows(sx[i], out=so[i]) for i in range(sm_copies)], reps)
+        report(f"softmax [{B * 32},4096] bf16", us, 2 * B * 32 * 4096 * 2, cpu_us=cpu("softmax", batch=B) if cpu else None)
+
+
+def suite_gemm_sweep(reps, cpu=None):
+    """Quantized GEMM sweep, W4-G128 (seed 4): M in {1, 16, 64, 256, 2048} x (N, K) in {(3584, 3584), (18944, 3584),
+    (3584, 18944), (152064, 3584)}; activations are bf16-valued N(0, 1) held as f32 (the operator API is f32)."""
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    for n, k in ((3584, 3584), (18944, 3584), (3584, 18944), (152064, 3584)):
+        wbytes = n * k * 0.515625
+        for m in (1, 16, 64, 256, 2048):
+            mats = 1 if m >= 256 else max(1, min(48, int(300e6 // wbytes) + 1))
+            ws = [_weight("w4", n, k) for _ in range(mats)]
+            x = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16).float()
+            out = torch.empty((m, n), device="cuda")
+            if m == 1:
+                if k <= 16384:
+                    ws = [ops.DeviceW4PMatrix.from_canonical(w) for w in ws]
+                calls = [lambda w=w: ops.linear(x[0], w, out=out[0]) for w in ws]
+            else:
+                scratch = ops.linear_batched_workspace(m, k)
+                calls = [lambda w=w: ops.linear_batched(x, w, m, k, n, out=out, workspace=scratch) for w in ws]
+            us = time_graph(calls, reps)
+            report(f"gemm w4 M={m} N={n} K={k}", us, wbytes + 4 * m * k + 4 * m * n, flops=2.0 * m * n * k,
+                   extra={"bound": "hbm" if m <= 16 else "tensor", "path": "stream kernel" if m == 1 else "tcgen05"},
+                   cpu_us=cpu("gemm_w4", m=m, n=n, k=k) if cpu else None)
+            del ws, calls
+            torch.cuda.empty_cache()
 
 
 def run_one(a):

@@ -32,6 +32,32 @@ def test_gemm_w4_vs_oracle(cuda, m, n, k):
     assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4  # every row, relative to its own largest output
 
 
+# 5 to 32 rows of x: the persistent small-batch kernel (byte digits, s8 x s8 MMAs, group scale after the MMA); shapes
+# with a ragged last row tile, one row tile only, split K (few row tiles) and no split (many), 16 and 32 row blocks
+SMALL = [(5, 100, 128), (16, 1024, 4096), (17, 4097, 1024), (32, 14336, 4096), (16, 4096, 14336), (8, 18944, 3584), (24, 3584, 18944),
+         (16, 32000, 4096)]
+
+
+@pytest.mark.parametrize("m,n,k", SMALL)
+def test_small_batch_w4_vs_oracle(cuda, m, n, k):
+    rng = np.random.default_rng(m * 3 + n + k)
+    _, packed, gs, w = w4_weight(rng, n, k)
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    x[0, :] *= F(1e-3)
+    x[m - 1, :] *= F(1e3)
+    x[1, 7] = F(300.0)  # an activation far above the rest of its row
+    ref = oracle.w4_linear_batched(x, packed, gs)
+    ws = ops.linear_batched_workspace(m, k)
+    r = rng.normal(0, 1, (m, n)).astype(F)
+    got = host(ops.linear_batched(dev(x), w, m, k, n, workspace=ws))
+    assert_close(got[m // 2], ref[m // 2], k, f"small batch {m}x{n}x{k} row {m // 2}")
+    scale = np.maximum(np.max(np.abs(ref), axis=1, keepdims=True), 1e-30)
+    assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4
+    again = host(ops.linear_batched(dev(x), w, m, k, n, workspace=ws))
+    assert np.array_equal(got, again)  # split-K partials are added in split order: bit-identical from call to call
+    del r
+
+
 @pytest.mark.parametrize("m,n,k", SHAPES[:5] + [(64, 1000, 896), (2048, 1024, 4096)])
 def test_gemm_i8_vs_oracle(cuda, m, n, k):
     rng = np.random.default_rng(m + n + k + 1)
@@ -56,6 +82,19 @@ def test_gemm_qkv_and_is_deterministic(cuda):
         assert float(np.max(np.abs(host(got) - ref))) <= 1e-4 * np.sqrt(k)
     q2, _, _ = ops.linear_qkv_batched(xd, mats[0][3], mats[1][3], mats[2][3], m, k)
     assert torch.equal(q, q2)
+
+
+def test_small_batch_qkv_one_launch(cuda):
+    """Three matrices of different heights share the digits of x and one persistent launch; RMSNorm fused in front."""
+    rng = np.random.default_rng(11)
+    m, k = 16, 4096
+    mats = [w4_weight(rng, rows, k) for rows in (4096, 1000, 1000)]
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    xd = dev(x)
+    q, kk, v = ops.linear_qkv_batched(xd, mats[0][3], mats[1][3], mats[2][3], m, k)
+    for got, (_, packed, gs, _) in zip((q, kk, v), mats):
+        ref = oracle.w4_linear_batched(x, packed, gs)
+        assert float(np.max(np.abs(host(got) - ref))) <= 1e-4 * np.sqrt(k)
 
 
 def test_gemm_without_workspace_still_works(cuda):
