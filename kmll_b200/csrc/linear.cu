@@ -1053,6 +1053,9 @@ static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int
     sp.inv_xscale = inv;
     sp.partial = partial;
     sp.counters = counters;
+#ifdef KMLL_ROLE_PROFILE
+    { const char* pv = std::getenv("KMLL_ROLE_PROF"); sp.prof = pv ? reinterpret_cast<unsigned long long*>(strtoull(pv, nullptr, 0)) : nullptr; }
+#endif
     const int grid = sp.units < 148 ? sp.units : 148;
     if (nb == 16) {
         auto kern = linear_gemm_small_kernel<16>;

@@ -12,37 +12,39 @@
 // per group.  No second weight plane and no cross terms are needed.
 //
 // Pipeline.  One persistent block per multiprocessor walks its (row tile, k-split) units group by group; up to three
-// matrices that share x (q / k / v, gate / up) are one launch, their row tiles numbered through.  Every hand-off between
-// the roles below costs 0.1 to 0.2 us, the same order as the whole HBM share of a group (8 KB at 44 GB/s per
-// multiprocessor), so throughput is ring depth / loop latency, and each buffer has a ring of its own, sized by how long
-// its contents live:
-//   * raw weight tiles (128 rows x 64 bytes of nibbles, TMA by warp 8): 11 to 15 slots - they wait out the HBM latency;
+// matrices that share x (q / k / v, gate / up) are one launch, their row tiles numbered through.  Measured on B200: every
+// mbarrier, TMA or tcgen05 instruction costs the thread that issues it 100 to 250 cycles, so ONE pass of any role over a
+// group takes 1100 to 1300 cycles however little it computes - several times the HBM share of a group (8 KB at 44 GB/s
+// per multiprocessor = 360 cycles).  Two things follow.  Each buffer has a ring of its own, sized by how long its contents
+// live; and the roles that do work per group exist twice and take the groups alternately:
+//   * raw weight tiles (128 rows x 64 bytes of nibbles, TMA by warp 8): 10 to 13 slots - they wait out the HBM latency;
 //   * digit planes of the same 128 columns (one 3-D TMA box, 128-byte swizzle, warp 4): 5 or 6 slots - L2 latency;
-//   * signed-byte weight tiles in the swizzled K-major layout the MMA reads (written by the eight expanding warps, seven
-//     integer instructions per word; the even and odd columns of a word come out as two runs, the digit planes are stored
-//     in that column order): 3 slots - they live from the expansion to the end of four MMAs;
+//   * signed-byte weight tiles in the swizzled K-major layout the MMA reads: 4 slots, written by two sets of four
+//     expanding warps (seven integer instructions per word; the even and odd columns of a word come out as two runs, the
+//     digit planes are stored in that column order);
 //   * accumulators in tensor memory: 8 (16 rows of x) or 4 (32 rows) buffers of 4 n_block columns.
-//   One thread of warp 0 waits for a stage's `a_ready` barrier (the expanding warps have by then also seen the digit planes
-//   land and the accumulator buffer read out), issues the four MMAs of the group (M = 128 weight rows, N = 4 n_block digit
-//   columns, K = 32 bytes each) and one commit on a ring of 16 `done` barriers; the producers, the expanding warps and the
-//   draining warps all derive what they wait for from that ring (the slot they want to refill was last used by the group
-//   `ring size` back).  Eight warps drain: tcgen05.ld of half the columns of the buffer, release it, integer -> f32
-//   without conversion instructions (the sums are below 2^22: add them to the bits of 1.5 * 2^23 and subtract that
-//   constant), combine the digits, one FMA with the group scale into f32 accumulators in registers.  After the last group
-//   of a unit they store the rows (or the split-K partial; the unit that arrives last adds the partials in split order).
+//   One thread of each of warps 0 and 11 waits for a group's `a_ready` barrier, its digit planes and its accumulator
+//   buffer, issues the four MMAs (M = 128 weight rows, N = 4 n_block digit columns, K = 32 bytes each) and one commit on a
+//   ring of 16 `done` barriers; the producers, the expanding warps and the draining warps all derive what they wait for
+//   from that ring (the slot they want to refill was last used by the group `ring size` back).  Two sets of four warps
+//   drain: tcgen05.ld of the buffer, release it, integer -> f32 without conversion instructions (the sums are below 2^22:
+//   add them to the bits of 1.5 * 2^23 and subtract that constant), combine the digits, one FMA with the group scale into
+//   f32 accumulators in registers.  After the last group of a unit the second set hands its sums to the first through
+//   shared memory, and the first stores the rows (or the split-K partial; the unit that arrives last adds the partials in
+//   split order, so results are bit-identical from call to call).
 // Because an accumulator lives for one group only, the pipeline runs on across unit boundaries without draining.
 // Tensor maps cover this GPU's memory only; no multicast.  Every wait is bounded (mbar_wait); a time-out raises the device
 // status word, and the block frees its tensor memory and returns.  There is no blocking hardware barrier inside the loops.
+// Compiled with -DKMLL_ROLE_PROFILE, block 0 records per role the cycles spent waiting and in all (the figures above).
 #pragma once
 
 namespace kmll {
 
-constexpr int kBtExpandWarps = 8;
-constexpr int kBtDrainWarps = 8;
+constexpr int kBtSetWarps = 4;     // warps per expanding set and per draining set; two sets of each take the groups alternately
 constexpr int kBtThreads = 20 * 32;  // roles by warp: see linear_gemm_small_kernel
 constexpr int kBtABytes = 128 * 128;  // expanded weight tile: 128 rows x 128 signed bytes
 constexpr int kBtRawBytes = 128 * 64;
-constexpr int kBtASlots = 3;
+constexpr int kBtASlots = 4;   // an even number: the two expanding sets alternate over them
 constexpr int kBtDoneRing = 16;    // `done` barriers; a power of two above every ring size
 constexpr int kBtMaxUnits = 592;   // split-K partial tiles the workspace holds (four per multiprocessor)
 constexpr int kBtMaxMats = 3;
@@ -62,6 +64,9 @@ struct SmallParams {
     const float* inv_xscale;   // [M] 2^-sh per row of x
     float* partial;            // split-K: [tile][split][n_block][128]
     unsigned int* counters;    // split-K: [tiles] arrivals, zero between launches
+#ifdef KMLL_ROLE_PROFILE
+    unsigned long long* prof;  // per role of block 0: cycles spent waiting, cycles in all
+#endif
 };
 
 // One block per row of x: optional RMSNorm (kmll's order x * inv * w), power-of-two scale, four balanced byte digits.
@@ -214,13 +219,15 @@ struct SmallShape {
     static constexpr int kBBytes = 4 * NB * 128;           // the four digit planes of one group
     static constexpr int kXSlots = NB == 16 ? 6 : 5;
     static constexpr int kBufs = NB == 16 ? 8 : 4;         // accumulator buffers of 4 NB columns: 512 columns of tensor memory
-    static constexpr int kRawSlots = (224 * 1024 - 2048 - kBtASlots * kBtABytes - kXSlots * kBBytes) / kBtRawBytes;
+    static constexpr int kXchgBytes = NB * 128 * 4;        // partial rows handed from the second drain set to the first
+    static constexpr int kRawSlots = (224 * 1024 - 2048 - kBtASlots * kBtABytes - kXSlots * kBBytes - kXchgBytes) / kBtRawBytes;
     static constexpr int kOffX = kRawSlots * kBtRawBytes;
     static constexpr int kOffA = kOffX + kXSlots * kBBytes;
-    static constexpr int kOffBars = kOffA + kBtASlots * kBtABytes;
-    static constexpr int kNumBars = 2 * kRawSlots + kXSlots + kBtASlots + kBtDoneRing + kBufs + 1;
+    static constexpr int kOffXchg = kOffA + kBtASlots * kBtABytes;
+    static constexpr int kOffBars = kOffXchg + kXchgBytes;
+    static constexpr int kNumBars = 2 * kRawSlots + kXSlots + kBtASlots + kBtDoneRing + kBufs + 3;
     static constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;  // + slack for the 1024-byte alignment
-    static_assert(kRawSlots >= 8 && kRawSlots < kBtDoneRing && kXSlots < kBtDoneRing && kBufs < kBtDoneRing, "ring sizes");
+    static_assert(kRawSlots >= 6 && kRawSlots < kBtDoneRing && kXSlots < kBtDoneRing && kBufs < kBtDoneRing, "ring sizes");
     static_assert(kOffX % 1024 == 0 && kOffA % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 };
 
@@ -248,6 +255,17 @@ struct UnitCursor {
     }
 };
 
+#ifdef KMLL_ROLE_PROFILE
+#define PROF_DECL long long prof_wait = 0, prof_t0 = clock64(), prof_w0 = 0
+#define PROF_W0 prof_w0 = clock64()
+#define PROF_W1 prof_wait += clock64() - prof_w0
+#define PROF_END(role) do { if (p.prof && blockIdx.x == 0) { p.prof[2 * (role)] = (unsigned long long)prof_wait; p.prof[2 * (role) + 1] = (unsigned long long)(clock64() - prof_t0); } } while (0)
+#else
+#define PROF_DECL
+#define PROF_W0
+#define PROF_W1
+#define PROF_END(role)
+#endif
 // NB = rows of x per block (16 or 32): N = 4 NB digit columns per MMA.
 // Warp roles are placed by scheduler (warp % 4): the MMA warp shares its scheduler with the two TMA warps, which sleep on
 // barriers most of the time, and two drain warps; the expanding warps, which spin and compute, sit on the other three.
@@ -261,7 +279,6 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
     using S = SmallShape<NB>;
     constexpr int kBBytes = S::kBBytes;
     constexpr int kN = 4 * NB;
-    constexpr int HB = NB / 2;  // rows of x per drain warp
     constexpr uint32_t kTmemCols = 512;
     extern __shared__ unsigned char ssmem_raw[];
     unsigned char* ssmem = ssmem_raw + ((1024u - (smem_u32(ssmem_raw) & 1023u)) & 1023u);
@@ -271,20 +288,24 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
     uint64_t* a_ready = x_full + S::kXSlots;        // [kBtASlots] the signed-byte tile is written and everything else the MMAs need is there
     uint64_t* done = a_ready + kBtASlots;           // [kBtDoneRing] the MMAs of group number n (n % 16 here) have completed
     uint64_t* tmem_free = done + kBtDoneRing;       // [kBufs] the drain warps have read the buffer
-    uint64_t* drain_bar = tmem_free + S::kBufs;     // meeting point of the drain warps (split-K hand-off)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+    uint64_t* drain_bar = tmem_free + S::kBufs;     // meeting point of the first drain set (split-K hand-off)
+    uint64_t* xchg_full = drain_bar + 1;            // the second drain set has written its partial rows of a unit
+    uint64_t* xchg_free = xchg_full + 1;            // the first set has taken them
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg_free + 1);
     uint32_t* last_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = p.K >> 7;  // groups = k-tiles
 
     if (tid == 0) {
-        for (int s = 0; s < S::kRawSlots; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_free[s], kBtExpandWarps); }
+        for (int s = 0; s < S::kRawSlots; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_free[s], kBtSetWarps); }
         for (int s = 0; s < S::kXSlots; ++s) mbar_init(&x_full[s], 1);
-        for (int s = 0; s < kBtASlots; ++s) mbar_init(&a_ready[s], kBtExpandWarps);
+        for (int s = 0; s < kBtASlots; ++s) mbar_init(&a_ready[s], kBtSetWarps);
         for (int s = 0; s < kBtDoneRing; ++s) mbar_init(&done[s], 1);
-        for (int b = 0; b < S::kBufs; ++b) mbar_init(&tmem_free[b], kBtDrainWarps);
-        mbar_init(drain_bar, kBtDrainWarps);
+        for (int b = 0; b < S::kBufs; ++b) mbar_init(&tmem_free[b], kBtSetWarps);
+        mbar_init(drain_bar, kBtSetWarps);
+        mbar_init(xchg_full, kBtSetWarps);
+        mbar_init(xchg_free, kBtSetWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (warp == 0) {
@@ -308,14 +329,18 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
         // kernel is still doing.
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
             RingPos<S::kRawSlots> rp;
+            PROF_DECL;
             do {
+                PROF_W0;
                 if (rp.wrapped && !mbar_wait<false>(&raw_free[rp.idx], rp.phase ^ 1u)) { ok = false; break; }
+                PROF_W1;
                 const int mi = (p.nmat > 2 && cur.tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && cur.tile >= p.mat[1].tile_start) ? 1 : 0;
                 const CUtensorMap* map = mi == 0 ? &map_w0 : mi == 1 ? &map_w1 : &map_w2;
                 mbar_arrive_expect_tx(&raw_full[rp.idx], (uint32_t)kBtRawBytes);
                 tma_load_2d(smem_base + (uint32_t)rp.idx * kBtRawBytes, map, cur.g * 64, (cur.tile - p.mat[mi].tile_start) * 128, &raw_full[rp.idx]);
                 rp.next();
             } while (cur.advance(p, G));
+            PROF_END(0);
         }
     } else if (warp == 4) {
         // ---- TMA of the digit planes: they come from the previous kernel; a slot is free when the group that used it
@@ -324,16 +349,23 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
             RingPos<S::kXSlots> xp;
             int it = 0;
+            PROF_DECL;
             do {
+                PROF_W0;
                 if (it >= S::kXSlots && !done_wait(it - S::kXSlots)) { ok = false; break; }
+                PROF_W1;
                 mbar_arrive_expect_tx(&x_full[xp.idx], (uint32_t)kBBytes);
                 tma_load_3d(smem_base + S::kOffX + (uint32_t)xp.idx * kBBytes, &map_x, cur.g * 128, 0, 0, &x_full[xp.idx]);
                 xp.next();
                 ++it;
             } while (cur.advance(p, G));
+            PROF_END(1);
         }
-    } else if (warp == 0) {
-        // ---- MMA issuer: one wait, four MMAs and one commit per group
+    } else if (warp == 0 || warp == 11) {
+        // ---- MMA issuers: one thread of each of two warps, alternate groups (their accumulators are different buffers, so
+        // no order is needed between them).  Per group: the stage is expanded, its digit planes have landed, its accumulator
+        // buffer has been read out; four MMAs; one commit.
+        const int set = warp == 0 ? 0 : 1;
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
             constexpr uint32_t idesc = gemm_idesc_s8s8(128, kN);
             const uint64_t desc_a0 = gemm_smem_desc(smem_base + S::kOffA), desc_b0 = gemm_smem_desc(smem_base + S::kOffX);
@@ -341,111 +373,133 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
             RingPos<S::kXSlots> xp;
             RingPos<S::kBufs> bp;
             int it = 0;
+            PROF_DECL;
             do {
-                if (!mbar_wait<false>(&a_ready[ap.idx], ap.phase)) { ok = false; break; }
-                tcgen05_fence_after();
-                const uint64_t da = desc_a0 + (uint64_t)((uint32_t)ap.idx * (kBtABytes >> 4));
-                const uint64_t db = desc_b0 + (uint64_t)((uint32_t)xp.idx * (kBBytes >> 4));
-                const uint32_t d = tmem_base + (uint32_t)(bp.idx * kN);
+                if ((it & 1) == set) {
+                    PROF_W0;
+                    if (!mbar_wait<false>(&a_ready[ap.idx], ap.phase) || !mbar_wait<false>(&x_full[xp.idx], xp.phase) ||
+                        (bp.wrapped && !mbar_wait<false>(&tmem_free[bp.idx], bp.phase ^ 1u))) {
+                        ok = false;
+                        break;
+                    }
+                    PROF_W1;
+                    tcgen05_fence_after();
+                    const uint64_t da = desc_a0 + (uint64_t)((uint32_t)ap.idx * (kBtABytes >> 4));
+                    const uint64_t db = desc_b0 + (uint64_t)((uint32_t)xp.idx * (kBBytes >> 4));
+                    const uint32_t d = tmem_base + (uint32_t)(bp.idx * kN);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) gemm_mma_i8(d, da + 2 * ks, db + 2 * ks, idesc, ks > 0 ? 1u : 0u);
-                umma_commit(&done[it & (kBtDoneRing - 1)]);
+                    for (int ks = 0; ks < 4; ++ks) gemm_mma_i8(d, da + 2 * ks, db + 2 * ks, idesc, ks > 0 ? 1u : 0u);
+                    umma_commit(&done[it & (kBtDoneRing - 1)]);
+                }
                 ap.next(); xp.next(); bp.next();
                 ++it;
             } while (cur.advance(p, G));
+            PROF_END(2 + set);
         }
     } else if (expander) {
-        // ---- weight expansion: thread (row r, half h) turns 32 raw bytes (64 columns) into 64 signed bytes = four 16-byte
-        // chunks of row r of the swizzled tile
+        // ---- weight expansion, two sets of four warps that take the groups alternately.  A thread turns four 16-byte pieces
+        // of the raw tile (32 columns each) into signed bytes: piece id = 128 i + (thread of the set) is (row id / 4, quarter
+        // id % 4), so a warp reads 512 contiguous bytes and writes 16-byte chunks that fall on distinct banks.
         const int e = warp - 1 - (warp > 4 ? 1 : 0) - (warp > 8 ? 1 : 0);  // 0..7
-        const int dt = e * 32 + lane;
-        const int r = dt >> 1, h = dt & 1;
+        const int set = e >> 2;
+        const int dt = (e & 3) * 32 + lane;  // thread of the set, 0..127
         if (cur.start(p, blockIdx.x, G)) {
             RingPos<S::kRawSlots> rp;
             RingPos<kBtASlots> ap;
-            RingPos<S::kXSlots> xp;
-            RingPos<S::kBufs> bp;
             int it = 0;
+            PROF_DECL;
             do {
-                // the raw tile has landed; the expanded slot is free (its last user, kBtASlots groups back, has been multiplied)
-                if (!mbar_wait<false>(&raw_full[rp.idx], rp.phase) || (it >= kBtASlots && !done_wait(it - kBtASlots))) { ok = false; break; }
-                const unsigned char* raw = ssmem + (size_t)rp.idx * kBtRawBytes;
-                unsigned char* a = ssmem + S::kOffA + (size_t)ap.idx * kBtABytes;
-                const uint4 w0 = *reinterpret_cast<const uint4*>(raw + r * 64 + h * 32);
-                const uint4 w1 = *reinterpret_cast<const uint4*>(raw + r * 64 + h * 32 + 16);
-                const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                if ((it & 1) == set) {
+                    // the raw tile has landed; the expanded slot is free (its last user, kBtASlots groups back, has been multiplied)
+                    PROF_W0;
+                    if (!mbar_wait<false>(&raw_full[rp.idx], rp.phase) || (it >= kBtASlots && !done_wait(it - kBtASlots))) { ok = false; break; }
+                    PROF_W1;
+                    const unsigned char* raw = ssmem + (size_t)rp.idx * kBtRawBytes;
+                    unsigned char* a = ssmem + S::kOffA + (size_t)ap.idx * kBtABytes;
+                    uint4 w[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 o = make_uint4(nibble_bytes_to_s8(ww[2 * c], 0), nibble_bytes_to_s8(ww[2 * c], 4),
-                                               nibble_bytes_to_s8(ww[2 * c + 1], 0), nibble_bytes_to_s8(ww[2 * c + 1], 4));
-                    *reinterpret_cast<uint4*>(a + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = o;
+                    for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(raw + (size_t)(i * 128 + dt) * 16);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int id = i * 128 + dt, r = id >> 2, j = id & 3;  // row, 16-byte quarter of its 64 raw bytes
+                        const uint4 lo = make_uint4(nibble_bytes_to_s8(w[i].x, 0), nibble_bytes_to_s8(w[i].x, 4), nibble_bytes_to_s8(w[i].y, 0),
+                                                    nibble_bytes_to_s8(w[i].y, 4));
+                        const uint4 hi = make_uint4(nibble_bytes_to_s8(w[i].z, 0), nibble_bytes_to_s8(w[i].z, 4), nibble_bytes_to_s8(w[i].w, 0),
+                                                    nibble_bytes_to_s8(w[i].w, 4));
+                        *reinterpret_cast<uint4*>(a + r * 128 + (((2 * j) ^ (r & 7)) << 4)) = lo;
+                        *reinterpret_cast<uint4*>(a + r * 128 + (((2 * j + 1) ^ (r & 7)) << 4)) = hi;
+                    }
+                    fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&raw_free[rp.idx]);
+                        mbar_arrive(&a_ready[ap.idx]);
+                    }
                 }
-                fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&raw_free[rp.idx]);
-                // everything else the MMAs of this group need: the digit planes, and the accumulator buffer read out
-                if (!mbar_wait<false>(&x_full[xp.idx], xp.phase) || (bp.wrapped && !mbar_wait<false>(&tmem_free[bp.idx], bp.phase ^ 1u))) {
-                    ok = false;
-                    break;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&a_ready[ap.idx]);
-                rp.next(); ap.next(); xp.next(); bp.next();
+                rp.next(); ap.next();
                 ++it;
             } while (cur.advance(p, G));
+            if (dt == 0) PROF_END(4 + set);
         }
     } else if (warp >= 12) {
-        // ---- drain: warp w may read tensor-memory lanes 32 (w % 4) ..; lane = weight row inside the tile; this warp owns
-        // rows [m_lo, m_lo + HB) of x
+        // ---- drain, two sets of four warps that take the groups alternately: warp w may read tensor-memory lanes
+        // 32 (w % 4) ..; lane = weight row inside the tile; each thread accumulates its row for all rows of x.  At the end of
+        // a unit the second set hands its sums to the first through shared memory; the first set finishes the rows.
         const int q = warp & 3;
         const int rl = q * 32 + lane;
-        const int m_lo = warp >= 16 ? HB : 0;
-        uint32_t drain_phase = 0;
+        const int set = warp >= 16 ? 1 : 0;
+        float* xchg = reinterpret_cast<float*>(ssmem + S::kOffXchg);  // [NB][128]
+        uint32_t drain_phase = 0, xchg_phase = 0;
         pdl_wait();  // inv_xscale, the residual and the cleared counters come from earlier kernels
         if (cur.start(p, blockIdx.x, G)) {
             RingPos<S::kBufs> bp;
             int it = 0;
             bool more = true;
+            PROF_DECL;
             while (more && ok) {
                 const int tile = cur.tile, z = cur.z;
                 const int mi = (p.nmat > 2 && tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && tile >= p.mat[1].tile_start) ? 1 : 0;
                 const SmallMat& mt = p.mat[mi];
                 const int row = (tile - mt.tile_start) * 128 + rl;
                 const uint16_t* srow = mt.scales + (size_t)min(row, mt.rows - 1) * G;
-                float acc[HB];
+                float acc[NB];
 #pragma unroll
-                for (int m = 0; m < HB; ++m) acc[m] = 0.0f;
-                // group scales of this row, requested two groups ahead of their use
-                uint32_t s_next = __ldg(srow + cur.g), s_next2 = cur.g + 1 < cur.g1 ? __ldg(srow + cur.g + 1) : 0u;
+                for (int m = 0; m < NB; ++m) acc[m] = 0.0f;
+                // group scale of this row for this set's next group, requested one of its groups ahead
+                int g_mine = cur.g + (((it & 1) == set) ? 0 : 1);
+                uint32_t s_next = g_mine < cur.g1 ? __ldg(srow + g_mine) : 0u;
                 bool same_unit = true;
                 while (same_unit) {
-                    const float sc = __half2float(__ushort_as_half((unsigned short)s_next));
-                    s_next = s_next2;
-                    s_next2 = cur.g + 2 < cur.g1 ? __ldg(srow + cur.g + 2) : 0u;
-                    if (!done_wait(it)) { ok = false; break; }
-                    tcgen05_fence_after();
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(bp.idx * kN + m_lo);
+                    if ((it & 1) == set) {
+                        const float sc = __half2float(__ushort_as_half((unsigned short)s_next));
+                        s_next = cur.g + 2 < cur.g1 ? __ldg(srow + cur.g + 2) : 0u;
+                        PROF_W0;
+                        if (!done_wait(it)) { ok = false; break; }
+                        PROF_W1;
+                        tcgen05_fence_after();
+                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(bp.idx * kN);
 #pragma unroll
-                    for (int m0 = 0; m0 < HB; m0 += 8) {
-                        uint32_t d0[8], d1[8], d2[8], d3[8];
-                        tmem_ld8(taddr + m0, d0);
-                        tmem_ld8(taddr + NB + m0, d1);
-                        tmem_ld8(taddr + 2 * NB + m0, d2);
-                        tmem_ld8(taddr + 3 * NB + m0, d3);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (m0 + 8 >= HB) {  // everything of this buffer is in registers: hand it back
-                            tcgen05_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&tmem_free[bp.idx]);
-                        }
-                        // |D_i| <= 128 * 8 * 128 = 2^17: the integer added to the bits of 1.5 * 2^23 is that float plus the integer
-                        const float kMagic = 12582912.0f;
+                        for (int m0 = 0; m0 < NB; m0 += 8) {
+                            uint32_t d0[8], d1[8], d2[8], d3[8];
+                            tmem_ld8(taddr + m0, d0);
+                            tmem_ld8(taddr + NB + m0, d1);
+                            tmem_ld8(taddr + 2 * NB + m0, d2);
+                            tmem_ld8(taddr + 3 * NB + m0, d3);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (m0 + 8 >= NB) {  // everything of this buffer is in registers: hand it back
+                                tcgen05_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&tmem_free[bp.idx]);
+                            }
+                            // |D_i| <= 128 * 8 * 128 = 2^17: the integer added to the bits of 1.5 * 2^23 is that float plus the integer
+                            const float kMagic = 12582912.0f;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float f0 = __uint_as_float(0x4b400000u + d0[j]) - kMagic, f1 = __uint_as_float(0x4b400000u + d1[j]) - kMagic;
-                            const float f2 = __uint_as_float(0x4b400000u + d2[j]) - kMagic, f3 = __uint_as_float(0x4b400000u + d3[j]) - kMagic;
-                            const float t = fmaf(fmaf(fmaf(f3, 256.0f, f2), 256.0f, f1), 256.0f, f0);
-                            acc[m0 + j] = fmaf(t, sc, acc[m0 + j]);
+                            for (int j = 0; j < 8; ++j) {
+                                const float f0 = __uint_as_float(0x4b400000u + d0[j]) - kMagic, f1 = __uint_as_float(0x4b400000u + d1[j]) - kMagic;
+                                const float f2 = __uint_as_float(0x4b400000u + d2[j]) - kMagic, f3 = __uint_as_float(0x4b400000u + d3[j]) - kMagic;
+                                const float t = fmaf(fmaf(fmaf(f3, 256.0f, f2), 256.0f, f1), 256.0f, f0);
+                                acc[m0 + j] = fmaf(t, sc, acc[m0 + j]);
+                            }
                         }
                     }
                     bp.next();
@@ -455,14 +509,29 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                     same_unit = more && cur.u == u_before;
                 }
                 if (!ok) break;
-                // ---- the unit's rows are complete
+                // ---- the unit's groups are done: the second set hands over, the first finishes the rows
+                if (set == 1) {
+                    if (xchg_phase > 0 && !mbar_wait<false>(xchg_free, (xchg_phase - 1) & 1u)) { ok = false; break; }
+#pragma unroll
+                    for (int m = 0; m < NB; ++m) xchg[m * 128 + rl] = acc[m];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xchg_full);
+                    ++xchg_phase;
+                    continue;
+                }
+                if (!mbar_wait<false>(xchg_full, xchg_phase & 1u)) { ok = false; break; }
+                ++xchg_phase;
+#pragma unroll
+                for (int m = 0; m < NB; ++m) acc[m] += xchg[m * 128 + rl];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xchg_free);
                 if (p.ksplit == 1) {
                     if (row < mt.rows) {
 #pragma unroll
-                        for (int m = 0; m < HB; ++m)
-                            if (m_lo + m < p.M) {
-                                float v = acc[m] * p.inv_xscale[m_lo + m];
-                                const size_t o = (size_t)(m_lo + m) * mt.ldo + row;
+                        for (int m = 0; m < NB; ++m)
+                            if (m < p.M) {
+                                float v = acc[m] * p.inv_xscale[m];
+                                const size_t o = (size_t)m * mt.ldo + row;
                                 if (mt.residual != nullptr) v = mt.residual[o] + v;
                                 mt.out[o] = v;
                             }
@@ -470,7 +539,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                 } else {
                     float* part = p.partial + ((size_t)tile * p.ksplit + z) * (size_t)(NB * 128);
 #pragma unroll
-                    for (int m = 0; m < HB; ++m) part[(m_lo + m) * 128 + rl] = acc[m];
+                    for (int m = 0; m < NB; ++m) part[m * 128 + rl] = acc[m];
                     __threadfence();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(drain_bar);
@@ -487,24 +556,23 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                     if (*reinterpret_cast<volatile uint32_t*>(last_flag) != 0u) {
                         // the last arrival of a tile adds the partials in split order; all loads of a split are issued together
                         __threadfence();
-                        const float* base = p.partial + (size_t)tile * p.ksplit * (size_t)(NB * 128) + (size_t)m_lo * 128 + rl;
-                        float sum[HB];
+                        const float* base = p.partial + (size_t)tile * p.ksplit * (size_t)(NB * 128) + rl;
 #pragma unroll
-                        for (int m = 0; m < HB; ++m) sum[m] = 0.0f;
-#pragma unroll 2
+                        for (int m = 0; m < NB; ++m) acc[m] = 0.0f;
+#pragma unroll 1
                         for (int zz = 0; zz < p.ksplit; ++zz) {
-                            float t[HB];
+                            float t[NB];
 #pragma unroll
-                            for (int m = 0; m < HB; ++m) t[m] = __ldcg(base + (size_t)zz * (NB * 128) + m * 128);
+                            for (int m = 0; m < NB; ++m) t[m] = __ldcg(base + (size_t)zz * (NB * 128) + m * 128);
 #pragma unroll
-                            for (int m = 0; m < HB; ++m) sum[m] += t[m];
+                            for (int m = 0; m < NB; ++m) acc[m] += t[m];
                         }
                         if (row < mt.rows) {
 #pragma unroll
-                            for (int m = 0; m < HB; ++m)
-                                if (m_lo + m < p.M) {
-                                    float v = sum[m] * p.inv_xscale[m_lo + m];
-                                    const size_t o = (size_t)(m_lo + m) * mt.ldo + row;
+                            for (int m = 0; m < NB; ++m)
+                                if (m < p.M) {
+                                    float v = acc[m] * p.inv_xscale[m];
+                                    const size_t o = (size_t)m * mt.ldo + row;
                                     if (mt.residual != nullptr) v = mt.residual[o] + v;
                                     mt.out[o] = v;
                                 }
@@ -513,6 +581,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                     }
                 }
             }
+            if (q == 0 && lane == 0) PROF_END(6 + set);
         }
     }
 
