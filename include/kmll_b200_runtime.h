@@ -130,10 +130,16 @@ int kmll_decoder_set_pending(kmll_decoder_t dec, kmll_stream_t stream, uint64_t 
 int kmll_decoder_position(kmll_decoder_t dec);
 /* Final hidden state of the last forward [dim] to host (parity checks); synchronises. */
 int kmll_decoder_last_hidden(kmll_decoder_t dec, kmll_stream_t stream, float* hidden_out);
-/* Kernel launches per decode step and bytes of weights / KV cache resident on this rank. */
+/* Next-token logits [vocab_size] of the sequence as it stands (final RMSNorm + lm_head over the last hidden state) into a
+ * DEVICE buffer of the caller; enqueues only.  Replaces what next_logits_to_host / next_top_logits start from
+ * (crates/inference/src/model.rs:5319-5352).  One GPU only (a tensor-parallel rank holds a slice of the vocabulary). */
+int kmll_decoder_next_logits(kmll_decoder_t dec, kmll_stream_t stream, float* logits_device);
+/* Kernel launches per decode step; bytes of weights / KV cache resident on this rank; bytes of every device allocation of
+ * the decoder (weights + KV cache + scratch: RuntimeMemoryStats, crates/inference/src/model.rs:803-808,5368-5391). */
 int kmll_decoder_launches_per_step(kmll_decoder_t dec);
 size_t kmll_decoder_weight_bytes(kmll_decoder_t dec);
 size_t kmll_decoder_kv_bytes(kmll_decoder_t dec);
+size_t kmll_decoder_resident_bytes(kmll_decoder_t dec);
 
 /* ---- on-disk archive of the quantized linear weights ---------------------------------------------------------
  * The directory layout of kmll's quantization export, so an archive written by either side loads on the other:

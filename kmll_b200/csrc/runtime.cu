@@ -114,7 +114,7 @@ struct Decoder {
     unsigned int* xc_epoch = nullptr;  // inside xc_local
     void* xc_peer_base[kMaxTp] = {};   // peers' buffers as mapped here (null for the own rank)
     std::vector<void*> allocs;
-    size_t weight_bytes = 0, kv_bytes = 0;
+    size_t weight_bytes = 0, kv_bytes = 0, resident_bytes = 0;  // resident = every device allocation of this decoder
     int launches_per_step = 0;
     bool weights_set = false;
     // chained decode step (W4-G128, fused): prepared weights, exchange words also on a single GPU
@@ -131,6 +131,7 @@ static int dalloc(Decoder* d, T** out, size_t count) {
     cudaError_t e = cudaMalloc(&p, count * sizeof(T) + 16);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaMalloc(%zu bytes): %s", count * sizeof(T), cudaGetErrorString(e));
     d->allocs.push_back(p);
+    d->resident_bytes += count * sizeof(T);
     *out = static_cast<T*>(p);
     return KMLL_OK;
 }
@@ -1441,6 +1442,24 @@ int kmll_decoder_last_hidden(kmll_decoder_t dec, kmll_stream_t stream, float* hi
     return KMLL_OK;
 }
 
+// Next-token logits of the sequence as it stands (final RMSNorm + lm_head over the last hidden state), into a device
+// buffer of the caller: what kmll's next_logits_to_host / next_top_logits start from (crates/inference/src/model.rs:5319-5352).
+int kmll_decoder_next_logits(kmll_decoder_t dec, kmll_stream_t stream, float* logits_device) {
+    KMLL_REQUIRE_PTR(dec);
+    KMLL_REQUIRE_PTR(logits_device);
+    Decoder* d = static_cast<Decoder*>(dec);
+    const kmll_decoder_config& c = d->cfg;
+    if (c.tp_size > 1) return fail(KMLL_ERR_UNSUPPORTED, "next_logits: a tensor-parallel decoder holds a slice of the vocabulary per rank");
+    cudaStream_t s = as_stream(stream);
+    KMLL_TRY(kmll_rmsnorm(s, d->hidden_a, d->final_norm, c.dim, c.norm_eps, d->normed));
+    if (c.format == KMLL_FORMAT_W4G128)
+        return kmll_linear_w4g128(s, d->normed, static_cast<const uint8_t*>(d->output.w), static_cast<const uint16_t*>(d->output.scales), c.vocab_size,
+                                  c.dim, logits_device);
+    return kmll_linear_i8(s, d->normed, static_cast<const int8_t*>(d->output.w), static_cast<const float*>(d->output.scales), c.vocab_size, c.dim,
+                          logits_device);
+}
+
+size_t kmll_decoder_resident_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->resident_bytes : 0; }
 int kmll_decoder_launches_per_step(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->launches_per_step : 0; }
 size_t kmll_decoder_weight_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->weight_bytes : 0; }
 size_t kmll_decoder_kv_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->kv_bytes : 0; }

@@ -204,6 +204,11 @@ class Decoder:
     def kv_bytes(self) -> int:
         return int(self._lib.kmll_decoder_kv_bytes(self._h))
 
+    @property
+    def resident_bytes(self) -> int:
+        """Bytes of every device allocation of the decoder (weights, KV cache, scratch)."""
+        return int(self._lib.kmll_decoder_resident_bytes(self._h))
+
 
 class BatchDecoder:
     """Lockstep batch of sequences decoded together (kmll_batch_*): shares a Decoder's weights, owns its KV caches.
