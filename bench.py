@@ -347,13 +347,13 @@ def run_ours(args):
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if args.profile:
+    if args.profile == "decode":
         torch.cuda.profiler.start()
     e0.record()
     dec.enqueue_steps(K)
     e1.record()
     barrier()
-    if args.profile:
+    if args.profile == "decode":
         torch.cuda.profiler.stop()
     clocks = sampler.stop()
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -386,7 +386,7 @@ def run_ours(args):
     batch16 = None
     if world == 1 and not args.no_batch16:
         B = 16
-        steps16 = max(4, min(K, 32))
+        steps16 = max(2, min(K, 32))
         dec.rewind(start_pos - W)
         dec.set_pending(first_packed)
         bd = rt.BatchDecoder(dec, B)
@@ -395,10 +395,14 @@ def run_ours(args):
         t16, l16 = bd.generate_greedy(3)  # warm-up steps, also a check: every slot holds the batch-1 sequence
         check["batch16_tokens_match_batch1"] = all(same_greedy_run(t16[slot], l16[slot], dev_tokens[:3], dev_logits[:3])[0] for slot in range(B))
         torch.cuda.synchronize()
+        if args.profile == "batch16":
+            torch.cuda.profiler.start()
         e0.record()
         bd.enqueue_steps(steps16)
         e1.record()
         torch.cuda.synchronize()
+        if args.profile == "batch16":
+            torch.cuda.profiler.stop()
         ms16 = e0.elapsed_time(e1) / steps16
         batch16 = {"metric": "decode_tokens_per_s_batch16_mistral7b_arch_w4g128", "value": B * 1e3 / ms16, "unit": "tokens/s", "batch": B,
                    "steps": steps16, "ms_per_step": ms16, "launches_per_step": bd.launches_per_step,
@@ -535,7 +539,8 @@ def main():
     ap.add_argument("--suite", default="", choices=["", "chain4096", "micro", "gemm_sweep"],
                     help="instead of the decode bench: one operator suite of kmll_b200.microbench, CPU port timed beside each line")
     ap.add_argument("--suite-reps", type=int, default=20)
-    ap.add_argument("--profile", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--profile", nargs="?", const="decode", default=None, choices=["decode", "batch16"],
+                    help="bracket the timed batch-1 decode loop (default) or the timed batch-16 loop with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

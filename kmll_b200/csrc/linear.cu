@@ -818,6 +818,18 @@ int w4_prepare(cudaStream_t stream, const uint8_t* pa, const uint16_t* sa, const
     return check_launch("w4g128_prepare");
 }
 
+// Opt a kernel in to all the dynamic shared memory a block can have (227 KB less the kernel's static part).  Set to the same
+// value at every launch, on whatever device is current: a CUDA graph replays its kernel nodes against the attribute the
+// function has at that time, so a value that followed the needs of the last captured launch would be too small for an
+// earlier node that needs more.
+template <typename K>
+static cudaError_t allow_all_dynamic_smem(K kernel) {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - (int)fa.sharedSizeBytes);
+}
+
 int launch_chain(cudaStream_t stream, ChainParams& cp) {
     if (cp.n_phases < 1 || cp.n_phases > kCMaxPhases) return fail(KMLL_ERR_SHAPE, "chain: %d phases", cp.n_phases);
     int kmax = 0, units_max = 0;
@@ -864,9 +876,8 @@ int launch_chain(cudaStream_t stream, ChainParams& cp) {
     // multiprocessor at most
     const int grid = units_max < num_sms() ? units_max : num_sms();
     cp.trace = trace_next_slot(400, 4 * grid);  // 24 stamps per block
-    // (the kernel also has a little static shared memory, so the dynamic limit is set to what this launch needs)
-    cudaError_t e = cudaFuncSetAttribute(linear_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu bytes): %s", smem, cudaGetErrorString(e));
+    cudaError_t e = allow_all_dynamic_smem(linear_chain_kernel);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute (chain, %zu bytes wanted): %s", smem, cudaGetErrorString(e));
     e = launch(linear_chain_kernel, dim3(grid), dim3(kSBlock), smem, stream, true, cp);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear chain launch: %s", cudaGetErrorString(e));
     return KMLL_OK;
@@ -914,10 +925,14 @@ static bool gemm_plan(int fmt, int M, int K, int rows, GemmPlan* out) {
     pl.row_tiles = (rows + kGRows - 1) / kGRows;
     const int tiles = pl.row_tiles * pl.x_blocks, kt_all = K / kGKT;
     pl.ksplit = 1;
-    if (tiles < 148 && pl.n_block <= 64) {  // few tiles (batches of sequences): split K so that every multiprocessor streams
+    if (tiles < 148) {  // few tiles (a narrow matrix, or few rows of x): split K so that every multiprocessor has work
         pl.ksplit = 148 / tiles;
         if (pl.ksplit > kGMaxSplit) pl.ksplit = kGMaxSplit;
-        if (pl.ksplit > kt_all / 8) pl.ksplit = kt_all / 8;
+        // a split must bring more than its merge costs (the last block of a tile reads every partial back): at least 8 k-tiles
+        // per split for narrow blocks of x, 32 for wide ones (measured: 3584 x 3584 at 256 rows loses with 5 splits of 11
+        // k-tiles, 3584 x 18944 doubles its rate with 5 splits of 59)
+        const int min_kt = pl.n_block <= 64 ? 8 : 32;
+        if (pl.ksplit > kt_all / min_kt) pl.ksplit = kt_all / min_kt;
         if (pl.ksplit < 1) pl.ksplit = 1;
     }
     // (raw weight tiles with 128-byte rows in a ring of their own - 4 k-tiles of W4, 2 of RS-I8 per TMA box - were measured
@@ -935,7 +950,7 @@ static bool gemm_plan(int fmt, int M, int K, int rows, GemmPlan* out) {
     // the layout depends on (M, K) only, so one workspace serves matrices of any height: split-K keeps tiles * splits
     // at or below 148 partial tiles; 16384 arrival counters
     if (tiles > 16384) return false;
-    size_t partial_bytes = pl.n_block <= 64 ? (size_t)148 * pl.n_block * kGRows * 4 : 0;
+    size_t partial_bytes = (size_t)148 * pl.n_block * kGRows * 4;
     if (M <= 32) {  // the small-batch kernel (linear_gemm_small.cuh) keeps up to kSMaxUnits partial tiles
         const size_t small = (size_t)kBtMaxUnits * (M <= 16 ? 16 : 32) * 128 * 4;
         partial_bytes = small > partial_bytes ? small : partial_bytes;
@@ -1059,11 +1074,11 @@ static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int
     const int grid = sp.units < 148 ? sp.units : 148;
     if (nb == 16) {
         auto kern = linear_gemm_small_kernel<16>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = allow_all_dynamic_smem(kern);
         if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
     } else {
         auto kern = linear_gemm_small_kernel<32>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = allow_all_dynamic_smem(kern);
         if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
     }
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_gemm_small (%zu bytes of shared memory): %s", smem, cudaGetErrorString(e));
@@ -1120,7 +1135,7 @@ static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, 
         gp.ldo = ldos[i];
         gp.partial = partial;
         gp.counters = counters;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+        e = allow_all_dynamic_smem(kern);
         if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", pl.smem, cudaGetErrorString(e));
         e = launch(kern, dim3(pl.row_tiles, pl.x_blocks, pl.ksplit), dim3(kGThreads), pl.smem, stream, true, gp, map_w, map_x);
         if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "linear_gemm: %s", cudaGetErrorString(e));

@@ -40,7 +40,8 @@ DECODE_SUITE = [("qkv", 6144, 4096, 16), ("linear_residual", 4096, 4096, 16), ("
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="linear", choices=["linear", "qkv", "linear_residual", "silu_gate_up", "linear_top1", "attention"])
+    ap.add_argument("--op", default="linear", choices=["linear", "qkv", "linear_residual", "silu_gate_up", "linear_top1", "attention", "linear_batched"])
+    ap.add_argument("--batch", type=int, default=16, help="rows of x for --op linear_batched (5..32: small-batch kernel; more: tcgen05 f16 kernel)")
     ap.add_argument("--fmt", default="w4", choices=["w4", "w4p", "i8"])
     ap.add_argument("--rows", type=int, default=14336)
     ap.add_argument("--cols", type=int, default=4096)
@@ -207,6 +208,15 @@ def run_one(a):
             kc, vc = torch.randn(max_seq * n_kv * hd, device="cuda"), torch.randn(max_seq * n_kv * hd, device="cuda")
             calls.append(lambda kc=kc, vc=vc: ops.single_query_attention(q, kc, vc, a.rows, max_seq, n_heads, n_kv, hd, out=out, workspace=ws))
         alg = 2 * a.rows * n_kv * hd * 4 + 2 * n_heads * hd * 4
+    elif a.op == "linear_batched":
+        m = a.batch
+        xb = torch.randn((m, a.cols), device="cuda")
+        outb = torch.empty((m, a.rows), device="cuda")
+        scratch = ops.linear_batched_workspace(m, a.cols)
+        for _ in range(a.mats):
+            w = _weight(a.fmt, a.rows, a.cols)
+            calls.append(lambda w=w: ops.linear_batched(xb, w, m, a.cols, a.rows, out=outb, workspace=scratch))
+        alg = weight_bytes(a.fmt, a.rows, a.cols) + 4 * m * a.cols + 4 * m * a.rows
     else:
         x = torch.randn(a.cols, device="cuda")
         gamma = torch.ones(a.cols, dtype=torch.bfloat16, device="cuda")
@@ -256,8 +266,12 @@ def run_one(a):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (a.reps * len(calls))
-    print(json.dumps({"op": a.op, "fmt": a.fmt, "rows": a.rows, "cols": a.cols, "us_per_launch": us,
-                      "algorithmic_bytes_per_launch": alg, "achieved_gbs": alg / us / 1e3}))
+    line = {"op": a.op, "fmt": a.fmt, "rows": a.rows, "cols": a.cols, "us_per_launch": us, "algorithmic_bytes_per_launch": alg,
+            "achieved_gbs": alg / us / 1e3}
+    if a.op == "linear_batched":
+        line["batch"] = a.batch
+        line["tflops"] = 2.0 * a.batch * a.rows * a.cols / us / 1e6
+    print(json.dumps(line))
 
 
 if __name__ == "__main__":
