@@ -322,6 +322,8 @@ def run_ours(args):
         dec.tp_init(bytes(uid.cpu().numpy().tobytes()))
     dec.init_random(SEED, 0.02, False)
     prompt = np.random.default_rng(SEED).integers(0, cfg.vocab_size, PROMPT_LEN)
+    dec.prefill(prompt)  # untimed: the first prefill allocates its scratch and encodes its tensor maps
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
     dec.prefill(prompt)
     torch.cuda.synchronize()

@@ -130,6 +130,9 @@ int kmll_decoder_set_pending(kmll_decoder_t dec, kmll_stream_t stream, uint64_t 
 int kmll_decoder_position(kmll_decoder_t dec);
 /* Final hidden state of the last forward [dim] to host (parity checks); synchronises. */
 int kmll_decoder_last_hidden(kmll_decoder_t dec, kmll_stream_t stream, float* hidden_out);
+/* Replace the RoPE frequency table (rotary_dim / 2 host values), e.g. with YaRN-scaled frequencies
+ * (yarn_rope_frequencies, crates/inference/src/model.rs:9257-9306).  Synchronises the device. */
+int kmll_decoder_set_rope_freqs(kmll_decoder_t dec, const float* freqs_host, int count);
 /* Next-token logits [vocab_size] of the sequence as it stands (final RMSNorm + lm_head over the last hidden state) into a
  * DEVICE buffer of the caller; enqueues only.  Replaces what next_logits_to_host / next_top_logits start from
  * (crates/inference/src/model.rs:5319-5352).  One GPU only (a tensor-parallel rank holds a slice of the vocabulary). */

@@ -1459,6 +1459,20 @@ int kmll_decoder_next_logits(kmll_decoder_t dec, kmll_stream_t stream, float* lo
                           logits_device);
 }
 
+// Replace the rotation frequencies (rotary_dim / 2 values; e.g. a YaRN-scaled table, crates/inference/src/model.rs:9257-9306).
+// They are read by kernels on every step, so the call synchronises the device first.
+int kmll_decoder_set_rope_freqs(kmll_decoder_t dec, const float* freqs_host, int count) {
+    KMLL_REQUIRE_PTR(dec);
+    KMLL_REQUIRE_PTR(freqs_host);
+    Decoder* d = static_cast<Decoder*>(dec);
+    KMLL_REQUIRE(count == d->cfg.rotary_dim / 2, "set_rope_freqs: %d values given, rotary_dim / 2 = %d expected", count, d->cfg.rotary_dim / 2);
+    for (int i = 0; i < count; ++i)
+        if (!std::isfinite(freqs_host[i])) return fail(KMLL_ERR_SHAPE, "set_rope_freqs: value %d is not finite", i);
+    KMLL_CUDA(cudaDeviceSynchronize());
+    KMLL_CUDA(cudaMemcpy(d->freqs, freqs_host, sizeof(float) * count, cudaMemcpyHostToDevice));
+    return KMLL_OK;
+}
+
 size_t kmll_decoder_resident_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->resident_bytes : 0; }
 int kmll_decoder_launches_per_step(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->launches_per_step : 0; }
 size_t kmll_decoder_weight_bytes(kmll_decoder_t dec) { return dec ? static_cast<Decoder*>(dec)->weight_bytes : 0; }

@@ -146,6 +146,11 @@ class Decoder:
         check(self._lib.kmll_decoder_load_archive(self._h, C.byref(c), directory.encode(),
                                                   None if expected_weights_path is None else expected_weights_path.encode()))
 
+    def set_rope_freqs(self, freqs) -> None:
+        """Replace the RoPE frequency table (rotary_dim / 2 values), e.g. by YaRN-scaled frequencies."""
+        f = np.ascontiguousarray(freqs, dtype=np.float32)
+        check(self._lib.kmll_decoder_set_rope_freqs(self._h, f.ctypes.data, int(f.size)))
+
     def prefill(self, tokens, token_loop: bool = False) -> None:
         t = np.ascontiguousarray(tokens, dtype=np.uint32)
         fn = self._lib.kmll_decoder_prefill_token_loop if token_loop else self._lib.kmll_decoder_prefill

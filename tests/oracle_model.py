@@ -11,7 +11,7 @@ F = np.float32
 
 
 class OracleDecoder:
-    def __init__(self, cfg: rt.DecoderConfig, dec: rt.Decoder):
+    def __init__(self, cfg: rt.DecoderConfig, dec: rt.Decoder, freqs=None):
         self.cfg = cfg
         self.w4 = cfg.format == rt.FORMAT_W4G128
         g = dec.get_tensor
@@ -26,7 +26,7 @@ class OracleDecoder:
         kv = cfg.n_kv_heads * cfg.head_dim
         self.key = [np.zeros((cfg.max_seq_len, kv), dtype=F) for _ in range(cfg.n_layers)]
         self.value = [np.zeros((cfg.max_seq_len, kv), dtype=F) for _ in range(cfg.n_layers)]
-        self.freqs = oracle.rope_frequencies(cfg.rope_theta, cfg.rotary_dim or cfg.head_dim)
+        self.freqs = oracle.rope_frequencies(cfg.rope_theta, cfg.rotary_dim or cfg.head_dim) if freqs is None else np.asarray(freqs, dtype=F)
         self.position = 0
         self.hidden = None
 

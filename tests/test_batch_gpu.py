@@ -71,6 +71,30 @@ def test_batch_gqa_head_dim_128(cuda):
     dec.close()
 
 
+def test_batch_attention_with_several_tiles_per_block(cuda):
+    """16 sequences x 8 KV heads fill the GPU along the batch axis, so the attention plan gives every block a slice of
+    several 64-position tiles (here 128 positions); with 200-token prompts the position being written lies in the second
+    tile of its block - the fused RoPE + KV-write + prefetch path with t0 > 0."""
+    cfg = _cfg(rt.FORMAT_W4G128, n_heads=8, n_kv_heads=8, head_dim=64, dim=512, max_seq_len=400)
+    dec = rt.Decoder(cfg)
+    dec.init_random(11, 0.05, False)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg.vocab_size, 200) for _ in range(16)]
+    singles = []
+    for p in prompts[:4]:
+        dec.prefill(p)
+        singles.append(dec.generate_greedy(6)[0].copy())
+    bd = rt.BatchDecoder(dec, 16)
+    for slot, p in enumerate(prompts):
+        dec.prefill(p)
+        bd.adopt(slot)
+    tokens, _ = bd.generate_greedy(6)
+    for slot in range(4):
+        assert tokens[slot].tolist() == singles[slot].tolist()
+    bd.close()
+    dec.close()
+
+
 def test_batch_errors(cuda):
     cfg = _cfg(rt.FORMAT_RS_I8)
     dec = rt.Decoder(cfg)
