@@ -1008,20 +1008,23 @@ static bool gemm_small_enabled() {
 }
 
 // Small batches of W4-G128 (linear_gemm_small.cuh): byte digits of x, then ONE persistent launch over the row tiles of
-// all matrices.  K is split so that the (row tile, split) units fill the 148 multiprocessors in whole rounds.
-static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps, const void* const* w,
+// all matrices.
+static int run_gemm_small(int fmt, cudaStream_t stream, const float* x, int M, int K, int ldx, const uint16_t* norm_w, float eps, const void* const* w,
                           const void* const* scales, const int* rows, float* const* outs, const float* const* residuals, const int* ldos,
                           int nmat, void* workspace, const GemmPlan& big) {
+    const bool w4 = fmt == FMT_W4;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     int8_t* digits = reinterpret_cast<int8_t*>(ws);
     float* inv = reinterpret_cast<float*>(ws + big.off_inv);
     float* partial = reinterpret_cast<float*>(ws + big.off_partial);
     unsigned int* counters = reinterpret_cast<unsigned int*>(ws + big.off_counters);
-    cudaError_t e = K <= 16384 ? launch(digit_rows_kernel<true>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384)
-                               : launch(digit_rows_kernel<false>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384);
+    const int permute = w4 ? 1 : 0;
+    cudaError_t e = K <= 16384 ? launch(digit_rows_kernel<true>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384, permute)
+                               : launch(digit_rows_kernel<false>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384, permute);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "digit_rows: %s", cudaGetErrorString(e));
     const int nb = M <= 16 ? 16 : 32;
-    const size_t smem = nb == 16 ? SmallShape<16>::kSmemBytes : SmallShape<32>::kSmemBytes;
+    const size_t smem = w4 ? (nb == 16 ? SmallShape<16>::kSmemBytes : SmallShape<32>::kSmemBytes)
+                           : (nb == 16 ? SmallShapeI8<16>::kSmemBytes : SmallShapeI8<32>::kSmemBytes);
     TensorMapEncodeFn enc = tensor_map_encoder();
     if (enc == nullptr) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     CUtensorMap map_x, map_w[kBtMaxMats];
@@ -1034,17 +1037,22 @@ static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled (digits) failed (%d)", (int)r);
     }
-    const int G = K / 128;
+    const int G = (K + 127) / 128;
     SmallParams sp;
     memset(&sp, 0, sizeof(sp));
     sp.K = K; sp.M = M; sp.nmat = nmat;
     int tiles = 0;
     for (int i = 0; i < kBtMaxMats; ++i) {
         const int src = i < nmat ? i : 0;  // unused tensor-map slots repeat the first matrix
-        KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K / 2, (uint64_t)rows[src], (uint64_t)K / 2, 64, 128,
-                                CU_TENSOR_MAP_SWIZZLE_NONE));
+        if (w4)
+            KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K / 2, (uint64_t)rows[src], (uint64_t)K / 2, 64, 128,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE));
+        else  // int8 rows as they lie: 128 rows x 128 bytes, 128-byte swizzle - the MMA reads the tile TMA wrote
+            KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K, (uint64_t)rows[src], (uint64_t)K, 128, 128,
+                                    CU_TENSOR_MAP_SWIZZLE_128B));
         if (i >= nmat) continue;
-        sp.mat[i].scales = static_cast<const uint16_t*>(scales[i]);
+        sp.mat[i].scales = w4 ? static_cast<const uint16_t*>(scales[i]) : nullptr;
+        sp.mat[i].row_scales = w4 ? nullptr : static_cast<const float*>(scales[i]);
         sp.mat[i].out = outs[i];
         sp.mat[i].residual = residuals[i];
         sp.mat[i].rows = rows[i];
@@ -1053,14 +1061,16 @@ static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int
         tiles += (rows[i] + 127) / 128;
     }
     if (tiles > 16384) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: too many row tiles for the split-K counters");
+    // k-split by a cost model fitted to measurements of both small-batch kernels: a block walks `rounds` units in sequence;
+    // a unit costs 0.45 us per 128-column group plus its hand-over - about 1 us when it stores its rows itself, about 4 us
+    // when its partial sums go through the workspace (fence, arrival counter, the last arrival reads every partial back)
     int best = 1;
-    double best_eff = 0.0;
+    double best_cost = 1e30;
     for (int ks = 1; ks <= kGMaxSplit; ++ks) {
         if (ks > 1 && (G / ks < 4 || tiles * ks > kBtMaxUnits)) break;
         const int units = tiles * ks, rounds = (units + 147) / 148;
-        const double eff = (double)units / (rounds * 148.0);
-        if (eff > best_eff + 0.02) { best_eff = eff; best = ks; }
-        if (best_eff >= 0.92) break;
+        const double cost = rounds * (((G + ks - 1) / ks) * 0.45 + (ks > 1 ? 4.0 : 1.0));
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
     }
     sp.tiles = tiles;
     sp.ksplit = best;
@@ -1072,7 +1082,17 @@ static int run_gemm_small(cudaStream_t stream, const float* x, int M, int K, int
     { const char* pv = std::getenv("KMLL_ROLE_PROF"); sp.prof = pv ? reinterpret_cast<unsigned long long*>(strtoull(pv, nullptr, 0)) : nullptr; }
 #endif
     const int grid = sp.units < 148 ? sp.units : 148;
-    if (nb == 16) {
+    if (!w4) {
+        if (nb == 16) {
+            auto kern = linear_gemm_small_i8_kernel<16>;
+            e = allow_all_dynamic_smem(kern);
+            if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(512), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
+        } else {
+            auto kern = linear_gemm_small_i8_kernel<32>;
+            e = allow_all_dynamic_smem(kern);
+            if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(512), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
+        }
+    } else if (nb == 16) {
         auto kern = linear_gemm_small_kernel<16>;
         e = allow_all_dynamic_smem(kern);
         if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
@@ -1094,8 +1114,10 @@ static int run_gemm(cudaStream_t stream, const float* x, int M, int K, int ldx, 
     for (int i = 0; i < nmat; ++i) max_rows = rows[i] > max_rows ? rows[i] : max_rows;
     GemmPlan big;
     if (!gemm_plan(FMT, M, K, max_rows, &big)) return fail(KMLL_ERR_UNSUPPORTED, "linear_batched: shape not supported by the tensor-core path");
-    if (FMT == FMT_W4 && M <= 32 && gemm_small_enabled())
-        return run_gemm_small(stream, x, M, K, ldx, norm_w, eps, w, scales, rows, outs, residuals, ldos, nmat, workspace, big);
+    // 5 to 32 rows of x: the persistent kind::i8 kernels (RS-I8 needs at least two 128-column groups and K <= 131072 for its
+    // s32 accumulators)
+    if (M <= 32 && gemm_small_enabled() && (FMT == FMT_W4 || (K >= 256 && K <= 131072)))
+        return run_gemm_small(FMT, stream, x, M, K, ldx, norm_w, eps, w, scales, rows, outs, residuals, ldos, nmat, workspace, big);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     __half* x_hi = reinterpret_cast<__half*>(ws);
     __half* x_lo = reinterpret_cast<__half*>(ws + big.off_lo);

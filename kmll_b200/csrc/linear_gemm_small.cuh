@@ -50,7 +50,8 @@ constexpr int kBtMaxUnits = 592;   // split-K partial tiles the workspace holds 
 constexpr int kBtMaxMats = 3;
 
 struct SmallMat {
-    const uint16_t* scales;    // binary16 [rows, K / 128]
+    const uint16_t* scales;    // W4-G128: binary16 [rows, K / 128]
+    const float* row_scales;   // RS-I8: float [rows]
     float* out;                // [M, ldo]
     const float* residual;     // [M, ldo] or null
     int rows, ldo;
@@ -70,15 +71,16 @@ struct SmallParams {
 };
 
 // One block per row of x: optional RMSNorm (kmll's order x * inv * w), power-of-two scale, four balanced byte digits.
-// digits = [4][M][K] signed bytes; inside every run of eight columns position p holds column {0,2,4,6,1,3,5,7}[p], the
-// order in which the weight expansion lays out the nibbles of a 32-bit word.  Block 0 also clears the split-K counters.
+// digits = [4][M][K] signed bytes; with `permute` (W4-G128) position p of every run of eight columns holds column
+// {0,2,4,6,1,3,5,7}[p], the order in which the weight expansion lays out the nibbles of a 32-bit word; RS-I8 weights are
+// used as they lie, so their digits keep the natural order.  Block 0 also clears the split-K counters.
 // RESIDENT (K <= 16384): the row is read once and stays in registers between the statistics and the digits.
-__device__ inline void digits_of_eight(const float (&v)[8], float xscale, uint32_t (&d)[4][2]) {
+__device__ inline void digits_of_eight(const float (&v)[8], float xscale, int permute, uint32_t (&d)[4][2]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) d[i][0] = d[i][1] = 0u;
 #pragma unroll
     for (int pos = 0; pos < 8; ++pos) {
-        const int col = pos < 4 ? 2 * pos : 2 * (pos - 4) + 1;
+        const int col = !permute ? pos : pos < 4 ? 2 * pos : 2 * (pos - 4) + 1;
         int X = __float2int_rn(v[col] * xscale);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -91,7 +93,7 @@ __device__ inline void digits_of_eight(const float (&v)[8], float xscale, uint32
 template <bool RESIDENT>
 __global__ void __launch_bounds__(512) digit_rows_kernel(const float* __restrict__ x, int ldx, int K, int M, const uint16_t* __restrict__ norm_w,
                                                          float eps, int8_t* __restrict__ digits, float* __restrict__ inv_xscale,
-                                                         unsigned int* counters, int n_counters) {
+                                                         unsigned int* counters, int n_counters, int permute) {
     __shared__ float scratch[40];
     pdl_wait();
     pdl_launch_dependents();  // the kernel that follows starts bringing in its weights; it waits for this grid before it reads the digits
@@ -159,7 +161,7 @@ __global__ void __launch_bounds__(512) digit_rows_kernel(const float* __restrict
             }
         }
         uint32_t d[4][2];
-        digits_of_eight(t, xscale, d);
+        digits_of_eight(t, xscale, permute, d);
 #pragma unroll
         for (int i = 0; i < 4; ++i) reinterpret_cast<uint2*>(drow + (size_t)i * plane)[k8] = make_uint2(d[i][0], d[i][1]);
     };
@@ -582,6 +584,239 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                 }
             }
             if (q == 0 && lane == 0) PROF_END(6 + set);
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (!ok) atomicCAS(&g_device_status, 0, 1);
+}
+
+// ---- RS-I8 form ---------------------------------------------------------------------------------------------------------
+// The int8 weights are MMA operands exactly as they lie in memory: TMA writes 128 rows x 128 bytes with the 128-byte
+// swizzle and the tensor core reads them; no thread touches a weight.  One row scale per output, so the s32 accumulators
+// run over the whole K range of a unit (|sum| <= 127 * 128 * K < 2^31 for K <= 131072) and are read once per unit.
+// Two MMA-issuing threads take the groups alternately; each keeps its OWN accumulator (the first MMA of a unit overwrites,
+// and nothing orders the two threads), the drain adds the two.  Buffers alternate with the unit's parity, so the MMAs of
+// the next unit run while the previous one is read out.
+//   warps 0, 11: MMA     warp 4: TMA digit planes     warp 8: TMA weights     warps 12..15: drain     others: idle
+template <int NB>
+struct SmallShapeI8 {
+    static constexpr int kWBytes = 128 * 128;
+    static constexpr int kBBytes = 4 * NB * 128;
+    static constexpr int kStageBytes = kWBytes + kBBytes;
+    static constexpr int kStages = NB == 16 ? 9 : 6;
+    static constexpr int kOffBars = kStages * kStageBytes;
+    static constexpr int kNumBars = kStages + kBtDoneRing + 2 + 2 + 1;
+    static constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;
+    static_assert(kStages < kBtDoneRing && kSmemBytes <= 227 * 1024, "ring");
+};
+
+template <int NB>
+__global__ void __launch_bounds__(512, 1) linear_gemm_small_i8_kernel(const SmallParams p, const __grid_constant__ CUtensorMap map_w0,
+                                                                       const __grid_constant__ CUtensorMap map_w1,
+                                                                       const __grid_constant__ CUtensorMap map_w2,
+                                                                       const __grid_constant__ CUtensorMap map_x) {
+    using S = SmallShapeI8<NB>;
+    constexpr int kN = 4 * NB;
+    constexpr uint32_t kTmemCols = 4 * kN;  // [unit parity][MMA thread]: 256 or 512 columns
+    extern __shared__ unsigned char ssmem_raw[];
+    unsigned char* ssmem = ssmem_raw + ((1024u - (smem_u32(ssmem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(ssmem + S::kOffBars);  // [kStages] weights and digit planes have landed (two arrivals)
+    uint64_t* done = full + S::kStages;                                 // [kBtDoneRing] the MMAs of group number n have completed
+    uint64_t* tmem_free = done + kBtDoneRing;                           // [2] the drain warps have read the buffers of that unit parity
+    uint64_t* unit_done = tmem_free + 2;                                // [2] both issuing threads' MMAs of a unit of that parity have completed
+    uint64_t* drain_bar = unit_done + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+    uint32_t* last_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = (p.K + 127) >> 7;  // 128-column groups (the last may be partial: TMA fills with zeros)
+    if (tid == 0) {
+        for (int s = 0; s < S::kStages; ++s) mbar_init(&full[s], 2);
+        for (int s = 0; s < kBtDoneRing; ++s) mbar_init(&done[s], 1);
+        mbar_init(&tmem_free[0], kBtSetWarps);
+        mbar_init(&tmem_free[1], kBtSetWarps);
+        mbar_init(&unit_done[0], 2);
+        mbar_init(&unit_done[1], 2);
+        mbar_init(drain_bar, kBtSetWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t smem_base = smem_u32(ssmem);
+    bool ok = true;
+    auto done_wait = [&](int n) { return mbar_wait<false>(&done[n & (kBtDoneRing - 1)], (uint32_t)(n >> 4) & 1u); };
+    UnitCursor cur;
+
+    if (warp == 4 || warp == 8) {
+        // ---- TMA producers: a stage is free when the group that used it last (kStages back) has been multiplied
+        if (warp == 4) pdl_wait();  // the digit planes come from the previous kernel; the weights never change
+        if (lane == 0 && cur.start(p, blockIdx.x, G)) {
+            RingPos<S::kStages> sp;
+            int it = 0;
+            do {
+                if (it >= S::kStages && !done_wait(it - S::kStages)) { ok = false; break; }
+                const uint32_t st = smem_base + (uint32_t)sp.idx * S::kStageBytes;
+                if (warp == 4) {
+                    mbar_arrive_expect_tx(&full[sp.idx], (uint32_t)S::kBBytes);
+                    tma_load_3d(st + S::kWBytes, &map_x, cur.g * 128, 0, 0, &full[sp.idx]);
+                } else {
+                    const int mi = (p.nmat > 2 && cur.tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && cur.tile >= p.mat[1].tile_start) ? 1 : 0;
+                    const CUtensorMap* map = mi == 0 ? &map_w0 : mi == 1 ? &map_w1 : &map_w2;
+                    mbar_arrive_expect_tx(&full[sp.idx], (uint32_t)S::kWBytes);
+                    tma_load_2d(st, map, cur.g * 128, (cur.tile - p.mat[mi].tile_start) * 128, &full[sp.idx]);
+                }
+                sp.next();
+                ++it;
+            } while (cur.advance(p, G));
+        }
+    } else if (warp == 0 || warp == 11) {
+        const int set = warp == 0 ? 0 : 1;
+        if (lane == 0 && cur.start(p, blockIdx.x, G)) {
+            constexpr uint32_t idesc = gemm_idesc_s8s8(128, kN);
+            const uint64_t desc_a0 = gemm_smem_desc(smem_base), desc_b0 = gemm_smem_desc(smem_base + S::kWBytes);
+            RingPos<S::kStages> sp;
+            int it = 0, unit_no = 0;
+            bool more = true;
+            while (more && ok) {
+                // accumulators of this unit: parity of the unit, then this thread's half
+                const int par = unit_no & 1;
+                if (unit_no >= 2 && !mbar_wait<false>(&tmem_free[par], (uint32_t)((unit_no >> 1) - 1) & 1u)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)((par * 2 + set) * kN);
+                bool first = true, same_unit = true;
+                while (same_unit) {
+                    if ((it & 1) == set) {
+                        if (!mbar_wait<false>(&full[sp.idx], sp.phase)) { ok = false; break; }
+                        tcgen05_fence_after();
+                        const uint64_t soff = (uint64_t)((uint32_t)sp.idx * (S::kStageBytes >> 4));
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) gemm_mma_i8(d, desc_a0 + soff + 2 * ks, desc_b0 + soff + 2 * ks, idesc, (first && ks == 0) ? 0u : 1u);
+                        first = false;
+                        umma_commit(&done[it & (kBtDoneRing - 1)]);
+                    }
+                    sp.next();
+                    ++it;
+                    const int u_before = cur.u;
+                    more = cur.advance(p, G);
+                    same_unit = more && cur.u == u_before;
+                }
+                if (!ok) break;
+                umma_commit(&unit_done[par]);  // everything this thread issued for the unit (a unit has at least two groups)
+                ++unit_no;
+            }
+        }
+    } else if (warp >= 12) {
+        // ---- drain: lane = weight row inside the tile; once per unit
+        const int q = warp & 3;
+        const int rl = q * 32 + lane;
+        uint32_t drain_phase = 0;
+        pdl_wait();
+        if (cur.start(p, blockIdx.x, G)) {
+            int it = 0, unit_no = 0;
+            bool more = true;
+            while (more && ok) {
+                const int tile = cur.tile, z = cur.z;
+                const int n_items = cur.g1 - cur.g;
+                const int mi = (p.nmat > 2 && tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && tile >= p.mat[1].tile_start) ? 1 : 0;
+                const SmallMat& mt = p.mat[mi];
+                const int row = (tile - mt.tile_start) * 128 + rl;
+                const int it_first = it;
+                it += n_items;
+                for (int k = 0; k < n_items && more; ++k) more = cur.advance(p, G);
+                const int par = unit_no & 1;
+                if (!mbar_wait<false>(&unit_done[par], (uint32_t)(unit_no >> 1) & 1u)) { ok = false; break; }
+                tcgen05_fence_after();
+                // which thread took the first group of the unit decides nothing here: both accumulators are simply added
+                const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((par * 2 + 0) * kN);
+                const uint32_t tb = ta + (uint32_t)kN;
+                float acc[NB];
+#pragma unroll
+                for (int m0 = 0; m0 < NB; m0 += 8) {
+                    long long v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = 0;
+#pragma unroll
+                    for (int dgt = 3; dgt >= 0; --dgt) {
+                        uint32_t a[8], b[8];
+                        tmem_ld8(ta + dgt * NB + m0, a);
+                        tmem_ld8(tb + dgt * NB + m0, b);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = v[j] * 256 + (long long)((int)a[j] + (int)b[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[m0 + j] = (float)v[j];
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_free[par]);
+                (void)it_first;
+                const float rscale = row < mt.rows ? mt.row_scales[row] : 0.0f;
+                if (p.ksplit == 1) {
+                    if (row < mt.rows) {
+#pragma unroll
+                        for (int m = 0; m < NB; ++m)
+                            if (m < p.M) {
+                                float y = acc[m] * p.inv_xscale[m] * rscale;
+                                const size_t o = (size_t)m * mt.ldo + row;
+                                if (mt.residual != nullptr) y = mt.residual[o] + y;
+                                mt.out[o] = y;
+                            }
+                    }
+                } else {
+                    float* part = p.partial + ((size_t)tile * p.ksplit + z) * (size_t)(NB * 128);
+#pragma unroll
+                    for (int m = 0; m < NB; ++m) part[m * 128 + rl] = acc[m];
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(drain_bar);
+                    if (!mbar_wait<false>(drain_bar, drain_phase & 1u)) { ok = false; break; }
+                    ++drain_phase;
+                    if (warp == 12 && lane == 0) {
+                        const unsigned int prev = atomicAdd(&p.counters[tile], 1u);
+                        *last_flag = prev == (unsigned int)p.ksplit - 1u ? 1u : 0u;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(drain_bar);
+                    if (!mbar_wait<false>(drain_bar, drain_phase & 1u)) { ok = false; break; }
+                    ++drain_phase;
+                    if (*reinterpret_cast<volatile uint32_t*>(last_flag) != 0u) {
+                        __threadfence();
+                        const float* base = p.partial + (size_t)tile * p.ksplit * (size_t)(NB * 128) + rl;
+#pragma unroll
+                        for (int m = 0; m < NB; ++m) acc[m] = 0.0f;
+#pragma unroll 1
+                        for (int zz = 0; zz < p.ksplit; ++zz) {
+                            float t[NB];
+#pragma unroll
+                            for (int m = 0; m < NB; ++m) t[m] = __ldcg(base + (size_t)zz * (NB * 128) + m * 128);
+#pragma unroll
+                            for (int m = 0; m < NB; ++m) acc[m] += t[m];
+                        }
+                        if (row < mt.rows) {
+#pragma unroll
+                            for (int m = 0; m < NB; ++m)
+                                if (m < p.M) {
+                                    float y = acc[m] * p.inv_xscale[m] * rscale;
+                                    const size_t o = (size_t)m * mt.ldo + row;
+                                    if (mt.residual != nullptr) y = mt.residual[o] + y;
+                                    mt.out[o] = y;
+                                }
+                        }
+                        if (warp == 12 && lane == 0) p.counters[tile] = 0u;
+                    }
+                }
+                ++unit_no;
+            }
         }
     }
 

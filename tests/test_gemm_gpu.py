@@ -58,6 +58,25 @@ def test_small_batch_w4_vs_oracle(cuda, m, n, k):
     del r
 
 
+@pytest.mark.parametrize("m,n,k", [(5, 100, 256), (16, 1024, 4096), (17, 4097, 1024), (32, 14336, 4096), (16, 4096, 14336), (9, 700, 320),
+                                   (16, 32000, 4096)])
+def test_small_batch_i8_vs_oracle(cuda, m, n, k):
+    """RS-I8, 5 to 32 rows of x: the int8 rows are MMA operands as they lie (K = 320: a partial last group)."""
+    rng = np.random.default_rng(m * 5 + n + k)
+    _, q, sc, w = i8_weight(rng, n, k)
+    x = rng.normal(0, 1, (m, k)).astype(F)
+    x[0, :] *= F(1e-3)
+    x[m - 1, :] *= F(1e3)
+    x[1, 7] = F(300.0)
+    ref = oracle.rs_i8_linear_batched(x, q, sc)
+    ws = ops.linear_batched_workspace(m, k)
+    got = host(ops.linear_batched(dev(x), w, m, k, n, workspace=ws))
+    assert_close(got[m // 2], ref[m // 2], k, f"small batch i8 {m}x{n}x{k} row {m // 2}")
+    scale = np.maximum(np.max(np.abs(ref), axis=1, keepdims=True), 1e-30)
+    assert float(np.max(np.abs(got - ref) / scale)) <= 1e-4
+    assert np.array_equal(got, host(ops.linear_batched(dev(x), w, m, k, n, workspace=ws)))
+
+
 @pytest.mark.parametrize("m,n,k", SHAPES[:5] + [(64, 1000, 896), (2048, 1024, 4096)])
 def test_gemm_i8_vs_oracle(cuda, m, n, k):
     rng = np.random.default_rng(m + n + k + 1)
