@@ -415,7 +415,7 @@ def run_ours(args):
     rs_i8 = None
     if world == 1 and not args.no_rsi8:
         steps8 = max(8, min(K, 64))
-        dec8 = rt.Decoder(rt.DecoderConfig.mistral_7b(max_seq_len=PROMPT_LEN + steps8 + 16, format=rt.FORMAT_RS_I8))
+        dec8 = rt.Decoder(rt.DecoderConfig.mistral_7b(max_seq_len=PROMPT_LEN + steps8 + 64, format=rt.FORMAT_RS_I8))
         dec8.init_random(SEED, 0.02, False)
         dec8.prefill(prompt)
         dec8.enqueue_steps(3)
@@ -429,6 +429,23 @@ def run_ours(args):
         rs_i8 = {"metric": "decode_tokens_per_s_batch1_mistral7b_arch_rs_i8", "value": 1e3 / ms8, "unit": "tokens/s", "steps": steps8,
                  "ms_per_step": ms8, "launches_per_step": dec8.launches_per_step, "algorithmic_bytes_per_step": bytes8,
                  "frac_of_peak": bytes8 / ms8 / 1e6 / peaks()[0]}
+        if not args.no_batch16:  # the same 16-sequence lockstep leg in the reference's own format
+            first8, logits8 = dec8.history(0, 1)
+            dec8.rewind(PROMPT_LEN)
+            dec8.set_pending((int(logits8[:1].view(np.uint32)[0]) << 32) | int(first8[0]))
+            bd8 = rt.BatchDecoder(dec8, 16)
+            for slot in range(16):
+                bd8.adopt(slot)
+            bd8.generate_greedy(3)
+            torch.cuda.synchronize()
+            n16 = max(2, min(K, 16))
+            e0.record()
+            bd8.enqueue_steps(n16)
+            e1.record()
+            torch.cuda.synchronize()
+            rs_i8["batch16"] = {"value": 16 * 1e3 / (e0.elapsed_time(e1) / n16), "unit": "tokens/s", "ms_per_step": e0.elapsed_time(e1) / n16,
+                                "steps": n16, "launches_per_step": bd8.launches_per_step}
+            bd8.close()
         dec8.close()
 
     # ---- roofline of the dominant kernel: the fused RMSNorm + gate/up + SiLU kernel over prepared-layout weights (the

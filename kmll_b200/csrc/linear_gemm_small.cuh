@@ -17,7 +17,7 @@
 // group takes 1100 to 1300 cycles however little it computes - several times the HBM share of a group (8 KB at 44 GB/s
 // per multiprocessor = 360 cycles).  Two things follow.  Each buffer has a ring of its own, sized by how long its contents
 // live; and the roles that do work per group exist twice and take the groups alternately:
-//   * raw weight tiles (128 rows x 64 bytes of nibbles, TMA by warp 8): 10 to 13 slots - they wait out the HBM latency;
+//   * raw weight tiles (128 rows x 64 bytes of nibbles, TMA by warp 8): 12 slots (7 with 32 rows of x) - they wait out the HBM latency;
 //   * digit planes of the same 128 columns (one 3-D TMA box, 128-byte swizzle, warp 4): 5 or 6 slots - L2 latency;
 //   * signed-byte weight tiles in the swizzled K-major layout the MMA reads: 4 slots, written by two sets of four
 //     expanding warps (seven integer instructions per word; the even and odd columns of a word come out as two runs, the
@@ -657,15 +657,18 @@ __global__ void __launch_bounds__(512, 1) linear_gemm_small_i8_kernel(const Smal
     UnitCursor cur;
 
     if (warp == 4 || warp == 8) {
-        // ---- TMA producers: a stage is free when the group that used it last (kStages back) has been multiplied
-        if (warp == 4) pdl_wait();  // the digit planes come from the previous kernel; the weights never change
+        // ---- TMA producers: a stage is free when the group that used it last (kStages back) has been multiplied.
+        // (Two alternating threads per stream were tried: no faster, and one run of a 250-tile matrix ended in a launch
+        // failure whose cause was not found by reading; the single-thread form below is the one that has run every shape.)
+        const bool digits = warp == 4;
+        if (digits) pdl_wait();  // the digit planes come from the previous kernel; the weights never change
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
             RingPos<S::kStages> sp;
             int it = 0;
             do {
                 if (it >= S::kStages && !done_wait(it - S::kStages)) { ok = false; break; }
                 const uint32_t st = smem_base + (uint32_t)sp.idx * S::kStageBytes;
-                if (warp == 4) {
+                if (digits) {
                     mbar_arrive_expect_tx(&full[sp.idx], (uint32_t)S::kBBytes);
                     tma_load_3d(st + S::kWBytes, &map_x, cur.g * 128, 0, 0, &full[sp.idx]);
                 } else {

@@ -51,6 +51,8 @@ def main():
                     help="decode: every batch-1 operator shape of a Mistral-7B-architecture step; chain4096: 4096x4096 matvec + residual + "
                          "RMSNorm in both formats; micro: RMSNorm / SwiGLU / RoPE / row softmax over B in {1,16,64}, bf16; gemm_sweep: "
                          "M in {1,16,64,256,2048} x four (N,K), W4-G128")
+    ap.add_argument("--shards", type=int, default=1, help="gemm_sweep: time one rank's share of every matrix when its N output rows are split over this "
+                                                           "many GPUs (column-parallel: disjoint output blocks, no collective)")
     ap.add_argument("--profile", action="store_true", help="bracket one graph replay with cudaProfilerStart/Stop")
     a = ap.parse_args()
     torch.cuda.set_device(0)
@@ -64,7 +66,7 @@ def main():
     if a.suite == "micro":
         return suite_micro(a.reps)
     if a.suite == "gemm_sweep":
-        return suite_gemm_sweep(a.reps)
+        return suite_gemm_sweep(a.reps, shards=a.shards)
     run_one(a)
 
 
@@ -170,11 +172,12 @@ def suite_micro(reps, cpu=None):
         report(f"softmax [{B * 32},4096] bf16", us, 2 * B * 32 * 4096 * 2, cpu_us=cpu("softmax", batch=B) if cpu else None)
 
 
-def suite_gemm_sweep(reps, cpu=None):
+def suite_gemm_sweep(reps, cpu=None, shards=1):
     """Quantized GEMM sweep, W4-G128 (seed 4): M in {1, 16, 64, 256, 2048} x (N, K) in {(3584, 3584), (18944, 3584),
     (3584, 18944), (152064, 3584)}; activations are bf16-valued N(0, 1) held as f32 (the operator API is f32)."""
     gen = torch.Generator(device="cuda").manual_seed(4)
-    for n, k in ((3584, 3584), (18944, 3584), (3584, 18944), (152064, 3584)):
+    for n_full, k in ((3584, 3584), (18944, 3584), (3584, 18944), (152064, 3584)):
+        n = n_full // shards
         wbytes = n * k * 0.515625
         for m in (1, 16, 64, 256, 2048):
             mats = 1 if m >= 256 else max(1, min(48, int(300e6 // wbytes) + 1))
@@ -190,7 +193,8 @@ def suite_gemm_sweep(reps, cpu=None):
                 calls = [lambda w=w: ops.linear_batched(x, w, m, k, n, out=out, workspace=scratch) for w in ws]
             us = time_graph(calls, reps)
             report(f"gemm w4 M={m} N={n} K={k}", us, wbytes + 4 * m * k + 4 * m * n, flops=2.0 * m * n * k,
-                   extra={"bound": "hbm" if m <= 16 else "tensor", "path": "stream kernel" if m == 1 else "tcgen05"},
+                   extra={"bound": "hbm" if m <= 16 else "tensor", "path": "stream kernel" if m == 1 else "tcgen05",
+                          **({"shard_of": n_full, "shards": shards} if shards > 1 else {})},
                    cpu_us=cpu("gemm_w4", m=m, n=n, k=k) if cpu else None)
             del ws, calls
             torch.cuda.empty_cache()
