@@ -1023,7 +1023,8 @@ static int run_gemm_small(int fmt, cudaStream_t stream, const float* x, int M, i
                                : launch(digit_rows_kernel<false>, dim3(M), dim3(512), 0, stream, true, x, ldx, K, M, norm_w, eps, digits, inv, counters, 16384, permute);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "digit_rows: %s", cudaGetErrorString(e));
     const int nb = M <= 16 ? 16 : 32;
-    const size_t smem = w4 ? (nb == 16 ? SmallShape<16>::kSmemBytes : SmallShape<32>::kSmemBytes)
+    const int gp = (w4 && nb == 16 && K >= 256) ? 2 : 1;  // groups per pipeline item (SmallShape)
+    const size_t smem = w4 ? (nb == 32 ? SmallShape<32, 1>::kSmemBytes : gp == 2 ? SmallShape<16, 2>::kSmemBytes : SmallShape<16, 1>::kSmemBytes)
                            : (nb == 16 ? SmallShapeI8<16>::kSmemBytes : SmallShapeI8<32>::kSmemBytes);
     TensorMapEncodeFn enc = tensor_map_encoder();
     if (enc == nullptr) return fail(KMLL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -1044,9 +1045,9 @@ static int run_gemm_small(int fmt, cudaStream_t stream, const float* x, int M, i
     int tiles = 0;
     for (int i = 0; i < kBtMaxMats; ++i) {
         const int src = i < nmat ? i : 0;  // unused tensor-map slots repeat the first matrix
-        if (w4)
-            KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K / 2, (uint64_t)rows[src], (uint64_t)K / 2, 64, 128,
-                                    CU_TENSOR_MAP_SWIZZLE_NONE));
+        if (w4)  // nibbles of one group per row and box, or of two groups in the 128-byte swizzle
+            KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K / 2, (uint64_t)rows[src], (uint64_t)K / 2, 64 * gp, 128,
+                                    gp == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE));
         else  // int8 rows as they lie: 128 rows x 128 bytes, 128-byte swizzle - the MMA reads the tile TMA wrote
             KMLL_TRY_RC(make_map_2d(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[src], (uint64_t)K, (uint64_t)rows[src], (uint64_t)K, 128, 128,
                                     CU_TENSOR_MAP_SWIZZLE_128B));
@@ -1092,12 +1093,16 @@ static int run_gemm_small(int fmt, cudaStream_t stream, const float* x, int M, i
             e = allow_all_dynamic_smem(kern);
             if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(512), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
         }
-    } else if (nb == 16) {
-        auto kern = linear_gemm_small_kernel<16>;
+    } else if (nb == 32) {
+        auto kern = linear_gemm_small_kernel<32, 1>;
+        e = allow_all_dynamic_smem(kern);
+        if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
+    } else if (gp == 2) {
+        auto kern = linear_gemm_small_kernel<16, 2>;
         e = allow_all_dynamic_smem(kern);
         if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
     } else {
-        auto kern = linear_gemm_small_kernel<32>;
+        auto kern = linear_gemm_small_kernel<16, 1>;
         e = allow_all_dynamic_smem(kern);
         if (e == cudaSuccess) e = launch(kern, dim3(grid), dim3(kBtThreads), smem, stream, true, sp, map_w[0], map_w[1], map_w[2], map_x);
     }

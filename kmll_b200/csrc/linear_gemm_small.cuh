@@ -44,7 +44,7 @@ constexpr int kBtSetWarps = 4;     // warps per expanding set and per draining s
 constexpr int kBtThreads = 20 * 32;  // roles by warp: see linear_gemm_small_kernel
 constexpr int kBtABytes = 128 * 128;  // expanded weight tile: 128 rows x 128 signed bytes
 constexpr int kBtRawBytes = 128 * 64;
-constexpr int kBtASlots = 4;   // an even number: the two expanding sets alternate over them
+constexpr int kBtASlots = 4;   // expanded-tile slots with one group per item
 constexpr int kBtDoneRing = 16;    // `done` barriers; a power of two above every ring size
 constexpr int kBtMaxUnits = 592;   // split-K partial tiles the workspace holds (four per multiprocessor)
 constexpr int kBtMaxMats = 3;
@@ -215,22 +215,28 @@ struct RingPos {
     }
 };
 
-// Ring sizes and the shared-memory plan: [raw slots | digit slots | expanded slots | barriers]
-template <int NB>
+// Ring sizes and the shared-memory plan: [raw slots | digit slots | expanded slots | hand-over | barriers].  An *item* - what
+// moves through the rings and what every role handles per pass - is GP consecutive 128-column groups: 2 with 16 rows of x
+// (every role's pass costs about the same however much it carries, so two groups per pass halve the cost per byte), 1 with
+// 32 rows (tensor memory holds 512 columns: four buffers of 4 x 32).
+template <int NB, int GP>
 struct SmallShape {
-    static constexpr int kBBytes = 4 * NB * 128;           // the four digit planes of one group
-    static constexpr int kXSlots = NB == 16 ? 6 : 5;
-    static constexpr int kBufs = NB == 16 ? 8 : 4;         // accumulator buffers of 4 NB columns: 512 columns of tensor memory
+    static constexpr int kBBytes = GP * 4 * NB * 128;      // the four digit planes of the item's groups
+    static constexpr int kABytes = GP * kBtABytes;         // expanded tiles of the item
+    static constexpr int kRawBytes = GP * kBtRawBytes;     // 128 rows x 64 GP bytes of nibbles
+    static constexpr int kASlots = GP == 2 ? 3 : kBtASlots;
+    static constexpr int kXSlots = GP == 2 ? 3 : (NB == 16 ? 6 : 5);
+    static constexpr int kBufs = 512 / (GP * 4 * NB);      // accumulator buffers of GP x 4 NB columns
     static constexpr int kXchgBytes = NB * 128 * 4;        // partial rows handed from the second drain set to the first
-    static constexpr int kRawSlots = (224 * 1024 - 2048 - kBtASlots * kBtABytes - kXSlots * kBBytes - kXchgBytes) / kBtRawBytes;
-    static constexpr int kOffX = kRawSlots * kBtRawBytes;
+    static constexpr int kRawSlots = (224 * 1024 - 2048 - kASlots * kABytes - kXSlots * kBBytes - kXchgBytes) / kRawBytes;
+    static constexpr int kOffX = kRawSlots * kRawBytes;
     static constexpr int kOffA = kOffX + kXSlots * kBBytes;
-    static constexpr int kOffXchg = kOffA + kBtASlots * kBtABytes;
+    static constexpr int kOffXchg = kOffA + kASlots * kABytes;
     static constexpr int kOffBars = kOffXchg + kXchgBytes;
-    static constexpr int kNumBars = 2 * kRawSlots + kXSlots + kBtASlots + kBtDoneRing + kBufs + 3;
+    static constexpr int kNumBars = 2 * kRawSlots + kXSlots + kASlots + kBtDoneRing + kBufs + 3;
     static constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;  // + slack for the 1024-byte alignment
-    static_assert(kRawSlots >= 6 && kRawSlots < kBtDoneRing && kXSlots < kBtDoneRing && kBufs < kBtDoneRing, "ring sizes");
-    static_assert(kOffX % 1024 == 0 && kOffA % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+    static_assert(kRawSlots >= 4 && kRawSlots < kBtDoneRing && kXSlots < kBtDoneRing && kBufs < kBtDoneRing && kBufs >= 2, "ring sizes");
+    static_assert(kOffX % 1024 == 0 && kOffA % 1024 == 0 && kSmemBytes <= 227 * 1024, "swizzled tiles start on 1024-byte boundaries");
 };
 
 // The unit sequence of one block: units u = blockIdx.x, + gridDim.x, ...; unit = (row tile over all matrices, split);
@@ -249,9 +255,10 @@ struct UnitCursor {
         g1 = (int)(((long long)(z + 1) * G) / p.ksplit);
         return true;
     }
-    // next group; false when the block's work is over
-    __device__ inline bool advance(const SmallParams& p, int G) {
-        if (++g < g1) return true;
+    // next item (`step` groups on); false when the block's work is over
+    __device__ inline bool advance(const SmallParams& p, int G, int step = 1) {
+        g += step;
+        if (g < g1) return true;
         u += gridDim.x;
         return load(p, G);
     }
@@ -268,18 +275,18 @@ struct UnitCursor {
 #define PROF_W1
 #define PROF_END(role)
 #endif
-// NB = rows of x per block (16 or 32): N = 4 NB digit columns per MMA.
-// Warp roles are placed by scheduler (warp % 4): the MMA warp shares its scheduler with the two TMA warps, which sleep on
-// barriers most of the time, and two drain warps; the expanding warps, which spin and compute, sit on the other three.
-//   warp 0: MMA     warp 4: TMA digits     warp 8: TMA weights     warps 1 2 3 5 6 7 9 10: expand     warp 11: idle
-//   warps 12..19: drain (tensor-memory lanes 32 (w % 4) .., warps 12..15 the lower half of the rows of x, 16..19 the upper)
-template <int NB>
+// NB = rows of x per block (16 or 32): N = 4 NB digit columns per MMA; GP = groups per item (SmallShape).
+// Warp roles are placed by scheduler (warp % 4): an MMA warp shares its scheduler with the two TMA warps, which sleep on
+// barriers most of the time, and drain warps; the expanding warps, which spin and compute, sit on the other three.
+//   warps 0, 11: MMA     warp 4: TMA digits     warp 8: TMA weights     warps 1 2 3 5 | 6 7 9 10: the two expanding sets
+//   warps 12..15 | 16..19: the two draining sets (tensor-memory lanes 32 (w % 4) ..)
+template <int NB, int GP>
 __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const SmallParams p, const __grid_constant__ CUtensorMap map_w0,
                                                                         const __grid_constant__ CUtensorMap map_w1,
                                                                         const __grid_constant__ CUtensorMap map_w2,
                                                                         const __grid_constant__ CUtensorMap map_x) {
-    using S = SmallShape<NB>;
-    constexpr int kBBytes = S::kBBytes;
+    using S = SmallShape<NB, GP>;
+    constexpr int kGroupB = 4 * NB * 128;  // digit planes of one group
     constexpr int kN = 4 * NB;
     constexpr uint32_t kTmemCols = 512;
     extern __shared__ unsigned char ssmem_raw[];
@@ -287,8 +294,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
     uint64_t* raw_full = reinterpret_cast<uint64_t*>(ssmem + S::kOffBars);  // [kRawSlots] the raw weight tile has landed
     uint64_t* raw_free = raw_full + S::kRawSlots;   // [kRawSlots] the expanding warps have read it
     uint64_t* x_full = raw_free + S::kRawSlots;     // [kXSlots] the digit planes have landed
-    uint64_t* a_ready = x_full + S::kXSlots;        // [kBtASlots] the signed-byte tile is written and everything else the MMAs need is there
-    uint64_t* done = a_ready + kBtASlots;           // [kBtDoneRing] the MMAs of group number n (n % 16 here) have completed
+    uint64_t* a_ready = x_full + S::kXSlots;        // [kASlots] the signed-byte tiles of an item are written
+    uint64_t* done = a_ready + S::kASlots;          // [kBtDoneRing] the MMAs of item number n (n % 16 here) have completed
     uint64_t* tmem_free = done + kBtDoneRing;       // [kBufs] the drain warps have read the buffer
     uint64_t* drain_bar = tmem_free + S::kBufs;     // meeting point of the first drain set (split-K hand-off)
     uint64_t* xchg_full = drain_bar + 1;            // the second drain set has written its partial rows of a unit
@@ -297,12 +304,12 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
     uint32_t* last_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int G = p.K >> 7;  // groups = k-tiles
+    const int G = p.K >> 7;  // 128-column groups
 
     if (tid == 0) {
         for (int s = 0; s < S::kRawSlots; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_free[s], kBtSetWarps); }
         for (int s = 0; s < S::kXSlots; ++s) mbar_init(&x_full[s], 1);
-        for (int s = 0; s < kBtASlots; ++s) mbar_init(&a_ready[s], kBtSetWarps);
+        for (int s = 0; s < S::kASlots; ++s) mbar_init(&a_ready[s], kBtSetWarps);
         for (int s = 0; s < kBtDoneRing; ++s) mbar_init(&done[s], 1);
         for (int b = 0; b < S::kBufs; ++b) mbar_init(&tmem_free[b], kBtSetWarps);
         mbar_init(drain_bar, kBtSetWarps);
@@ -320,7 +327,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t smem_base = smem_u32(ssmem);
     bool ok = true;
-    // the `done` barrier and parity that report the completion of group number n of this block
+    // the `done` barrier and parity that report the completion of item number n of this block
     auto done_wait = [&](int n) { return mbar_wait<false>(&done[n & (kBtDoneRing - 1)], (uint32_t)(n >> 4) & 1u); };
     static_assert(kBtDoneRing == 16, "done_wait shifts by 4");
     const bool expander = warp < 11 && (warp & 3) != 0;  // warps 1 2 3 5 6 7 9 10
@@ -328,7 +335,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
 
     if (warp == 8) {
         // ---- TMA of the raw weight tiles.  The weights never change, so these copies start at once, whatever the previous
-        // kernel is still doing.
+        // kernel is still doing.  With two groups per item the box is 128 bytes wide (128-byte swizzle, which the expanding
+        // warps undo when they read); a box that reaches past the unit or past K brings bytes nobody uses, or zeros.
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
             RingPos<S::kRawSlots> rp;
             PROF_DECL;
@@ -338,14 +346,14 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                 PROF_W1;
                 const int mi = (p.nmat > 2 && cur.tile >= p.mat[2].tile_start) ? 2 : (p.nmat > 1 && cur.tile >= p.mat[1].tile_start) ? 1 : 0;
                 const CUtensorMap* map = mi == 0 ? &map_w0 : mi == 1 ? &map_w1 : &map_w2;
-                mbar_arrive_expect_tx(&raw_full[rp.idx], (uint32_t)kBtRawBytes);
-                tma_load_2d(smem_base + (uint32_t)rp.idx * kBtRawBytes, map, cur.g * 64, (cur.tile - p.mat[mi].tile_start) * 128, &raw_full[rp.idx]);
+                mbar_arrive_expect_tx(&raw_full[rp.idx], (uint32_t)S::kRawBytes);
+                tma_load_2d(smem_base + (uint32_t)rp.idx * S::kRawBytes, map, cur.g * 64, (cur.tile - p.mat[mi].tile_start) * 128, &raw_full[rp.idx]);
                 rp.next();
-            } while (cur.advance(p, G));
+            } while (cur.advance(p, G, GP));
             PROF_END(0);
         }
     } else if (warp == 4) {
-        // ---- TMA of the digit planes: they come from the previous kernel; a slot is free when the group that used it
+        // ---- TMA of the digit planes: they come from the previous kernel; a slot is free when the item that used it
         // last (kXSlots back) has been multiplied
         pdl_wait();
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
@@ -356,22 +364,24 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                 PROF_W0;
                 if (it >= S::kXSlots && !done_wait(it - S::kXSlots)) { ok = false; break; }
                 PROF_W1;
-                mbar_arrive_expect_tx(&x_full[xp.idx], (uint32_t)kBBytes);
-                tma_load_3d(smem_base + S::kOffX + (uint32_t)xp.idx * kBBytes, &map_x, cur.g * 128, 0, 0, &x_full[xp.idx]);
+                mbar_arrive_expect_tx(&x_full[xp.idx], (uint32_t)S::kBBytes);
+#pragma unroll
+                for (int j = 0; j < GP; ++j)
+                    tma_load_3d(smem_base + S::kOffX + (uint32_t)xp.idx * S::kBBytes + j * kGroupB, &map_x, (cur.g + j) * 128, 0, 0, &x_full[xp.idx]);
                 xp.next();
                 ++it;
-            } while (cur.advance(p, G));
+            } while (cur.advance(p, G, GP));
             PROF_END(1);
         }
     } else if (warp == 0 || warp == 11) {
-        // ---- MMA issuers: one thread of each of two warps, alternate groups (their accumulators are different buffers, so
-        // no order is needed between them).  Per group: the stage is expanded, its digit planes have landed, its accumulator
-        // buffer has been read out; four MMAs; one commit.
+        // ---- MMA issuers: one thread of each of two warps, alternate items (their accumulators are different buffers, so
+        // no order is needed between them).  Per item: the tiles are expanded, the digit planes have landed, the accumulator
+        // buffer has been read out; four MMAs per group; one commit.
         const int set = warp == 0 ? 0 : 1;
         if (lane == 0 && cur.start(p, blockIdx.x, G)) {
             constexpr uint32_t idesc = gemm_idesc_s8s8(128, kN);
             const uint64_t desc_a0 = gemm_smem_desc(smem_base + S::kOffA), desc_b0 = gemm_smem_desc(smem_base + S::kOffX);
-            RingPos<kBtASlots> ap;
+            RingPos<S::kASlots> ap;
             RingPos<S::kXSlots> xp;
             RingPos<S::kBufs> bp;
             int it = 0;
@@ -386,52 +396,79 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                     }
                     PROF_W1;
                     tcgen05_fence_after();
-                    const uint64_t da = desc_a0 + (uint64_t)((uint32_t)ap.idx * (kBtABytes >> 4));
-                    const uint64_t db = desc_b0 + (uint64_t)((uint32_t)xp.idx * (kBBytes >> 4));
-                    const uint32_t d = tmem_base + (uint32_t)(bp.idx * kN);
+                    const int ng = min(GP, cur.g1 - cur.g);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) gemm_mma_i8(d, da + 2 * ks, db + 2 * ks, idesc, ks > 0 ? 1u : 0u);
+                    for (int j = 0; j < GP; ++j) {
+                        if (j < ng) {
+                            const uint64_t da = desc_a0 + (uint64_t)((uint32_t)ap.idx * (S::kABytes >> 4) + j * (kBtABytes >> 4));
+                            const uint64_t db = desc_b0 + (uint64_t)((uint32_t)xp.idx * (S::kBBytes >> 4) + j * (kGroupB >> 4));
+                            const uint32_t d = tmem_base + (uint32_t)(bp.idx * GP * kN + j * kN);
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks) gemm_mma_i8(d, da + 2 * ks, db + 2 * ks, idesc, ks > 0 ? 1u : 0u);
+                        }
+                    }
                     umma_commit(&done[it & (kBtDoneRing - 1)]);
                 }
                 ap.next(); xp.next(); bp.next();
                 ++it;
-            } while (cur.advance(p, G));
+            } while (cur.advance(p, G, GP));
             PROF_END(2 + set);
         }
     } else if (expander) {
-        // ---- weight expansion, two sets of four warps that take the groups alternately.  A thread turns four 16-byte pieces
-        // of the raw tile (32 columns each) into signed bytes: piece id = 128 i + (thread of the set) is (row id / 4, quarter
-        // id % 4), so a warp reads 512 contiguous bytes and writes 16-byte chunks that fall on distinct banks.
+        // ---- weight expansion, two sets of four warps that take the items alternately.  A thread turns four 16-byte pieces
+        // of raw nibbles per group (32 columns each) into signed bytes.  One group per item: piece id = 128 i + (thread of
+        // the set) is (row id / 4, quarter id % 4) of the 64-byte rows - a warp reads 512 contiguous bytes.  Two groups per
+        // item: the raw rows are 128 bytes in the 128-byte swizzle, and the eight lanes of a quarter warp take eight
+        // consecutive rows at the same quarter, so that their reads and their writes fall on distinct banks.
         const int e = warp - 1 - (warp > 4 ? 1 : 0) - (warp > 8 ? 1 : 0);  // 0..7
         const int set = e >> 2;
-        const int dt = (e & 3) * 32 + lane;  // thread of the set, 0..127
+        const int wv = e & 3;
+        const int dt = wv * 32 + lane;  // thread of the set, 0..127
         if (cur.start(p, blockIdx.x, G)) {
             RingPos<S::kRawSlots> rp;
-            RingPos<kBtASlots> ap;
+            RingPos<S::kASlots> ap;
             int it = 0;
             PROF_DECL;
             do {
                 if ((it & 1) == set) {
-                    // the raw tile has landed; the expanded slot is free (its last user, kBtASlots groups back, has been multiplied)
+                    // the raw tile has landed; the expanded slot is free (its last user, kASlots items back, has been multiplied)
                     PROF_W0;
-                    if (!mbar_wait<false>(&raw_full[rp.idx], rp.phase) || (it >= kBtASlots && !done_wait(it - kBtASlots))) { ok = false; break; }
+                    if (!mbar_wait<false>(&raw_full[rp.idx], rp.phase) || (it >= S::kASlots && !done_wait(it - S::kASlots))) { ok = false; break; }
                     PROF_W1;
-                    const unsigned char* raw = ssmem + (size_t)rp.idx * kBtRawBytes;
-                    unsigned char* a = ssmem + S::kOffA + (size_t)ap.idx * kBtABytes;
-                    uint4 w[4];
+                    const unsigned char* raw = ssmem + (size_t)rp.idx * S::kRawBytes;
+                    const int ng = min(GP, cur.g1 - cur.g);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(raw + (size_t)(i * 128 + dt) * 16);
+                    for (int j = 0; j < GP; ++j) {
+                        if (j < ng) {
+                            unsigned char* a = ssmem + S::kOffA + (size_t)ap.idx * S::kABytes + (size_t)j * kBtABytes;
+                            uint4 w[4];
+                            int row[4], qt[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int id = i * 128 + dt, r = id >> 2, j = id & 3;  // row, 16-byte quarter of its 64 raw bytes
-                        const uint4 lo = make_uint4(nibble_bytes_to_s8(w[i].x, 0), nibble_bytes_to_s8(w[i].x, 4), nibble_bytes_to_s8(w[i].y, 0),
-                                                    nibble_bytes_to_s8(w[i].y, 4));
-                        const uint4 hi = make_uint4(nibble_bytes_to_s8(w[i].z, 0), nibble_bytes_to_s8(w[i].z, 4), nibble_bytes_to_s8(w[i].w, 0),
-                                                    nibble_bytes_to_s8(w[i].w, 4));
-                        *reinterpret_cast<uint4*>(a + r * 128 + (((2 * j) ^ (r & 7)) << 4)) = lo;
-                        *reinterpret_cast<uint4*>(a + r * 128 + (((2 * j + 1) ^ (r & 7)) << 4)) = hi;
+                            for (int i = 0; i < 4; ++i) {
+                                if (GP == 1) {
+                                    const int id = i * 128 + dt;
+                                    row[i] = id >> 2;
+                                    qt[i] = id & 3;
+                                    w[i] = *reinterpret_cast<const uint4*>(raw + (size_t)id * 16);
+                                } else {
+                                    row[i] = i * 32 + wv * 8 + (lane & 7);
+                                    qt[i] = lane >> 3;
+                                    w[i] = *reinterpret_cast<const uint4*>(raw + row[i] * 128 + (((4 * j + qt[i]) ^ (row[i] & 7)) << 4));
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int r = row[i];
+                                const uint4 lo = make_uint4(nibble_bytes_to_s8(w[i].x, 0), nibble_bytes_to_s8(w[i].x, 4), nibble_bytes_to_s8(w[i].y, 0),
+                                                            nibble_bytes_to_s8(w[i].y, 4));
+                                const uint4 hi = make_uint4(nibble_bytes_to_s8(w[i].z, 0), nibble_bytes_to_s8(w[i].z, 4), nibble_bytes_to_s8(w[i].w, 0),
+                                                            nibble_bytes_to_s8(w[i].w, 4));
+                                *reinterpret_cast<uint4*>(a + r * 128 + (((2 * qt[i]) ^ (r & 7)) << 4)) = lo;
+                                *reinterpret_cast<uint4*>(a + r * 128 + (((2 * qt[i] + 1) ^ (r & 7)) << 4)) = hi;
+                            }
+                        }
                     }
-                    fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+                    fence_proxy_async_smem();  // the tensor core reads the tiles through the async proxy
                     __syncwarp();
                     if (lane == 0) {
                         mbar_arrive(&raw_free[rp.idx]);
@@ -440,11 +477,11 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                 }
                 rp.next(); ap.next();
                 ++it;
-            } while (cur.advance(p, G));
+            } while (cur.advance(p, G, GP));
             if (dt == 0) PROF_END(4 + set);
         }
     } else if (warp >= 12) {
-        // ---- drain, two sets of four warps that take the groups alternately: warp w may read tensor-memory lanes
+        // ---- drain, two sets of four warps that take the items alternately: warp w may read tensor-memory lanes
         // 32 (w % 4) ..; lane = weight row inside the tile; each thread accumulates its row for all rows of x.  At the end of
         // a unit the second set hands its sums to the first through shared memory; the first set finishes the rows.
         const int q = warp & 3;
@@ -467,47 +504,63 @@ __global__ void __launch_bounds__(kBtThreads, 1) linear_gemm_small_kernel(const 
                 float acc[NB];
 #pragma unroll
                 for (int m = 0; m < NB; ++m) acc[m] = 0.0f;
-                // group scale of this row for this set's next group, requested one of its groups ahead
-                int g_mine = cur.g + (((it & 1) == set) ? 0 : 1);
-                uint32_t s_next = g_mine < cur.g1 ? __ldg(srow + g_mine) : 0u;
+                // group scales of this row for this set's next item, requested one of its items ahead
+                uint32_t s_next[GP];
+                {
+                    const int g_mine = cur.g + (((it & 1) == set) ? 0 : GP);
+#pragma unroll
+                    for (int j = 0; j < GP; ++j) s_next[j] = g_mine + j < cur.g1 ? __ldg(srow + g_mine + j) : 0u;
+                }
                 bool same_unit = true;
                 while (same_unit) {
                     if ((it & 1) == set) {
-                        const float sc = __half2float(__ushort_as_half((unsigned short)s_next));
-                        s_next = cur.g + 2 < cur.g1 ? __ldg(srow + cur.g + 2) : 0u;
+                        float sc[GP];
+#pragma unroll
+                        for (int j = 0; j < GP; ++j) {
+                            sc[j] = __half2float(__ushort_as_half((unsigned short)s_next[j]));
+                            s_next[j] = cur.g + 2 * GP + j < cur.g1 ? __ldg(srow + cur.g + 2 * GP + j) : 0u;
+                        }
                         PROF_W0;
                         if (!done_wait(it)) { ok = false; break; }
                         PROF_W1;
                         tcgen05_fence_after();
-                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(bp.idx * kN);
+                        const int ng = min(GP, cur.g1 - cur.g);
+                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(bp.idx * GP * kN);
 #pragma unroll
-                        for (int m0 = 0; m0 < NB; m0 += 8) {
-                            uint32_t d0[8], d1[8], d2[8], d3[8];
-                            tmem_ld8(taddr + m0, d0);
-                            tmem_ld8(taddr + NB + m0, d1);
-                            tmem_ld8(taddr + 2 * NB + m0, d2);
-                            tmem_ld8(taddr + 3 * NB + m0, d3);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            if (m0 + 8 >= NB) {  // everything of this buffer is in registers: hand it back
-                                tcgen05_fence_before();
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(&tmem_free[bp.idx]);
-                            }
-                            // |D_i| <= 128 * 8 * 128 = 2^17: the integer added to the bits of 1.5 * 2^23 is that float plus the integer
-                            const float kMagic = 12582912.0f;
+                        for (int j = 0; j < GP; ++j) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float f0 = __uint_as_float(0x4b400000u + d0[j]) - kMagic, f1 = __uint_as_float(0x4b400000u + d1[j]) - kMagic;
-                                const float f2 = __uint_as_float(0x4b400000u + d2[j]) - kMagic, f3 = __uint_as_float(0x4b400000u + d3[j]) - kMagic;
-                                const float t = fmaf(fmaf(fmaf(f3, 256.0f, f2), 256.0f, f1), 256.0f, f0);
-                                acc[m0 + j] = fmaf(t, sc, acc[m0 + j]);
+                            for (int m0 = 0; m0 < NB; m0 += 8) {
+                                uint32_t d0[8], d1[8], d2[8], d3[8];
+                                if (j < ng) {
+                                    tmem_ld8(taddr + j * kN + m0, d0);
+                                    tmem_ld8(taddr + j * kN + NB + m0, d1);
+                                    tmem_ld8(taddr + j * kN + 2 * NB + m0, d2);
+                                    tmem_ld8(taddr + j * kN + 3 * NB + m0, d3);
+                                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                                }
+                                if (j == GP - 1 && m0 + 8 >= NB) {  // everything of this buffer is in registers: hand it back
+                                    tcgen05_fence_before();
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(&tmem_free[bp.idx]);
+                                }
+                                if (j < ng) {
+                                    // |D_i| <= 128 * 8 * 128 = 2^17: the integer added to the bits of 1.5 * 2^23 is that float plus the integer
+                                    const float kMagic = 12582912.0f;
+#pragma unroll
+                                    for (int t8 = 0; t8 < 8; ++t8) {
+                                        const float f0 = __uint_as_float(0x4b400000u + d0[t8]) - kMagic, f1 = __uint_as_float(0x4b400000u + d1[t8]) - kMagic;
+                                        const float f2 = __uint_as_float(0x4b400000u + d2[t8]) - kMagic, f3 = __uint_as_float(0x4b400000u + d3[t8]) - kMagic;
+                                        const float t = fmaf(fmaf(fmaf(f3, 256.0f, f2), 256.0f, f1), 256.0f, f0);
+                                        acc[m0 + t8] = fmaf(t, sc[j], acc[m0 + t8]);
+                                    }
+                                }
                             }
                         }
                     }
                     bp.next();
                     ++it;
                     const int u_before = cur.u;
-                    more = cur.advance(p, G);
+                    more = cur.advance(p, G, GP);
                     same_unit = more && cur.u == u_before;
                 }
                 if (!ok) break;
