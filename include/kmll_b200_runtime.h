@@ -44,7 +44,9 @@ enum {
     KMLL_T_W2 = 8,             /* down [dim, hidden_dim] */
     KMLL_T_FINAL_NORM = 9,     /* bf16 [dim]            (layer = -1) */
     KMLL_T_EMBEDDING = 10,     /* bf16 [vocab, dim]     (layer = -1) */
-    KMLL_T_OUTPUT = 11         /* lm_head [vocab, dim]  (layer = -1) */
+    KMLL_T_OUTPUT = 11,        /* lm_head [vocab, dim]  (layer = -1) */
+    KMLL_T_Q_NORM = 12,        /* optional, bf16 [head_dim]: per-head RMSNorm of the query rows before RoPE (model.rs:10165-10194); */
+    KMLL_T_K_NORM = 13         /* same for the key rows.  Set them before the first decode step; a model without them sets neither. */
 };
 
 /* TextConfig of kmll (crates/inference/src/model.rs:271-366) reduced to what the decoder path uses. */

@@ -319,8 +319,9 @@ def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = TextConfig.from_config_json(f.read())
     weights = ModelWeights(model_dir)
-    if weights.tensor_opt("layers.0.attention.q_norm.weight") is not None or weights.tensor_opt("layers.0.attention.k_norm.weight") is not None:
-        raise CheckpointError("checkpoints with per-head q/k RMSNorm are not supported by this decoder")
+    qk_norm = weights.tensor_opt("layers.0.attention.q_norm.weight") is not None
+    if qk_norm != (weights.tensor_opt("layers.0.attention.k_norm.weight") is not None):
+        raise CheckpointError("a checkpoint must carry both q_norm and k_norm or neither")
     dcfg = rt.DecoderConfig(n_layers=cfg.n_layers, dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
                             hidden_dim=cfg.hidden_dim, vocab_size=cfg.vocab_size, rope_theta=cfg.rope_theta, norm_eps=cfg.norm_eps,
                             max_seq_len=max_seq_len or cfg.max_position_embeddings, rotary_dim=cfg.rotary_dim, format=fmt, fused=fused)
@@ -350,6 +351,9 @@ def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused
         p = f"layers.{l}."
         dec.set_tensor(l, rt.T_ATTENTION_NORM, bf16(p + "attention_norm.weight", (cfg.dim,)))
         dec.set_tensor(l, rt.T_FFN_NORM, bf16(p + "ffn_norm.weight", (cfg.dim,)))
+        if qk_norm:  # per-head RMSNorm of query and key rows before RoPE (model.rs:10165-10194)
+            dec.set_tensor(l, rt.T_Q_NORM, bf16(p + "attention.q_norm.weight", (cfg.head_dim,)))
+            dec.set_tensor(l, rt.T_K_NORM, bf16(p + "attention.k_norm.weight", (cfg.head_dim,)))
         linear(l, rt.T_WQ, p + "attention.wq.weight", (q, cfg.dim))
         linear(l, rt.T_WK, p + "attention.wk.weight", (kv, cfg.dim))
         linear(l, rt.T_WV, p + "attention.wv.weight", (kv, cfg.dim))

@@ -196,6 +196,39 @@ __global__ void prepare_incremental_kernel(const float* __restrict__ q, const fl
 }
 
 // prepare_prefill_attention_batch (crates/inference/src/kernels/inference.rs:896-949): row = position
+// Per-head RMSNorm of query and key rows in place (rmsnorm_batched_bf16 over [n_heads, head_dim] with one [head_dim]
+// weight, before RoPE: crates/inference/src/model.rs:10165-10194).  One warp per (row, head); q heads first, then k heads.
+__global__ void __launch_bounds__(256) qk_head_rmsnorm_kernel(float* q, float* k, const uint16_t* __restrict__ q_w, const uint16_t* __restrict__ k_w,
+                                                              int rows, int n_heads, int n_kv_heads, int head_dim, float eps, size_t q_stride,
+                                                              size_t k_stride) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int per_row = n_heads + n_kv_heads;
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (long long)rows * per_row) return;
+    const int row = (int)(item / per_row), hh = (int)(item - (long long)row * per_row);
+    const bool is_q = hh < n_heads;
+    const uint16_t* w = is_q ? q_w : k_w;
+    if (w == nullptr) return;
+    float* x = is_q ? q + (size_t)row * q_stride + (size_t)hh * head_dim : k + (size_t)row * k_stride + (size_t)(hh - n_heads) * head_dim;
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < head_dim ? x[i] : 0.0f;
+        ss += v[j] * v[j];
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = lane + 32 * j;
+        if (i < head_dim) x[i] = v[j] * inv * __uint_as_float((uint32_t)w[i] << 16);
+    }
+}
+
 __global__ void prepare_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k,
                                        const float* __restrict__ v, const float* __restrict__ freqs, int half,
                                        int prompt_len, int q_len, int kv_len, int head_dim, int position0,
@@ -434,6 +467,17 @@ int prepare_incremental_dyn(cudaStream_t stream, const float* q, const float* k,
     cudaError_t e = launch(prepare_incremental_dyn_kernel, dim3((width + 255) / 256), dim3(256), 0, stream, true, q, k, v,
                            freqs, n_freqs, state, q_len, kv_len, head_dim, q_rot, k_cache, v_cache);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prepare_incremental_dyn: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int qk_head_rmsnorm(cudaStream_t stream, float* q, float* k, const uint16_t* q_w, const uint16_t* k_w, int rows, int n_heads, int n_kv_heads,
+                    int head_dim, float eps, size_t q_stride, size_t k_stride) {
+    if (q_w == nullptr && k_w == nullptr) return KMLL_OK;
+    if (head_dim > 256) return fail(KMLL_ERR_UNSUPPORTED, "q/k RMSNorm: head_dim %d above 256", head_dim);
+    const long long items = (long long)rows * (n_heads + n_kv_heads);
+    cudaError_t e = launch(qk_head_rmsnorm_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, stream, true, q, k, q_w, k_w, rows, n_heads,
+                           n_kv_heads, head_dim, eps, q_stride, k_stride);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "qk_head_rmsnorm: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }
 

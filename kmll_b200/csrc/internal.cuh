@@ -154,6 +154,8 @@ size_t decode_attention_workspace_floats(int n_heads, int head_dim, int seq_cap)
 int prepare_incremental_dyn(cudaStream_t stream, const float* q, const float* k, const float* v, const float* freqs,
                             int n_freqs, const DecodeState* state, int max_seq_len, int n_heads, int n_kv_heads,
                             int head_dim, float* q_rot, float* k_cache, float* v_cache);
+int qk_head_rmsnorm(cudaStream_t stream, float* q, float* k, const uint16_t* q_w, const uint16_t* k_w, int rows, int n_heads, int n_kv_heads,
+                    int head_dim, float eps, size_t q_stride, size_t k_stride);
 int prepare_prefill_offset(cudaStream_t stream, const float* q, const float* k, const float* v, const float* freqs,
                            int n_freqs, int rows, int q_len, int kv_len, int head_dim, int position0, float* q_rot,
                            float* k_cache, float* v_cache);

@@ -68,6 +68,8 @@ struct QWeight {
 
 struct Layer {
     uint16_t* attention_norm = nullptr;
+    uint16_t* q_norm = nullptr;  // optional per-head RMSNorm weights [head_dim] of the query / key rows (null: the model has none)
+    uint16_t* k_norm = nullptr;
     uint16_t* ffn_norm = nullptr;
     QWeight wq, wk, wv, wo, w1, w3, w2;
     uint8_t* w13_prep = nullptr;  // W4-G128: gate (w1) and up (w3) interleaved in the prepared layout
@@ -205,6 +207,14 @@ static int op_linear_batched(Decoder* d, cudaStream_t s, const float* x, const Q
     return kmll_linear_batched_i8(s, x, (const int8_t*)w.w, (const float*)w.scales, batch, w.cols, w.rows, workspace, y);
 }
 
+// Per-head q/k RMSNorm between the projections and RoPE (crates/inference/src/model.rs:10165-10194); nothing is launched for
+// a model without these weights.
+static int apply_qk_norm(Decoder* d, cudaStream_t s, const Layer& L, float* q, float* k, int rows) {
+    const kmll_decoder_config& c = d->cfg;
+    return qk_head_rmsnorm(s, q, k, L.q_norm, L.k_norm, rows, d->n_heads_l, d->n_kv_l, c.head_dim, c.norm_eps, (size_t)d->n_heads_l * c.head_dim,
+                           (size_t)d->n_kv_l * c.head_dim);
+}
+
 // Row-parallel projection followed by the residual add; under tensor parallelism rank 0 adds the
 // residual in its epilogue and the partial sums meet in an all-reduce.
 // With push_index >= 0 the partial vector goes to every rank's inbox instead (peer-memory exchange) and the kernel
@@ -279,6 +289,7 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
                                                    (const float*)L.wv.scales, q_len, kv_len, c.dim, d->q, d->k, d->v));
         }
         ++n;
+        if (L.q_norm != nullptr || L.k_norm != nullptr) { KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1)); ++n; }
         if (c.rotary_dim == c.head_dim) {
             // RoPE of q and of the new K row and the KV-cache write happen inside the attention kernel
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
@@ -425,6 +436,7 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
     }
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = d->layers[l];
+        KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1));
         if (c.rotary_dim == c.head_dim) {
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache));
@@ -565,6 +577,7 @@ static int enqueue_step_unfused(Decoder* d, cudaStream_t s, uint32_t token, int 
         KMLL_TRY(op_linear(d, s, d->normed, L.wq, d->q));
         KMLL_TRY(op_linear(d, s, d->normed, L.wk, d->k));
         KMLL_TRY(op_linear(d, s, d->normed, L.wv, d->v));
+        KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1));
         KMLL_TRY(kmll_apply_rope(s, d->q, d->freqs, nf, position, c.head_dim, (size_t)q_len, d->q_rot));
         KMLL_TRY(kmll_apply_rope(s, d->k, d->freqs, nf, position, c.head_dim, (size_t)kv_len, d->k_rot));
         KMLL_TRY(kmll_write_kv_cache(s, d->k_rot, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.key_cache));
@@ -680,7 +693,7 @@ static int tensor_ref(Decoder* d, int layer, int tensor, TensorRef* out) {
     const kmll_decoder_config& c = d->cfg;
     TensorRef t;
     const int q_full = c.n_heads * c.head_dim, kv_full = c.n_kv_heads * c.head_dim;
-    if (tensor >= KMLL_T_FINAL_NORM) {
+    if (tensor >= KMLL_T_FINAL_NORM && tensor <= KMLL_T_OUTPUT) {
         if (layer != -1) return fail(KMLL_ERR_SHAPE, "tensor %d is not a per-layer tensor (use layer = -1)", tensor);
         if (tensor == KMLL_T_FINAL_NORM) { t.bf16 = &d->final_norm; t.bf16_count = c.dim; }
         else if (tensor == KMLL_T_EMBEDDING) { t.bf16 = &d->embedding; t.bf16_count = (size_t)c.vocab_size * c.dim; }
@@ -692,6 +705,8 @@ static int tensor_ref(Decoder* d, int layer, int tensor, TensorRef* out) {
         switch (tensor) {
             case KMLL_T_ATTENTION_NORM: t.bf16 = &L.attention_norm; t.bf16_count = c.dim; break;
             case KMLL_T_FFN_NORM: t.bf16 = &L.ffn_norm; t.bf16_count = c.dim; break;
+            case KMLL_T_Q_NORM: t.bf16 = &L.q_norm; t.bf16_count = c.head_dim; break;
+            case KMLL_T_K_NORM: t.bf16 = &L.k_norm; t.bf16_count = c.head_dim; break;
             case KMLL_T_WQ: t.q = &L.wq; t.full_rows = q_full; t.full_cols = c.dim; t.kind = SHARD_ROWS; break;
             case KMLL_T_WK: t.q = &L.wk; t.full_rows = kv_full; t.full_cols = c.dim; t.kind = SHARD_ROWS; break;
             case KMLL_T_WV: t.q = &L.wv; t.full_rows = kv_full; t.full_cols = c.dim; t.kind = SHARD_ROWS; break;
@@ -765,6 +780,7 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
             float* outs[3] = {b->q, b->k, b->v};
             KMLL_TRY(linear_batched_form(0, s, c.format, hidden, B, L.attention_norm, c.norm_eps, w, sc, rows, c.dim, outs, nullptr, b->linear_ws));
         }
+        KMLL_TRY(apply_qk_norm(d, s, L, b->q, b->k, B));
         KMLL_TRY(decode_attention_launch(s, b->q, b->key_cache[l], b->value_cache[l], &b->state->seq_len, 0, c.max_seq_len, c.n_heads,
                                          c.n_kv_heads, c.head_dim, b->attn_ws, b->attn, b->k, b->v, d->freqs, b->key_cache[l],
                                          b->value_cache[l], B, b->cache_stride));
@@ -1108,6 +1124,10 @@ int kmll_decoder_set_tensor(kmll_decoder_t dec, int layer, int tensor, const voi
     TensorRef t;
     KMLL_TRY(tensor_ref(d, layer, tensor, &t));
     if (t.bf16 != nullptr) {
+        if (*t.bf16 == nullptr) {  // an optional tensor (q / k norm) seen for the first time: the step gains a launch
+            if (d->graph != nullptr) return fail(KMLL_ERR_STATE, "set_tensor: optional tensors must be set before the first decode step");
+            KMLL_TRY(dalloc(d, t.bf16, t.bf16_count));
+        }
         KMLL_CUDA(cudaMemcpy(*t.bf16, values, t.bf16_count * 2, cudaMemcpyHostToDevice));
         d->weights_set = true;
         return KMLL_OK;
@@ -1137,6 +1157,7 @@ int kmll_decoder_get_tensor(kmll_decoder_t dec, int layer, int tensor, void* val
     KMLL_TRY(tensor_ref(d, layer, tensor, &t));
     KMLL_CUDA(cudaDeviceSynchronize());
     if (t.bf16 != nullptr) {
+        if (*t.bf16 == nullptr) return fail(KMLL_ERR_STATE, "get_tensor: the model has no tensor %d in layer %d", tensor, layer);
         if (values) KMLL_CUDA(cudaMemcpy(values, *t.bf16, t.bf16_count * 2, cudaMemcpyDeviceToHost));
         return KMLL_OK;
     }
@@ -1263,6 +1284,7 @@ int kmll_decoder_prefill(kmll_decoder_t dec, kmll_stream_t stream, const uint32_
                                                     (const float*)L.wk.scales, (const int8_t*)L.wv.w, (const float*)L.wv.scales, n, c.dim,
                                                     q_len, kv_len, ws, qb, kb, vb));
             }
+            KMLL_TRY(apply_qk_norm(d, s, L, qb, kb, n));
             KMLL_TRY(prepare_prefill_offset(s, qb, kb, vb, d->freqs, c.rotary_dim / 2, n, q_len, kv_len, c.head_dim, 0, qrb, L.key_cache,
                                             L.value_cache));
             KMLL_TRY(kmll_prefill_causal_attention(s, qrb, L.key_cache, L.value_cache, n, c.max_seq_len, d->n_heads_l, d->n_kv_l, c.head_dim, ab));

@@ -17,7 +17,7 @@ from .lib import KmllError, check, load
 FORMAT_RS_I8 = 0
 FORMAT_W4G128 = 1
 
-T_ATTENTION_NORM, T_WQ, T_WK, T_WV, T_WO, T_FFN_NORM, T_W1, T_W3, T_W2, T_FINAL_NORM, T_EMBEDDING, T_OUTPUT = range(12)
+T_ATTENTION_NORM, T_WQ, T_WK, T_WV, T_WO, T_FFN_NORM, T_W1, T_W3, T_W2, T_FINAL_NORM, T_EMBEDDING, T_OUTPUT, T_Q_NORM, T_K_NORM = range(14)
 
 
 class _Config(C.Structure):
@@ -115,8 +115,8 @@ class Decoder:
     def get_tensor(self, layer: int, tensor: int):
         """This rank's shard: bf16 bits (uint16) for norms/embedding, else (values, scales) numpy arrays."""
         cfg = self.cfg
-        if tensor in (T_ATTENTION_NORM, T_FFN_NORM, T_FINAL_NORM, T_EMBEDDING):
-            n = cfg.vocab_size * cfg.dim if tensor == T_EMBEDDING else cfg.dim
+        if tensor in (T_ATTENTION_NORM, T_FFN_NORM, T_FINAL_NORM, T_EMBEDDING, T_Q_NORM, T_K_NORM):
+            n = cfg.vocab_size * cfg.dim if tensor == T_EMBEDDING else cfg.head_dim if tensor in (T_Q_NORM, T_K_NORM) else cfg.dim
             out = np.empty(n, dtype=np.uint16)
             check(self._lib.kmll_decoder_get_tensor(self._h, layer, tensor, out.ctypes.data, None))
             return out.reshape(-1, cfg.dim) if tensor == T_EMBEDDING else out

@@ -20,6 +20,12 @@ class OracleDecoder:
             self.layers.append({name: g(l, tid) for name, tid in (("attention_norm", rt.T_ATTENTION_NORM), ("wq", rt.T_WQ), ("wk", rt.T_WK),
                                                                    ("wv", rt.T_WV), ("wo", rt.T_WO), ("ffn_norm", rt.T_FFN_NORM),
                                                                    ("w1", rt.T_W1), ("w3", rt.T_W3), ("w2", rt.T_W2))})
+        self.qk_norm = []
+        for l in range(cfg.n_layers):
+            try:
+                self.qk_norm.append((g(l, rt.T_Q_NORM), g(l, rt.T_K_NORM)))
+            except rt.KmllError:
+                self.qk_norm.append(None)
         self.final_norm = g(-1, rt.T_FINAL_NORM)
         self.embedding = g(-1, rt.T_EMBEDDING)
         self.output = g(-1, rt.T_OUTPUT)
@@ -40,6 +46,10 @@ class OracleDecoder:
         for l, L in enumerate(self.layers):
             normed = oracle.rmsnorm(hidden, L["attention_norm"], c.norm_eps)
             q, k, v = self.matvec(L["wq"], normed), self.matvec(L["wk"], normed), self.matvec(L["wv"], normed)
+            if self.qk_norm[l] is not None:  # per-head RMSNorm before RoPE (model.rs:10165-10194)
+                hd = c.head_dim
+                q = np.concatenate([oracle.rmsnorm(q[h * hd:(h + 1) * hd], self.qk_norm[l][0], c.norm_eps) for h in range(c.n_heads)])
+                k = np.concatenate([oracle.rmsnorm(k[h * hd:(h + 1) * hd], self.qk_norm[l][1], c.norm_eps) for h in range(c.n_kv_heads)])
             q_rot = oracle.apply_rope(q, self.freqs, pos, c.head_dim)
             self.key[l][pos] = oracle.apply_rope(k, self.freqs, pos, c.head_dim)
             self.value[l][pos] = v

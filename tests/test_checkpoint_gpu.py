@@ -43,6 +43,8 @@ def make_checkpoint(tmp_path, yarn=True, tied=False, with_qk_norm=False):
         t[p + "mlp.down_proj.weight"] = bf16(256, 512)
         if with_qk_norm:
             t[p + "self_attn.q_norm.weight"] = bf16(64, std=0.1, mean=1.0)
+            if with_qk_norm != "q only":
+                t[p + "self_attn.k_norm.weight"] = bf16(64, std=0.1, mean=1.0)
     names = list(t)
     shards = {"model-00001-of-00002.safetensors": names[: len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
     for shard, keys in shards.items():
@@ -96,6 +98,37 @@ def test_tied_embeddings_and_refusals(cuda, tmp_path):
     dec.close()
     b = tmp_path / "qk"
     b.mkdir()
-    make_checkpoint(b, with_qk_norm=True)
+    make_checkpoint(b, with_qk_norm="q only")
     with pytest.raises(CheckpointError):
         load_decoder(str(b), rt.FORMAT_W4G128, max_seq_len=32)
+
+
+@pytest.mark.parametrize("fmt,fused", [(rt.FORMAT_W4G128, True), (rt.FORMAT_RS_I8, True), (rt.FORMAT_W4G128, False)])
+def test_checkpoint_with_qk_norm_decodes_like_the_oracle(cuda, tmp_path, fmt, fused):
+    """Per-head RMSNorm of the query and key rows before RoPE (Qwen3-style checkpoints): batched prefill, the graph step
+    (fused and kmll's operator order) and the lockstep batch all agree with the oracle model."""
+    t = make_checkpoint(tmp_path, yarn=False, with_qk_norm=True)
+    dec, cfg = load_decoder(str(tmp_path), fmt, max_seq_len=64, fused=fused)
+    assert np.array_equal(dec.get_tensor(1, rt.T_K_NORM), t["model.layers.1.self_attn.k_norm.weight"])
+    ora = OracleDecoder(dec.cfg, dec)
+    assert ora.qk_norm[0] is not None
+    prompt = np.random.default_rng(6).integers(0, 640, 11)
+    logits = ora.prefill(prompt)
+    dec.prefill(prompt)
+    hid = dec.last_hidden()
+    assert np.max(np.abs(hid - ora.hidden)) <= 2e-4 * max(float(np.max(np.abs(ora.hidden))), 1.0)
+    steps, _ = ora.generate_greedy(logits, 6)
+    tokens, glogits = dec.generate_greedy(6)
+    for i, (tok, logit, margin) in enumerate(steps):
+        if margin < 1e-3:
+            break
+        assert int(tokens[i]) == tok and abs(float(glogits[i]) - logit) <= 1e-3 * max(abs(logit), 1.0)
+    if fused:  # the lockstep batch takes the same tokens
+        dec.prefill(prompt)
+        bd = rt.BatchDecoder(dec, 3)
+        for slot in range(3):
+            bd.adopt(slot)
+        btok, _ = bd.generate_greedy(6)
+        assert all(btok[slot].tolist() == [int(v) for v in tokens] for slot in range(3))
+        bd.close()
+    dec.close()
