@@ -160,8 +160,8 @@ class CpuModel:
         return o.unpack_top1(o.top1_packed(o.w4_matvec(*self.head, o.rmsnorm(h, self.gamma, 1e-5))))[0]
 
 
-def cpu_sample(steps: int, warmup: int, threads: int, budget_s: float):
-    """Whole decode steps on the host.  The number of timed steps is cut so that the run stays near budget_s."""
+def cpu_sample(steps: int, warmup: int, threads: int, limit_s: float):
+    """Whole decode steps on the host.  The number of timed steps is cut so that the run stays near limit_s."""
     import oracle
     oracle.set_threads(threads)
     cores = oracle.max_threads()
@@ -171,10 +171,10 @@ def cpu_sample(steps: int, warmup: int, threads: int, budget_s: float):
     token = model.step(token, pos)
     pos += 1
     first = time.perf_counter() - t0
-    for _ in range(max(0, min(warmup - 1, int(budget_s / 4 / max(first, 1e-3))))):
+    for _ in range(max(0, min(warmup - 1, int(limit_s / 4 / max(first, 1e-3))))):
         token = model.step(token, pos)
         pos += 1
-    run = max(1, min(steps, int(budget_s / max(first, 1e-3))))
+    run = max(1, min(steps, int(limit_s / max(first, 1e-3))))
     t0 = time.perf_counter()
     for _ in range(run):
         token = model.step(token, pos)
