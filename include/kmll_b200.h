@@ -120,6 +120,14 @@ int kmll_linear_triple_w4g128(kmll_stream_t stream, const float* x, const uint8_
                               const uint8_t* wv, const uint16_t* sv, int q_rows, int kv_rows,
                               int cols, float* q, float* k, float* v);
 
+/* a, b = Wa.x, Wb.x in one launch, two matrices of the same shape — linear_pair_bf16,
+ * crates/inference/src/ops/inference.rs:712-775 (kernel matvec_pair, crates/inference/src/kernels/inference.rs:458-532). */
+int kmll_linear_pair_i8(kmll_stream_t stream, const float* x, const int8_t* wa, const float* sa, const int8_t* wb,
+                        const float* sb, int rows, int cols, float* out_a, float* out_b);
+int kmll_linear_pair_w4g128(kmll_stream_t stream, const float* x, const uint8_t* wa, const uint16_t* sa,
+                            const uint8_t* wb, const uint16_t* sb, int rows, int cols, float* out_a,
+                            float* out_b);
+
 /* out = silu(Wgate.x) * (Wup.x) — silu_gate_up_bf16, crates/inference/src/ops/inference.rs:777-869. */
 int kmll_silu_gate_up_i8(kmll_stream_t stream, const float* x, const int8_t* w_gate,
                          const float* s_gate, const int8_t* w_up, const float* s_up, int rows,

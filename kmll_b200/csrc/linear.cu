@@ -1495,6 +1495,16 @@ int kmll_linear_triple_w4g128(kmll_stream_t s, const float* x, const uint8_t* wq
     MatArg m[3] = {{wq, sq, q_rows, q, nullptr}, {wk, sk, kv_rows, k, nullptr}, {wv, sv, kv_rows, v, nullptr}};
     return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 3, 0, nullptr, nullptr);
 }
+int kmll_linear_pair_i8(kmll_stream_t s, const float* x, const int8_t* wa, const float* sa, const int8_t* wb, const float* sb, int rows,
+                        int cols, float* out_a, float* out_b) {
+    MatArg m[2] = {{wa, sa, rows, out_a, nullptr}, {wb, sb, rows, out_b, nullptr}};
+    return run_linear<FMT_I8, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 2, 0, nullptr, nullptr);
+}
+int kmll_linear_pair_w4g128(kmll_stream_t s, const float* x, const uint8_t* wa, const uint16_t* sa, const uint8_t* wb, const uint16_t* sb,
+                            int rows, int cols, float* out_a, float* out_b) {
+    MatArg m[2] = {{wa, sa, rows, out_a, nullptr}, {wb, sb, rows, out_b, nullptr}};
+    return run_linear<FMT_W4, EPI_STORE>(__func__, as_stream(s), x, 1, cols, cols, nullptr, 0.f, m, 2, 0, nullptr, nullptr);
+}
 int kmll_rmsnorm_linear_triple_i8(kmll_stream_t s, const float* x, const uint16_t* nw, float eps, const int8_t* wq,
                                   const float* sq, const int8_t* wk, const float* sk, const int8_t* wv, const float* sv,
                                   int q_rows, int kv_rows, int cols, float* q, float* k, float* v) {

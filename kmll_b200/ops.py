@@ -223,6 +223,20 @@ def linear_triple(x, wq: Weight, wk: Weight, wv: Weight, norm_weight=None, eps: 
     return q, k, v
 
 
+def linear_pair(x, wa: Weight, wb: Weight):
+    """linear_pair_bf16 (ops/inference.rs:712-775) for quantized weights: two matrices of the same shape, one launch."""
+    fmt = _same_fmt(wa, wb)
+    if fmt == "w4p":
+        raise KmllError(-3, "linear pair takes canonical weights")
+    if (wa.rows, wa.cols) != (wb.rows, wb.cols) or wa.cols != x.numel():
+        raise KmllError(-2, "paired linear operand shape mismatch")
+    a = torch.empty(wa.rows, dtype=torch.float32, device=x.device)
+    b = torch.empty(wb.rows, dtype=torch.float32, device=x.device)
+    (_, pa, sa), (_, pb, sb) = _w(wa), _w(wb)
+    check(_fn("linear_pair", fmt)(_stream(), _p(_f32(x, "input")), pa, sa, pb, sb, wa.rows, wa.cols, _p(a), _p(b)))
+    return a, b
+
+
 def silu_gate_up(x, w_gate: Weight, w_up: Weight | None, norm_weight=None, eps: float = 0.0, out=None):
     """silu_gate_up_bf16 (ops/inference.rs:777-869) for quantized weights: silu(Wg.x) * (Wu.x).  A prepared gate/up pair
     (DeviceW4PMatrix.from_gate_up) is passed as w_gate with w_up = None."""

@@ -196,6 +196,12 @@ def test_fused_linear_forms(cuda, fmt):
     q, k, v = ops.linear_triple(dev(x), wq[3], wk[3], wv[3], norm_weight=bf16_dev(gamma), eps=1e-5)
     for got, w in ((q, wq), (k, wk), (v, wv)):
         assert_close(host(got), mv(*w[:3], xn), dim, "norm+triple")
+    # pair (two matrices of one shape, one launch)
+    a, b = ops.linear_pair(dev(x), wk[3], wv[3])
+    assert_close(host(a), mv(*wk[:3], x), dim, "pair a")
+    assert_close(host(b), mv(*wv[:3], x), dim, "pair b")
+    with pytest.raises(ops.KmllError):
+        ops.linear_pair(dev(x), wq[3], wk[3])
     # residual
     res = rng.normal(0, 1, qr).astype(F)
     assert_close(host(ops.linear_residual(dev(x), wq[3], dev(res))), oracle.add(res, mv(*wq[:3], x)), dim, "residual")
@@ -516,3 +522,28 @@ def test_top_k_vs_oracle(cuda):
         assert np.array_equal(host(tokens).astype(np.uint32), rt) and np.array_equal(host(values), rv)
     with pytest.raises(KmllError):
         ops.top_k_f32(dev(logits), 17)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_thread_two_devices(cuda):
+    """The shared-memory opt-in of a kernel is per device: a thread that moves to a second GPU must get the same results
+    there (the large-shared-memory kernels would fail to launch without it)."""
+    rng = np.random.default_rng(21)
+    w_host = rng.normal(0, 0.02, (512, 4096)).astype(F)
+    packed, gs = oracle.w4_quantize(w_host)
+    x = rng.normal(0, 1, 4096).astype(F)
+    ref = oracle.w4_matvec(packed, gs, x)
+    xb = rng.normal(0, 1, (16, 4096)).astype(F)
+    refb = oracle.w4_linear_batched(xb, packed, gs)
+    try:
+        for device in (0, 1, 0):
+            torch.cuda.set_device(device)
+            w = ops.DeviceW4G128Matrix(torch.from_numpy(packed).cuda(), torch.from_numpy(gs.view(np.int16)).cuda().view(torch.float16), 512, 4096)
+            assert_close(host(ops.linear(torch.from_numpy(x).cuda(), w)), ref, 4096, f"device {device}")
+            p = ops.DeviceW4PMatrix.from_canonical(w)
+            assert_close(host(ops.linear(torch.from_numpy(x).cuda(), p)), ref, 4096, f"prepared, device {device}")
+            ws = ops.linear_batched_workspace(16, 4096)
+            got = host(ops.linear_batched(torch.from_numpy(xb).cuda(), w, 16, 4096, 512, workspace=ws))
+            assert float(np.max(np.abs(got - refb))) <= 1e-4 * np.sqrt(4096)
+    finally:
+        torch.cuda.set_device(0)
