@@ -448,6 +448,45 @@ def run_ours(args):
             bd8.close()
         dec8.close()
 
+    # ---- the same W4-G128 decode with the KV cache kept in bf16 (an option kmll does not have: its cache is f32) -------
+    kv_bf16 = None
+    if world == 1 and not args.no_kvbf16:
+        steps_h = max(8, min(K, 64))
+        dech = rt.Decoder(rt.DecoderConfig.mistral_7b(max_seq_len=PROMPT_LEN + steps_h + 64, format=rt.FORMAT_W4G128, kv_bf16=True))
+        dech.init_random(SEED, 0.02, False)
+        dech.prefill(prompt)
+        dech.enqueue_steps(3)
+        torch.cuda.synchronize()
+        e0.record()
+        dech.enqueue_steps(steps_h)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_h = e0.elapsed_time(e1) / steps_h
+        tok_h, log_h = dech.history(0, 3 + steps_h)
+        n_same = 0
+        while n_same < min(len(tok_h), len(dev_tokens)) and int(tok_h[n_same]) == int(dev_tokens[n_same]):
+            n_same += 1
+        kv_bf16 = {"metric": "decode_tokens_per_s_batch1_mistral7b_arch_w4g128_kv_bf16", "value": 1e3 / ms_h, "unit": "tokens/s",
+                   "steps": steps_h, "ms_per_step": ms_h, "launches_per_step": dech.launches_per_step, "kv_cache_bytes": dech.kv_bytes,
+                   "leading_tokens_equal_to_f32_cache_run": n_same, "of": min(len(tok_h), len(dev_tokens))}
+        if not args.no_batch16:
+            dech.rewind(PROMPT_LEN)
+            dech.set_pending((int(log_h[:1].view(np.uint32)[0]) << 32) | int(tok_h[0]))
+            bdh = rt.BatchDecoder(dech, 16)
+            for slot in range(16):
+                bdh.adopt(slot)
+            bdh.generate_greedy(3)
+            torch.cuda.synchronize()
+            n16 = max(2, min(K, 16))
+            e0.record()
+            bdh.enqueue_steps(n16)
+            e1.record()
+            torch.cuda.synchronize()
+            kv_bf16["batch16"] = {"value": 16 * 1e3 / (e0.elapsed_time(e1) / n16), "unit": "tokens/s", "ms_per_step": e0.elapsed_time(e1) / n16,
+                                  "steps": n16, "launches_per_step": bdh.launches_per_step}
+            bdh.close()
+        dech.close()
+
     # ---- roofline of the dominant kernel: the fused RMSNorm + gate/up + SiLU kernel over prepared-layout weights (the
     # one the decode step above launches 32 times), timed live over 8 layers' worth of distinct weights (1.9 GB per
     # pass) on the launching stream ----------------------------------------------------------------------
@@ -515,6 +554,8 @@ def run_ours(args):
         line["batch16"] = batch16
     if rs_i8 is not None:
         line["rs_i8"] = rs_i8
+    if kv_bf16 is not None:
+        line["kv_bf16"] = kv_bf16
     if rank == 0 and world == 1 and not args.no_cpu:
         cb = cpu_sample(8, 1, cpu_threads(args.cpu_threads), 12.0)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -555,6 +596,7 @@ def main():
     ap.add_argument("--cpu-threads", type=int, default=0, help="threads of the CPU arm (default: every core of the host)")
     ap.add_argument("--no-batch16", action="store_true", help="skip the batch-16 leg")
     ap.add_argument("--no-rsi8", action="store_true", help="skip the RS-I8 (the reference's own format) decode leg")
+    ap.add_argument("--no-kvbf16", action="store_true", help="skip the leg that keeps the KV cache in bf16")
     ap.add_argument("--suite", default="", choices=["", "chain4096", "micro", "gemm_sweep"],
                     help="instead of the decode bench: one operator suite of kmll_b200.microbench, CPU port timed beside each line")
     ap.add_argument("--suite-reps", type=int, default=20)

@@ -67,6 +67,9 @@ typedef struct {
                      launch per kmll operator, in kmll's order (crates/inference/src/model.rs:10102-10300) */
     int tp_rank;  /* tensor parallel rank / size; 0 / 1 for a single GPU */
     int tp_size;
+    int kv_bf16;  /* 1: the KV cache holds bf16 (rounded to nearest-even when a row is written) instead of kmll's f32 rows
+                     (crates/inference/src/model.rs:10160-10186 writes f32): half the cache bytes and half the attention
+                     traffic, results no longer bit-equal to kmll's. */
 } kmll_decoder_config;
 
 int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out);

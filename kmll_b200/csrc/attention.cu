@@ -87,6 +87,12 @@ struct DecodeAttnParams {
     size_t q_stride, new_stride, cache_stride, ws_stride, out_stride;
 };
 
+// bf16 KV cache (kernel template flag KVB): the caches hold bf16 bit patterns (2 bytes per element, same
+// [max_seq, n_kv, head_dim] layout); rows are staged raw and widened to f32 where they are used, the new K / V rows
+// are rounded to nearest-even once, and that rounded value is both what is stored and what this step attends over.
+__device__ inline float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ inline float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
 // Half-split RoPE of a head slice held 4 (or 2) consecutive dims per lane: the partner dim d +- HD/2 lives
 // in lane ^ 16 (crates/inference/src/kernels/inference.rs:1078-1098 with rotary_dim == head_dim).
 // `cs_sn` holds (cos, sin) of position * freqs[pair] for the HD/2 pairs, computed once per block.
@@ -131,31 +137,36 @@ __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" 
 // seq_len - 1 were written by earlier steps, and the sequence length by a kernel at least two launches back.
 // GQM bounds the query heads per KV head at compile time (4 or 8): the per-head register arrays and unrolled
 // loops are sized by it.
-template <int HD, int GQM>
+template <int HD, int GQM, bool KVB>
 __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p_in) {
     DecodeAttnParams p = p_in;
+    constexpr size_t ESZ = KVB ? 2 : 4;  // bytes per cache element
     if (gridDim.z > 1) {  // sequence blockIdx.z of a batch: shift every per-sequence operand
         const size_t b = blockIdx.z;
+        const size_t cache_shift = b * p.cache_stride * ESZ;
         p.q += b * p.q_stride;
         p.out += b * p.out_stride;
-        p.k_cache += b * p.cache_stride;
-        p.v_cache += b * p.cache_stride;
+        p.k_cache = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.k_cache) + cache_shift);
+        p.v_cache = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.v_cache) + cache_shift);
         if (p.k_new != nullptr) {
             p.k_new += b * p.new_stride;
             p.v_new += b * p.new_stride;
-            p.k_cache_w += b * p.cache_stride;
-            p.v_cache_w += b * p.cache_stride;
+            p.k_cache_w = reinterpret_cast<float*>(reinterpret_cast<char*>(p.k_cache_w) + cache_shift);
+            p.v_cache_w = reinterpret_cast<float*>(reinterpret_cast<char*>(p.v_cache_w) + cache_shift);
         }
         p.part_acc += b * p.ws_stride;
         p.part_ml += b * p.ws_stride;
         p.counters += b * p.ws_stride;
     }
     constexpr int EPL = HD / 32;        // elements per lane
-    constexpr int V16 = HD / 4;         // 16-byte pieces per row
-    constexpr int KP = HD + 16;         // padded K row: the score pass reads 16-byte pieces at stride KP conflict-free
+    constexpr int V16 = HD * (int)ESZ / 16;  // 16-byte pieces per row
+    constexpr int KP = HD + 16;         // padded K row (elements): the score pass reads its pieces at stride KP conflict-free
+    constexpr int KROWB = KP * (int)ESZ, VROWB = HD * (int)ESZ;  // bytes per staged K / V row
     extern __shared__ __align__(16) float smem[];
-    float* Ks = smem;                         // [kAttnTile][KP]
+    float* Ks = smem;                         // [kAttnTile][KP]   (bf16 cache: the same areas, half used)
     float* Vs = Ks + kAttnTile * KP;          // [kAttnTile][HD]
+    char* const Kb = reinterpret_cast<char*>(Ks);
+    char* const Vb = reinterpret_cast<char*>(Vs);
     float* sc = Vs + kAttnTile * HD;          // [GQM][kAttnTile] scores, then weights
     float* hstat = sc + GQM * kAttnTile;   // [GQM][4]: running max, running sum, correction
     float* qs = hstat + GQM * 4;           // [GQM][HD] rotated query heads
@@ -173,21 +184,21 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     // one commit group per K tile and per V tile (also when the tile does not exist, so the group count is uniform)
     auto issue_k = [&](int t0) {
         const int nt = min(kAttnTile, n - t0);
-        const float* kg = p.k_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+        const char* kg = reinterpret_cast<const char*>(p.k_cache) + ((size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD) * ESZ;
 #pragma unroll 2
         for (int i = tid; i < nt * V16; i += kAttnThreads) {
             const int r = i / V16, cidx = i - r * V16;
-            cp_async16(Ks + r * KP + cidx * 4, kg + (size_t)r * kv_stride + cidx * 4);
+            cp_async16(Kb + r * KROWB + cidx * 16, kg + (size_t)r * kv_stride * ESZ + cidx * 16);
         }
         cp_async_commit();
     };
     auto issue_v = [&](int t0) {
         const int nt = min(kAttnTile, n - t0);
-        const float* vg = p.v_cache + (size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD;
+        const char* vg = reinterpret_cast<const char*>(p.v_cache) + ((size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD) * ESZ;
 #pragma unroll 2
         for (int i = tid; i < nt * V16; i += kAttnThreads) {
             const int r = i / V16, cidx = i - r * V16;
-            cp_async16(Vs + r * HD + cidx * 4, vg + (size_t)r * kv_stride + cidx * 4);
+            cp_async16(Vb + r * VROWB + cidx * 16, vg + (size_t)r * kv_stride * ESZ + cidx * 16);
         }
         cp_async_commit();
     };
@@ -232,6 +243,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         for (int e = 0; e < EPL; ++e) qs[warp * HD + lane * EPL + e] = qh[e];
     }
     if (owns_new && warp == kAttnWarps - 2) rope_lane_slice<EPL>(kvn, cs_sn, lane);
+    if (KVB && owns_new && warp >= kAttnWarps - 2) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) kvn[e] = bf16_bits_to_f32(f32_to_bf16_bits(kvn[e]));
+    }
 
     float acc[GQM][EPL];
 #pragma unroll
@@ -258,18 +273,34 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         if (has_new && warp == kAttnWarps - 2) {
 #pragma unroll
             for (int e = 0; e < EPL; ++e) {
-                Ks[newrow * KP + lane * EPL + e] = kvn[e];
-                p.k_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kvn[e];
+                const size_t at = (size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e;
+                if (KVB) {
+                    const uint16_t bits = (uint16_t)(__float_as_uint(kvn[e]) >> 16);
+                    reinterpret_cast<uint16_t*>(Ks)[newrow * KP + lane * EPL + e] = bits;
+                    reinterpret_cast<uint16_t*>(p.k_cache_w)[at] = bits;
+                } else {
+                    Ks[newrow * KP + lane * EPL + e] = kvn[e];
+                    p.k_cache_w[at] = kvn[e];
+                }
             }
         }
         if (has_new) __syncthreads();
         // scores: four lanes per position, each over an interleaved quarter of the head dimension
         {
             const int pl = tid >> 2, c = tid & 3;
-            const float* kr = Ks + (pl < nt ? pl : 0) * KP + c * 4;
             float4 kk[HD / 16];
+            if (KVB) {
+                const uint16_t* kr = reinterpret_cast<const uint16_t*>(Ks) + (pl < nt ? pl : 0) * KP + c * 4;
 #pragma unroll
-            for (int i = 0; i < HD / 16; ++i) kk[i] = *reinterpret_cast<const float4*>(kr + i * 16);
+                for (int i = 0; i < HD / 16; ++i) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(kr + i * 16);
+                    kk[i] = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+                }
+            } else {
+                const float* kr = Ks + (pl < nt ? pl : 0) * KP + c * 4;
+#pragma unroll
+                for (int i = 0; i < HD / 16; ++i) kk[i] = *reinterpret_cast<const float4*>(kr + i * 16);
+            }
 #pragma unroll 1
             for (int h = 0; h < gq; ++h) {
                 const float* qr = qs + h * HD + c * 4;
@@ -306,8 +337,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
             if (warp == kAttnWarps - 1) {
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) {
-                    Vs[newrow * HD + lane * EPL + e] = kvn[e];
-                    p.v_cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = kvn[e];
+                    const size_t at = (size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e;
+                    if (KVB) {
+                        const uint16_t bits = (uint16_t)(__float_as_uint(kvn[e]) >> 16);
+                        reinterpret_cast<uint16_t*>(Vs)[newrow * HD + lane * EPL + e] = bits;
+                        reinterpret_cast<uint16_t*>(p.v_cache_w)[at] = bits;
+                    } else {
+                        Vs[newrow * HD + lane * EPL + e] = kvn[e];
+                        p.v_cache_w[at] = kvn[e];
+                    }
                 }
             }
             __syncthreads();
@@ -323,7 +361,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll 2
         for (int i = warp; i < nt; i += kAttnWarps) {
             float vv[EPL];
-            load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
+            if (KVB) {
+                const uint16_t* vr = reinterpret_cast<const uint16_t*>(Vs) + i * HD + lane * EPL;
+                if (EPL == 4) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+                    vv[0] = bf16_lo(raw.x); vv[1] = bf16_hi(raw.x); vv[EPL - 2] = bf16_lo(raw.y); vv[EPL - 1] = bf16_hi(raw.y);
+                } else {
+                    const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
+                    vv[0] = bf16_lo(raw); vv[1] = bf16_hi(raw);
+                }
+            } else {
+                load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
+            }
 #pragma unroll
             for (int h = 0; h < GQM; ++h) {
                 if (h < gq) {
@@ -483,7 +532,8 @@ template <int HD>
 __global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __restrict__ q_batch,
                                                                 const float* __restrict__ k_cache,
                                                                 const float* __restrict__ v_cache, int prompt_len,
-                                                                int n_heads, int n_kv_heads, float* __restrict__ out) {
+                                                                int n_heads, int n_kv_heads, float* __restrict__ out,
+                                                                int kv_bf16) {
     constexpr int EPL = HD / 32;
     constexpr int KP = HD + 4;  // padded K row: 16-byte lane accesses hit disjoint banks
     __shared__ __align__(16) float Qs[kPfBQ][HD];
@@ -518,8 +568,14 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __r
             const int kk = idx / HD, d = idx - kk * HD;
             const int pos = t0 + kk;
             const bool ok = pos <= last_row;
-            Ks[kk][d] = ok ? k_cache[(size_t)pos * kv_stride + (size_t)kv_head * HD + d] : 0.0f;
-            Vs[kk][d] = ok ? v_cache[(size_t)pos * kv_stride + (size_t)kv_head * HD + d] : 0.0f;
+            const size_t at = (size_t)pos * kv_stride + (size_t)kv_head * HD + d;
+            if (kv_bf16) {
+                Ks[kk][d] = ok ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(k_cache)[at]) : 0.0f;
+                Vs[kk][d] = ok ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(v_cache)[at]) : 0.0f;
+            } else {
+                Ks[kk][d] = ok ? k_cache[at] : 0.0f;
+                Vs[kk][d] = ok ? v_cache[at] : 0.0f;
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -595,7 +651,8 @@ static AttnPlan plan_decode_attention(int seq_cap, int kv_heads_times_batch = 0)
 int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_cache, const float* v_cache,
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
                             int head_dim, float* workspace, float* out, const float* k_new, const float* v_new,
-                            const float* freqs, float* k_cache_w, float* v_cache_w, int batch, size_t cache_stride) {
+                            const float* freqs, float* k_cache_w, float* v_cache_w, int batch, size_t cache_stride,
+                            int kv_bf16) {
     const int gq = n_heads / n_kv_heads;
     AttnPlan pl = plan_decode_attention(seq_cap, batch > 1 ? n_kv_heads * batch : 0);
     DecodeAttnParams p;
@@ -624,9 +681,29 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem, stream, true, p);
     };
-    if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4>) : go(decode_attention_kernel<128, 8>);
-    else e = gq <= 4 ? go(decode_attention_kernel<64, 4>) : go(decode_attention_kernel<64, 8>);
+    if (kv_bf16) {
+        if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4, true>) : go(decode_attention_kernel<128, 8, true>);
+        else e = gq <= 4 ? go(decode_attention_kernel<64, 4, true>) : go(decode_attention_kernel<64, 8, true>);
+    } else {
+        if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4, false>) : go(decode_attention_kernel<128, 8, false>);
+        else e = gq <= 4 ? go(decode_attention_kernel<64, 4, false>) : go(decode_attention_kernel<64, 8, false>);
+    }
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int prefill_attention_launch(cudaStream_t stream, const float* q_batch, const float* k_cache, const float* v_cache, int prompt_len,
+                             int n_heads, int n_kv_heads, int head_dim, float* out, int kv_bf16) {
+    const dim3 grid(n_heads, (prompt_len + kPfBQ - 1) / kPfBQ);
+    cudaError_t e;
+    if (head_dim == 128) {
+        e = launch(prefill_attention_kernel<128>, grid, dim3(128), 0, stream, true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out, kv_bf16);
+    } else if (head_dim == 64) {
+        e = launch(prefill_attention_kernel<64>, grid, dim3(128), 0, stream, true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out, kv_bf16);
+    } else {
+        return fail(KMLL_ERR_UNSUPPORTED, "prefill_causal_attention: head_dim must be 64 or 128, got %d", head_dim);
+    }
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prefill_causal_attention: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }
 
@@ -752,17 +829,7 @@ int kmll_prefill_causal_attention(kmll_stream_t s, const float* q_batch, const f
     KMLL_REQUIRE_PTR(q_batch); KMLL_REQUIRE_PTR(k_cache); KMLL_REQUIRE_PTR(v_cache); KMLL_REQUIRE_PTR(out);
     int rc = check_geometry("prefill_causal_attention", prompt_len, max_seq_len, n_heads, n_kv_heads, head_dim);
     if (rc) return rc;
-    const dim3 grid(n_heads, (prompt_len + kPfBQ - 1) / kPfBQ);
-    cudaError_t e;
-    if (head_dim == 128) {
-        e = launch(prefill_attention_kernel<128>, grid, dim3(128), 0, as_stream(s), true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out);
-    } else if (head_dim == 64) {
-        e = launch(prefill_attention_kernel<64>, grid, dim3(128), 0, as_stream(s), true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out);
-    } else {
-        return fail(KMLL_ERR_UNSUPPORTED, "prefill_causal_attention: head_dim must be 64 or 128, got %d", head_dim);
-    }
-    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prefill_causal_attention: %s", cudaGetErrorString(e));
-    return KMLL_OK;
+    return prefill_attention_launch(as_stream(s), q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, head_dim, out, 0);
 }
 
 }  // extern "C"

@@ -162,7 +162,7 @@ __global__ void rope_batched_bf16_kernel(const uint16_t* __restrict__ x, const f
 // write_kv_cache / apply_rope_write_kv_cache (crates/inference/src/kernels/inference.rs:1103-1162)
 template <int ROPE>
 __global__ void kv_write_kernel(const float* __restrict__ x, const float* __restrict__ freqs, int half, int position,
-                                int head_dim, int token_len, float* __restrict__ cache) {
+                                int head_dim, int token_len, float* __restrict__ cache, int kv_bf16) {
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= token_len) return;
@@ -173,7 +173,8 @@ __global__ void kv_write_kernel(const float* __restrict__ x, const float* __rest
     } else {
         v = x[i];
     }
-    cache[(size_t)position * token_len + i] = v;
+    if (kv_bf16) reinterpret_cast<uint16_t*>(cache)[(size_t)position * token_len + i] = f32_to_bf16_bits(v);
+    else cache[(size_t)position * token_len + i] = v;
 }
 
 // prepare_incremental_attention (crates/inference/src/kernels/inference.rs:952-987)
@@ -195,7 +196,6 @@ __global__ void prepare_incremental_kernel(const float* __restrict__ q, const fl
     }
 }
 
-// prepare_prefill_attention_batch (crates/inference/src/kernels/inference.rs:896-949): row = position
 // Per-head RMSNorm of query and key rows in place (rmsnorm_batched_bf16 over [n_heads, head_dim] with one [head_dim]
 // weight, before RoPE: crates/inference/src/model.rs:10165-10194).  One warp per (row, head); q heads first, then k heads.
 __global__ void __launch_bounds__(256) qk_head_rmsnorm_kernel(float* q, float* k, const uint16_t* __restrict__ q_w, const uint16_t* __restrict__ k_w,
@@ -229,11 +229,12 @@ __global__ void __launch_bounds__(256) qk_head_rmsnorm_kernel(float* q, float* k
     }
 }
 
+// prepare_prefill_attention_batch (crates/inference/src/kernels/inference.rs:896-949): row = position
 __global__ void prepare_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k,
                                        const float* __restrict__ v, const float* __restrict__ freqs, int half,
                                        int prompt_len, int q_len, int kv_len, int head_dim, int position0,
                                        float* __restrict__ q_rot, float* __restrict__ k_cache,
-                                       float* __restrict__ v_cache) {
+                                       float* __restrict__ v_cache, int kv_bf16) {
     pdl_wait();
     const int width = q_len > kv_len ? q_len : kv_len;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -250,8 +251,15 @@ __global__ void prepare_prefill_kernel(const float* __restrict__ q, const float*
         const int head = col / head_dim;
         const size_t base = (size_t)row * kv_len + (size_t)head * head_dim;
         const size_t off = (size_t)(position0 + row) * kv_len + col;
-        k_cache[off] = rope_value(k, base, col - head * head_dim, freqs, half, position);
-        v_cache[off] = v[(size_t)row * kv_len + col];
+        const float kr = rope_value(k, base, col - head * head_dim, freqs, half, position);
+        const float vr = v[(size_t)row * kv_len + col];
+        if (kv_bf16) {  // bf16 cache: the same layout in 2-byte elements, rounded to nearest-even
+            reinterpret_cast<uint16_t*>(k_cache)[off] = f32_to_bf16_bits(kr);
+            reinterpret_cast<uint16_t*>(v_cache)[off] = f32_to_bf16_bits(vr);
+        } else {
+            k_cache[off] = kr;
+            v_cache[off] = vr;
+        }
     }
 }
 
@@ -416,7 +424,7 @@ __global__ void prepare_incremental_dyn_kernel(const float* __restrict__ q, cons
                                                const float* __restrict__ v, const float* __restrict__ freqs, int half,
                                                const DecodeState* __restrict__ state, int q_len, int kv_len, int head_dim,
                                                float* __restrict__ q_rot, float* __restrict__ k_cache,
-                                               float* __restrict__ v_cache) {
+                                               float* __restrict__ v_cache, int kv_bf16) {
     pdl_wait();
     const int position = state->position;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -427,8 +435,14 @@ __global__ void prepare_incremental_dyn_kernel(const float* __restrict__ q, cons
     if (i < kv_len) {
         const int head = i / head_dim;
         const size_t off = (size_t)position * kv_len + i;
-        k_cache[off] = rope_value(k, (size_t)head * head_dim, i - head * head_dim, freqs, half, (float)position);
-        v_cache[off] = v[i];
+        const float kr = rope_value(k, (size_t)head * head_dim, i - head * head_dim, freqs, half, (float)position);
+        if (kv_bf16) {
+            reinterpret_cast<uint16_t*>(k_cache)[off] = f32_to_bf16_bits(kr);
+            reinterpret_cast<uint16_t*>(v_cache)[off] = f32_to_bf16_bits(v[i]);
+        } else {
+            k_cache[off] = kr;
+            v_cache[off] = v[i];
+        }
     }
 }
 
@@ -460,12 +474,12 @@ __global__ void decode_end_kernel(const uint64_t* __restrict__ packed, DecodeSta
 
 int prepare_incremental_dyn(cudaStream_t stream, const float* q, const float* k, const float* v, const float* freqs,
                             int n_freqs, const DecodeState* state, int max_seq_len, int n_heads, int n_kv_heads,
-                            int head_dim, float* q_rot, float* k_cache, float* v_cache) {
+                            int head_dim, float* q_rot, float* k_cache, float* v_cache, int kv_bf16) {
     (void)max_seq_len;
     const int q_len = n_heads * head_dim, kv_len = n_kv_heads * head_dim;
     const int width = q_len > kv_len ? q_len : kv_len;
     cudaError_t e = launch(prepare_incremental_dyn_kernel, dim3((width + 255) / 256), dim3(256), 0, stream, true, q, k, v,
-                           freqs, n_freqs, state, q_len, kv_len, head_dim, q_rot, k_cache, v_cache);
+                           freqs, n_freqs, state, q_len, kv_len, head_dim, q_rot, k_cache, v_cache, kv_bf16);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prepare_incremental_dyn: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }
@@ -483,12 +497,19 @@ int qk_head_rmsnorm(cudaStream_t stream, float* q, float* k, const uint16_t* q_w
 
 int prepare_prefill_offset(cudaStream_t stream, const float* q, const float* k, const float* v, const float* freqs,
                            int n_freqs, int rows, int q_len, int kv_len, int head_dim, int position0, float* q_rot,
-                           float* k_cache, float* v_cache) {
+                           float* k_cache, float* v_cache, int kv_bf16) {
     const int width = q_len > kv_len ? q_len : kv_len;
     const size_t total = (size_t)rows * width;
     cudaError_t e = launch(prepare_prefill_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, true, q, k, v,
-                           freqs, n_freqs, rows, q_len, kv_len, head_dim, position0, q_rot, k_cache, v_cache);
+                           freqs, n_freqs, rows, q_len, kv_len, head_dim, position0, q_rot, k_cache, v_cache, kv_bf16);
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "prepare_prefill: %s", cudaGetErrorString(e));
+    return KMLL_OK;
+}
+
+int write_kv_row(cudaStream_t stream, const float* x, int position, int token_len, int head_dim, float* cache, int kv_bf16) {
+    cudaError_t e = launch(kv_write_kernel<0>, dim3((token_len + 255) / 256), dim3(256), 0, stream, true, x, (const float*)nullptr, 0,
+                           position, head_dim, token_len, cache, kv_bf16);
+    if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "write_kv_cache: %s", cudaGetErrorString(e));
     return KMLL_OK;
 }
 
@@ -695,7 +716,7 @@ int kmll_write_kv_cache(kmll_stream_t s, const float* x, int position, int max_s
     int rc = check_cache("write_kv_cache", position, max_seq_len, n_kv_heads, head_dim);
     if (rc) return rc;
     const int token_len = n_kv_heads * head_dim;
-    KMLL_LAUNCH_CHECK(launch(kv_write_kernel<0>, dim3((token_len + 255) / 256), dim3(256), 0, as_stream(s), true, x, (const float*)nullptr, 0, position, head_dim, token_len, cache), "write_kv_cache");
+    KMLL_LAUNCH_CHECK(launch(kv_write_kernel<0>, dim3((token_len + 255) / 256), dim3(256), 0, as_stream(s), true, x, (const float*)nullptr, 0, position, head_dim, token_len, cache, 0), "write_kv_cache");
     return KMLL_OK;
 }
 int kmll_apply_rope_write_kv_cache(kmll_stream_t s, const float* x, const float* freqs, int n_freqs, int position, int max_seq_len,
@@ -706,7 +727,7 @@ int kmll_apply_rope_write_kv_cache(kmll_stream_t s, const float* x, const float*
     rc = check_rope("apply_rope_write_kv_cache", n_freqs, head_dim);
     if (rc) return rc;
     const int token_len = n_kv_heads * head_dim;
-    KMLL_LAUNCH_CHECK(launch(kv_write_kernel<1>, dim3((token_len + 255) / 256), dim3(256), 0, as_stream(s), true, x, freqs, n_freqs, position, head_dim, token_len, cache), "apply_rope_write_kv_cache");
+    KMLL_LAUNCH_CHECK(launch(kv_write_kernel<1>, dim3((token_len + 255) / 256), dim3(256), 0, as_stream(s), true, x, freqs, n_freqs, position, head_dim, token_len, cache, 0), "apply_rope_write_kv_cache");
     return KMLL_OK;
 }
 
@@ -737,7 +758,7 @@ int kmll_prepare_prefill_attention_batch(kmll_stream_t s, const float* q, const 
     KMLL_REQUIRE(kv_len > 0 && kv_len % head_dim == 0, "prepare_prefill_attention_batch: KV row shape mismatch");
     const int width = q_len > kv_len ? q_len : kv_len;
     const size_t total = (size_t)prompt_len * width;
-    KMLL_LAUNCH_CHECK(launch(prepare_prefill_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, as_stream(s), true, q, k, v, freqs, n_freqs, prompt_len, q_len, kv_len, head_dim, 0, q_rot, k_cache, v_cache), "prepare_prefill_attention_batch");
+    KMLL_LAUNCH_CHECK(launch(prepare_prefill_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, as_stream(s), true, q, k, v, freqs, n_freqs, prompt_len, q_len, kv_len, head_dim, 0, q_rot, k_cache, v_cache, 0), "prepare_prefill_attention_batch");
     return KMLL_OK;
 }
 

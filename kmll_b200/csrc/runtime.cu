@@ -178,6 +178,7 @@ static int validate_config(const kmll_decoder_config& c) {
         return fail(KMLL_ERR_SHAPE, "decoder config: n_kv_heads, hidden_dim and vocab_size must be divisible by tp_size");
     if (c.dim % unit != 0 || ((c.n_heads / c.tp_size) * c.head_dim) % unit != 0 || (c.hidden_dim / c.tp_size) % unit != 0)
         return fail(KMLL_ERR_SHAPE, "decoder config: every (sharded) input dimension must be a multiple of %d", unit);
+    if (c.kv_bf16 != 0 && c.kv_bf16 != 1) return fail(KMLL_ERR_SHAPE, "decoder config: kv_bf16 must be 0 or 1");
     return KMLL_OK;
 }
 
@@ -293,13 +294,14 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
         if (c.rotary_dim == c.head_dim) {
             // RoPE of q and of the new K row and the KV-cache write happen inside the attention kernel
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache, 1, 0, c.kv_bf16));
             ++n;
         } else {
             KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache));
+                                             d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache, c.kv_bf16));
             KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0,
+                                             c.kv_bf16));
             n += 2;
         }
         KMLL_TRY(row_parallel_residual(d, s, d->attn, L.wo, hidden, d->hidden_mid, peer ? 2 * l : -1));
@@ -439,12 +441,13 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
         KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1));
         if (c.rotary_dim == c.head_dim) {
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache, 1, 0, c.kv_bf16));
         } else {
             KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache));
+                                             d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache, c.kv_bf16));
             KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0,
+                                             c.kv_bf16));
         }
         ChainParams cp;
         memset(&cp, 0, sizeof(cp));
@@ -580,10 +583,17 @@ static int enqueue_step_unfused(Decoder* d, cudaStream_t s, uint32_t token, int 
         KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1));
         KMLL_TRY(kmll_apply_rope(s, d->q, d->freqs, nf, position, c.head_dim, (size_t)q_len, d->q_rot));
         KMLL_TRY(kmll_apply_rope(s, d->k, d->freqs, nf, position, c.head_dim, (size_t)kv_len, d->k_rot));
-        KMLL_TRY(kmll_write_kv_cache(s, d->k_rot, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.key_cache));
-        KMLL_TRY(kmll_write_kv_cache(s, d->v, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.value_cache));
-        KMLL_TRY(kmll_single_query_attention(s, d->q_rot, L.key_cache, L.value_cache, position + 1, c.max_seq_len, d->n_heads_l, d->n_kv_l,
-                                             c.head_dim, d->attn_ws, d->attn));
+        if (c.kv_bf16) {  // the same three operators over a bf16 cache (the C-ABI forms are f32 only)
+            KMLL_TRY(write_kv_row(s, d->k_rot, position, kv_len, c.head_dim, L.key_cache, 1));
+            KMLL_TRY(write_kv_row(s, d->v, position, kv_len, c.head_dim, L.value_cache, 1));
+            KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, nullptr, position + 1, c.max_seq_len, d->n_heads_l,
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0, 1));
+        } else {
+            KMLL_TRY(kmll_write_kv_cache(s, d->k_rot, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.key_cache));
+            KMLL_TRY(kmll_write_kv_cache(s, d->v, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.value_cache));
+            KMLL_TRY(kmll_single_query_attention(s, d->q_rot, L.key_cache, L.value_cache, position + 1, c.max_seq_len, d->n_heads_l, d->n_kv_l,
+                                                 c.head_dim, d->attn_ws, d->attn));
+        }
         KMLL_TRY(op_linear(d, s, d->attn, L.wo, d->delta));
         KMLL_TRY(tp_allreduce(d, s, d->delta, (size_t)c.dim));
         KMLL_TRY(kmll_add(s, hidden, d->delta, (size_t)c.dim, d->hidden_mid));
@@ -783,7 +793,7 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
         KMLL_TRY(apply_qk_norm(d, s, L, b->q, b->k, B));
         KMLL_TRY(decode_attention_launch(s, b->q, b->key_cache[l], b->value_cache[l], &b->state->seq_len, 0, c.max_seq_len, c.n_heads,
                                          c.n_kv_heads, c.head_dim, b->attn_ws, b->attn, b->k, b->v, d->freqs, b->key_cache[l],
-                                         b->value_cache[l], B, b->cache_stride));
+                                         b->value_cache[l], B, b->cache_stride, c.kv_bf16));
         {
             const void* w[1] = {L.wo.w};
             const void* sc[1] = {L.wo.scales};
@@ -957,7 +967,8 @@ int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out) 
             KMLL_TRY(alloc_qweight(d, &L.w1, d->hidden_l, c.dim));
             KMLL_TRY(alloc_qweight(d, &L.w3, d->hidden_l, c.dim));
             KMLL_TRY(alloc_qweight(d, &L.w2, c.dim, d->hidden_l));
-            const size_t cache = (size_t)c.max_seq_len * kv_len;
+            // f32 elements, or bf16 bit patterns in the same [max_seq, n_kv, head_dim] layout (kv_len is even)
+            const size_t cache = (size_t)c.max_seq_len * kv_len / (c.kv_bf16 ? 2 : 1);
             KMLL_TRY(dalloc(d, &L.key_cache, cache));
             KMLL_TRY(dalloc(d, &L.value_cache, cache));
             KMLL_CUDA(cudaMemset(L.key_cache, 0, cache * sizeof(float)));
@@ -1286,8 +1297,8 @@ int kmll_decoder_prefill(kmll_decoder_t dec, kmll_stream_t stream, const uint32_
             }
             KMLL_TRY(apply_qk_norm(d, s, L, qb, kb, n));
             KMLL_TRY(prepare_prefill_offset(s, qb, kb, vb, d->freqs, c.rotary_dim / 2, n, q_len, kv_len, c.head_dim, 0, qrb, L.key_cache,
-                                            L.value_cache));
-            KMLL_TRY(kmll_prefill_causal_attention(s, qrb, L.key_cache, L.value_cache, n, c.max_seq_len, d->n_heads_l, d->n_kv_l, c.head_dim, ab));
+                                            L.value_cache, c.kv_bf16));
+            KMLL_TRY(prefill_attention_launch(s, qrb, L.key_cache, L.value_cache, n, d->n_heads_l, d->n_kv_l, c.head_dim, ab, c.kv_bf16));
             KMLL_TRY(op_linear_batched(d, s, ab, L.wo, n, ws, ob));
             KMLL_TRY(tp_allreduce(d, s, ob, (size_t)n * c.dim));
             KMLL_TRY(kmll_add_prefix(s, xb, ob, (size_t)n * c.dim, x2b));
@@ -1525,14 +1536,15 @@ int kmll_batch_create(kmll_decoder_t dec, int batch, kmll_batch_t* out) {
     b->batch = batch;
     auto body = [&]() -> int {
         const int q_len = c.n_heads * c.head_dim, kv_len = c.n_kv_heads * c.head_dim;
-        b->cache_stride = (size_t)c.max_seq_len * kv_len;
+        b->cache_stride = (size_t)c.max_seq_len * kv_len;  // elements (f32, or bf16 with kv_bf16) between two sequences
+        const size_t cache_floats = b->cache_stride * batch / (c.kv_bf16 ? 2 : 1);
         b->key_cache.resize(c.n_layers);
         b->value_cache.resize(c.n_layers);
         for (int l = 0; l < c.n_layers; ++l) {
-            KMLL_TRY(balloc(b, &b->key_cache[l], b->cache_stride * batch));
-            KMLL_TRY(balloc(b, &b->value_cache[l], b->cache_stride * batch));
-            KMLL_CUDA(cudaMemset(b->key_cache[l], 0, b->cache_stride * batch * sizeof(float)));
-            KMLL_CUDA(cudaMemset(b->value_cache[l], 0, b->cache_stride * batch * sizeof(float)));
+            KMLL_TRY(balloc(b, &b->key_cache[l], cache_floats));
+            KMLL_TRY(balloc(b, &b->value_cache[l], cache_floats));
+            KMLL_CUDA(cudaMemset(b->key_cache[l], 0, cache_floats * sizeof(float)));
+            KMLL_CUDA(cudaMemset(b->value_cache[l], 0, cache_floats * sizeof(float)));
         }
         KMLL_TRY(balloc(b, &b->hidden_a, (size_t)batch * c.dim));
         KMLL_TRY(balloc(b, &b->hidden_b, (size_t)batch * c.dim));
@@ -1584,10 +1596,11 @@ int kmll_batch_adopt(kmll_batch_t batch, kmll_stream_t stream, int slot) {
                     b->host_position);
     const kmll_decoder_config& c = d->cfg;
     const size_t kv_len = (size_t)c.n_kv_heads * c.head_dim;
-    const size_t bytes = (size_t)d->host_position * kv_len * sizeof(float);
+    const size_t esz = c.kv_bf16 ? 2 : sizeof(float);
+    const size_t bytes = (size_t)d->host_position * kv_len * esz, slot_at = (size_t)slot * b->cache_stride * esz;
     for (int l = 0; l < c.n_layers; ++l) {
-        KMLL_CUDA(cudaMemcpyAsync(b->key_cache[l] + (size_t)slot * b->cache_stride, d->layers[l].key_cache, bytes, cudaMemcpyDeviceToDevice, s));
-        KMLL_CUDA(cudaMemcpyAsync(b->value_cache[l] + (size_t)slot * b->cache_stride, d->layers[l].value_cache, bytes, cudaMemcpyDeviceToDevice, s));
+        KMLL_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(b->key_cache[l]) + slot_at, d->layers[l].key_cache, bytes, cudaMemcpyDeviceToDevice, s));
+        KMLL_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(b->value_cache[l]) + slot_at, d->layers[l].value_cache, bytes, cudaMemcpyDeviceToDevice, s));
     }
     KMLL_CUDA(cudaMemcpyAsync(&b->state->next_top[slot], &d->state->next_top, sizeof(uint64_t), cudaMemcpyDeviceToDevice, s));
     if (b->filled == 0) {

@@ -51,7 +51,10 @@ class OracleDecoder:
                 q = np.concatenate([oracle.rmsnorm(q[h * hd:(h + 1) * hd], self.qk_norm[l][0], c.norm_eps) for h in range(c.n_heads)])
                 k = np.concatenate([oracle.rmsnorm(k[h * hd:(h + 1) * hd], self.qk_norm[l][1], c.norm_eps) for h in range(c.n_kv_heads)])
             q_rot = oracle.apply_rope(q, self.freqs, pos, c.head_dim)
-            self.key[l][pos] = oracle.apply_rope(k, self.freqs, pos, c.head_dim)
+            k_row = oracle.apply_rope(k, self.freqs, pos, c.head_dim)
+            if c.kv_bf16:  # the cache keeps bf16: rows rounded to nearest-even once, when they are written
+                k_row, v = oracle.bf16_to_f32(oracle.bf16_from_f32(k_row)), oracle.bf16_to_f32(oracle.bf16_from_f32(v))
+            self.key[l][pos] = k_row
             self.value[l][pos] = v
             attn = oracle.single_query_attention(q_rot, self.key[l][:pos + 1], self.value[l][:pos + 1], pos + 1, c.n_heads, c.n_kv_heads,
                                                  c.head_dim)

@@ -26,20 +26,20 @@ def make(cfg, seed=2, std=0.05, tie=False):
     return dec
 
 
-def check_against_oracle(dec, cfg, prompt, n_steps, batched_prefill):
+def check_against_oracle(dec, cfg, prompt, n_steps, batched_prefill, hid_tol=2e-4, min_margin=1e-3, logit_tol=1e-3):
     ora = OracleDecoder(cfg, dec)
     logits = ora.prefill(prompt)
     dec.prefill(prompt, token_loop=not batched_prefill)
     hid = dec.last_hidden()
     scale = np.max(np.abs(ora.hidden))
-    assert np.max(np.abs(hid - ora.hidden)) <= 2e-4 * max(scale, 1.0), "hidden state after prefill"
+    assert np.max(np.abs(hid - ora.hidden)) <= hid_tol * max(scale, 1.0), "hidden state after prefill"
     steps, _ = ora.generate_greedy(logits, n_steps)
     tokens, glogits = dec.generate_greedy(n_steps)
     for i, (tok, logit, margin) in enumerate(steps):
-        if margin < 1e-3:
+        if margin < min_margin:
             break  # a near-tie in the oracle: either token is a faithful arg-max, later steps diverge legitimately
         assert int(tokens[i]) == tok, f"greedy token differs at step {i} (oracle margin {margin})"
-        assert abs(float(glogits[i]) - logit) <= 1e-3 * max(abs(logit), 1.0)
+        assert abs(float(glogits[i]) - logit) <= logit_tol * max(abs(logit), 1.0)
     assert dec.position == len(prompt) + n_steps
 
 
@@ -51,6 +51,41 @@ def test_decode_matches_oracle(cuda, fmt, fused):
     rng = np.random.default_rng(2)
     prompt = rng.integers(0, cfg.vocab_size, 9)
     check_against_oracle(dec, cfg, prompt, 6, batched_prefill=False)
+    dec.close()
+
+
+BF16_KV_BOUND = dict(hid_tol=2e-3, min_margin=1e-2, logit_tol=5e-3)
+
+
+@pytest.mark.parametrize("fmt", [rt.FORMAT_RS_I8, rt.FORMAT_W4G128])
+@pytest.mark.parametrize("head_dim,n_heads,n_kv", [(64, 4, 2), (128, 8, 1), (128, 8, 2)])
+@pytest.mark.parametrize("batched_prefill", [False, True])
+def test_bf16_kv_cache_matches_oracle(cuda, fmt, head_dim, n_heads, n_kv, batched_prefill):
+    """kv_bf16: the oracle rounds the K / V rows it stores to bf16 (nearest-even) and is otherwise unchanged.  The bound
+    is the option's own: a K / V value that the two sides compute a few f32 ulps apart can fall on either side of a bf16
+    rounding tie, which moves that cache element by one bf16 ulp (2^-8 relative) - hidden state within 2e-3 of its scale,
+    logits within 5e-3, tokens compared while the oracle's top-2 margin is at least 1e-2.  The sequence crosses a
+    64-position tile so that staged rows, the row being written and both prefill paths are covered.  The cache bytes are
+    half those of the f32 cache."""
+    cfg = tiny(fmt, True, n_heads=n_heads, n_kv_heads=n_kv, head_dim=head_dim, dim=256, max_seq_len=160, kv_bf16=True)
+    dec = make(cfg)
+    ref = make(tiny(fmt, True, n_heads=n_heads, n_kv_heads=n_kv, head_dim=head_dim, dim=256, max_seq_len=160))
+    assert dec.kv_bytes * 2 == ref.kv_bytes
+    ref.close()
+    rng = np.random.default_rng(11)
+    prompt = rng.integers(0, cfg.vocab_size, 61)
+    check_against_oracle(dec, cfg, prompt, 8, batched_prefill=batched_prefill, **BF16_KV_BOUND)
+    dec.close()
+
+
+@pytest.mark.parametrize("fused,rotary_dim", [(False, None), (True, 32), (False, 32)])
+def test_bf16_kv_cache_on_the_other_step_forms(cuda, fused, rotary_dim):
+    """The operator-by-operator step and the partial-rotary step (RoPE + cache write in a kernel of their own) over a
+    bf16 cache."""
+    cfg = tiny(rt.FORMAT_W4G128, fused, rotary_dim=rotary_dim, max_seq_len=96, kv_bf16=True)
+    dec = make(cfg)
+    prompt = np.random.default_rng(5).integers(0, cfg.vocab_size, 66)
+    check_against_oracle(dec, cfg, prompt, 5, batched_prefill=fused, **BF16_KV_BOUND)
     dec.close()
 
 
