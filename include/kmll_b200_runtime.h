@@ -70,6 +70,9 @@ typedef struct {
     int kv_bf16;  /* 1: the KV cache holds bf16 (rounded to nearest-even when a row is written) instead of kmll's f32 rows
                      (crates/inference/src/model.rs:10160-10186 writes f32): half the cache bytes and half the attention
                      traffic, results no longer bit-equal to kmll's. */
+    int sliding_window;  /* > 0: every position attends only the last `sliding_window` positions (itself included), the
+                            mask of Mistral-style checkpoints; 0: full causal attention, which is all kmll implements
+                            (crates/inference/src/kernels/inference.rs:1420-1686).  The cache still keeps every row. */
 } kmll_decoder_config;
 
 int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out);

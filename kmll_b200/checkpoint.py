@@ -309,7 +309,8 @@ def rope_frequencies(cfg: TextConfig) -> np.ndarray:
     return out
 
 
-def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused: bool = True, kv_bf16: bool = False):
+def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused: bool = True, kv_bf16: bool = False,
+                 sliding_window: int = 0):
     """config.json + safetensors -> a Decoder with its linear weights quantized to `fmt` on the device (RS-I8 from the
     bf16 values as kmll's exporter does, rowwise_scaled.rs:21-51; W4-G128 from their f32 values).  Returns (decoder, config)."""
     import torch
@@ -324,7 +325,8 @@ def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused
         raise CheckpointError("a checkpoint must carry both q_norm and k_norm or neither")
     dcfg = rt.DecoderConfig(n_layers=cfg.n_layers, dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
                             hidden_dim=cfg.hidden_dim, vocab_size=cfg.vocab_size, rope_theta=cfg.rope_theta, norm_eps=cfg.norm_eps,
-                            max_seq_len=max_seq_len or cfg.max_position_embeddings, rotary_dim=cfg.rotary_dim, format=fmt, fused=fused, kv_bf16=kv_bf16)
+                            max_seq_len=max_seq_len or cfg.max_position_embeddings, rotary_dim=cfg.rotary_dim, format=fmt, fused=fused, kv_bf16=kv_bf16,
+                            sliding_window=sliding_window)
     dec = rt.Decoder(dcfg)
     q, kv = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
 

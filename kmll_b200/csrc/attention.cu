@@ -71,6 +71,7 @@ struct DecodeAttnParams {
     int n_heads, n_kv_heads, gq;
     int chunk;    // positions per block
     int nsplit;   // gridDim.y
+    int window;   // sliding window: only the last `window` positions are attended (0: all of them)
     float* part_acc;  // [n_heads, nsplit, HD]
     float* part_ml;   // [n_heads, nsplit, 2]
     unsigned int* counters;  // [n_kv_heads], zero on entry, zero on exit
@@ -175,12 +176,22 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     __shared__ float2 cs_sn[HD / 2];  // fused form: (cos, sin) of the rotation angles of this position
 
     trace_stamp(p.trace, 0);
-    const int kv_head = blockIdx.x, split = blockIdx.y, gq = p.gq;
+    const int kv_head = blockIdx.x, gq = p.gq;
+    int split = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t kv_stride = (size_t)p.n_kv_heads * HD;
     const bool fused = p.k_new != nullptr;
-    const int s0 = split * p.chunk;
-    int seq_len = 0, n = 0;
+    // this block's positions: its slice of the sequence, cut to [first attended position, seq_len)
+    int s0 = split * p.chunk;
+    int seq_len = 0, n = 0, first_split = 0;
+    auto set_range = [&]() {
+        seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
+        const int lo = (p.window > 0 && seq_len > p.window) ? seq_len - p.window : 0;
+        first_split = lo / p.chunk;  // splits before it hold no attended position and leave at once
+        const int slice_end = min(s0 + p.chunk, seq_len);
+        s0 = max(s0, lo);
+        n = slice_end - s0;
+    };
     // one commit group per K tile and per V tile (also when the tile does not exist, so the group count is uniform)
     auto issue_k = [&](int t0) {
         const int nt = min(kAttnTile, n - t0);
@@ -203,8 +214,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         cp_async_commit();
     };
     if (fused) {
-        seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
-        n = min(s0 + p.chunk, seq_len) - s0;
+        set_range();
         if (n > 0) {
             issue_k(0);
             issue_v(0);
@@ -220,12 +230,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     if (tid < GQM) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
     pdl_wait();
     trace_stamp(p.trace, 1);
-    if (!fused) {
-        seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
-        n = min(s0 + p.chunk, seq_len) - s0;
-    }
-    const int nactive = (seq_len + p.chunk - 1) / p.chunk;  // splits that hold positions; the others leave at once
+    if (!fused) set_range();
+    const int nactive = (seq_len + p.chunk - 1) / p.chunk - first_split;  // splits that hold attended positions
     if (n <= 0) return;
+    split -= first_split;  // index of this block's partial among the active splits
     const float scale = 1.0f / sqrtf((float)HD);
 
     // Everything this block needs from the previous kernel is requested at once: the query heads (warp h loads
@@ -533,7 +541,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __r
                                                                 const float* __restrict__ k_cache,
                                                                 const float* __restrict__ v_cache, int prompt_len,
                                                                 int n_heads, int n_kv_heads, float* __restrict__ out,
-                                                                int kv_bf16) {
+                                                                int kv_bf16, int window) {
     constexpr int EPL = HD / 32;
     constexpr int KP = HD + 4;  // padded K row: 16-byte lane accesses hit disjoint banks
     __shared__ __align__(16) float Qs[kPfBQ][HD];
@@ -562,7 +570,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __r
         for (int e = 0; e < EPL; ++e) acc[j][e] = 0.0f;
     }
     const int last_row = min(r0 + kPfBQ, prompt_len) - 1;
-    for (int t0 = 0; t0 <= last_row; t0 += kPfBK) {
+    // sliding window: row r attends keys r - window + 1 .. r; tiles wholly before the first row's window are skipped
+    const int first_key = window > 0 ? max(0, r0 - window + 1) : 0;
+    for (int t0 = first_key / kPfBK * kPfBK; t0 <= last_row; t0 += kPfBK) {
         __syncthreads();
         for (int idx = threadIdx.x; idx < kPfBK * HD; idx += blockDim.x) {
             const int kk = idx / HD, d = idx - kk * HD;
@@ -583,6 +593,8 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __r
             const int r = warp * QPW + j;
             const int row = r0 + r;
             if (row >= prompt_len || t0 > row) continue;  // warp-uniform
+            const int row_lo = window > 0 ? row - window + 1 : 0;  // first key this row attends
+            if (t0 + kPfBK - 1 < row_lo) continue;  // the tile lies before this row's window (warp-uniform)
             // lane = key index inside the tile
             float s = 0.0f;
 #pragma unroll 8
@@ -594,7 +606,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const float* __r
                 s += qq.z * kq.z;
                 s += qq.w * kq.w;
             }
-            s = (t0 + lane) <= row ? s * scale : -INFINITY;
+            s = ((t0 + lane) <= row && (t0 + lane) >= row_lo) ? s * scale : -INFINITY;
             const float m_new = fmaxf(m[j], warp_max(s));
             const float pexp = expf(s - m_new);  // exp(-inf) = 0 for masked keys
             const float corr = expf(m[j] - m_new);
@@ -652,7 +664,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
                             const int* seq_len_ptr, int seq_len, int seq_cap, int n_heads, int n_kv_heads,
                             int head_dim, float* workspace, float* out, const float* k_new, const float* v_new,
                             const float* freqs, float* k_cache_w, float* v_cache_w, int batch, size_t cache_stride,
-                            int kv_bf16) {
+                            int kv_bf16, int window) {
     const int gq = n_heads / n_kv_heads;
     AttnPlan pl = plan_decode_attention(seq_cap, batch > 1 ? n_kv_heads * batch : 0);
     DecodeAttnParams p;
@@ -660,6 +672,7 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     p.seq_len_ptr = seq_len_ptr; p.seq_len = seq_len;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.gq = gq;
     p.chunk = pl.chunk; p.nsplit = pl.nsplit;
+    p.window = window > 0 ? window : 0;
     p.part_acc = workspace;
     p.part_ml = workspace + (size_t)n_heads * pl.nsplit * head_dim;
     p.counters = reinterpret_cast<unsigned int*>(p.part_ml + (size_t)n_heads * pl.nsplit * 2);
@@ -693,13 +706,13 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
 }
 
 int prefill_attention_launch(cudaStream_t stream, const float* q_batch, const float* k_cache, const float* v_cache, int prompt_len,
-                             int n_heads, int n_kv_heads, int head_dim, float* out, int kv_bf16) {
+                             int n_heads, int n_kv_heads, int head_dim, float* out, int kv_bf16, int window) {
     const dim3 grid(n_heads, (prompt_len + kPfBQ - 1) / kPfBQ);
     cudaError_t e;
     if (head_dim == 128) {
-        e = launch(prefill_attention_kernel<128>, grid, dim3(128), 0, stream, true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out, kv_bf16);
+        e = launch(prefill_attention_kernel<128>, grid, dim3(128), 0, stream, true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out, kv_bf16, window);
     } else if (head_dim == 64) {
-        e = launch(prefill_attention_kernel<64>, grid, dim3(128), 0, stream, true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out, kv_bf16);
+        e = launch(prefill_attention_kernel<64>, grid, dim3(128), 0, stream, true, q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, out, kv_bf16, window);
     } else {
         return fail(KMLL_ERR_UNSUPPORTED, "prefill_causal_attention: head_dim must be 64 or 128, got %d", head_dim);
     }
@@ -829,7 +842,7 @@ int kmll_prefill_causal_attention(kmll_stream_t s, const float* q_batch, const f
     KMLL_REQUIRE_PTR(q_batch); KMLL_REQUIRE_PTR(k_cache); KMLL_REQUIRE_PTR(v_cache); KMLL_REQUIRE_PTR(out);
     int rc = check_geometry("prefill_causal_attention", prompt_len, max_seq_len, n_heads, n_kv_heads, head_dim);
     if (rc) return rc;
-    return prefill_attention_launch(as_stream(s), q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, head_dim, out, 0);
+    return prefill_attention_launch(as_stream(s), q_batch, k_cache, v_cache, prompt_len, n_heads, n_kv_heads, head_dim, out, 0, 0);
 }
 
 }  // extern "C"

@@ -179,6 +179,7 @@ static int validate_config(const kmll_decoder_config& c) {
     if (c.dim % unit != 0 || ((c.n_heads / c.tp_size) * c.head_dim) % unit != 0 || (c.hidden_dim / c.tp_size) % unit != 0)
         return fail(KMLL_ERR_SHAPE, "decoder config: every (sharded) input dimension must be a multiple of %d", unit);
     if (c.kv_bf16 != 0 && c.kv_bf16 != 1) return fail(KMLL_ERR_SHAPE, "decoder config: kv_bf16 must be 0 or 1");
+    if (c.sliding_window < 0) return fail(KMLL_ERR_SHAPE, "decoder config: sliding_window must be 0 (off) or a positive number of positions");
     return KMLL_OK;
 }
 
@@ -294,14 +295,15 @@ static int enqueue_step_fused(Decoder* d, cudaStream_t s, int* launches) {
         if (c.rotary_dim == c.head_dim) {
             // RoPE of q and of the new K row and the KV-cache write happen inside the attention kernel
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache, 1, 0, c.kv_bf16));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache, 1, 0, c.kv_bf16,
+                                             c.sliding_window));
             ++n;
         } else {
             KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache, c.kv_bf16));
             KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0,
-                                             c.kv_bf16));
+                                             c.kv_bf16, c.sliding_window));
             n += 2;
         }
         KMLL_TRY(row_parallel_residual(d, s, d->attn, L.wo, hidden, d->hidden_mid, peer ? 2 * l : -1));
@@ -441,13 +443,14 @@ static int enqueue_step_chain(Decoder* d, cudaStream_t s, int* launches) {
         KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1));
         if (c.rotary_dim == c.head_dim) {
             KMLL_TRY(decode_attention_launch(s, d->q, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache, 1, 0, c.kv_bf16));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, d->k, d->v, d->freqs, L.key_cache, L.value_cache, 1, 0, c.kv_bf16,
+                                             c.sliding_window));
         } else {
             KMLL_TRY(prepare_incremental_dyn(s, d->q, d->k, d->v, d->freqs, c.rotary_dim / 2, d->state, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->q_rot, L.key_cache, L.value_cache, c.kv_bf16));
             KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, &d->state->seq_len, 0, c.max_seq_len, d->n_heads_l,
                                              d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0,
-                                             c.kv_bf16));
+                                             c.kv_bf16, c.sliding_window));
         }
         ChainParams cp;
         memset(&cp, 0, sizeof(cp));
@@ -583,11 +586,12 @@ static int enqueue_step_unfused(Decoder* d, cudaStream_t s, uint32_t token, int 
         KMLL_TRY(apply_qk_norm(d, s, L, d->q, d->k, 1));
         KMLL_TRY(kmll_apply_rope(s, d->q, d->freqs, nf, position, c.head_dim, (size_t)q_len, d->q_rot));
         KMLL_TRY(kmll_apply_rope(s, d->k, d->freqs, nf, position, c.head_dim, (size_t)kv_len, d->k_rot));
-        if (c.kv_bf16) {  // the same three operators over a bf16 cache (the C-ABI forms are f32 only)
-            KMLL_TRY(write_kv_row(s, d->k_rot, position, kv_len, c.head_dim, L.key_cache, 1));
-            KMLL_TRY(write_kv_row(s, d->v, position, kv_len, c.head_dim, L.value_cache, 1));
+        if (c.kv_bf16 || c.sliding_window > 0) {  // the same three operators with the options kmll's forms do not have
+            KMLL_TRY(write_kv_row(s, d->k_rot, position, kv_len, c.head_dim, L.key_cache, c.kv_bf16));
+            KMLL_TRY(write_kv_row(s, d->v, position, kv_len, c.head_dim, L.value_cache, c.kv_bf16));
             KMLL_TRY(decode_attention_launch(s, d->q_rot, L.key_cache, L.value_cache, nullptr, position + 1, c.max_seq_len, d->n_heads_l,
-                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0, 1));
+                                             d->n_kv_l, c.head_dim, d->attn_ws, d->attn, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0,
+                                             c.kv_bf16, c.sliding_window));
         } else {
             KMLL_TRY(kmll_write_kv_cache(s, d->k_rot, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.key_cache));
             KMLL_TRY(kmll_write_kv_cache(s, d->v, position, c.max_seq_len, d->n_kv_l, c.head_dim, L.value_cache));
@@ -793,7 +797,7 @@ static int enqueue_batch_step(BatchDecoder* b, cudaStream_t s, int* launches) {
         KMLL_TRY(apply_qk_norm(d, s, L, b->q, b->k, B));
         KMLL_TRY(decode_attention_launch(s, b->q, b->key_cache[l], b->value_cache[l], &b->state->seq_len, 0, c.max_seq_len, c.n_heads,
                                          c.n_kv_heads, c.head_dim, b->attn_ws, b->attn, b->k, b->v, d->freqs, b->key_cache[l],
-                                         b->value_cache[l], B, b->cache_stride, c.kv_bf16));
+                                         b->value_cache[l], B, b->cache_stride, c.kv_bf16, c.sliding_window));
         {
             const void* w[1] = {L.wo.w};
             const void* sc[1] = {L.wo.scales};
@@ -1298,7 +1302,8 @@ int kmll_decoder_prefill(kmll_decoder_t dec, kmll_stream_t stream, const uint32_
             KMLL_TRY(apply_qk_norm(d, s, L, qb, kb, n));
             KMLL_TRY(prepare_prefill_offset(s, qb, kb, vb, d->freqs, c.rotary_dim / 2, n, q_len, kv_len, c.head_dim, 0, qrb, L.key_cache,
                                             L.value_cache, c.kv_bf16));
-            KMLL_TRY(prefill_attention_launch(s, qrb, L.key_cache, L.value_cache, n, d->n_heads_l, d->n_kv_l, c.head_dim, ab, c.kv_bf16));
+            KMLL_TRY(prefill_attention_launch(s, qrb, L.key_cache, L.value_cache, n, d->n_heads_l, d->n_kv_l, c.head_dim, ab, c.kv_bf16,
+                                              c.sliding_window));
             KMLL_TRY(op_linear_batched(d, s, ab, L.wo, n, ws, ob));
             KMLL_TRY(tp_allreduce(d, s, ob, (size_t)n * c.dim));
             KMLL_TRY(kmll_add_prefix(s, xb, ob, (size_t)n * c.dim, x2b));

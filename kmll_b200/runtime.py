@@ -24,7 +24,7 @@ class _Config(C.Structure):
     _fields_ = [("n_layers", C.c_int), ("dim", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("head_dim", C.c_int),
                 ("hidden_dim", C.c_int), ("vocab_size", C.c_int), ("rotary_dim", C.c_int), ("rope_theta", C.c_float),
                 ("norm_eps", C.c_float), ("max_seq_len", C.c_int), ("format", C.c_int), ("fused", C.c_int), ("tp_rank", C.c_int),
-                ("tp_size", C.c_int), ("kv_bf16", C.c_int)]
+                ("tp_size", C.c_int), ("kv_bf16", C.c_int), ("sliding_window", C.c_int)]
 
 
 @dataclass
@@ -46,6 +46,7 @@ class DecoderConfig:
     tp_rank: int = 0
     tp_size: int = 1
     kv_bf16: bool = False  # KV cache in bf16 (not kmll's f32 rows): half the cache bytes and attention traffic
+    sliding_window: int = 0  # > 0: attend only the last `sliding_window` positions (kmll: full causal attention only)
 
     @staticmethod
     def mistral_7b(**kw) -> "DecoderConfig":
@@ -66,7 +67,7 @@ class DecoderConfig:
     def _c(self) -> _Config:
         return _Config(self.n_layers, self.dim, self.n_heads, self.n_kv_heads, self.head_dim, self.hidden_dim, self.vocab_size,
                        self.rotary_dim or self.head_dim, self.rope_theta, self.norm_eps, self.max_seq_len, self.format,
-                       1 if self.fused else 0, self.tp_rank, self.tp_size, 1 if self.kv_bf16 else 0)
+                       1 if self.fused else 0, self.tp_rank, self.tp_size, 1 if self.kv_bf16 else 0, int(self.sliding_window))
 
 
 def _tensor_shape(cfg: DecoderConfig, tensor: int, sharded: bool):

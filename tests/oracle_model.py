@@ -56,8 +56,9 @@ class OracleDecoder:
                 k_row, v = oracle.bf16_to_f32(oracle.bf16_from_f32(k_row)), oracle.bf16_to_f32(oracle.bf16_from_f32(v))
             self.key[l][pos] = k_row
             self.value[l][pos] = v
-            attn = oracle.single_query_attention(q_rot, self.key[l][:pos + 1], self.value[l][:pos + 1], pos + 1, c.n_heads, c.n_kv_heads,
-                                                 c.head_dim)
+            lo = max(0, pos + 1 - c.sliding_window) if c.sliding_window > 0 else 0  # sliding window: the last rows only
+            attn = oracle.single_query_attention(q_rot, self.key[l][lo:pos + 1], self.value[l][lo:pos + 1], pos + 1 - lo, c.n_heads,
+                                                 c.n_kv_heads, c.head_dim)
             hidden = oracle.add(hidden, self.matvec(L["wo"], attn))
             normed = oracle.rmsnorm(hidden, L["ffn_norm"], c.norm_eps)
             act = oracle.silu_mul(self.matvec(L["w1"], normed), self.matvec(L["w3"], normed))

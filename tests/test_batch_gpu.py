@@ -72,12 +72,12 @@ def test_batch_gqa_head_dim_128(cuda, kv_bf16):
     dec.close()
 
 
-@pytest.mark.parametrize("kv_bf16", [False, True])
-def test_batch_attention_with_several_tiles_per_block(cuda, kv_bf16):
+@pytest.mark.parametrize("kv_bf16,window", [(False, 0), (True, 0), (False, 90)])
+def test_batch_attention_with_several_tiles_per_block(cuda, kv_bf16, window):
     """16 sequences x 8 KV heads fill the GPU along the batch axis, so the attention plan gives every block a slice of
     several 64-position tiles (here 128 positions); with 200-token prompts the position being written lies in the second
     tile of its block - the fused RoPE + KV-write + prefetch path with t0 > 0."""
-    cfg = _cfg(rt.FORMAT_W4G128, n_heads=8, n_kv_heads=8, head_dim=64, dim=512, max_seq_len=400, kv_bf16=kv_bf16)
+    cfg = _cfg(rt.FORMAT_W4G128, n_heads=8, n_kv_heads=8, head_dim=64, dim=512, max_seq_len=400, kv_bf16=kv_bf16, sliding_window=window)
     dec = rt.Decoder(cfg)
     dec.init_random(11, 0.05, False)
     rng = np.random.default_rng(2)

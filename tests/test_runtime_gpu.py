@@ -54,6 +54,29 @@ def test_decode_matches_oracle(cuda, fmt, fused):
     dec.close()
 
 
+@pytest.mark.parametrize("fmt", [rt.FORMAT_RS_I8, rt.FORMAT_W4G128])
+@pytest.mark.parametrize("window", [1, 24, 70])
+@pytest.mark.parametrize("batched_prefill", [False, True])
+def test_sliding_window_matches_oracle(cuda, fmt, window, batched_prefill):
+    """sliding_window: the oracle attends the last `window` rows of its cache.  max_seq_len 200 gives the decode kernel
+    four 52-position slices; with 110-token prompts a window of 24 lies inside one slice or straddles two, one of 70
+    covers slices partly, and the slices before the window leave without a partial.  f32 cache: the f32 tolerances."""
+    cfg = tiny(fmt, True, n_heads=8, n_kv_heads=2, head_dim=128, dim=256, max_seq_len=200, sliding_window=window)
+    dec = make(cfg)
+    prompt = np.random.default_rng(window).integers(0, cfg.vocab_size, 110)
+    check_against_oracle(dec, cfg, prompt, 8, batched_prefill=batched_prefill)
+    dec.close()
+
+
+def test_sliding_window_other_step_forms_and_bf16(cuda):
+    for fused, rotary_dim, kv_bf16 in [(False, None, False), (True, 32, False), (True, None, True)]:
+        cfg = tiny(rt.FORMAT_W4G128, fused, rotary_dim=rotary_dim, max_seq_len=96, sliding_window=20, kv_bf16=kv_bf16)
+        dec = make(cfg)
+        prompt = np.random.default_rng(6).integers(0, cfg.vocab_size, 66)
+        check_against_oracle(dec, cfg, prompt, 5, batched_prefill=fused, **(BF16_KV_BOUND if kv_bf16 else {}))
+        dec.close()
+
+
 BF16_KV_BOUND = dict(hid_tol=2e-3, min_margin=1e-2, logit_tol=5e-3)
 
 
