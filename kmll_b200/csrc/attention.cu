@@ -130,6 +130,151 @@ __device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;"
 template <int N>
 __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// End of a block of the decode attention kernels.  On entry `red` holds NW planes [gq][HD] of un-normalised
+// accumulators (summed here) and hstat[h * 4], hstat[h * 4 + 1] the block's running max and sum per head, all
+// visible to the block.  Writes the result (one split) or this split's partial; the last block of each KV head to
+// arrive merges the partials.  `scratch` is shared memory of at least 3 * GQM * 64 + GQM floats that is free.
+template <int HD, int GQM, int NW>
+__device__ __forceinline__ void finish_split(const DecodeAttnParams& p, int kv_head, int split, int nactive, float* red,
+                                             float* hstat, float* scratch, bool* is_last) {
+    constexpr int EPL = HD / 32;
+    const int gq = p.gq;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* const Ks = scratch;
+    float acc[GQM][EPL];
+    pdl_launch_dependents();
+
+    // write this split's partial (or the final result when there is a single split)
+#pragma unroll 1
+    for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
+        const int h = idx / HD, d = idx - h * HD;
+        const int head = kv_head * gq + h;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) v += red[(w * gq + h) * HD + d];
+        if (p.nsplit == 1) {
+            p.out[(size_t)head * HD + d] = v / hstat[h * 4 + 1];
+        } else {
+            p.part_acc[((size_t)head * p.nsplit + split) * HD + d] = v;
+            if (d == 0) {
+                p.part_ml[((size_t)head * p.nsplit + split) * 2] = hstat[h * 4];
+                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = hstat[h * 4 + 1];
+            }
+        }
+    }
+    trace_stamp(p.trace, 3);
+    if (p.nsplit == 1) return;
+
+    // last block of this KV head merges the splits
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int prev = atomicAdd(&p.counters[kv_head], 1u);
+        *is_last = (prev == (unsigned int)nactive - 1);
+    }
+    __syncthreads();
+    if (!*is_last) return;
+    __threadfence();
+    // merge: bring every split's (max, sum) into shared memory, derive the weights exp(m_s - m) once per head,
+    // then combine the partial accumulators - warp w takes splits w, w+8, ... for all heads, so every load of a
+    // round is independent of the others and a handful of L2 round trips cover the whole merge
+    float* ml_s = Ks;                       // [gq][nsplit][2]
+    float* f_s = Ks + 2 * GQM * 64;      // [gq][nsplit] weights, then [gq] denominators after them
+    float* l_s = f_s + GQM * 64;
+    const int ns = nactive;  // only these splits wrote partials
+    // the first round of partial accumulators (splits w, w+8, w+16, w+24) is requested before the statistics are even
+    // loaded, so that both L2 round trips overlap (only where the registers allow it: 4 heads x 4 floats per lane)
+    constexpr bool kHoist = (GQM == 4 && EPL == 4);
+    float4 early[kHoist ? 4 : 1][kHoist ? GQM : 1];
+    if (kHoist) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sp = warp + kAttnWarps * i;
+#pragma unroll
+            for (int h = 0; h < GQM; ++h) {
+                early[kHoist ? i : 0][kHoist ? h : 0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (h < gq && sp < ns)
+                    early[kHoist ? i : 0][kHoist ? h : 0] = __ldcg(reinterpret_cast<const float4*>(
+                        p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + sp) * HD + lane * EPL));
+            }
+        }
+    }
+#pragma unroll 1
+    for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
+        const int h = idx / (ns * 2), r = idx - h * ns * 2;
+        ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * p.nsplit * 2 + r);
+    }
+    __syncthreads();
+    if (warp < gq) {
+        const int h = warp;
+        const float m_a = lane < ns ? ml_s[(h * ns + lane) * 2] : -INFINITY;
+        const float m_b = lane + 32 < ns ? ml_s[(h * ns + lane + 32) * 2] : -INFINITY;
+        const float m = warp_max(fmaxf(m_a, m_b));
+        const float f_a = m_a == -INFINITY ? 0.0f : expf(m_a - m), f_b = m_b == -INFINITY ? 0.0f : expf(m_b - m);
+        float l = 0.0f;
+        if (lane < ns) { f_s[h * ns + lane] = f_a; l += ml_s[(h * ns + lane) * 2 + 1] * f_a; }
+        if (lane + 32 < ns) { f_s[h * ns + lane + 32] = f_b; l += ml_s[(h * ns + lane + 32) * 2 + 1] * f_b; }
+        l = warp_sum(l);
+        if (lane == 0) l_s[h] = l;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < GQM; ++h)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
+    if (kHoist) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sp = warp + kAttnWarps * i;
+#pragma unroll
+            for (int h = 0; h < GQM; ++h)
+                if (h < gq && sp < ns) {
+                    const float4 t4 = early[kHoist ? i : 0][kHoist ? h : 0];
+                    const float f = f_s[h * ns + sp];
+                    acc[h][0] = fmaf(t4.x, f, acc[h][0]);
+                    acc[h][1] = fmaf(t4.y, f, acc[h][1]);
+                    acc[h][EPL - 2] = fmaf(t4.z, f, acc[h][EPL - 2]);
+                    acc[h][EPL - 1] = fmaf(t4.w, f, acc[h][EPL - 1]);
+                }
+        }
+    }
+#pragma unroll(GQM == 4 ? 4 : 2)
+    for (int s = warp + (kHoist ? 4 * kAttnWarps : 0); s < ns; s += kAttnWarps) {
+#pragma unroll
+        for (int h = 0; h < GQM; ++h)
+            if (h < gq) {
+                float pv[EPL];
+                const float* src = p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + s) * HD + lane * EPL;
+                if (EPL == 4) {
+                    const float4 t4 = __ldcg(reinterpret_cast<const float4*>(src));
+                    pv[0] = t4.x; pv[1] = t4.y; pv[EPL - 2] = t4.z; pv[EPL - 1] = t4.w;
+                } else {
+                    const float2 t2 = __ldcg(reinterpret_cast<const float2*>(src));
+                    pv[0] = t2.x; pv[1] = t2.y;
+                }
+                const float f = f_s[h * ns + s];
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(pv[e], f, acc[h][e]);
+            }
+    }
+#pragma unroll
+    for (int h = 0; h < GQM; ++h)
+        if (h < gq)
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
+    __syncthreads();
+#pragma unroll 1
+    for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
+        const int h = idx / HD, d = idx - h * HD;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
+        p.out[(size_t)(kv_head * gq + h) * HD + d] = v / l_s[h];
+    }
+    if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
+    trace_stamp(p.trace, 4);
+}
+
 // One block = one KV head x one slice of the sequence.  The K and V rows of up to 64 positions are
 // brought into shared memory with 16-byte asynchronous copies that are all issued up front
 // (64 KB in flight per block, two blocks per SM), so the f32 KV cache streams at HBM rate; the
@@ -312,12 +457,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll 1
             for (int h = 0; h < gq; ++h) {
                 const float* qr = qs + h * HD + c * 4;
-                float v = 0.0f;
+                // two packed accumulators (even / odd dims of each 16-byte piece): half the multiply-add instructions
+                float2 v2 = make_float2(0.0f, 0.0f), w2 = make_float2(0.0f, 0.0f);
 #pragma unroll
                 for (int i = 0; i < HD / 16; ++i) {
                     const float4 qq = *reinterpret_cast<const float4*>(qr + i * 16);
-                    v = fmaf(kk[i].x, qq.x, fmaf(kk[i].y, qq.y, fmaf(kk[i].z, qq.z, fmaf(kk[i].w, qq.w, v))));
+                    v2 = __ffma2_rn(make_float2(kk[i].x, kk[i].y), make_float2(qq.x, qq.y), v2);
+                    w2 = __ffma2_rn(make_float2(kk[i].z, kk[i].w), make_float2(qq.z, qq.w), w2);
                 }
+                float v = (v2.x + w2.x) + (v2.y + w2.y);
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 if (c == 0 && pl < nt) sc[h * kAttnTile + pl] = v * scale;
@@ -386,7 +534,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
                 if (h < gq) {
                     const float w = sc[h * kAttnTile + i];
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(w, vv[e], acc[h][e]);
+                    for (int e = 0; e < EPL; e += 2) {
+                        const float2 r2 = __ffma2_rn(make_float2(w, w), make_float2(vv[e], vv[e + 1]), make_float2(acc[h][e], acc[h][e + 1]));
+                        acc[h][e] = r2.x;
+                        acc[h][e + 1] = r2.y;
+                    }
                 }
             }
         }
@@ -399,137 +551,282 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll
             for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
     __syncthreads();
-    pdl_launch_dependents();
+    finish_split<HD, GQM, kAttnWarps>(p, kv_head, split, nactive, red, hstat, Ks, &is_last);
+}
 
-    // write this split's partial (or the final result when there is a single split)
-#pragma unroll 1
-    for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
-        const int h = idx / HD, d = idx - h * HD;
-        const int head = kv_head * gq + h;
-        float v = 0.0f;
+// ---- decode attention over a bf16 KV cache: tensor-core form ------------------------------------------
+// The f32 kernel above spends its time issuing multiply-adds (about 950 instructions per thread and 64-position tile);
+// with bf16 rows the two contractions fit the tensor cores without touching the cache values: K and V are MMA operands
+// exactly as stored, and the f32 side of each product (the query, the softmax weights) is split into a bf16 head and a
+// bf16 remainder, two MMAs with f32 accumulation (16 mantissa bits of the f32 operand, products exact).
+//   S[h][pos] = q[h] . K[pos]:  A = query heads (rows 0..gq-1 of a 16-row fragment, built once per block),
+//                               B = K tile as it lies in shared memory ([pos][dim], ldmatrix); warp w owns positions 8w..8w+7
+//   O[h][dim] += P[h][pos] V[pos][dim]:  A = softmax weights of the tile, B = V tile ([pos][dim], ldmatrix.trans);
+//                               warp w owns dims w*HD/8 .. of every head, so no cross-warp reduction at the end
+// Tiles of 64 positions in a two-stage ring: the K and V rows of tile t+1 are requested before tile t is touched.
+// Rows are padded by 16 bytes so that the 8 row addresses of an ldmatrix fall in distinct banks; rows a tile does not
+// have are zero-filled by the copy.  Range, split plan, fused RoPE + row write and the split merge are those of the
+// f32 kernel.
+__device__ inline void cp_async16_zfill(void* smem_dst, const void* gmem_src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ inline void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row))
+                 : "memory");
+}
+__device__ inline void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row))
+                 : "memory");
+}
+__device__ inline void ldmatrix_x2_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1])
+                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row))
+                 : "memory");
+}
+// D += A * B, m16n8k16, bf16 operands, f32 accumulate; only rows 0..7 of A are populated (a1 = a3 = 0)
+__device__ inline void mma_bf16_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// (x0, x1) -> bf16 pair of the values rounded to nearest-even (x0 in the low half) and bf16 pair of the remainders
+__device__ inline void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(x1), "f"(x0));
+    const float r0 = x0 - __uint_as_float(hi << 16), r1 = x1 - __uint_as_float(hi & 0xffff0000u);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(r1), "f"(r0));
+}
+
+template <int HD, int GQM>
+__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(const DecodeAttnParams p_in) {
+    DecodeAttnParams p = p_in;
+    if (gridDim.z > 1) {  // sequence blockIdx.z of a batch: shift every per-sequence operand
+        const size_t b = blockIdx.z;
+        const size_t cache_shift = b * p.cache_stride * 2;
+        p.q += b * p.q_stride;
+        p.out += b * p.out_stride;
+        p.k_cache = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.k_cache) + cache_shift);
+        p.v_cache = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.v_cache) + cache_shift);
+        if (p.k_new != nullptr) {
+            p.k_new += b * p.new_stride;
+            p.v_new += b * p.new_stride;
+            p.k_cache_w = reinterpret_cast<float*>(reinterpret_cast<char*>(p.k_cache_w) + cache_shift);
+            p.v_cache_w = reinterpret_cast<float*>(reinterpret_cast<char*>(p.v_cache_w) + cache_shift);
+        }
+        p.part_acc += b * p.ws_stride;
+        p.part_ml += b * p.ws_stride;
+        p.counters += b * p.ws_stride;
+    }
+    constexpr int EPL = HD / 32;          // elements per lane where a warp holds one row (query, new K / V row)
+    constexpr int RP = HD + 8;            // padded row, elements
+    constexpr int ROWB = RP * 2;          // bytes per staged row
+    constexpr int V16 = HD / 8;           // 16-byte pieces per row
+    constexpr int TILEB = kAttnTile * ROWB;
+    constexpr int KSTEPS = HD / 16;       // MMA k-steps over the head dimension
+    constexpr int NBW = HD / 64;          // 8-dim output blocks per warp (8 warps cover the head dimension)
+    constexpr int SCP = kAttnTile + 8;    // padded score row: the fragment accesses of four heads fall in distinct banks
+    extern __shared__ __align__(16) float smem[];
+    char* const tiles = reinterpret_cast<char*>(smem);                // [2 stages][K tile, V tile]
+    float* sc = reinterpret_cast<float*>(tiles + 4 * TILEB);          // [GQM][SCP] scores, then weights
+    float* hstat = sc + GQM * SCP;                              // [GQM][4]: running max, running sum, correction
+    float* qs = hstat + GQM * 4;                                      // [GQM][HD] rotated query heads
+    float* red = reinterpret_cast<float*>(tiles + 2 * TILEB);         // after the loop: [kAttnWarps][gq][HD]
+    __shared__ bool is_last;
+    __shared__ float2 cs_sn[HD / 2];
+
+    trace_stamp(p.trace, 0);
+    const int kv_head = blockIdx.x, gq = p.gq;
+    int split = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t kv_stride = (size_t)p.n_kv_heads * HD;
+    const bool fused = p.k_new != nullptr;
+    int s0 = split * p.chunk;
+    int seq_len = 0, n = 0, first_split = 0;
+    auto set_range = [&]() {
+        seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
+        const int lo = (p.window > 0 && seq_len > p.window) ? seq_len - p.window : 0;
+        first_split = lo / p.chunk;
+        const int slice_end = min(s0 + p.chunk, seq_len);
+        s0 = max(s0, lo);
+        n = slice_end - s0;
+    };
+    // K and V rows of tile t into stage t & 1, one commit group (also when the tile does not exist)
+    auto issue_tile = [&](int t) {
+        const int t0 = t * kAttnTile;
+        const int nt = n - t0;
+        if (nt > 0) {
+            char* ks = tiles + (t & 1) * 2 * TILEB;
+            char* vs = ks + TILEB;
+            const size_t g0 = ((size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD) * 2;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
-        if (p.nsplit == 1) {
-            p.out[(size_t)head * HD + d] = v / hstat[h * 4 + 1];
-        } else {
-            p.part_acc[((size_t)head * p.nsplit + split) * HD + d] = v;
-            if (d == 0) {
-                p.part_ml[((size_t)head * p.nsplit + split) * 2] = hstat[h * 4];
-                p.part_ml[((size_t)head * p.nsplit + split) * 2 + 1] = hstat[h * 4 + 1];
+            for (int i = tid; i < kAttnTile * V16; i += kAttnThreads) {
+                const int r = i / V16, cidx = i - r * V16;
+                const bool have = r < nt;
+                const size_t off = g0 + (have ? (size_t)r * kv_stride * 2 : 0) + cidx * 16;
+                cp_async16_zfill(ks + r * ROWB + cidx * 16, reinterpret_cast<const char*>(p.k_cache) + off, have ? 16u : 0u);
+                cp_async16_zfill(vs + r * ROWB + cidx * 16, reinterpret_cast<const char*>(p.v_cache) + off, have ? 16u : 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    if (fused) {
+        set_range();
+        if (n > 0) {
+            issue_tile(0);  // rows below seq_len - 1 were written by earlier steps
+            if (tid < HD / 2) {
+                float sn, cs;
+                sincosf((float)(seq_len - 1) * p.freqs[tid], &sn, &cs);
+                cs_sn[tid] = make_float2(cs, sn);
             }
         }
     }
-    trace_stamp(p.trace, 3);
-    if (p.nsplit == 1) return;
+    if (tid < GQM) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
+    pdl_wait();
+    trace_stamp(p.trace, 1);
+    if (!fused) set_range();
+    const int nactive = (seq_len + p.chunk - 1) / p.chunk - first_split;
+    if (n <= 0) return;
+    split -= first_split;
+    if (!fused) issue_tile(0);
+    const float scale = 1.0f / sqrtf((float)HD);
 
-    // last block of this KV head merges the splits
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned int prev = atomicAdd(&p.counters[kv_head], 1u);
-        is_last = (prev == (unsigned int)nactive - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // merge: bring every split's (max, sum) into shared memory, derive the weights exp(m_s - m) once per head,
-    // then combine the partial accumulators - warp w takes splits w, w+8, ... for all heads, so every load of a
-    // round is independent of the others and a handful of L2 round trips cover the whole merge
-    float* ml_s = Ks;                       // [gq][nsplit][2]
-    float* f_s = Ks + 2 * GQM * 64;      // [gq][nsplit] weights, then [gq] denominators after them
-    float* l_s = f_s + GQM * 64;
-    const int ns = nactive;  // only these splits wrote partials
-    // the first round of partial accumulators (splits w, w+8, w+16, w+24) is requested before the statistics are even
-    // loaded, so that both L2 round trips overlap (only where the registers allow it: 4 heads x 4 floats per lane)
-    constexpr bool kHoist = (GQM == 4 && EPL == 4);
-    float4 early[kHoist ? 4 : 1][kHoist ? GQM : 1];
-    if (kHoist) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int sp = warp + kAttnWarps * i;
-#pragma unroll
-            for (int h = 0; h < GQM; ++h) {
-                early[kHoist ? i : 0][kHoist ? h : 0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (h < gq && sp < ns)
-                    early[kHoist ? i : 0][kHoist ? h : 0] = __ldcg(reinterpret_cast<const float4*>(
-                        p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + sp) * HD + lane * EPL));
-            }
-        }
-    }
-#pragma unroll 1
-    for (int idx = tid; idx < gq * ns * 2; idx += kAttnThreads) {
-        const int h = idx / (ns * 2), r = idx - h * ns * 2;
-        ml_s[idx] = __ldcg(p.part_ml + (size_t)(kv_head * gq + h) * p.nsplit * 2 + r);
-    }
-    __syncthreads();
+    const int newpos = seq_len - 1 - s0;  // position being written, relative to this block's slice
+    const bool owns_new = fused && newpos >= 0 && newpos < n;
+    float qh[EPL], kvn[EPL];
+    if (warp < gq) load_lane_slice<EPL>(p.q + (size_t)(kv_head * gq + warp) * HD + lane * EPL, qh);
+    if (owns_new && warp == kAttnWarps - 2) load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kvn);
+    if (owns_new && warp == kAttnWarps - 1) load_lane_slice<EPL>(p.v_new + (size_t)kv_head * HD + lane * EPL, kvn);
+    if (fused) __syncthreads();  // cs_sn is visible
     if (warp < gq) {
-        const int h = warp;
-        const float m_a = lane < ns ? ml_s[(h * ns + lane) * 2] : -INFINITY;
-        const float m_b = lane + 32 < ns ? ml_s[(h * ns + lane + 32) * 2] : -INFINITY;
-        const float m = warp_max(fmaxf(m_a, m_b));
-        const float f_a = m_a == -INFINITY ? 0.0f : expf(m_a - m), f_b = m_b == -INFINITY ? 0.0f : expf(m_b - m);
-        float l = 0.0f;
-        if (lane < ns) { f_s[h * ns + lane] = f_a; l += ml_s[(h * ns + lane) * 2 + 1] * f_a; }
-        if (lane + 32 < ns) { f_s[h * ns + lane + 32] = f_b; l += ml_s[(h * ns + lane + 32) * 2 + 1] * f_b; }
-        l = warp_sum(l);
-        if (lane == 0) l_s[h] = l;
+        if (fused) rope_lane_slice<EPL>(qh, cs_sn, lane);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) qs[warp * HD + lane * EPL + e] = qh[e];
     }
-    __syncthreads();
+    if (owns_new && warp == kAttnWarps - 2) rope_lane_slice<EPL>(kvn, cs_sn, lane);
+    __syncthreads();  // qs is visible
+
+    // A fragments of the query heads: row g = head, this lane's column pairs of every k-step, head and remainder
+    const int g = lane >> 2, tq = lane & 3;
+    uint32_t qhi[KSTEPS][2], qlo[KSTEPS][2];
 #pragma unroll
-    for (int h = 0; h < GQM; ++h)
+    for (int ks = 0; ks < KSTEPS; ++ks)
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[h][e] = 0.0f;
-    if (kHoist) {
+        for (int half = 0; half < 2; ++half) {
+            float2 x = make_float2(0.0f, 0.0f);
+            if (g < gq) x = *reinterpret_cast<const float2*>(qs + g * HD + ks * 16 + half * 8 + tq * 2);
+            split_bf16x2(x.x, x.y, qhi[ks][half], qlo[ks][half]);
+        }
+    float o[NBW][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int sp = warp + kAttnWarps * i;
+    for (int nb = 0; nb < NBW; ++nb)
 #pragma unroll
-            for (int h = 0; h < GQM; ++h)
-                if (h < gq && sp < ns) {
-                    const float4 t4 = early[kHoist ? i : 0][kHoist ? h : 0];
-                    const float f = f_s[h * ns + sp];
-                    acc[h][0] = fmaf(t4.x, f, acc[h][0]);
-                    acc[h][1] = fmaf(t4.y, f, acc[h][1]);
-                    acc[h][EPL - 2] = fmaf(t4.z, f, acc[h][EPL - 2]);
-                    acc[h][EPL - 1] = fmaf(t4.w, f, acc[h][EPL - 1]);
+        for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
+
+    const int ntiles = (n + kAttnTile - 1) / kAttnTile;
+#pragma unroll 1
+    for (int t = 0; t < ntiles; ++t) {
+        cp_async_wait<0>();  // tile t has landed (this thread's copies; the barrier covers everybody's)
+        __syncthreads();     // ... and every warp is done with tile t - 1: its stage and the weights are free
+        issue_tile(t + 1);
+        char* const ks_t = tiles + (t & 1) * 2 * TILEB;
+        char* const vs_t = ks_t + TILEB;
+        const int nt = min(kAttnTile, n - t * kAttnTile);
+        const int newrow = newpos - t * kAttnTile;
+        if (owns_new && newrow >= 0 && newrow < nt) {  // block-uniform
+            if (warp >= kAttnWarps - 2) {
+                char* const tile = warp == kAttnWarps - 2 ? ks_t : vs_t;
+                uint16_t* const cache_w = reinterpret_cast<uint16_t*>(warp == kAttnWarps - 2 ? p.k_cache_w : p.v_cache_w);
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    const uint16_t bits = f32_to_bf16_bits(kvn[e]);
+                    reinterpret_cast<uint16_t*>(tile + newrow * ROWB)[lane * EPL + e] = bits;
+                    cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = bits;
                 }
+            }
+            __syncthreads();
+        }
+        // scores of positions 8 * warp .. + 7 for every head
+        {
+            float ch[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cl[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int k2 = 0; k2 < KSTEPS / 2; ++k2) {
+                uint32_t b[4];  // 8 positions x 32 dims: B fragments of two k-steps
+                ldmatrix_x4(b, ks_t + (warp * 8 + (lane & 7)) * ROWB + (k2 * 32 + (lane >> 3) * 8) * 2);
+                mma_bf16_rows8(ch, qhi[2 * k2][0], qhi[2 * k2][1], b[0], b[1]);
+                mma_bf16_rows8(cl, qlo[2 * k2][0], qlo[2 * k2][1], b[0], b[1]);
+                mma_bf16_rows8(ch, qhi[2 * k2 + 1][0], qhi[2 * k2 + 1][1], b[2], b[3]);
+                mma_bf16_rows8(cl, qlo[2 * k2 + 1][0], qlo[2 * k2 + 1][1], b[2], b[3]);
+            }
+            if (g < gq)
+                *reinterpret_cast<float2*>(sc + g * SCP + warp * 8 + tq * 2) = make_float2((ch[0] + cl[0]) * scale, (ch[1] + cl[1]) * scale);
+        }
+        __syncthreads();
+        // running softmax statistics: one warp per query head (rows the tile does not have get weight 0)
+        if (warp < gq) {
+            const int h = warp;
+            const float m_old = hstat[h * 4], l_old = hstat[h * 4 + 1];
+            const float s_a = lane < nt ? sc[h * SCP + lane] : -INFINITY;
+            const float s_b = lane + 32 < nt ? sc[h * SCP + lane + 32] : -INFINITY;
+            const float m = warp_max(fmaxf(m_old, fmaxf(s_a, s_b)));
+            const float e_a = lane < nt ? expf(s_a - m) : 0.0f, e_b = lane + 32 < nt ? expf(s_b - m) : 0.0f;
+            sc[h * SCP + lane] = e_a;
+            sc[h * SCP + lane + 32] = e_b;
+            const float l = warp_sum(e_a + e_b);
+            const float corr = expf(m_old - m);  // exp(-inf) = 0 on the first tile
+            if (lane == 0) { hstat[h * 4] = m; hstat[h * 4 + 1] = l_old * corr + l; hstat[h * 4 + 2] = corr; }
+        }
+        __syncthreads();
+        // weighted sum of V: dims warp * HD/8 .. of every head
+        {
+            const float corr = g < gq ? hstat[g * 4 + 2] : 0.0f;
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) { o[nb][0] *= corr; o[nb][1] *= corr; }
+            float ol[NBW][4];
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ol[nb][e] = 0.0f;
+#pragma unroll
+            for (int k4 = 0; k4 < kAttnTile / 16; ++k4) {
+                float2 pa = make_float2(0.0f, 0.0f), pb = make_float2(0.0f, 0.0f);
+                if (g < gq) {
+                    pa = *reinterpret_cast<const float2*>(sc + g * SCP + k4 * 16 + tq * 2);
+                    pb = *reinterpret_cast<const float2*>(sc + g * SCP + k4 * 16 + 8 + tq * 2);
+                }
+                uint32_t ah0, al0, ah2, al2;
+                split_bf16x2(pa.x, pa.y, ah0, al0);
+                split_bf16x2(pb.x, pb.y, ah2, al2);
+                uint32_t b[4];  // 16 positions x (8 * NBW) dims, transposed on the way in
+                const char* row = vs_t + (k4 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (warp * (HD / 8)) * 2;
+                if (NBW == 2) ldmatrix_x4_trans(b, row + (lane >> 4) * 16);
+                else ldmatrix_x2_trans(b, row);
+                mma_bf16_rows8(o[0], ah0, ah2, b[0], b[1]);
+                mma_bf16_rows8(ol[0], al0, al2, b[0], b[1]);
+                if (NBW == 2) {
+                    mma_bf16_rows8(o[NBW - 1], ah0, ah2, b[2], b[3]);
+                    mma_bf16_rows8(ol[NBW - 1], al0, al2, b[2], b[3]);
+                }
+            }
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) { o[nb][0] += ol[nb][0]; o[nb][1] += ol[nb][1]; }
         }
     }
-#pragma unroll(GQM == 4 ? 4 : 2)
-    for (int s = warp + (kHoist ? 4 * kAttnWarps : 0); s < ns; s += kAttnWarps) {
+    trace_stamp(p.trace, 2);
+    __syncthreads();  // every warp is done with the last tile: the stages are free
+    // every (head, dim) is complete in one lane: one plane for the common end
+    if (g < gq) {
 #pragma unroll
-        for (int h = 0; h < GQM; ++h)
-            if (h < gq) {
-                float pv[EPL];
-                const float* src = p.part_acc + ((size_t)(kv_head * gq + h) * p.nsplit + s) * HD + lane * EPL;
-                if (EPL == 4) {
-                    const float4 t4 = __ldcg(reinterpret_cast<const float4*>(src));
-                    pv[0] = t4.x; pv[1] = t4.y; pv[EPL - 2] = t4.z; pv[EPL - 1] = t4.w;
-                } else {
-                    const float2 t2 = __ldcg(reinterpret_cast<const float2*>(src));
-                    pv[0] = t2.x; pv[1] = t2.y;
-                }
-                const float f = f_s[h * ns + s];
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(pv[e], f, acc[h][e]);
-            }
+        for (int nb = 0; nb < NBW; ++nb)
+            *reinterpret_cast<float2*>(red + g * HD + warp * (HD / 8) + nb * 8 + tq * 2) = make_float2(o[nb][0], o[nb][1]);
     }
-#pragma unroll
-    for (int h = 0; h < GQM; ++h)
-        if (h < gq)
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) red[(warp * gq + h) * HD + lane * EPL + e] = acc[h][e];
     __syncthreads();
-#pragma unroll 1
-    for (int idx = tid; idx < gq * HD; idx += kAttnThreads) {
-        const int h = idx / HD, d = idx - h * HD;
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) v += red[(w * gq + h) * HD + d];
-        p.out[(size_t)(kv_head * gq + h) * HD + d] = v / l_s[h];
-    }
-    if (tid == 0) p.counters[kv_head] = 0;  // leave the counter area zero for the next call
-    trace_stamp(p.trace, 4);
+    finish_split<HD, GQM, 1>(p, kv_head, split, nactive, red, hstat, reinterpret_cast<float*>(tiles), &is_last);
 }
 
 // ---- prefill: tiled causal attention ---------------------------------------------------------------
@@ -643,11 +940,12 @@ static AttnPlan plan_decode_attention(int seq_cap, int kv_heads_times_batch = 0)
     AttnPlan pl;
     int nsplit = (seq_cap + 63) / 64;
     if (nsplit > 64) nsplit = 64;
-    // A batch of sequences already fills the GPU along the batch axis: aim at about two waves of blocks (2 x 296
-    // resident) with longer slices per block instead of many waves of one-tile blocks, each of which would pay the
-    // full latency chain of a block.
+    // A batch of sequences already fills the GPU along the batch axis: aim at one wave of blocks (296 are resident at
+    // two per SM) with longer slices per block.  Measured at 16 sequences x 8 KV heads x 2051 positions: 256 blocks of 17
+    // tiles beat 512 blocks of 9 (a second, partly filled wave) and every finer split (each block pays its own latency
+    // chain: query load, RoPE table, partial results, merge).
     if (kv_heads_times_batch > 0) {
-        int cap = 592 / kv_heads_times_batch;
+        int cap = 296 / kv_heads_times_batch;
         if (cap < 1) cap = 1;
         if (nsplit > cap) nsplit = cap;
     }
@@ -695,8 +993,15 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
         return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem, stream, true, p);
     };
     if (kv_bf16) {
-        if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4, true>) : go(decode_attention_kernel<128, 8, true>);
-        else e = gq <= 4 ? go(decode_attention_kernel<64, 4, true>) : go(decode_attention_kernel<64, 8, true>);
+        // two stages of (K tile, V tile) with padded bf16 rows, scores, statistics, query heads
+        const size_t gqm = gq <= 4 ? 4 : kMaxGq;
+        const size_t smem16 = (size_t)4 * kAttnTile * (head_dim + 8) * 2 + (gqm * (kAttnTile + 8) + gqm * 4 + gqm * head_dim) * sizeof(float);
+        auto go16 = [&](auto kern) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem16, stream, true, p);
+        };
+        if (head_dim == 128) e = gq <= 4 ? go16(decode_attention_bf16_kernel<128, 4>) : go16(decode_attention_bf16_kernel<128, 8>);
+        else e = gq <= 4 ? go16(decode_attention_bf16_kernel<64, 4>) : go16(decode_attention_bf16_kernel<64, 8>);
     } else {
         if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4, false>) : go(decode_attention_kernel<128, 8, false>);
         else e = gq <= 4 ? go(decode_attention_kernel<64, 4, false>) : go(decode_attention_kernel<64, 8, false>);

@@ -40,7 +40,8 @@ DECODE_SUITE = [("qkv", 6144, 4096, 16), ("linear_residual", 4096, 4096, 16), ("
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="linear", choices=["linear", "qkv", "linear_residual", "silu_gate_up", "linear_top1", "attention", "linear_batched"])
+    ap.add_argument("--op", default="linear", choices=["linear", "qkv", "linear_residual", "silu_gate_up", "linear_top1", "attention", "linear_batched",
+                                                        "decode_batch"])
     ap.add_argument("--batch", type=int, default=16, help="rows of x for --op linear_batched (5..32: small-batch kernel; more: tcgen05 f16 kernel)")
     ap.add_argument("--fmt", default="w4", choices=["w4", "w4p", "i8"])
     ap.add_argument("--rows", type=int, default=14336)
@@ -54,6 +55,8 @@ def main():
     ap.add_argument("--shards", type=int, default=1, help="gemm_sweep: time one rank's share of every matrix when its N output rows are split over this "
                                                            "many GPUs (column-parallel: disjoint output blocks, no collective)")
     ap.add_argument("--profile", action="store_true", help="bracket one graph replay with cudaProfilerStart/Stop")
+    ap.add_argument("--layers", type=int, default=2, help="decode_batch: layers of the Mistral-7B-shaped decoder (a small case for profiling)")
+    ap.add_argument("--kv-bf16", action="store_true", help="decode_batch: keep the KV cache in bf16")
     a = ap.parse_args()
     torch.cuda.set_device(0)
     if a.suite == "decode":
@@ -200,7 +203,45 @@ def suite_gemm_sweep(reps, cpu=None, shards=1):
             torch.cuda.empty_cache()
 
 
+def run_decode_batch(a):
+    """--batch sequences in lockstep on a Mistral-7B-shaped decoder of --layers layers, each at context --rows: the whole
+    step per layer (batched linears + attention over --batch caches), small enough for a profiler capture."""
+    import numpy as np
+
+    from . import runtime as rt
+    ctx, B, steps = a.rows, a.batch, max(2, a.reps)
+    cfg = rt.DecoderConfig(n_layers=a.layers, dim=4096, n_heads=32, n_kv_heads=8, head_dim=128, hidden_dim=14336, vocab_size=32000,
+                           rope_theta=1.0e6, norm_eps=1.0e-5, max_seq_len=ctx + steps + 24,
+                           format=rt.FORMAT_RS_I8 if a.fmt == "i8" else rt.FORMAT_W4G128, kv_bf16=a.kv_bf16)
+    dec = rt.Decoder(cfg)
+    dec.init_random(3, 0.02, False)
+    dec.prefill(np.random.default_rng(3).integers(0, cfg.vocab_size, ctx))
+    bd = rt.BatchDecoder(dec, B)
+    for slot in range(B):
+        bd.adopt(slot)
+    bd.generate_greedy(3)
+    torch.cuda.synchronize()
+    if a.profile:
+        torch.cuda.profiler.start()
+        bd.enqueue_steps(1)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    bd.enqueue_steps(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    kv_bytes = a.layers * B * 2 * (ctx + 3 + steps / 2) * 1024 * (2 if a.kv_bf16 else 4)
+    print(json.dumps({"op": "decode_batch", "fmt": a.fmt, "layers": a.layers, "batch": B, "context": ctx, "kv_bf16": a.kv_bf16,
+                      "ms_per_step": ms, "launches_per_step": bd.launches_per_step, "kv_bytes_per_step": kv_bytes}))
+    bd.close()
+    dec.close()
+
+
 def run_one(a):
+    if a.op == "decode_batch":
+        return run_decode_batch(a)
     calls = []
     if a.op == "attention":
         n_heads, n_kv, hd = 32, 8, 128
