@@ -88,12 +88,6 @@ struct DecodeAttnParams {
     size_t q_stride, new_stride, cache_stride, ws_stride, out_stride;
 };
 
-// bf16 KV cache (kernel template flag KVB): the caches hold bf16 bit patterns (2 bytes per element, same
-// [max_seq, n_kv, head_dim] layout); rows are staged raw and widened to f32 where they are used, the new K / V rows
-// are rounded to nearest-even once, and that rounded value is both what is stored and what this step attends over.
-__device__ inline float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ inline float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-
 // Half-split RoPE of a head slice held 4 (or 2) consecutive dims per lane: the partner dim d +- HD/2 lives
 // in lane ^ 16 (crates/inference/src/kernels/inference.rs:1078-1098 with rotary_dim == head_dim).
 // `cs_sn` holds (cos, sin) of position * freqs[pair] for the HD/2 pairs, computed once per block.
@@ -283,10 +277,10 @@ __device__ __forceinline__ void finish_split(const DecodeAttnParams& p, int kv_h
 // seq_len - 1 were written by earlier steps, and the sequence length by a kernel at least two launches back.
 // GQM bounds the query heads per KV head at compile time (4 or 8): the per-head register arrays and unrolled
 // loops are sized by it.
-template <int HD, int GQM, bool KVB>
+template <int HD, int GQM>
 __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const DecodeAttnParams p_in) {
     DecodeAttnParams p = p_in;
-    constexpr size_t ESZ = KVB ? 2 : 4;  // bytes per cache element
+    constexpr size_t ESZ = 4;  // bytes per cache element (the bf16 cache has a kernel of its own)
     if (gridDim.z > 1) {  // sequence blockIdx.z of a batch: shift every per-sequence operand
         const size_t b = blockIdx.z;
         const size_t cache_shift = b * p.cache_stride * ESZ;
@@ -309,7 +303,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
     constexpr int KP = HD + 16;         // padded K row (elements): the score pass reads its pieces at stride KP conflict-free
     constexpr int KROWB = KP * (int)ESZ, VROWB = HD * (int)ESZ;  // bytes per staged K / V row
     extern __shared__ __align__(16) float smem[];
-    float* Ks = smem;                         // [kAttnTile][KP]   (bf16 cache: the same areas, half used)
+    float* Ks = smem;                         // [kAttnTile][KP]   
     float* Vs = Ks + kAttnTile * KP;          // [kAttnTile][HD]
     char* const Kb = reinterpret_cast<char*>(Ks);
     char* const Vb = reinterpret_cast<char*>(Vs);
@@ -396,10 +390,6 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         for (int e = 0; e < EPL; ++e) qs[warp * HD + lane * EPL + e] = qh[e];
     }
     if (owns_new && warp == kAttnWarps - 2) rope_lane_slice<EPL>(kvn, cs_sn, lane);
-    if (KVB && owns_new && warp >= kAttnWarps - 2) {
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) kvn[e] = bf16_bits_to_f32(f32_to_bf16_bits(kvn[e]));
-    }
 
     float acc[GQM][EPL];
 #pragma unroll
@@ -427,14 +417,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll
             for (int e = 0; e < EPL; ++e) {
                 const size_t at = (size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e;
-                if (KVB) {
-                    const uint16_t bits = (uint16_t)(__float_as_uint(kvn[e]) >> 16);
-                    reinterpret_cast<uint16_t*>(Ks)[newrow * KP + lane * EPL + e] = bits;
-                    reinterpret_cast<uint16_t*>(p.k_cache_w)[at] = bits;
-                } else {
-                    Ks[newrow * KP + lane * EPL + e] = kvn[e];
-                    p.k_cache_w[at] = kvn[e];
-                }
+                Ks[newrow * KP + lane * EPL + e] = kvn[e];
+                p.k_cache_w[at] = kvn[e];
             }
         }
         if (has_new) __syncthreads();
@@ -442,18 +426,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
         {
             const int pl = tid >> 2, c = tid & 3;
             float4 kk[HD / 16];
-            if (KVB) {
-                const uint16_t* kr = reinterpret_cast<const uint16_t*>(Ks) + (pl < nt ? pl : 0) * KP + c * 4;
+            const float* kr = Ks + (pl < nt ? pl : 0) * KP + c * 4;
 #pragma unroll
-                for (int i = 0; i < HD / 16; ++i) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(kr + i * 16);
-                    kk[i] = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
-                }
-            } else {
-                const float* kr = Ks + (pl < nt ? pl : 0) * KP + c * 4;
-#pragma unroll
-                for (int i = 0; i < HD / 16; ++i) kk[i] = *reinterpret_cast<const float4*>(kr + i * 16);
-            }
+            for (int i = 0; i < HD / 16; ++i) kk[i] = *reinterpret_cast<const float4*>(kr + i * 16);
 #pragma unroll 1
             for (int h = 0; h < gq; ++h) {
                 const float* qr = qs + h * HD + c * 4;
@@ -494,14 +469,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) {
                     const size_t at = (size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e;
-                    if (KVB) {
-                        const uint16_t bits = (uint16_t)(__float_as_uint(kvn[e]) >> 16);
-                        reinterpret_cast<uint16_t*>(Vs)[newrow * HD + lane * EPL + e] = bits;
-                        reinterpret_cast<uint16_t*>(p.v_cache_w)[at] = bits;
-                    } else {
-                        Vs[newrow * HD + lane * EPL + e] = kvn[e];
-                        p.v_cache_w[at] = kvn[e];
-                    }
+                    Vs[newrow * HD + lane * EPL + e] = kvn[e];
+                    p.v_cache_w[at] = kvn[e];
                 }
             }
             __syncthreads();
@@ -517,18 +486,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 #pragma unroll 2
         for (int i = warp; i < nt; i += kAttnWarps) {
             float vv[EPL];
-            if (KVB) {
-                const uint16_t* vr = reinterpret_cast<const uint16_t*>(Vs) + i * HD + lane * EPL;
-                if (EPL == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                    vv[0] = bf16_lo(raw.x); vv[1] = bf16_hi(raw.x); vv[EPL - 2] = bf16_lo(raw.y); vv[EPL - 1] = bf16_hi(raw.y);
-                } else {
-                    const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
-                    vv[0] = bf16_lo(raw); vv[1] = bf16_hi(raw);
-                }
-            } else {
-                load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
-            }
+            load_lane_slice<EPL>(Vs + i * HD + lane * EPL, vv);
 #pragma unroll
             for (int h = 0; h < GQM; ++h) {
                 if (h < gq) {
@@ -559,18 +517,28 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 // with bf16 rows the two contractions fit the tensor cores without touching the cache values: K and V are MMA operands
 // exactly as stored, and the f32 side of each product (the query, the softmax weights) is split into a bf16 head and a
 // bf16 remainder, two MMAs with f32 accumulation (16 mantissa bits of the f32 operand, products exact).
-//   S[h][pos] = q[h] . K[pos]:  A = query heads (rows 0..gq-1 of a 16-row fragment, built once per block),
-//                               B = K tile as it lies in shared memory ([pos][dim], ldmatrix); warp w owns positions 8w..8w+7
-//   O[h][dim] += P[h][pos] V[pos][dim]:  A = softmax weights of the tile, B = V tile ([pos][dim], ldmatrix.trans);
-//                               warp w owns dims w*HD/8 .. of every head, so no cross-warp reduction at the end
-// Tiles of 64 positions in a two-stage ring: the K and V rows of tile t+1 are requested before tile t is touched.
-// Rows are padded by 16 bytes so that the 8 row addresses of an ldmatrix fall in distinct banks; rows a tile does not
-// have are zero-filled by the copy.  Range, split plan, fused RoPE + row write and the split merge are those of the
-// f32 kernel.
-__device__ inline void cp_async16_zfill(void* smem_dst, const void* gmem_src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src),
-                 "r"(src_bytes)
-                 : "memory");
+// Every warp is a pipeline of its own over stages of 16 positions (stage j = rows 16j.., warp w takes w, w + 8, ...):
+//   S^T[pos][head] = K[pos] . q[head]:  A = the warp's K stage as it lies in shared memory ([pos][dim], ldmatrix),
+//                                       B = the query heads (fragments built once per block)
+//   running softmax per head in registers (a lane holds two heads of two positions; quad-of-lanes shuffles)
+//   O^T[dim][head] += V^T[dim][pos] P^T[pos][head]:  A = the warp's V stage (ldmatrix.trans), B = the weights, moved from
+//                                       the accumulator layout of S^T to an operand layout by movmatrix
+// The warp copies its own rows (16-byte asynchronous copies; rows a stage does not have are zero-filled), requests its
+// next K stage as soon as the scores are done and its next V stage after the weighted sum: warp-level synchronisation
+// only.  Rows are padded by 16 bytes so that the 8 row addresses of an ldmatrix fall in distinct banks.  The warps'
+// states are combined once at the end.  Range, split plan, fused RoPE + row write and the split merge are those of the
+// f32 kernel; in the fused form the row being written is attended from shared memory (f32 arithmetic, one row).
+// the same copies with the destination given as a shared-space address; the second form writes zeros when src_bytes is 0
+__device__ inline void cp_async16_to(uint32_t smem_addr, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gmem_src) : "memory");
+}
+__device__ inline void cp_async16_zfill_to(uint32_t smem_addr, const void* gmem_src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ inline float ex2_approx(float x) {  // 2^x, about 2 ulp; ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ inline void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -584,17 +552,17 @@ __device__ inline void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row)
                  : "r"((uint32_t)__cvta_generic_to_shared(smem_row))
                  : "memory");
 }
-__device__ inline void ldmatrix_x2_trans(uint32_t (&r)[4], const void* smem_row) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];"
-                 : "=r"(r[0]), "=r"(r[1])
-                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row))
-                 : "memory");
+// 8x8 transpose of 16-bit elements across the warp: lane T holds row T/4, columns 2(T%4), 2(T%4)+1 before and after
+__device__ inline uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
 }
-// D += A * B, m16n8k16, bf16 operands, f32 accumulate; only rows 0..7 of A are populated (a1 = a3 = 0)
-__device__ inline void mma_bf16_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+// D += A * B, m16n8k16, bf16 operands, f32 accumulate
+__device__ inline void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 // (x0, x1) -> bf16 pair of the values rounded to nearest-even (x0 in the low half) and bf16 pair of the remainders
 __device__ inline void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
@@ -627,18 +595,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
     constexpr int RP = HD + 8;            // padded row, elements
     constexpr int ROWB = RP * 2;          // bytes per staged row
     constexpr int V16 = HD / 8;           // 16-byte pieces per row
-    constexpr int TILEB = kAttnTile * ROWB;
-    constexpr int KSTEPS = HD / 16;       // MMA k-steps over the head dimension
-    constexpr int NBW = HD / 64;          // 8-dim output blocks per warp (8 warps cover the head dimension)
-    constexpr int SCP = kAttnTile + 8;    // padded score row: the fragment accesses of four heads fall in distinct banks
+    constexpr int R = 16;                 // positions per stage
+    constexpr int STAGEB = R * ROWB;      // bytes per K or V stage
+    constexpr int KSTEPS = HD / 16;       // MMA k-steps over the head dimension (scores)
+    constexpr int DBLOCKS = HD / 16;      // 16-dim output blocks (weighted sum)
+    constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
     extern __shared__ __align__(16) float smem[];
-    char* const tiles = reinterpret_cast<char*>(smem);                // [2 stages][K tile, V tile]
-    float* sc = reinterpret_cast<float*>(tiles + 4 * TILEB);          // [GQM][SCP] scores, then weights
-    float* hstat = sc + GQM * SCP;                              // [GQM][4]: running max, running sum, correction
-    float* qs = hstat + GQM * 4;                                      // [GQM][HD] rotated query heads
-    float* red = reinterpret_cast<float*>(tiles + 2 * TILEB);         // after the loop: [kAttnWarps][gq][HD]
+    char* const stages = reinterpret_cast<char*>(smem);                          // [kAttnWarps][K stage, V stage]
+    float* wstat = reinterpret_cast<float*>(stages + kAttnWarps * 2 * STAGEB);   // [kAttnWarps][8][2]: every warp's (max, sum)
+    float* hstat = wstat + kAttnWarps * 8 * 2;                                   // [GQM][4]: block max, block sum
+    float* qs = hstat + GQM * 4;                                                 // [GQM][HD] rotated query heads
+    float* red = reinterpret_cast<float*>(stages) + 2048;                        // after the loop: [kAttnWarps][gq][HD]
     __shared__ bool is_last;
     __shared__ float2 cs_sn[HD / 2];
+    __shared__ __align__(16) float newrow[2][HD];  // fused form: the K and V rows of the position being written, as stored
 
     trace_stamp(p.trace, 0);
     const int kv_head = blockIdx.x, gq = p.gq;
@@ -647,7 +617,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
     const size_t kv_stride = (size_t)p.n_kv_heads * HD;
     const bool fused = p.k_new != nullptr;
     int s0 = split * p.chunk;
-    int seq_len = 0, n = 0, first_split = 0;
+    int seq_len = 0, n = 0, first_split = 0, n_stream = 0;
+    bool owns_new = false;
     auto set_range = [&]() {
         seq_len = p.seq_len_ptr ? *p.seq_len_ptr : p.seq_len;
         const int lo = (p.window > 0 && seq_len > p.window) ? seq_len - p.window : 0;
@@ -655,22 +626,33 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
         const int slice_end = min(s0 + p.chunk, seq_len);
         s0 = max(s0, lo);
         n = slice_end - s0;
+        owns_new = fused && n > 0 && slice_end == seq_len;  // the row being written is the last of the sequence
+        n_stream = n - (owns_new ? 1 : 0);                   // ... and is not read from the cache
     };
-    // K and V rows of tile t into stage t & 1, one commit group (also when the tile does not exist)
-    auto issue_tile = [&](int t) {
-        const int t0 = t * kAttnTile;
-        const int nt = n - t0;
-        if (nt > 0) {
-            char* ks = tiles + (t & 1) * 2 * TILEB;
-            char* vs = ks + TILEB;
-            const size_t g0 = ((size_t)(s0 + t0) * kv_stride + (size_t)kv_head * HD) * 2;
+    char* const kw = stages + warp * 2 * STAGEB;
+    char* const vw = kw + STAGEB;
+    // Stage copies: one warp-wide copy instruction moves RSTEP rows (a lane always copies piece `cidx` of rows r0,
+    // r0 + RSTEP, ...), so everything but the stage's first row is a per-lane constant.
+    constexpr int RSTEP = 32 / V16;
+    const int r0 = lane / V16, cidx = lane - r0 * V16;
+    const size_t lane_goff = ((size_t)r0 * kv_stride + (size_t)kv_head * HD) * 2 + cidx * 16;
+    const size_t gstep = (size_t)RSTEP * kv_stride * 2;
+    const uint32_t lane_soff = (uint32_t)(r0 * ROWB + cidx * 16);
+    const uint32_t kw_addr = (uint32_t)__cvta_generic_to_shared(kw) + lane_soff, vw_addr = (uint32_t)__cvta_generic_to_shared(vw) + lane_soff;
+    // rows 16j .. 16j+15 of the streamed rows into this warp's stage; one commit group (also when the stage does not exist)
+    auto issue_stage = [&](const float* cache, uint32_t dst, int j) {
+        const int rows = n_stream - j * R;
+        if (rows > 0) {
+            const char* gsrc = reinterpret_cast<const char*>(cache) + (size_t)(s0 + j * R) * kv_stride * 2 + lane_goff;
+            if (rows >= R) {
 #pragma unroll
-            for (int i = tid; i < kAttnTile * V16; i += kAttnThreads) {
-                const int r = i / V16, cidx = i - r * V16;
-                const bool have = r < nt;
-                const size_t off = g0 + (have ? (size_t)r * kv_stride * 2 : 0) + cidx * 16;
-                cp_async16_zfill(ks + r * ROWB + cidx * 16, reinterpret_cast<const char*>(p.k_cache) + off, have ? 16u : 0u);
-                cp_async16_zfill(vs + r * ROWB + cidx * 16, reinterpret_cast<const char*>(p.v_cache) + off, have ? 16u : 0u);
+                for (int it = 0; it < R / RSTEP; ++it) cp_async16_to(dst + it * RSTEP * ROWB, gsrc + it * gstep);
+            } else {  // the last stage of the slice: rows it does not have are zero-filled (the source is then not read)
+#pragma unroll
+                for (int it = 0; it < R / RSTEP; ++it) {
+                    const bool have = r0 + it * RSTEP < rows;
+                    cp_async16_zfill_to(dst + it * RSTEP * ROWB, have ? gsrc + it * gstep : reinterpret_cast<const char*>(cache), have ? 16u : 0u);
+                }
             }
         }
         cp_async_commit();
@@ -678,7 +660,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
     if (fused) {
         set_range();
         if (n > 0) {
-            issue_tile(0);  // rows below seq_len - 1 were written by earlier steps
+            issue_stage(p.k_cache, kw_addr, warp);  // rows below seq_len - 1 were written by earlier steps
+            issue_stage(p.v_cache, vw_addr, warp);
             if (tid < HD / 2) {
                 float sn, cs;
                 sincosf((float)(seq_len - 1) * p.freqs[tid], &sn, &cs);
@@ -686,18 +669,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
             }
         }
     }
-    if (tid < GQM) { hstat[tid * 4] = -INFINITY; hstat[tid * 4 + 1] = 0.0f; hstat[tid * 4 + 2] = 1.0f; }
     pdl_wait();
     trace_stamp(p.trace, 1);
     if (!fused) set_range();
     const int nactive = (seq_len + p.chunk - 1) / p.chunk - first_split;
     if (n <= 0) return;
     split -= first_split;
-    if (!fused) issue_tile(0);
-    const float scale = 1.0f / sqrtf((float)HD);
+    if (!fused) {
+        issue_stage(p.k_cache, kw_addr, warp);
+        issue_stage(p.v_cache, vw_addr, warp);
+    }
 
-    const int newpos = seq_len - 1 - s0;  // position being written, relative to this block's slice
-    const bool owns_new = fused && newpos >= 0 && newpos < n;
     float qh[EPL], kvn[EPL];
     if (warp < gq) load_lane_slice<EPL>(p.q + (size_t)(kv_head * gq + warp) * HD + lane * EPL, qh);
     if (owns_new && warp == kAttnWarps - 2) load_lane_slice<EPL>(p.k_new + (size_t)kv_head * HD + lane * EPL, kvn);
@@ -709,9 +691,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
         for (int e = 0; e < EPL; ++e) qs[warp * HD + lane * EPL + e] = qh[e];
     }
     if (owns_new && warp == kAttnWarps - 2) rope_lane_slice<EPL>(kvn, cs_sn, lane);
-    __syncthreads();  // qs is visible
+    if (owns_new && warp >= kAttnWarps - 2) {
+        uint16_t* const cache_w = reinterpret_cast<uint16_t*>(warp == kAttnWarps - 2 ? p.k_cache_w : p.v_cache_w);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            const uint16_t bits = f32_to_bf16_bits(kvn[e]);  // rounded once; the stored value is what this step attends
+            cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = bits;
+            newrow[warp - (kAttnWarps - 2)][lane * EPL + e] = bf16_bits_to_f32(bits);
+        }
+    }
+    __syncthreads();  // qs and newrow are visible
 
-    // A fragments of the query heads: row g = head, this lane's column pairs of every k-step, head and remainder
+    // B fragments of the query heads: column g = head, this lane's dim pairs of every k-step, head and remainder
     const int g = lane >> 2, tq = lane & 3;
     uint32_t qhi[KSTEPS][2], qlo[KSTEPS][2];
 #pragma unroll
@@ -722,111 +713,143 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
             if (g < gq) x = *reinterpret_cast<const float2*>(qs + g * HD + ks * 16 + half * 8 + tq * 2);
             split_bf16x2(x.x, x.y, qhi[ks][half], qlo[ks][half]);
         }
-    float o[NBW][4];
+    // this lane's two heads (2 tq, 2 tq + 1): running max in log2 units, running sum; accumulators of dims g, g + 8 of
+    // every 16-dim block for those two heads
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[DBLOCKS][4];
 #pragma unroll
-    for (int nb = 0; nb < NBW; ++nb)
+    for (int db = 0; db < DBLOCKS; ++db)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
+        for (int e = 0; e < 4; ++e) o[db][e] = 0.0f;
+    const float scale2 = kLog2e / sqrtf((float)HD);  // scores in log2 units: the weights are exp2(s - m)
 
-    const int ntiles = (n + kAttnTile - 1) / kAttnTile;
+    const int nstages = (n_stream + R - 1) / R;
 #pragma unroll 1
-    for (int t = 0; t < ntiles; ++t) {
-        cp_async_wait<0>();  // tile t has landed (this thread's copies; the barrier covers everybody's)
-        __syncthreads();     // ... and every warp is done with tile t - 1: its stage and the weights are free
-        issue_tile(t + 1);
-        char* const ks_t = tiles + (t & 1) * 2 * TILEB;
-        char* const vs_t = ks_t + TILEB;
-        const int nt = min(kAttnTile, n - t * kAttnTile);
-        const int newrow = newpos - t * kAttnTile;
-        if (owns_new && newrow >= 0 && newrow < nt) {  // block-uniform
-            if (warp >= kAttnWarps - 2) {
-                char* const tile = warp == kAttnWarps - 2 ? ks_t : vs_t;
-                uint16_t* const cache_w = reinterpret_cast<uint16_t*>(warp == kAttnWarps - 2 ? p.k_cache_w : p.v_cache_w);
+    for (int j = warp; j < nstages; j += kAttnWarps) {
+        const int rows = min(R, n_stream - j * R);
+        cp_async_wait<1>();  // this lane's K copies have landed (at most the V stage is still in flight)
+        __syncwarp();        // ... and every other lane's
+        float sh[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sl[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) {
-                    const uint16_t bits = f32_to_bf16_bits(kvn[e]);
-                    reinterpret_cast<uint16_t*>(tile + newrow * ROWB)[lane * EPL + e] = bits;
-                    cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = bits;
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t a[4];  // 16 positions x 16 dims
+            ldmatrix_x4(a, kw + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (ks * 16 + (lane >> 4) * 8) * 2);
+            mma_bf16(sh, a, qhi[ks][0], qhi[ks][1]);
+            mma_bf16(sl, a, qlo[ks][0], qlo[ks][1]);
+        }
+        __syncwarp();  // every lane has read the K stage: it is free
+        issue_stage(p.k_cache, kw_addr, j + kAttnWarps);
+        // s[0], s[1]: position g, heads 2tq, 2tq+1;  s[2], s[3]: position g + 8
+        float s[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] = (sh[e] + sl[e]) * scale2;
+        if (g >= rows) s[0] = s[1] = -INFINITY;
+        if (g + 8 >= rows) s[2] = s[3] = -INFINITY;
+        float corr[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float mx = fmaxf(s[hh], s[hh + 2]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[hh], mx);  // finite: row 0 of a stage always exists
+            s[hh] = ex2_approx(s[hh] - m_new);              // exp2(-inf) = 0 for rows the stage does not have
+            s[hh + 2] = ex2_approx(s[hh + 2] - m_new);
+            corr[hh] = ex2_approx(m_run[hh] - m_new);       // 0 on the first stage
+            float ps = s[hh] + s[hh + 2];
+            ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+            l_run[hh] = l_run[hh] * corr[hh] + ps;
+            m_run[hh] = m_new;
+        }
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+            for (int db = 0; db < DBLOCKS; ++db) { o[db][0] *= corr[0]; o[db][1] *= corr[1]; o[db][2] *= corr[0]; o[db][3] *= corr[1]; }
+        }
+        // weights as B fragments: (position g; heads 2tq, 2tq+1) -> (head g; positions 2tq, 2tq+1), head and remainder
+        uint32_t ph0, pl0, ph1, pl1;
+        split_bf16x2(s[0], s[1], ph0, pl0);
+        split_bf16x2(s[2], s[3], ph1, pl1);
+        ph0 = movmatrix_trans(ph0); pl0 = movmatrix_trans(pl0);
+        ph1 = movmatrix_trans(ph1); pl1 = movmatrix_trans(pl1);
+        cp_async_wait<1>();  // V has landed (at most the next K stage is still in flight)
+        __syncwarp();
+#pragma unroll
+        for (int db = 0; db < DBLOCKS; ++db) {
+            uint32_t a[4];  // V^T: 16 dims x 16 positions
+            ldmatrix_x4_trans(a, vw + ((lane & 7) + (lane >> 4) * 8) * ROWB + (db * 16 + ((lane >> 3) & 1) * 8) * 2);
+            mma_bf16(o[db], a, ph0, ph1);
+            mma_bf16(o[db], a, pl0, pl1);
+        }
+        __syncwarp();  // every lane has read the V stage: it is free
+        issue_stage(p.v_cache, vw_addr, j + kAttnWarps);
+    }
+    // the position being written: one more row, attended from shared memory by warp 0 (plain f32 arithmetic)
+    if (owns_new && warp == 0) {
+        float snew[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int h = 0; h < GQM; ++h) {
+            if (h < gq) {
+                float v = 0.0f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) v = fmaf(qs[h * HD + lane * EPL + e], newrow[0][lane * EPL + e], v);
+                v = warp_sum(v) * scale2;
+                if (h == 2 * tq) snew[0] = v;
+                if (h == 2 * tq + 1) snew[1] = v;
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            if (2 * tq + hh < gq) {
+                const float m_new = fmaxf(m_run[hh], snew[hh]);
+                const float pw = ex2_approx(snew[hh] - m_new), c = ex2_approx(m_run[hh] - m_new);
+                l_run[hh] = l_run[hh] * c + pw;
+                m_run[hh] = m_new;
+#pragma unroll
+                for (int db = 0; db < DBLOCKS; ++db) {
+                    o[db][hh] = fmaf(pw, newrow[1][db * 16 + g], o[db][hh] * c);
+                    o[db][hh + 2] = fmaf(pw, newrow[1][db * 16 + g + 8], o[db][hh + 2] * c);
                 }
             }
-            __syncthreads();
-        }
-        // scores of positions 8 * warp .. + 7 for every head
-        {
-            float ch[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cl[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int k2 = 0; k2 < KSTEPS / 2; ++k2) {
-                uint32_t b[4];  // 8 positions x 32 dims: B fragments of two k-steps
-                ldmatrix_x4(b, ks_t + (warp * 8 + (lane & 7)) * ROWB + (k2 * 32 + (lane >> 3) * 8) * 2);
-                mma_bf16_rows8(ch, qhi[2 * k2][0], qhi[2 * k2][1], b[0], b[1]);
-                mma_bf16_rows8(cl, qlo[2 * k2][0], qlo[2 * k2][1], b[0], b[1]);
-                mma_bf16_rows8(ch, qhi[2 * k2 + 1][0], qhi[2 * k2 + 1][1], b[2], b[3]);
-                mma_bf16_rows8(cl, qlo[2 * k2 + 1][0], qlo[2 * k2 + 1][1], b[2], b[3]);
-            }
-            if (g < gq)
-                *reinterpret_cast<float2*>(sc + g * SCP + warp * 8 + tq * 2) = make_float2((ch[0] + cl[0]) * scale, (ch[1] + cl[1]) * scale);
-        }
-        __syncthreads();
-        // running softmax statistics: one warp per query head (rows the tile does not have get weight 0)
-        if (warp < gq) {
-            const int h = warp;
-            const float m_old = hstat[h * 4], l_old = hstat[h * 4 + 1];
-            const float s_a = lane < nt ? sc[h * SCP + lane] : -INFINITY;
-            const float s_b = lane + 32 < nt ? sc[h * SCP + lane + 32] : -INFINITY;
-            const float m = warp_max(fmaxf(m_old, fmaxf(s_a, s_b)));
-            const float e_a = lane < nt ? expf(s_a - m) : 0.0f, e_b = lane + 32 < nt ? expf(s_b - m) : 0.0f;
-            sc[h * SCP + lane] = e_a;
-            sc[h * SCP + lane + 32] = e_b;
-            const float l = warp_sum(e_a + e_b);
-            const float corr = expf(m_old - m);  // exp(-inf) = 0 on the first tile
-            if (lane == 0) { hstat[h * 4] = m; hstat[h * 4 + 1] = l_old * corr + l; hstat[h * 4 + 2] = corr; }
-        }
-        __syncthreads();
-        // weighted sum of V: dims warp * HD/8 .. of every head
-        {
-            const float corr = g < gq ? hstat[g * 4 + 2] : 0.0f;
-#pragma unroll
-            for (int nb = 0; nb < NBW; ++nb) { o[nb][0] *= corr; o[nb][1] *= corr; }
-            float ol[NBW][4];
-#pragma unroll
-            for (int nb = 0; nb < NBW; ++nb)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) ol[nb][e] = 0.0f;
-#pragma unroll
-            for (int k4 = 0; k4 < kAttnTile / 16; ++k4) {
-                float2 pa = make_float2(0.0f, 0.0f), pb = make_float2(0.0f, 0.0f);
-                if (g < gq) {
-                    pa = *reinterpret_cast<const float2*>(sc + g * SCP + k4 * 16 + tq * 2);
-                    pb = *reinterpret_cast<const float2*>(sc + g * SCP + k4 * 16 + 8 + tq * 2);
-                }
-                uint32_t ah0, al0, ah2, al2;
-                split_bf16x2(pa.x, pa.y, ah0, al0);
-                split_bf16x2(pb.x, pb.y, ah2, al2);
-                uint32_t b[4];  // 16 positions x (8 * NBW) dims, transposed on the way in
-                const char* row = vs_t + (k4 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (warp * (HD / 8)) * 2;
-                if (NBW == 2) ldmatrix_x4_trans(b, row + (lane >> 4) * 16);
-                else ldmatrix_x2_trans(b, row);
-                mma_bf16_rows8(o[0], ah0, ah2, b[0], b[1]);
-                mma_bf16_rows8(ol[0], al0, al2, b[0], b[1]);
-                if (NBW == 2) {
-                    mma_bf16_rows8(o[NBW - 1], ah0, ah2, b[2], b[3]);
-                    mma_bf16_rows8(ol[NBW - 1], al0, al2, b[2], b[3]);
-                }
-            }
-#pragma unroll
-            for (int nb = 0; nb < NBW; ++nb) { o[nb][0] += ol[nb][0]; o[nb][1] += ol[nb][1]; }
         }
     }
     trace_stamp(p.trace, 2);
-    __syncthreads();  // every warp is done with the last tile: the stages are free
-    // every (head, dim) is complete in one lane: one plane for the common end
-    if (g < gq) {
+    // combine the warps: block max per head, every warp's accumulators rescaled to it, summed by the common end
+    if (g == 0) {
+        wstat[(warp * 8 + 2 * tq) * 2] = m_run[0];
+        wstat[(warp * 8 + 2 * tq) * 2 + 1] = l_run[0];
+        wstat[(warp * 8 + 2 * tq + 1) * 2] = m_run[1];
+        wstat[(warp * 8 + 2 * tq + 1) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();  // every warp is done with its stages: their memory is free for the cross-warp reduction
 #pragma unroll
-        for (int nb = 0; nb < NBW; ++nb)
-            *reinterpret_cast<float2*>(red + g * HD + warp * (HD / 8) + nb * 8 + tq * 2) = make_float2(o[nb][0], o[nb][1]);
+    for (int hh = 0; hh < 2; ++hh) {
+        const int h = 2 * tq + hh;
+        if (h < gq) {
+            float mb = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; ++w) mb = fmaxf(mb, wstat[(w * 8 + h) * 2]);
+            const float f = m_run[hh] == -INFINITY ? 0.0f : ex2_approx(m_run[hh] - mb);  // a warp without rows contributes nothing
+#pragma unroll
+            for (int db = 0; db < DBLOCKS; ++db) {
+                red[(warp * gq + h) * HD + db * 16 + g] = o[db][hh] * f;
+                red[(warp * gq + h) * HD + db * 16 + g + 8] = o[db][hh + 2] * f;
+            }
+            if (warp == 0 && g == 0) {
+                float lb = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kAttnWarps; ++w) {
+                    const float mw = wstat[(w * 8 + h) * 2];
+                    lb += mw == -INFINITY ? 0.0f : wstat[(w * 8 + h) * 2 + 1] * ex2_approx(mw - mb);
+                }
+                hstat[h * 4] = mb * kLn2;  // natural-log units, as the merge of the splits expects
+                hstat[h * 4 + 1] = lb;
+            }
+        }
     }
     __syncthreads();
-    finish_split<HD, GQM, 1>(p, kv_head, split, nactive, red, hstat, reinterpret_cast<float*>(tiles), &is_last);
+    finish_split<HD, GQM, kAttnWarps>(p, kv_head, split, nactive, red, hstat, reinterpret_cast<float*>(stages), &is_last);
 }
 
 // ---- prefill: tiled causal attention ---------------------------------------------------------------
@@ -993,9 +1016,9 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
         return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem, stream, true, p);
     };
     if (kv_bf16) {
-        // two stages of (K tile, V tile) with padded bf16 rows, scores, statistics, query heads
+        // per warp a K stage and a V stage of 16 padded bf16 rows; the warps' statistics, the block's, the query heads
         const size_t gqm = gq <= 4 ? 4 : kMaxGq;
-        const size_t smem16 = (size_t)4 * kAttnTile * (head_dim + 8) * 2 + (gqm * (kAttnTile + 8) + gqm * 4 + gqm * head_dim) * sizeof(float);
+        const size_t smem16 = (size_t)kAttnWarps * 2 * 16 * (head_dim + 8) * 2 + ((size_t)kAttnWarps * 16 + gqm * 4 + gqm * head_dim) * sizeof(float);
         auto go16 = [&](auto kern) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem16, stream, true, p);
@@ -1003,8 +1026,8 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
         if (head_dim == 128) e = gq <= 4 ? go16(decode_attention_bf16_kernel<128, 4>) : go16(decode_attention_bf16_kernel<128, 8>);
         else e = gq <= 4 ? go16(decode_attention_bf16_kernel<64, 4>) : go16(decode_attention_bf16_kernel<64, 8>);
     } else {
-        if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4, false>) : go(decode_attention_kernel<128, 8, false>);
-        else e = gq <= 4 ? go(decode_attention_kernel<64, 4, false>) : go(decode_attention_kernel<64, 8, false>);
+        if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4>) : go(decode_attention_kernel<128, 8>);
+        else e = gq <= 4 ? go(decode_attention_kernel<64, 4>) : go(decode_attention_kernel<64, 8>);
     }
     if (e != cudaSuccess) return fail(KMLL_ERR_CUDA, "single_query_attention: %s", cudaGetErrorString(e));
     return KMLL_OK;
