@@ -486,6 +486,24 @@ def run_ours(args):
                                   "steps": n16, "launches_per_step": bdh.launches_per_step}
             bdh.close()
         dech.close()
+        if not args.no_batch16 and not args.no_rsi8:  # the same 16-sequence leg with RS-I8 weights and the bf16 cache
+            dec8h = rt.Decoder(rt.DecoderConfig.mistral_7b(max_seq_len=PROMPT_LEN + 64, format=rt.FORMAT_RS_I8, kv_bf16=True))
+            dec8h.init_random(SEED, 0.02, False)
+            dec8h.prefill(prompt)
+            bd8h = rt.BatchDecoder(dec8h, 16)
+            for slot in range(16):
+                bd8h.adopt(slot)
+            bd8h.generate_greedy(3)
+            torch.cuda.synchronize()
+            n16 = max(2, min(K, 16))
+            e0.record()
+            bd8h.enqueue_steps(n16)
+            e1.record()
+            torch.cuda.synchronize()
+            kv_bf16["rs_i8_batch16"] = {"value": 16 * 1e3 / (e0.elapsed_time(e1) / n16), "unit": "tokens/s",
+                                        "ms_per_step": e0.elapsed_time(e1) / n16, "steps": n16, "launches_per_step": bd8h.launches_per_step}
+            bd8h.close()
+            dec8h.close()
 
     # ---- roofline of the dominant kernel: the fused RMSNorm + gate/up + SiLU kernel over prepared-layout weights (the
     # one the decode step above launches 32 times), timed live over 8 layers' worth of distinct weights (1.9 GB per

@@ -850,13 +850,23 @@ __global__ void __launch_bounds__(512, 1) linear_gemm_small_i8_kernel(const Smal
                         const float* base = p.partial + (size_t)tile * p.ksplit * (size_t)(NB * 128) + rl;
 #pragma unroll
                         for (int m = 0; m < NB; ++m) acc[m] = 0.0f;
+                        // (two splits per round trip where the registers allow it - this kernel has 128 per thread; the order of the additions stays)
+                        constexpr int kPerTrip = NB <= 16 ? 2 : 1;
 #pragma unroll 1
-                        for (int zz = 0; zz < p.ksplit; ++zz) {
-                            float t[NB];
+                        for (int zz = 0; zz < p.ksplit; zz += kPerTrip) {
+                            float t[kPerTrip][NB];
 #pragma unroll
-                            for (int m = 0; m < NB; ++m) t[m] = __ldcg(base + (size_t)zz * (NB * 128) + m * 128);
+                            for (int q2 = 0; q2 < kPerTrip; ++q2)
+                                if (zz + q2 < p.ksplit) {
 #pragma unroll
-                            for (int m = 0; m < NB; ++m) acc[m] += t[m];
+                                    for (int m = 0; m < NB; ++m) t[q2][m] = __ldcg(base + (size_t)(zz + q2) * (NB * 128) + m * 128);
+                                }
+#pragma unroll
+                            for (int q2 = 0; q2 < kPerTrip; ++q2)
+                                if (zz + q2 < p.ksplit) {
+#pragma unroll
+                                    for (int m = 0; m < NB; ++m) acc[m] += t[q2][m];
+                                }
                         }
                         if (row < mt.rows) {
 #pragma unroll
