@@ -72,12 +72,16 @@ def test_batch_gqa_head_dim_128(cuda, kv_bf16):
     dec.close()
 
 
-@pytest.mark.parametrize("kv_bf16,window", [(False, 0), (True, 0), (False, 90)])
-def test_batch_attention_with_several_tiles_per_block(cuda, kv_bf16, window):
-    """16 sequences x 8 KV heads fill the GPU along the batch axis, so the attention plan gives every block a slice of
-    several 64-position tiles (here 128 positions); with 200-token prompts the position being written lies in the second
-    tile of its block - the fused RoPE + KV-write + prefetch path with t0 > 0."""
-    cfg = _cfg(rt.FORMAT_W4G128, n_heads=8, n_kv_heads=8, head_dim=64, dim=512, max_seq_len=400, kv_bf16=kv_bf16, sliding_window=window)
+@pytest.mark.parametrize("kv_bf16,window,head_dim,n_heads", [(False, 0, 64, 8), (True, 0, 64, 8), (False, 90, 64, 8), (True, 0, 128, 32),
+                                                             (True, 150, 128, 16), (False, 0, 128, 32)])
+def test_batch_attention_with_several_tiles_per_block(cuda, kv_bf16, window, head_dim, n_heads):
+    """16 sequences x 8 KV heads fill the GPU along the batch axis, so the attention plan gives every block a long slice
+    of the sequence (here 256 positions: several 64-position tiles of the f32 kernel, several 16-position stages per
+    warp of the bf16-cache kernel); with 200-token prompts the position being written lies deep inside its block's slice.
+    The single-sequence runs they are compared with use one block per 64 positions: a different partition of the same
+    sums.  Head dimension 128 with 4 and 2 query heads per KV head covers the fragment layouts of the tensor-core kernel."""
+    cfg = _cfg(rt.FORMAT_W4G128, n_heads=n_heads, n_kv_heads=8, head_dim=head_dim, dim=512, max_seq_len=400, kv_bf16=kv_bf16,
+               sliding_window=window)
     dec = rt.Decoder(cfg)
     dec.init_random(11, 0.05, False)
     rng = np.random.default_rng(2)
