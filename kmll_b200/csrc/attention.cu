@@ -528,6 +528,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const
 // only.  Rows are padded by 16 bytes so that the 8 row addresses of an ldmatrix fall in distinct banks.  The warps'
 // states are combined once at the end.  Range, split plan, fused RoPE + row write and the split merge are those of the
 // f32 kernel; in the fused form the row being written is attended from shared memory (f32 arithmetic, one row).
+// F32KV: the same pipelines over an f32 cache (used for batches of sequences, where the f32 kernel above is bound by
+// instruction issue): the K and V fragments are read from the staged f32 rows in place and split into a bf16 head and
+// remainder like the other operand; three of the four partial products are accumulated, so both operands count with 16
+// mantissa bits (a relative 2^-17 per product, far inside the tolerance of the parity tests, but not the f32 products
+// of the kernel above).  One block per multiprocessor (137 KB of stages).
 // the same copies with the destination given as a shared-space address; the second form writes zeros when src_bytes is 0
 __device__ inline void cp_async16_to(uint32_t smem_addr, const void* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gmem_src) : "memory");
@@ -571,12 +576,12 @@ __device__ inline void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& 
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(r1), "f"(r0));
 }
 
-template <int HD, int GQM>
-__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(const DecodeAttnParams p_in) {
+template <int HD, int GQM, bool F32KV>
+__global__ void __launch_bounds__(kAttnThreads, F32KV ? 1 : 2) decode_attention_mma_kernel(const DecodeAttnParams p_in) {
     DecodeAttnParams p = p_in;
     if (gridDim.z > 1) {  // sequence blockIdx.z of a batch: shift every per-sequence operand
         const size_t b = blockIdx.z;
-        const size_t cache_shift = b * p.cache_stride * 2;
+        const size_t cache_shift = b * p.cache_stride * (F32KV ? 4 : 2);
         p.q += b * p.q_stride;
         p.out += b * p.out_stride;
         p.k_cache = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.k_cache) + cache_shift);
@@ -592,17 +597,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
         p.counters += b * p.ws_stride;
     }
     constexpr int EPL = HD / 32;          // elements per lane where a warp holds one row (query, new K / V row)
-    constexpr int RP = HD + 8;            // padded row, elements
-    constexpr int ROWB = RP * 2;          // bytes per staged row
-    constexpr int V16 = HD / 8;           // 16-byte pieces per row
+    constexpr int ESZ = F32KV ? 4 : 2;    // bytes per cache element
+    // padded rows (elements): 8 row addresses of an ldmatrix fall in distinct banks (bf16); f32 rows are read as
+    // fragments directly, K two dims per lane (stride = 8 mod 32 words), V one dim of two rows (2 x stride = 8 mod 32)
+    constexpr int KRP = HD + 8, VRP = F32KV ? HD + 4 : HD + 8;
+    constexpr int KROWB = KRP * ESZ, VROWB = VRP * ESZ;  // bytes per staged row
+    constexpr int V16 = HD * ESZ / 16;    // 16-byte pieces per row
     constexpr int R = 16;                 // positions per stage
-    constexpr int STAGEB = R * ROWB;      // bytes per K or V stage
+    constexpr int KSTAGEB = R * KROWB, VSTAGEB = R * VROWB;
     constexpr int KSTEPS = HD / 16;       // MMA k-steps over the head dimension (scores)
     constexpr int DBLOCKS = HD / 16;      // 16-dim output blocks (weighted sum)
     constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
     extern __shared__ __align__(16) float smem[];
     char* const stages = reinterpret_cast<char*>(smem);                          // [kAttnWarps][K stage, V stage]
-    float* wstat = reinterpret_cast<float*>(stages + kAttnWarps * 2 * STAGEB);   // [kAttnWarps][8][2]: every warp's (max, sum)
+    float* wstat = reinterpret_cast<float*>(stages + kAttnWarps * (KSTAGEB + VSTAGEB));   // [kAttnWarps][8][2]: every warp's (max, sum)
     float* hstat = wstat + kAttnWarps * 8 * 2;                                   // [GQM][4]: block max, block sum
     float* qs = hstat + GQM * 4;                                                 // [GQM][HD] rotated query heads
     float* red = reinterpret_cast<float*>(stages) + 2048;                        // after the loop: [kAttnWarps][gq][HD]
@@ -629,21 +637,21 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
         owns_new = fused && n > 0 && slice_end == seq_len;  // the row being written is the last of the sequence
         n_stream = n - (owns_new ? 1 : 0);                   // ... and is not read from the cache
     };
-    char* const kw = stages + warp * 2 * STAGEB;
-    char* const vw = kw + STAGEB;
+    char* const kw = stages + warp * (KSTAGEB + VSTAGEB);
+    char* const vw = kw + KSTAGEB;
     // Stage copies: one warp-wide copy instruction moves RSTEP rows (a lane always copies piece `cidx` of rows r0,
     // r0 + RSTEP, ...), so everything but the stage's first row is a per-lane constant.
     constexpr int RSTEP = 32 / V16;
     const int r0 = lane / V16, cidx = lane - r0 * V16;
-    const size_t lane_goff = ((size_t)r0 * kv_stride + (size_t)kv_head * HD) * 2 + cidx * 16;
-    const size_t gstep = (size_t)RSTEP * kv_stride * 2;
-    const uint32_t lane_soff = (uint32_t)(r0 * ROWB + cidx * 16);
-    const uint32_t kw_addr = (uint32_t)__cvta_generic_to_shared(kw) + lane_soff, vw_addr = (uint32_t)__cvta_generic_to_shared(vw) + lane_soff;
+    const size_t lane_goff = ((size_t)r0 * kv_stride + (size_t)kv_head * HD) * ESZ + cidx * 16;
+    const size_t gstep = (size_t)RSTEP * kv_stride * ESZ;
+    const uint32_t kw_addr = (uint32_t)__cvta_generic_to_shared(kw) + (uint32_t)(r0 * KROWB + cidx * 16);
+    const uint32_t vw_addr = (uint32_t)__cvta_generic_to_shared(vw) + (uint32_t)(r0 * VROWB + cidx * 16);
     // rows 16j .. 16j+15 of the streamed rows into this warp's stage; one commit group (also when the stage does not exist)
-    auto issue_stage = [&](const float* cache, uint32_t dst, int j) {
+    auto issue_stage = [&](const float* cache, uint32_t dst, int ROWB, int j) {
         const int rows = n_stream - j * R;
         if (rows > 0) {
-            const char* gsrc = reinterpret_cast<const char*>(cache) + (size_t)(s0 + j * R) * kv_stride * 2 + lane_goff;
+            const char* gsrc = reinterpret_cast<const char*>(cache) + (size_t)(s0 + j * R) * kv_stride * ESZ + lane_goff;
             if (rows >= R) {
 #pragma unroll
                 for (int it = 0; it < R / RSTEP; ++it) cp_async16_to(dst + it * RSTEP * ROWB, gsrc + it * gstep);
@@ -660,8 +668,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
     if (fused) {
         set_range();
         if (n > 0) {
-            issue_stage(p.k_cache, kw_addr, warp);  // rows below seq_len - 1 were written by earlier steps
-            issue_stage(p.v_cache, vw_addr, warp);
+            issue_stage(p.k_cache, kw_addr, KROWB, warp);  // rows below seq_len - 1 were written by earlier steps
+            issue_stage(p.v_cache, vw_addr, VROWB, warp);
             if (tid < HD / 2) {
                 float sn, cs;
                 sincosf((float)(seq_len - 1) * p.freqs[tid], &sn, &cs);
@@ -676,8 +684,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
     if (n <= 0) return;
     split -= first_split;
     if (!fused) {
-        issue_stage(p.k_cache, kw_addr, warp);
-        issue_stage(p.v_cache, vw_addr, warp);
+        issue_stage(p.k_cache, kw_addr, KROWB, warp);
+        issue_stage(p.v_cache, vw_addr, VROWB, warp);
     }
 
     float qh[EPL], kvn[EPL];
@@ -692,12 +700,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
     }
     if (owns_new && warp == kAttnWarps - 2) rope_lane_slice<EPL>(kvn, cs_sn, lane);
     if (owns_new && warp >= kAttnWarps - 2) {
-        uint16_t* const cache_w = reinterpret_cast<uint16_t*>(warp == kAttnWarps - 2 ? p.k_cache_w : p.v_cache_w);
+        float* const cache_w = warp == kAttnWarps - 2 ? p.k_cache_w : p.v_cache_w;
 #pragma unroll
         for (int e = 0; e < EPL; ++e) {
-            const uint16_t bits = f32_to_bf16_bits(kvn[e]);  // rounded once; the stored value is what this step attends
-            cache_w[(size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e] = bits;
-            newrow[warp - (kAttnWarps - 2)][lane * EPL + e] = bf16_bits_to_f32(bits);
+            const size_t at = (size_t)(seq_len - 1) * kv_stride + (size_t)kv_head * HD + lane * EPL + e;
+            if (F32KV) {
+                cache_w[at] = kvn[e];
+                newrow[warp - (kAttnWarps - 2)][lane * EPL + e] = kvn[e];
+            } else {
+                const uint16_t bits = f32_to_bf16_bits(kvn[e]);  // rounded once; the stored value is what this step attends
+                reinterpret_cast<uint16_t*>(cache_w)[at] = bits;
+                newrow[warp - (kAttnWarps - 2)][lane * EPL + e] = bf16_bits_to_f32(bits);
+            }
         }
     }
     __syncthreads();  // qs and newrow are visible
@@ -733,12 +747,26 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             uint32_t a[4];  // 16 positions x 16 dims
-            ldmatrix_x4(a, kw + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (ks * 16 + (lane >> 4) * 8) * 2);
+            if (F32KV) {
+                // f32 rows: the fragment is read in place (positions g, g + 8; dims 2tq.. and 8 + 2tq..) and split into a
+                // bf16 head and remainder like the query: three of the four partial products (the last is below 2^-16)
+                const float* kf = reinterpret_cast<const float*>(kw) + g * KRP + ks * 16 + 2 * tq;
+                uint32_t al[4];
+                const float2 x0 = *reinterpret_cast<const float2*>(kf), x1 = *reinterpret_cast<const float2*>(kf + 8 * KRP);
+                const float2 x2 = *reinterpret_cast<const float2*>(kf + 8), x3 = *reinterpret_cast<const float2*>(kf + 8 * KRP + 8);
+                split_bf16x2(x0.x, x0.y, a[0], al[0]);
+                split_bf16x2(x1.x, x1.y, a[1], al[1]);
+                split_bf16x2(x2.x, x2.y, a[2], al[2]);
+                split_bf16x2(x3.x, x3.y, a[3], al[3]);
+                mma_bf16(sl, al, qhi[ks][0], qhi[ks][1]);
+            } else {
+                ldmatrix_x4(a, kw + ((lane & 7) + ((lane >> 3) & 1) * 8) * KROWB + (ks * 16 + (lane >> 4) * 8) * 2);
+            }
             mma_bf16(sh, a, qhi[ks][0], qhi[ks][1]);
             mma_bf16(sl, a, qlo[ks][0], qlo[ks][1]);
         }
         __syncwarp();  // every lane has read the K stage: it is free
-        issue_stage(p.k_cache, kw_addr, j + kAttnWarps);
+        issue_stage(p.k_cache, kw_addr, KROWB, j + kAttnWarps);
         // s[0], s[1]: position g, heads 2tq, 2tq+1;  s[2], s[3]: position g + 8
         float s[4];
 #pragma unroll
@@ -778,12 +806,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_bf16_kernel(
 #pragma unroll
         for (int db = 0; db < DBLOCKS; ++db) {
             uint32_t a[4];  // V^T: 16 dims x 16 positions
-            ldmatrix_x4_trans(a, vw + ((lane & 7) + (lane >> 4) * 8) * ROWB + (db * 16 + ((lane >> 3) & 1) * 8) * 2);
+            if (F32KV) {
+                // dims g, g + 8 of positions 2tq, 2tq+1 and 8 + 2tq, 9 + 2tq
+                const float* vf = reinterpret_cast<const float*>(vw) + (2 * tq) * VRP + db * 16 + g;
+                uint32_t al[4];
+                split_bf16x2(vf[0], vf[VRP], a[0], al[0]);
+                split_bf16x2(vf[8], vf[VRP + 8], a[1], al[1]);
+                split_bf16x2(vf[8 * VRP], vf[9 * VRP], a[2], al[2]);
+                split_bf16x2(vf[8 * VRP + 8], vf[9 * VRP + 8], a[3], al[3]);
+                mma_bf16(o[db], al, ph0, ph1);
+            } else {
+                ldmatrix_x4_trans(a, vw + ((lane & 7) + (lane >> 4) * 8) * VROWB + (db * 16 + ((lane >> 3) & 1) * 8) * 2);
+            }
             mma_bf16(o[db], a, ph0, ph1);
             mma_bf16(o[db], a, pl0, pl1);
         }
         __syncwarp();  // every lane has read the V stage: it is free
-        issue_stage(p.v_cache, vw_addr, j + kAttnWarps);
+        issue_stage(p.v_cache, vw_addr, VROWB, j + kAttnWarps);
     }
     // the position being written: one more row, attended from shared memory by warp 0 (plain f32 arithmetic)
     if (owns_new && warp == 0) {
@@ -959,16 +998,16 @@ struct AttnPlan {
 
 // Split plan: a pure function of the sequence capacity, so a CUDA graph captured for a given
 // max_seq_len stays valid while the device-side sequence length grows.
-static AttnPlan plan_decode_attention(int seq_cap, int kv_heads_times_batch = 0) {
+static AttnPlan plan_decode_attention(int seq_cap, int kv_heads_times_batch = 0, int resident_blocks = 296) {
     AttnPlan pl;
     int nsplit = (seq_cap + 63) / 64;
     if (nsplit > 64) nsplit = 64;
-    // A batch of sequences already fills the GPU along the batch axis: aim at one wave of blocks (296 are resident at
-    // two per SM) with longer slices per block.  Measured at 16 sequences x 8 KV heads x 2051 positions: 256 blocks of 17
+    // A batch of sequences already fills the GPU along the batch axis: aim at one wave of blocks (`resident_blocks`: 296
+    // at two per SM, 148 for the kernel that runs one per SM) with longer slices per block.  Measured at 16 sequences x 8 KV heads x 2051 positions: 256 blocks of 17
     // tiles beat 512 blocks of 9 (a second, partly filled wave) and every finer split (each block pays its own latency
     // chain: query load, RoPE table, partial results, merge).
     if (kv_heads_times_batch > 0) {
-        int cap = 296 / kv_heads_times_batch;
+        int cap = resident_blocks / kv_heads_times_batch;
         if (cap < 1) cap = 1;
         if (nsplit > cap) nsplit = cap;
     }
@@ -987,7 +1026,10 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
                             const float* freqs, float* k_cache_w, float* v_cache_w, int batch, size_t cache_stride,
                             int kv_bf16, int window) {
     const int gq = n_heads / n_kv_heads;
-    AttnPlan pl = plan_decode_attention(seq_cap, batch > 1 ? n_kv_heads * batch : 0);
+    // f32 cache and a batch of sequences: the tensor-core kernel (one block per SM); KMLL_ATTN_MMA_F32=0 keeps the f32 kernel
+    static const bool mma_f32_allowed = [] { const char* e = getenv("KMLL_ATTN_MMA_F32"); return !(e != nullptr && e[0] == '0'); }();
+    const bool mma_f32 = !kv_bf16 && batch > 1 && mma_f32_allowed;
+    AttnPlan pl = plan_decode_attention(seq_cap, batch > 1 ? n_kv_heads * batch : 0, mma_f32 ? 148 : 296);
     DecodeAttnParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
     p.seq_len_ptr = seq_len_ptr; p.seq_len = seq_len;
@@ -1015,16 +1057,22 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem, stream, true, p);
     };
-    if (kv_bf16) {
-        // per warp a K stage and a V stage of 16 padded bf16 rows; the warps' statistics, the block's, the query heads
+    if (kv_bf16 || mma_f32) {
+        // per warp a K stage and a V stage of 16 padded rows; the warps' statistics, the block's, the query heads
         const size_t gqm = gq <= 4 ? 4 : kMaxGq;
-        const size_t smem16 = (size_t)kAttnWarps * 2 * 16 * (head_dim + 8) * 2 + ((size_t)kAttnWarps * 16 + gqm * 4 + gqm * head_dim) * sizeof(float);
+        const size_t stage_bytes = kv_bf16 ? (size_t)2 * 16 * (head_dim + 8) * 2 : (size_t)16 * ((head_dim + 8) + (head_dim + 4)) * 4;
+        const size_t smem16 = (size_t)kAttnWarps * stage_bytes + ((size_t)kAttnWarps * 16 + gqm * 4 + gqm * head_dim) * sizeof(float);
         auto go16 = [&](auto kern) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             return launch(kern, dim3(n_kv_heads, pl.nsplit, batch > 1 ? batch : 1), dim3(kAttnThreads), smem16, stream, true, p);
         };
-        if (head_dim == 128) e = gq <= 4 ? go16(decode_attention_bf16_kernel<128, 4>) : go16(decode_attention_bf16_kernel<128, 8>);
-        else e = gq <= 4 ? go16(decode_attention_bf16_kernel<64, 4>) : go16(decode_attention_bf16_kernel<64, 8>);
+        if (kv_bf16) {
+            if (head_dim == 128) e = gq <= 4 ? go16(decode_attention_mma_kernel<128, 4, false>) : go16(decode_attention_mma_kernel<128, 8, false>);
+            else e = gq <= 4 ? go16(decode_attention_mma_kernel<64, 4, false>) : go16(decode_attention_mma_kernel<64, 8, false>);
+        } else {
+            if (head_dim == 128) e = gq <= 4 ? go16(decode_attention_mma_kernel<128, 4, true>) : go16(decode_attention_mma_kernel<128, 8, true>);
+            else e = gq <= 4 ? go16(decode_attention_mma_kernel<64, 4, true>) : go16(decode_attention_mma_kernel<64, 8, true>);
+        }
     } else {
         if (head_dim == 128) e = gq <= 4 ? go(decode_attention_kernel<128, 4>) : go(decode_attention_kernel<128, 8>);
         else e = gq <= 4 ? go(decode_attention_kernel<64, 4>) : go(decode_attention_kernel<64, 8>);
