@@ -324,10 +324,13 @@ def run_ours(args):
     prompt = np.random.default_rng(SEED).integers(0, cfg.vocab_size, PROMPT_LEN)
     dec.prefill(prompt)  # untimed: the first prefill allocates its scratch and encodes its tensor maps
     torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    dec.prefill(prompt)
-    torch.cuda.synchronize()
-    prefill_s = time.perf_counter() - t0
+    prefill_s = None
+    for _ in range(2):  # host wall clock around a synchronised call: the shorter of two (a host hiccup once read 0.8 s for 0.2)
+        t0 = time.perf_counter()
+        dec.prefill(prompt)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        prefill_s = dt if prefill_s is None else min(prefill_s, dt)
 
     def barrier():
         torch.cuda.synchronize()
