@@ -1031,8 +1031,14 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
     static const bool mma_f32_allowed = [] { const char* e = getenv("KMLL_ATTN_MMA_F32"); return !(e != nullptr && e[0] == '0'); }();
     // (also the decoder's fused batch-1 form: 136 blocks of one stage per warp instead of 264, half as many partials to
     // merge - 673 against 661 tokens/s on the Mistral-7B shape; the plain operator form keeps the f32 kernel)
-    const bool mma_f32 = !kv_bf16 && (batch > 1 || k_new != nullptr) && mma_f32_allowed;
+    bool mma_f32 = !kv_bf16 && (batch > 1 || k_new != nullptr) && mma_f32_allowed;
     AttnPlan pl = plan_decode_attention(seq_cap, batch > 1 ? n_kv_heads * batch : (mma_f32 ? n_kv_heads : 0), mma_f32 ? 148 : 296);
+    if (mma_f32 && batch == 1 && pl.chunk < 128) {
+        // few KV heads (a tensor-parallel shard of 1 or 2) or a short cache: slices under 8 stages would leave warps of
+        // the tensor-core kernel idle; the f32 kernel's 64-position blocks are faster there (TP4: 857 against 840 tokens/s)
+        mma_f32 = false;
+        pl = plan_decode_attention(seq_cap, 0, 296);
+    }
     DecodeAttnParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
     p.seq_len_ptr = seq_len_ptr; p.seq_len = seq_len;

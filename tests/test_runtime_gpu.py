@@ -77,6 +77,18 @@ def test_sliding_window_other_step_forms_and_bf16(cuda):
         dec.close()
 
 
+@pytest.mark.parametrize("kv_bf16", [False, True])
+def test_long_context_fused_step_matches_oracle(cuda, kv_bf16):
+    """A cache of 1300 positions x 8 KV heads: the fused batch-1 step plans slices of 128 positions (8 stages of 16, one
+    per warp) and attends through the tensor-core kernel for the f32 cache as well (operands split into two bf16 parts,
+    about 2^-17 per product): the f32 tolerances of the other tests hold."""
+    cfg = tiny(rt.FORMAT_W4G128, True, n_heads=8, n_kv_heads=8, head_dim=64, dim=512, max_seq_len=1300, kv_bf16=kv_bf16)
+    dec = make(cfg)
+    prompt = np.random.default_rng(21).integers(0, cfg.vocab_size, 1210)
+    check_against_oracle(dec, cfg, prompt, 6, batched_prefill=True, **(BF16_KV_BOUND if kv_bf16 else {}))
+    dec.close()
+
+
 BF16_KV_BOUND = dict(hid_tol=2e-3, min_margin=1e-2, logit_tol=5e-3)
 
 
