@@ -163,7 +163,7 @@ int prepare_prefill_offset(cudaStream_t stream, const float* q, const float* k, 
 // one row of the KV cache at `position` (f32, or rounded to bf16 when the decoder keeps its cache in bf16)
 int write_kv_row(cudaStream_t stream, const float* x, int position, int token_len, int head_dim, float* cache, int kv_bf16);
 int prefill_attention_launch(cudaStream_t stream, const float* q_batch, const float* k_cache, const float* v_cache, int prompt_len,
-                             int n_heads, int n_kv_heads, int head_dim, float* out, int kv_bf16, int window);
+                             int n_heads, int n_kv_heads, int head_dim, float* out, int kv_bf16, int window, int tensor_cores);
 // hidden = embedding[state->next_top.token]; also records next_top into history[state->step] and
 // sets seq_len = position + 1.
 int decode_begin(cudaStream_t stream, const uint16_t* table, int vocab, int dim, DecodeState* state, uint64_t* history,
