@@ -41,7 +41,7 @@ DECODE_SUITE = [("qkv", 6144, 4096, 16), ("linear_residual", 4096, 4096, 16), ("
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="linear", choices=["linear", "qkv", "linear_residual", "silu_gate_up", "linear_top1", "attention", "linear_batched",
-                                                        "decode_batch"])
+                                                        "decode_batch", "prefill"])
     ap.add_argument("--batch", type=int, default=16, help="rows of x for --op linear_batched (5..32: small-batch kernel; more: tcgen05 f16 kernel)")
     ap.add_argument("--fmt", default="w4", choices=["w4", "w4p", "i8"])
     ap.add_argument("--rows", type=int, default=14336)
@@ -55,8 +55,8 @@ def main():
     ap.add_argument("--shards", type=int, default=1, help="gemm_sweep: time one rank's share of every matrix when its N output rows are split over this "
                                                            "many GPUs (column-parallel: disjoint output blocks, no collective)")
     ap.add_argument("--profile", action="store_true", help="bracket one graph replay with cudaProfilerStart/Stop")
-    ap.add_argument("--layers", type=int, default=2, help="decode_batch: layers of the Mistral-7B-shaped decoder (a small case for profiling)")
-    ap.add_argument("--kv-bf16", action="store_true", help="decode_batch: keep the KV cache in bf16")
+    ap.add_argument("--layers", type=int, default=2, help="decode_batch, prefill: layers of the Mistral-7B-shaped decoder (a small case for profiling)")
+    ap.add_argument("--kv-bf16", action="store_true", help="decode_batch, prefill: keep the KV cache in bf16")
     a = ap.parse_args()
     torch.cuda.set_device(0)
     if a.suite == "decode":
@@ -239,9 +239,45 @@ def run_decode_batch(a):
     dec.close()
 
 
+def run_prefill(a):
+    """Batched prefill of a --rows-token prompt on the Mistral-7B-shaped decoder (--layers layers; 32 = the whole model):
+    wall time of the call (host clock around a synchronised call, best of three warm calls)."""
+    import time
+
+    import numpy as np
+
+    from . import runtime as rt
+    n = a.rows
+    cfg = rt.DecoderConfig(n_layers=a.layers, dim=4096, n_heads=32, n_kv_heads=8, head_dim=128, hidden_dim=14336, vocab_size=32000,
+                           rope_theta=1.0e6, norm_eps=1.0e-5, max_seq_len=n + 64,
+                           format=rt.FORMAT_RS_I8 if a.fmt == "i8" else rt.FORMAT_W4G128, kv_bf16=a.kv_bf16)
+    dec = rt.Decoder(cfg)
+    dec.init_random(3, 0.02, False)
+    prompt = np.random.default_rng(3).integers(0, cfg.vocab_size, n)
+    dec.prefill(prompt)  # allocates the scratch
+    best = None
+    for _ in range(3):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        dec.prefill(prompt)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    if a.profile:
+        torch.cuda.profiler.start()
+        dec.prefill(prompt)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    print(json.dumps({"op": "prefill", "fmt": a.fmt, "layers": a.layers, "prompt_len": n, "kv_bf16": a.kv_bf16, "seconds": best,
+                      "tokens_per_s": n / best}))
+    dec.close()
+
+
 def run_one(a):
     if a.op == "decode_batch":
         return run_decode_batch(a)
+    if a.op == "prefill":
+        return run_prefill(a)
     calls = []
     if a.op == "attention":
         n_heads, n_kv, hd = 32, 8, 128
