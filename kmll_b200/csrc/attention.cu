@@ -1242,6 +1242,11 @@ int decode_attention_launch(cudaStream_t stream, const float* q, const float* k_
         mma_f32 = false;
         pl = plan_decode_attention(seq_cap, 0, 296);
     }
+    if (kv_bf16 && batch == 1) {
+        // bf16 cache, one sequence: slices of 8 stages (one per warp) where the KV heads allow it, like the f32 form
+        const AttnPlan wide = plan_decode_attention(seq_cap, n_kv_heads, 148);
+        if (wide.chunk >= 128) pl = wide;
+    }
     DecodeAttnParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
     p.seq_len_ptr = seq_len_ptr; p.seq_len = seq_len;
