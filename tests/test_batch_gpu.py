@@ -72,15 +72,17 @@ def test_batch_gqa_head_dim_128(cuda, kv_bf16):
     dec.close()
 
 
-@pytest.mark.parametrize("kv_bf16,window,head_dim,n_heads", [(False, 0, 64, 8), (True, 0, 64, 8), (False, 90, 64, 8), (True, 0, 128, 32),
-                                                             (True, 150, 128, 16), (False, 0, 128, 32)])
-def test_batch_attention_with_several_tiles_per_block(cuda, kv_bf16, window, head_dim, n_heads):
+@pytest.mark.parametrize("kv_bf16,window,head_dim,n_heads,n_kv", [(False, 0, 64, 8, 8), (True, 0, 64, 8, 8), (False, 90, 64, 8, 8), (True, 0, 128, 32, 8),
+                                                                  (True, 150, 128, 16, 8), (False, 0, 128, 32, 8), (False, 0, 64, 16, 2),
+                                                                  (True, 0, 128, 16, 2)])
+def test_batch_attention_with_several_tiles_per_block(cuda, kv_bf16, window, head_dim, n_heads, n_kv):
     """16 sequences x 8 KV heads fill the GPU along the batch axis, so the attention plan gives every block a long slice
     of the sequence (here 256 positions: several 64-position tiles of the f32 kernel, several 16-position stages per
     warp of the bf16-cache kernel); with 200-token prompts the position being written lies deep inside its block's slice.
     The single-sequence runs they are compared with use one block per 64 positions: a different partition of the same
-    sums.  Head dimension 128 with 4 and 2 query heads per KV head covers the fragment layouts of the tensor-core kernel."""
-    cfg = _cfg(rt.FORMAT_W4G128, n_heads=n_heads, n_kv_heads=8, head_dim=head_dim, dim=512, max_seq_len=400, kv_bf16=kv_bf16,
+    sums.  Head dimensions 64 and 128 with 1, 2, 4 and 8 query heads per KV head cover the fragment layouts of the tensor-core
+    kernel."""
+    cfg = _cfg(rt.FORMAT_W4G128, n_heads=n_heads, n_kv_heads=n_kv, head_dim=head_dim, dim=512, max_seq_len=400, kv_bf16=kv_bf16,
                sliding_window=window)
     dec = rt.Decoder(cfg)
     dec.init_random(11, 0.05, False)
