@@ -89,6 +89,17 @@ def test_long_context_fused_step_matches_oracle(cuda, kv_bf16):
     dec.close()
 
 
+@pytest.mark.parametrize("kv_bf16", [False, True])
+@pytest.mark.parametrize("batched_prefill", [False, True])
+def test_single_token_prompt(cuda, kv_bf16, batched_prefill):
+    """The shortest sequences: a one-token prompt (one query row, one key), then steps whose blocks hold only the row
+    being written plus a handful of cached rows."""
+    cfg = tiny(rt.FORMAT_RS_I8, True, n_heads=8, n_kv_heads=2, head_dim=128, dim=256, max_seq_len=40, kv_bf16=kv_bf16)
+    dec = make(cfg)
+    check_against_oracle(dec, cfg, np.asarray([7]), 6, batched_prefill=batched_prefill, **(BF16_KV_BOUND if kv_bf16 else {}))
+    dec.close()
+
+
 BF16_KV_BOUND = dict(hid_tol=2e-3, min_margin=1e-2, logit_tol=5e-3)
 
 
