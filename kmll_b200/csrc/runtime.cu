@@ -1303,7 +1303,7 @@ int kmll_decoder_prefill(kmll_decoder_t dec, kmll_stream_t stream, const uint32_
             KMLL_TRY(prepare_prefill_offset(s, qb, kb, vb, d->freqs, c.rotary_dim / 2, n, q_len, kv_len, c.head_dim, 0, qrb, L.key_cache,
                                             L.value_cache, c.kv_bf16));
             KMLL_TRY(prefill_attention_launch(s, qrb, L.key_cache, L.value_cache, n, d->n_heads_l, d->n_kv_l, c.head_dim, ab, c.kv_bf16,
-                                              c.sliding_window, 1));
+                                              c.sliding_window, c.fused ? 1 : 0));  // fused = 0: kmll's f32 operator arithmetic throughout
             KMLL_TRY(op_linear_batched(d, s, ab, L.wo, n, ws, ob));
             KMLL_TRY(tp_allreduce(d, s, ob, (size_t)n * c.dim));
             KMLL_TRY(kmll_add_prefix(s, xb, ob, (size_t)n * c.dim, x2b));
