@@ -75,6 +75,9 @@ typedef struct {
                             (crates/inference/src/kernels/inference.rs:1420-1686).  The cache still keeps every row. */
 } kmll_decoder_config;
 
+/* sizeof(kmll_decoder_config) as this library was compiled: a binding checks its own mirror of the struct against it
+   (fields are only ever appended) */
+size_t kmll_decoder_config_bytes(void);
 int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out);
 int kmll_decoder_destroy(kmll_decoder_t dec);
 

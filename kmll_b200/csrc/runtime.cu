@@ -944,6 +944,8 @@ static int setup_exchange(Decoder* d) {
 
 extern "C" {
 
+size_t kmll_decoder_config_bytes(void) { return sizeof(kmll_decoder_config); }
+
 int kmll_decoder_create(const kmll_decoder_config* config, kmll_decoder_t* out) {
     KMLL_REQUIRE_PTR(config);
     KMLL_REQUIRE_PTR(out);

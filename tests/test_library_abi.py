@@ -18,6 +18,15 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert handle.kmll_compiled_arch() == 100
 
 
+def test_config_struct_mirror_matches_the_library():
+    from kmll_b200 import runtime as rt
+    handle = lib.load()
+    assert handle.kmll_decoder_config_bytes() == C.sizeof(rt._Config)
+    c = rt.DecoderConfig(n_layers=1, dim=128, n_heads=2, n_kv_heads=1, head_dim=64, hidden_dim=128, vocab_size=64, kv_bf16=True,
+                         sliding_window=7)._c()
+    assert (c.kv_bf16, c.sliding_window, c.tp_size, c.fused) == (1, 7, 1, 1)
+
+
 def test_header_parser_sees_expected_signatures():
     protos = lib.parse_prototypes(lib.HEADERS[0])
     restype, argtypes = protos["kmll_linear_i8"]
