@@ -219,6 +219,7 @@ class TextConfig:
     vocab_size: int
     norm_eps: float
     eos_token_id: int | None
+    sliding_window: int | None = None  # config.json's `sliding_window`; kmll does not read it (full causal attention)
 
     @staticmethod
     def from_config_json(text: str) -> "TextConfig":
@@ -244,11 +245,13 @@ class TextConfig:
             yarn = YarnRopeConfig(need(rope, "factor", float), need(rope, "original_max_position_embeddings", int), need(rope, "beta_fast", float),
                                   need(rope, "beta_slow", float), float(rope.get("mscale", 1.0)))
         eos = cfg.get("eos_token_id", top.get("eos_token_id"))
+        window = cfg.get("sliding_window", top.get("sliding_window"))
         out = TextConfig(dim=need(cfg, "hidden_size", int), hidden_dim=need(cfg, "intermediate_size", int), n_layers=need(cfg, "num_hidden_layers", int),
                          n_heads=need(cfg, "num_attention_heads", int), n_kv_heads=need(cfg, "num_key_value_heads", int), head_dim=head_dim,
                          rotary_dim=rotary_dim, rope_theta=float((rope or {}).get("rope_theta", cfg.get("rope_theta", 10000.0))), rope_yarn=yarn,
                          max_position_embeddings=need(cfg, "max_position_embeddings", int), vocab_size=need(cfg, "vocab_size", int),
-                         norm_eps=need(cfg, "rms_norm_eps", float), eos_token_id=int(eos) if isinstance(eos, int) else None)
+                         norm_eps=need(cfg, "rms_norm_eps", float), eos_token_id=int(eos) if isinstance(eos, int) else None,
+                         sliding_window=int(window) if isinstance(window, int) and not isinstance(window, bool) and window > 0 else None)
         out.validate_for_inference()
         return out
 
@@ -310,9 +313,11 @@ def rope_frequencies(cfg: TextConfig) -> np.ndarray:
 
 
 def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused: bool = True, kv_bf16: bool = False,
-                 sliding_window: int = 0):
+                 sliding_window: int | str = 0):
     """config.json + safetensors -> a Decoder with its linear weights quantized to `fmt` on the device (RS-I8 from the
-    bf16 values as kmll's exporter does, rowwise_scaled.rs:21-51; W4-G128 from their f32 values).  Returns (decoder, config)."""
+    bf16 values as kmll's exporter does, rowwise_scaled.rs:21-51; W4-G128 from their f32 values).  Returns (decoder, config).
+    sliding_window: 0 = full causal attention as kmll runs every model; a positive number = that window; "config" = the
+    checkpoint's own `sliding_window` when it has one."""
     import torch
 
     from . import ops
@@ -323,6 +328,8 @@ def load_decoder(model_dir: str, fmt: int, max_seq_len: int | None = None, fused
     qk_norm = weights.tensor_opt("layers.0.attention.q_norm.weight") is not None
     if qk_norm != (weights.tensor_opt("layers.0.attention.k_norm.weight") is not None):
         raise CheckpointError("a checkpoint must carry both q_norm and k_norm or neither")
+    if sliding_window == "config":
+        sliding_window = cfg.sliding_window or 0
     dcfg = rt.DecoderConfig(n_layers=cfg.n_layers, dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
                             hidden_dim=cfg.hidden_dim, vocab_size=cfg.vocab_size, rope_theta=cfg.rope_theta, norm_eps=cfg.norm_eps,
                             max_seq_len=max_seq_len or cfg.max_position_embeddings, rotary_dim=cfg.rotary_dim, format=fmt, fused=fused, kv_bf16=kv_bf16,

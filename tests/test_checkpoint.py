@@ -95,6 +95,11 @@ def test_config_json():
         with pytest.raises(CheckpointError):
             TextConfig.from_config_json(json.dumps(broken))
     assert rotary_dim_from_partial_factor(128, 1.0) == 128 and rotary_dim_from_partial_factor(128, 0.25) == 32
+    # `sliding_window` is read but not applied unless the caller asks for it (kmll runs full causal attention)
+    assert TextConfig.from_config_json(json.dumps(BASE)).sliding_window is None
+    assert TextConfig.from_config_json(json.dumps({**BASE, "sliding_window": 4096})).sliding_window == 4096
+    assert TextConfig.from_config_json(json.dumps({**BASE, "sliding_window": None})).sliding_window is None
+    assert TextConfig.from_config_json(json.dumps({"text_config": {**BASE, "sliding_window": 128}})).sliding_window == 128
 
 
 def test_rope_frequencies_match_the_oracle():

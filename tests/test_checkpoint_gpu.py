@@ -15,8 +15,9 @@ pytestmark = pytest.mark.gpu
 F = np.float32
 
 
-def make_checkpoint(tmp_path, yarn=True, tied=False, with_qk_norm=False):
+def make_checkpoint(tmp_path, yarn=True, tied=False, with_qk_norm=False, sliding_window=None):
     cfg = {"model_type": "mistral3", "text_config": {
+        **({"sliding_window": sliding_window} if sliding_window else {}),
         "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
         "max_position_embeddings": 4096, "vocab_size": 640, "rms_norm_eps": 1e-5, "eos_token_id": 2,
         "rope_parameters": ({"rope_type": "yarn", "rope_theta": 1e6, "factor": 16.0, "original_max_position_embeddings": 64, "beta_fast": 32.0,
@@ -131,4 +132,28 @@ def test_checkpoint_with_qk_norm_decodes_like_the_oracle(cuda, tmp_path, fmt, fu
         btok, _ = bd.generate_greedy(6)
         assert all(btok[slot].tolist() == [int(v) for v in tokens] for slot in range(3))
         bd.close()
+    dec.close()
+
+
+def test_sliding_window_and_bf16_cache_from_a_checkpoint(cuda, tmp_path):
+    """The checkpoint's own `sliding_window` is applied only on request ("config"); with it and the bf16 KV cache the decoder
+    still follows the oracle model given the same two options."""
+    make_checkpoint(tmp_path, yarn=False, sliding_window=24)
+    dec, cfg = load_decoder(str(tmp_path), rt.FORMAT_W4G128, max_seq_len=96)
+    assert cfg.sliding_window == 24 and dec.cfg.sliding_window == 0 and not dec.cfg.kv_bf16
+    dec.close()
+    dec, cfg = load_decoder(str(tmp_path), rt.FORMAT_W4G128, max_seq_len=96, sliding_window="config", kv_bf16=True)
+    assert dec.cfg.sliding_window == 24 and dec.cfg.kv_bf16
+    ora = OracleDecoder(dec.cfg, dec)
+    prompt = np.random.default_rng(8).integers(0, 640, 70)
+    logits = ora.prefill(prompt)
+    dec.prefill(prompt)
+    hid = dec.last_hidden()
+    assert np.max(np.abs(hid - ora.hidden)) <= 2e-3 * max(float(np.max(np.abs(ora.hidden))), 1.0)
+    steps, _ = ora.generate_greedy(logits, 6)
+    tokens, glogits = dec.generate_greedy(6)
+    for i, (tok, logit, margin) in enumerate(steps):
+        if margin < 1e-2:
+            break
+        assert int(tokens[i]) == tok and abs(float(glogits[i]) - logit) <= 5e-3 * max(abs(logit), 1.0)
     dec.close()
