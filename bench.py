@@ -8,6 +8,10 @@
 
 A step is one decode token: RMSNorm+QKV, RoPE/KV write, attention over the whole context, output
 projection, gated MLP, residuals, and the lm_head arg-max.  Prints one JSON line (rank 0).
+Beside the headline value the line carries, on one GPU: `e2e` (per-token host API), `roofline` (the gate/up kernel timed
+live), `step_roofline`, `prefill_s`, `batch16` (16 sequences in lockstep), `rs_i8` (kmll's own weight format, batch 1 and
+16), `kv_bf16` (the same legs with the KV cache in bf16), `cpu_baseline` (the CPU port on the host cores) and `check`
+(device status, token agreement between the loops, with batch 1 and - tensor parallel - with a single-GPU decoder).
 """
 from __future__ import annotations
 
